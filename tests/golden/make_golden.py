@@ -1,0 +1,104 @@
+#!/usr/bin/env python3
+"""Regenerate the golden fixtures in this directory from the reference tree.
+
+Run in a container that has the reference checked out (default /root/reference):
+
+    python tests/golden/make_golden.py [--ref /root/reference]
+
+It never copies reference code into the repo; it runs / imports the reference's
+own Python (lib/golden/golden.py, kernels/simt_quant/gen_quant.py) from a
+scratch copy under a temp dir (the generator writes next to itself and the
+reference tree is read-only) and stores only input/output vectors:
+
+  simt_quant_kat.npz      the reference's own known-answer test for the MX block
+                          quantizer: X_raw fp32 [64,512] and gold_all (8192
+                          packed code words then 1024 E8M0 scale words), exactly
+                          what kernels/simt_quant/kernel.cpp verifies on device.
+  golden_py_vectors.npz   outputs of lib/golden/golden.py primitives on seeded
+                          edge-case inputs chosen here: fp8_code_rshift (ties,
+                          subnormals, saturation, signed zero, inf), block_exp /
+                          pow2_neg_e, softcap (fp64 tanh reference).
+"""
+import argparse
+import importlib.util
+import pathlib
+import re
+import shutil
+import subprocess
+import sys
+import tempfile
+
+import numpy as np
+
+HERE = pathlib.Path(__file__).resolve().parent
+
+
+def load_golden(ref):
+    spec = importlib.util.spec_from_file_location("ref_golden", ref / "lib" / "golden" / "golden.py")
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def parse_c_array(text, name):
+    m = re.search(name + r"\[\d+\]\s*=\s*\{(.*?)\};", text, re.S)
+    return [t.strip() for t in m.group(1).replace("\n", " ").split(",") if t.strip()]
+
+
+def make_simt_quant_kat(ref):
+    with tempfile.TemporaryDirectory() as td:
+        td = pathlib.Path(td)
+        (td / "kernels" / "simt_quant").mkdir(parents=True)
+        (td / "lib" / "golden").mkdir(parents=True)
+        shutil.copy(ref / "kernels" / "simt_quant" / "gen_quant.py", td / "kernels" / "simt_quant")
+        shutil.copy(ref / "lib" / "golden" / "golden.py", td / "lib" / "golden")
+        subprocess.run([sys.executable, "gen_quant.py"], cwd=td / "kernels" / "simt_quant", check=True,
+                       stdout=subprocess.DEVNULL)
+        text = (td / "kernels" / "simt_quant" / "data").read_text()
+    x = np.array([float(t.rstrip("f")) for t in parse_c_array(text, "X_raw")], dtype=np.float64).astype(np.float32)
+    gold = np.array([int(t.rstrip("u"), 16) for t in parse_c_array(text, "gold_all")], dtype=np.uint32)
+    assert x.size == 64 * 512 and gold.size == 8192 + 1024
+    np.savez_compressed(HERE / "simt_quant_kat.npz", X_raw=x.reshape(64, 512), gold_all=gold)
+    print("simt_quant_kat.npz:", x.shape, gold.shape, "scale range", gold[8192:].min(), gold[8192:].max())
+
+
+def make_golden_py_vectors(ref):
+    G = load_golden(ref)
+    rng = np.random.default_rng(20240607)
+    bits = []
+    # every exponent around the E4M3 range with mantissas that sit on / next to
+    # rounding ties of a 3-bit mantissa, both signs
+    for e in range(127 - 14, 127 + 12):
+        for m3 in range(8):
+            for low in (0x00000, 0x7FFFF, 0x80000, 0x80001, 0xFFFFF, 0x40000, 0xC0000):
+                for s in (0, 1):
+                    bits.append((s << 31) | (e << 23) | (m3 << 20) | low)
+    bits += [0x00000000, 0x80000000, 0x7F800000, 0xFF800000, 0x43E00000, 0x43DFFFFF, 0x43E00001,
+             0x43D00000, 0x43D80000, 0x00000001, 0x007FFFFF, 0x00800000]
+    bits = np.array(bits, dtype=np.uint32)
+    rnd = (rng.standard_normal(4096) * np.exp2(rng.integers(-12, 10, 4096))).astype(np.float32)
+    xin = np.concatenate([bits.view(np.float32), rnd])
+    codes = np.array([G.fp8_code_rshift(float(v)) for v in xin], dtype=np.uint8)
+
+    amax_bits = np.concatenate([
+        np.array([(e << 23) | m for e in range(1, 255, 3) for m in (0, 1, 0x5FFFFF, 0x600000, 0x600001, 0x7FFFFF)],
+                 dtype=np.uint32),
+        rng.integers(0x00800000, 0x7F000000, 512, dtype=np.uint32)])
+    bexp = np.array([G.block_exp(int(b)) for b in amax_bits], dtype=np.int32)
+    ok = (bexp > -127) & (bexp < 128)
+    p2 = np.array([G.pow2_neg_e(int(e)) if o else 0.0 for e, o in zip(bexp, ok)], dtype=np.float32)
+
+    cap_x = (rng.standard_normal(2048) * 60).astype(np.float32)
+    cap_y = G.softcap(cap_x, 50.0)
+    np.savez_compressed(HERE / "golden_py_vectors.npz", enc_in=xin, enc_codes=codes,
+                        amax_bits=amax_bits, block_exp=bexp, pow2_ok=ok, pow2_neg_e=p2,
+                        cap_x=cap_x, cap_y=cap_y)
+    print("golden_py_vectors.npz:", xin.size, "encode cases,", amax_bits.size, "block_exp cases")
+
+
+if __name__ == "__main__":
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--ref", default="/root/reference")
+    ref = pathlib.Path(ap.parse_args().ref)
+    make_simt_quant_kat(ref)
+    make_golden_py_vectors(ref)

@@ -1,0 +1,89 @@
+"""Pins the CPU oracle to the reference: golden vectors made by the reference's
+own Python (tests/golden/make_golden.py) and, where oracle/_ref was built, the
+reference's codec header compiled as it lies in the reference tree."""
+import os
+
+import numpy as np
+import pytest
+
+import oracle
+
+G = os.path.join(os.path.dirname(__file__), "golden")
+
+
+def test_simt_quant_known_answer():
+    """kernels/simt_quant: 64x512 tile -> 8192 packed code words + 1024 scale words, bit for bit."""
+    kat = np.load(os.path.join(G, "simt_quant_kat.npz"))
+    codes, scales = oracle.quantize(kat["X_raw"], oracle.E4M3)
+    packed = codes.reshape(-1, 4).astype(np.uint32)
+    words = packed[:, 0] | (packed[:, 1] << 8) | (packed[:, 2] << 16) | (packed[:, 3] << 24)
+    gold = kat["gold_all"]
+    assert np.array_equal(words, gold[:8192])
+    assert np.array_equal(scales.reshape(-1).astype(np.uint32), gold[8192:])
+
+
+def test_encode_matches_golden_py():
+    v = np.load(os.path.join(G, "golden_py_vectors.npz"))
+    L = oracle.lib()
+    got = np.array([L.rko_encode_elem_rne(float(x), oracle.E4M3) for x in v["enc_in"]], np.uint8)
+    assert np.array_equal(got, v["enc_codes"])
+
+
+def test_block_exp_matches_golden_py():
+    """Scale selection: quantize a block whose amax has the given bit pattern, compare the E8M0 code."""
+    v = np.load(os.path.join(G, "golden_py_vectors.npz"))
+    amax = v["amax_bits"].view(np.float32)
+    x = np.zeros((amax.size, 32), np.float32)
+    x[:, 5] = -amax
+    _, scales = oracle.quantize(x)
+    want = np.clip(v["block_exp"] + 127, 0, 254)
+    assert np.array_equal(scales[:, 0].astype(np.int32), want)
+
+
+def test_softcap_reference_values():
+    v = np.load(os.path.join(G, "golden_py_vectors.npz"))
+    got = (50.0 * np.tanh(v["cap_x"].astype(np.float32) / np.float32(50.0))).astype(np.float32)
+    # tolerance of kernels/logit_softcap/kernel.cpp:18-23
+    assert np.all(np.abs(got - v["cap_y"]) <= 2e-4 + 1e-3 * np.abs(v["cap_y"]))
+
+
+def test_codecs_against_reference_header():
+    R = oracle.ref_codec()
+    if R is None:
+        pytest.skip("oracle/_ref not built (reference tree absent)")
+    L = oracle.lib()
+    for c in range(256):
+        assert L.rko_decode_elem(c, oracle.E4M3) == R.ref_fp8_e4m3_decode(c)
+        if c != 0xFF:
+            assert L.rko_e8m0_decode(c) == R.ref_fpe8m0_decode(c)
+    assert np.isnan(L.rko_e8m0_decode(0xFF))
+    for c in range(64):
+        assert L.rko_decode_elem(c, oracle.E3M2) == R.ref_fp6_e3m2_decode(c)
+    rng = np.random.default_rng(3)
+    xs = np.concatenate([rng.standard_normal(4000).astype(np.float32) * 100,
+                         np.array([0.0, -0.0, 1e-30, 3.4e38, np.inf], np.float32)])
+    for x in xs:
+        assert L.rko_f32_to_bf16(float(x)) == R.ref_f32_to_bf16_rne(float(x))
+    # decode(encode(v)) == v on every representable value, all four formats
+    for fmt, nbits in ((oracle.E4M3, 8), (oracle.E5M2, 8), (oracle.E2M3, 6), (oracle.E3M2, 6)):
+        for c in range(1 << nbits):
+            val = L.rko_decode_elem(c, fmt)
+            if fmt == oracle.E4M3 and (c & 0x7F) == 0x7F:
+                continue  # 480: above the saturation value, never emitted
+            if fmt == oracle.E5M2 and ((c >> 2) & 0x1F) == 0x1F:
+                continue  # inf/NaN encodings of E5M2, never emitted
+            assert L.rko_encode_elem_rne(val, fmt) == c, (fmt, c, val)
+
+
+def test_rne_encoder_agrees_with_reference_fp8_to_code_on_normals():
+    """lib/golden/mx_fp_math.h fp8_e4m3_to_code (log2f form, subnormals flushed) equals the
+    round-shift encoder wherever the value is a normal E4M3 magnitude away from the flush range."""
+    R = oracle.ref_codec()
+    if R is None:
+        pytest.skip("oracle/_ref not built")
+    L = oracle.lib()
+    rng = np.random.default_rng(5)
+    xs = (rng.standard_normal(5000) * np.exp2(rng.integers(-5, 8, 5000))).astype(np.float32)
+    xs = xs[np.abs(xs) >= 2.0 ** -6]
+    for x in xs:
+        assert L.rko_encode_elem_rne(float(x), oracle.E4M3) == R.ref_fp8_e4m3_to_code(float(x))
