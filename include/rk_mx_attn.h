@@ -1,0 +1,176 @@
+/*
+ * rk_mx_attn.h -- C ABI of the B200 (sm_100a) MX flash-attention path.
+ *
+ * Drop-in boundary for the MXFP8 attention path of radiance-kernels: the MX
+ * block quantizer, the tiled prefill attention (MHA / GQA / Gemma soft-cap /
+ * sliding window / MXFP6 operands) and single-token decode attention over an
+ * MX KV cache.  The reference exposes this path as bare-metal kernel entry
+ * points whose operands are link-time arrays; every entry point below names the
+ * reference interface it stands in for (file:line inside the reference tree).
+ *
+ * Conventions
+ *   - plain C, no C++/torch types; every pointer is a DEVICE pointer unless the
+ *     parameter name ends in `_host`; the caller owns all memory, nothing is
+ *     retained or freed.
+ *   - `stream` is a cudaStream_t passed as void* (NULL = default stream).  Calls
+ *     are asynchronous on that stream.
+ *   - return value: 0 = RK_OK, negative = argument error (nothing launched),
+ *     positive = a cudaError_t reported by the runtime.
+ *   - element codes are one byte each (6-bit formats use the low 6 bits);
+ *     E8M0 scale codes are one byte per 32-element block, value 2^(code-127);
+ *     callers must not pass E4M3 codes 0x7F/0xFF or scale code 0xFF (NaN in
+ *     hardware, a number in the reference's decoder -- lib/golden/mx_fp_math.h
+ *     :227-236,249-252); the quantizer never emits them.
+ */
+#ifndef RK_MX_ATTN_H_
+#define RK_MX_ATTN_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define RK_API __attribute__((visibility("default")))
+#else
+#define RK_API
+#endif
+
+#define RK_OK 0
+#define RK_ERR_NULL_POINTER (-1)
+#define RK_ERR_BAD_SHAPE (-2)       /* d not in {64,128,256}, H % H_kv != 0, sizes <= 0 ... */
+#define RK_ERR_BAD_FORMAT (-3)      /* unknown / unsupported element format or layout */
+#define RK_ERR_WORKSPACE (-4)       /* workspace missing, too small or misaligned */
+#define RK_ERR_MISALIGNED (-5)      /* a tensor pointer breaks the 16-byte alignment TMA needs */
+#define RK_ERR_UNSUPPORTED (-6)     /* valid request this build does not implement */
+#define RK_ERR_NO_DEVICE (-7)       /* no sm_100 device / driver entry point missing */
+#define RK_ERR_KERNEL_TIMEOUT (-8)  /* a bounded device-side wait gave up (see rk_last_device_status) */
+#define RK_ERR_TOO_LARGE (-9)       /* request exceeds a fixed capacity (no-allocation entry points) */
+
+/* Element formats (codes as in OCP MX; E4M3 and E3M2 decode exactly as
+ * lib/golden/mx_fp_math.h:227-236,256-264). */
+enum { RK_FMT_E4M3 = 0, RK_FMT_E5M2 = 1, RK_FMT_E2M3 = 2, RK_FMT_E3M2 = 3 };
+
+/* Where V's block-32 scales run.
+ * KEYS: scales [B][H_kv][ceil(S_kv/32)][d], the reference's own V layout
+ *       (kernels/flash_attention_mx_gqa/fa_gen_data.py:106-117: V_scales[Bk/32][d]).
+ * D   : scales [B][H_kv][S_kv][d/32], what a KV cache quantized "along d" holds;
+ *       V is re-blocked along the keys into the workspace before the kernel runs. */
+enum { RK_V_SCALES_ALONG_KEYS = 0, RK_V_SCALES_ALONG_D = 1 };
+
+RK_API const char* rk_error_string(int code);
+RK_API int rk_version(void);
+
+/* ---------------------------------------------------------------------------
+ * MX block quantizer.  Replaces kernel_body/quantize_one_block of
+ * kernels/simt_quant/kernel.cpp:95-137 (KernelArgs{X,out,nblocks} :83-87) and
+ * its golden lib/golden/golden.py:118-170.  Bit-exact with both.
+ *   x      fp32 [rows][cols] row-major
+ *   codes  u8   [rows][cols]
+ *   scales u8   [rows][cols/32]           (rk_mx_quantize: blocks along cols)
+ *          u8   [batch][ceil(rows/32)][cols]  (rk_mx_quantize_keys: blocks run
+ *               down the rows of each [rows][cols] matrix of the batch -- how
+ *               the reference quantizes V, kernels/flash_attention_mx/gen_data.py:77)
+ * cols must be a multiple of 32 for rk_mx_quantize.
+ * ------------------------------------------------------------------------- */
+RK_API int rk_mx_quantize(const float* x, int64_t rows, int64_t cols, int fmt,
+                   uint8_t* codes, uint8_t* scales, void* stream);
+RK_API int rk_mx_quantize_keys(const float* x, int64_t batch, int64_t rows, int64_t cols, int fmt,
+                        uint8_t* codes, uint8_t* scales, void* stream);
+
+/* Re-block V from scales along d to scales along the keys (decode exactly, then
+ * the same block rule down each column).  No reference counterpart: the
+ * reference generates V already blocked along the keys.
+ *   codes [batch][S][d], scales [batch][S][d/32] -> out_codes [batch][S][d],
+ *   out_scales [batch][ceil(S/32)][d]. */
+RK_API int rk_mx_rebase_v(const uint8_t* codes, const uint8_t* scales, int64_t batch, int64_t S, int64_t d,
+                   int fmt, uint8_t* out_codes, uint8_t* out_scales, void* stream);
+
+/* ---------------------------------------------------------------------------
+ * Prefill attention.  Replaces fa_entry(void*, tid, threads, block_id) of
+ * kernels/flash_attention_mx_gqa/kernel.cpp:91-184 (GQA + causal),
+ * kernels/flash_attention_mx/kernel.cpp:3768 (single head) and
+ * kernels/flash_attention_mx_gemma/kernel.cpp (soft-cap, sliding window); the
+ * fields carry what those kernels read from include/fa_data.h
+ * (QK_A_in, QK_A_scales_row, QK_B_blocks, QK_B_scales_blocks, V_in, V_scales,
+ * FA_SQ FA_SK FA_D FA_NQ FA_NKV FA_QPOS0 FA_SOFTMAX_SCALE FA_ATTN_SOFTCAP
+ * FA_WINDOW -- kernels/flash_attention_mx_gemma/fa_gen_data.py:148-192),
+ * generalised by a batch dimension.
+ * ------------------------------------------------------------------------- */
+typedef struct rk_prefill_args {
+  const uint8_t* q;        /* codes [B][H][S_q][d]      (QK_A_in) */
+  const uint8_t* k;        /* codes [B][H_kv][S_kv][d]  (QK_B_blocks, natural [key][d] order) */
+  const uint8_t* v;        /* codes [B][H_kv][S_kv][d]  (V_in) */
+  const uint8_t* q_scale;  /* E8M0 [B][H][S_q][d/32]    (QK_A_scales_row, row-major) */
+  const uint8_t* k_scale;  /* E8M0 [B][H_kv][S_kv][d/32] */
+  const uint8_t* v_scale;  /* E8M0, layout chosen by v_scale_axis */
+  void* o;                 /* bf16 [B][H][S_q][d]  (O_GMEM, kernels/flash_attention_mx_gqa/kernel.cpp:50,115) */
+  float* lse;              /* optional fp32 [B][H][S_q]: running max + log(l), natural log */
+  int32_t B, H, H_kv, S_q, S_kv, d;   /* d in {64,128,256}; H % H_kv == 0 */
+  int32_t q_pos0;          /* global position of query row 0 (FA_QPOS0) */
+  int32_t causal;          /* mask key_pos > q_pos0 + row */
+  int32_t window;          /* >0: also mask key_pos <= q_pos - window (FA_WINDOW); 0 = off */
+  float softcap;           /* >0: s <- cap*tanh(s/cap) after the softmax scale, before mask/max; 0 = off */
+  float softmax_scale;     /* FA_SOFTMAX_SCALE; 0 selects 1/sqrt(d) */
+  int32_t q_fmt, kv_fmt;   /* RK_FMT_*; P is always E4M3 as in the reference */
+  int32_t v_scale_axis;    /* RK_V_SCALES_ALONG_KEYS | RK_V_SCALES_ALONG_D */
+  int32_t block_n;         /* keys per online-softmax step; 0 = default.  On return from
+                              rk_attn_prefill_block_n() the value the kernel uses (128). */
+  void* workspace;         /* >= rk_attn_prefill_workspace_bytes(), 256-byte aligned */
+  size_t workspace_bytes;
+} rk_prefill_args;
+
+/* Keys per online-softmax step the kernel uses (results depend on it; an oracle
+ * must be run with the same value). */
+RK_API int rk_attn_prefill_block_n(const rk_prefill_args* a);
+RK_API size_t rk_attn_prefill_workspace_bytes(const rk_prefill_args* a);
+RK_API int rk_attn_prefill(const rk_prefill_args* a, void* stream);
+
+/* Same call with HOST buffers: copies q/k/v and their scales to the device arena
+ * (256-byte aligned, at least rk_attn_prefill_host_arena_bytes()), runs rk_attn_prefill and
+ * copies O (and lse) back.  The reference's counterpart is the host stub that
+ * releases the kernel and waits for it (kernels/flash_attention_mx_gqa/host.cpp:5-18).
+ * Synchronises the stream before returning. */
+RK_API size_t rk_attn_prefill_host_arena_bytes(const rk_prefill_args* a_host);
+RK_API int rk_attn_prefill_host(const rk_prefill_args* a_host, void* device_arena, size_t arena_bytes, void* stream);
+
+/* ---------------------------------------------------------------------------
+ * Decode attention over an MX KV cache (one query token per sequence), split
+ * over the keys with an fp32 log-sum-exp combine.  The reference has no decode
+ * attention kernel (its nearest is the batched projection GEMV
+ * kernels/gemv_batched_fp8_m128/kernel.cpp:1-33); semantics are the prefill
+ * path at S_q = 1, q_pos = kv_len-1, GQA head map of
+ * kernels/flash_attention_mx_gqa/kernel.cpp:109-115, no P requant.
+ * ------------------------------------------------------------------------- */
+typedef struct rk_decode_args {
+  const void* q;           /* bf16 [B][H][d] */
+  const uint8_t* k;        /* codes [B][H_kv][L][d] */
+  const uint8_t* v;        /* codes [B][H_kv][L][d] */
+  const uint8_t* k_scale;  /* E8M0 [B][H_kv][L][d/32] */
+  const uint8_t* v_scale;  /* E8M0 [B][H_kv][L][d/32] */
+  const int32_t* kv_len;   /* [B] valid keys per sequence, or NULL for L everywhere */
+  void* o;                 /* bf16 [B][H][d] */
+  float* lse;              /* optional fp32 [B][H] */
+  int32_t B, H, H_kv, L, d;   /* d == 128; H / H_kv in {1,2,4,8} */
+  float softmax_scale;     /* 0 selects 1/sqrt(d) */
+  int32_t kv_fmt;          /* RK_FMT_E4M3 */
+  int32_t num_splits;      /* 0 = choose; otherwise 1..64 */
+  void* workspace;         /* >= rk_attn_decode_workspace_bytes(), 16-byte aligned */
+  size_t workspace_bytes;
+} rk_decode_args;
+
+RK_API int rk_attn_decode_num_splits(const rk_decode_args* a);
+RK_API size_t rk_attn_decode_workspace_bytes(const rk_decode_args* a);
+RK_API int rk_attn_decode(const rk_decode_args* a, void* stream);
+
+/* Status word of the last kernel that ran on the current device: 0 = clean;
+ * non-zero = a bounded wait inside a kernel gave up (the code says which) and
+ * the output of that launch is not valid.  Synchronises the device. */
+RK_API int rk_last_device_status(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RK_MX_ATTN_H_ */

@@ -1,0 +1,14 @@
+"""B200-native MX flash-attention path of radiance-kernels.
+
+Host-side mirror of the C ABI in include/rk_mx_attn.h.  Every function here
+launches the CUDA kernels of librk_mx_attn.so on torch CUDA tensors; there is
+no CPU path and no fallback: a missing library or a missing GPU raises.
+"""
+from ._lib import lib, build_library, RkError, check  # noqa: F401
+from .api import (  # noqa: F401
+    E4M3, E5M2, E2M3, E3M2, V_SCALES_ALONG_KEYS, V_SCALES_ALONG_D,
+    mx_quantize, mx_quantize_keys, mx_rebase_v,
+    attn_prefill, attn_prefill_workspace_bytes, attn_prefill_host, PrefillHostRunner,
+    attn_decode, attn_decode_workspace_bytes, attn_decode_num_splits,
+    last_device_status, shard_range,
+)

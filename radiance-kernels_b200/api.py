@@ -1,0 +1,188 @@
+"""Torch-tensor front end of the C ABI (include/rk_mx_attn.h).
+
+Argument names and meaning follow the reference kernels' data headers
+(kernels/flash_attention_mx_gemma/fa_gen_data.py:148-192): Q/K/V element codes
+with E8M0 block scales, B/H/H_kv/S/d, q_pos0, causal, window, softcap,
+softmax_scale.  torch is used for device memory and streams only; all math runs
+in the library's CUDA kernels.
+"""
+import ctypes as C
+
+import torch
+
+from ._lib import DecodeArgs, PrefillArgs, check, lib
+
+E4M3, E5M2, E2M3, E3M2 = 0, 1, 2, 3
+V_SCALES_ALONG_KEYS, V_SCALES_ALONG_D = 0, 1
+
+
+def _stream():
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _ptr(t):
+    return None if t is None else C.c_void_p(t.data_ptr())
+
+
+def _need_cuda(*ts):
+    for t in ts:
+        if t is not None and (not t.is_cuda or not t.is_contiguous()):
+            raise ValueError("expected contiguous CUDA tensors")
+
+
+def mx_quantize(x, fmt=E4M3):
+    """fp32 [..., cols] -> (codes uint8 [..., cols], scales uint8 [..., cols/32]); blocks along the last axis."""
+    _need_cuda(x)
+    if x.dtype != torch.float32:
+        raise ValueError("mx_quantize takes float32")
+    cols = x.shape[-1]
+    rows = x.numel() // max(cols, 1)
+    codes = torch.empty(x.shape, dtype=torch.uint8, device=x.device)
+    scales = torch.empty(x.shape[:-1] + (cols // 32,), dtype=torch.uint8, device=x.device)
+    check(lib().rk_mx_quantize(_ptr(x), rows, cols, fmt, _ptr(codes), _ptr(scales), _stream()), "rk_mx_quantize")
+    return codes, scales
+
+
+def mx_quantize_keys(x, fmt=E4M3):
+    """fp32 [..., rows, cols] -> codes same shape, scales [..., ceil(rows/32), cols]; blocks run down the rows."""
+    _need_cuda(x)
+    if x.dtype != torch.float32:
+        raise ValueError("mx_quantize_keys takes float32")
+    rows, cols = x.shape[-2], x.shape[-1]
+    batch = x.numel() // max(rows * cols, 1)
+    codes = torch.empty(x.shape, dtype=torch.uint8, device=x.device)
+    scales = torch.empty(x.shape[:-2] + ((rows + 31) // 32, cols), dtype=torch.uint8, device=x.device)
+    check(lib().rk_mx_quantize_keys(_ptr(x), batch, rows, cols, fmt, _ptr(codes), _ptr(scales), _stream()),
+          "rk_mx_quantize_keys")
+    return codes, scales
+
+
+def mx_rebase_v(codes, scales, fmt=E4M3):
+    """[..., S, d] codes + [..., S, d/32] scales -> codes [..., S, d] + scales [..., ceil(S/32), d] (blocks along keys)."""
+    _need_cuda(codes, scales)
+    S, d = codes.shape[-2], codes.shape[-1]
+    batch = codes.numel() // max(S * d, 1)
+    oc = torch.empty_like(codes)
+    osc = torch.empty(codes.shape[:-2] + ((S + 31) // 32, d), dtype=torch.uint8, device=codes.device)
+    check(lib().rk_mx_rebase_v(_ptr(codes), _ptr(scales), batch, S, d, fmt, _ptr(oc), _ptr(osc), _stream()), "rk_mx_rebase_v")
+    return oc, osc
+
+
+def _prefill_args(q, k, v, q_scale, k_scale, v_scale, o, lse, causal, softmax_scale, q_pos0, window, softcap,
+                  q_fmt, kv_fmt, v_scale_axis):
+    B, H, S_q, d = q.shape
+    H_kv, S_kv = k.shape[1], k.shape[2]
+    a = PrefillArgs()
+    a.q, a.k, a.v = _ptr(q), _ptr(k), _ptr(v)
+    a.q_scale, a.k_scale, a.v_scale = _ptr(q_scale), _ptr(k_scale), _ptr(v_scale)
+    a.o, a.lse = _ptr(o), _ptr(lse)
+    a.B, a.H, a.H_kv, a.S_q, a.S_kv, a.d = B, H, H_kv, S_q, S_kv, d
+    a.q_pos0, a.causal, a.window = q_pos0, int(bool(causal)), window
+    a.softcap, a.softmax_scale = float(softcap), float(softmax_scale)
+    a.q_fmt, a.kv_fmt, a.v_scale_axis, a.block_n = q_fmt, kv_fmt, v_scale_axis, 0
+    return a
+
+
+def attn_prefill_workspace_bytes(B, H, H_kv, S_q, S_kv, d, v_scale_axis=V_SCALES_ALONG_D):
+    a = PrefillArgs()
+    a.B, a.H, a.H_kv, a.S_q, a.S_kv, a.d = B, H, H_kv, S_q, S_kv, d
+    a.v_scale_axis = v_scale_axis
+    return lib().rk_attn_prefill_workspace_bytes(C.byref(a))
+
+
+def attn_prefill(q, k, v, q_scale, k_scale, v_scale, *, causal, softmax_scale=0.0, q_pos0=0, window=0, softcap=0.0,
+                 q_fmt=E4M3, kv_fmt=E4M3, v_scale_axis=V_SCALES_ALONG_D, out=None, lse=None, workspace=None):
+    """MX flash-attention prefill.  q [B,H,S_q,d], k/v [B,H_kv,S_kv,d] uint8 codes; scales as the C header says.
+    Returns O bf16 [B,H,S_q,d]."""
+    _need_cuda(q, k, v, q_scale, k_scale, v_scale, out, lse, workspace)
+    B, H, S_q, d = q.shape
+    o = out if out is not None else torch.empty((B, H, S_q, d), dtype=torch.bfloat16, device=q.device)
+    a = _prefill_args(q, k, v, q_scale, k_scale, v_scale, o, lse, causal, softmax_scale, q_pos0, window, softcap,
+                      q_fmt, kv_fmt, v_scale_axis)
+    need = lib().rk_attn_prefill_workspace_bytes(C.byref(a))
+    if workspace is None:
+        workspace = torch.empty(max(need, 1024), dtype=torch.uint8, device=q.device)
+    a.workspace, a.workspace_bytes = _ptr(workspace), workspace.numel()
+    check(lib().rk_attn_prefill(C.byref(a), _stream()), "rk_attn_prefill")
+    return o
+
+
+class PrefillHostRunner:
+    """Prefill through the host-buffer entry point (rk_attn_prefill_host): inputs and output live in
+    pinned host memory, the device arena is allocated once and reused."""
+
+    def __init__(self, q, k, v, q_scale, k_scale, v_scale, *, causal, softmax_scale=0.0, q_pos0=0, window=0,
+                 softcap=0.0, q_fmt=E4M3, kv_fmt=E4M3, v_scale_axis=V_SCALES_ALONG_D, device="cuda"):
+        for t in (q, k, v, q_scale, k_scale, v_scale):
+            if t.is_cuda or not t.is_contiguous():
+                raise ValueError("host runner takes contiguous CPU tensors (pinned for full copy speed)")
+        self.keep = (q, k, v, q_scale, k_scale, v_scale)
+        B, H, S_q, d = q.shape
+        self.o = torch.empty((B, H, S_q, d), dtype=torch.bfloat16).pin_memory()
+        self.args = _prefill_args(q, k, v, q_scale, k_scale, v_scale, self.o, None, causal, softmax_scale, q_pos0,
+                                  window, softcap, q_fmt, kv_fmt, v_scale_axis)
+        need = lib().rk_attn_prefill_host_arena_bytes(C.byref(self.args))
+        self.arena = torch.empty(need + 1024, dtype=torch.uint8, device=device)
+        self.h2d_bytes = sum(t.numel() * t.element_size() for t in self.keep)
+        self.d2h_bytes = self.o.numel() * 2
+
+    def run(self):
+        check(lib().rk_attn_prefill_host(C.byref(self.args), _ptr(self.arena), self.arena.numel(), _stream()),
+              "rk_attn_prefill_host")
+        return self.o
+
+
+def attn_prefill_host(q, k, v, q_scale, k_scale, v_scale, **kw):
+    return PrefillHostRunner(q, k, v, q_scale, k_scale, v_scale, **kw).run()
+
+
+def _decode_args(q, k, v, k_scale, v_scale, kv_len, o, lse, softmax_scale, kv_fmt, num_splits):
+    B, H, d = q.shape
+    H_kv, L = k.shape[1], k.shape[2]
+    a = DecodeArgs()
+    a.q, a.k, a.v, a.k_scale, a.v_scale = _ptr(q), _ptr(k), _ptr(v), _ptr(k_scale), _ptr(v_scale)
+    a.kv_len, a.o, a.lse = _ptr(kv_len), _ptr(o), _ptr(lse)
+    a.B, a.H, a.H_kv, a.L, a.d = B, H, H_kv, L, d
+    a.softmax_scale, a.kv_fmt, a.num_splits = float(softmax_scale), kv_fmt, num_splits
+    return a
+
+
+def attn_decode_num_splits(B, H, H_kv, L, d=128, num_splits=0):
+    a = DecodeArgs()
+    a.B, a.H, a.H_kv, a.L, a.d, a.num_splits = B, H, H_kv, L, d, num_splits
+    return lib().rk_attn_decode_num_splits(C.byref(a))
+
+
+def attn_decode_workspace_bytes(B, H, H_kv, L, d=128, num_splits=0):
+    a = DecodeArgs()
+    a.B, a.H, a.H_kv, a.L, a.d, a.num_splits = B, H, H_kv, L, d, num_splits
+    return lib().rk_attn_decode_workspace_bytes(C.byref(a))
+
+
+def attn_decode(q, k, v, k_scale, v_scale, *, kv_len=None, softmax_scale=0.0, kv_fmt=E4M3, num_splits=0, out=None,
+                lse=None, workspace=None):
+    """Decode attention: q bf16 [B,H,d]; k/v codes [B,H_kv,L,d]; scales [B,H_kv,L,d/32]; kv_len int32 [B] or None.
+    Returns O bf16 [B,H,d]."""
+    _need_cuda(q, k, v, k_scale, v_scale, kv_len, out, lse, workspace)
+    if q.dtype != torch.bfloat16:
+        raise ValueError("decode query must be bfloat16")
+    B, H, d = q.shape
+    o = out if out is not None else torch.empty((B, H, d), dtype=torch.bfloat16, device=q.device)
+    a = _decode_args(q, k, v, k_scale, v_scale, kv_len, o, lse, softmax_scale, kv_fmt, num_splits)
+    need = lib().rk_attn_decode_workspace_bytes(C.byref(a))
+    if workspace is None:
+        workspace = torch.empty(max(need, 16), dtype=torch.uint8, device=q.device)
+    a.workspace, a.workspace_bytes = _ptr(workspace), workspace.numel()
+    check(lib().rk_attn_decode(C.byref(a), _stream()), "rk_attn_decode")
+    return o
+
+
+def last_device_status():
+    return lib().rk_last_device_status()
+
+
+def shard_range(n_units, rank, world):
+    """Contiguous block partition of n_units independent (batch, KV-head) units over `world` ranks."""
+    base, rem = divmod(n_units, world)
+    lo = rank * base + min(rank, rem)
+    return lo, lo + base + (1 if rank < rem else 0)

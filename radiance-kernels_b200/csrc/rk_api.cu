@@ -1,0 +1,260 @@
+// extern "C" entry points of librk_mx_attn.so: argument validation, workspace
+// carving, the preparation passes and the kernel launches.  See
+// include/rk_mx_attn.h for the contract of every function.
+#include <cuda_runtime.h>
+
+#include <mutex>
+
+#include "rk_internal.h"
+
+namespace rk {
+
+namespace {
+struct DeviceState { int sms = 0; int* status = nullptr; };
+std::mutex g_mu;
+DeviceState g_dev[64];
+
+DeviceState& dev_state() {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  std::lock_guard<std::mutex> lk(g_mu);
+  DeviceState& s = g_dev[dev & 63];
+  if (s.sms == 0) {
+    cudaDeviceGetAttribute(&s.sms, cudaDevAttrMultiProcessorCount, dev);
+    if (s.sms <= 0) s.sms = 1;
+    if (cudaMalloc(&s.status, sizeof(int)) == cudaSuccess) cudaMemset(s.status, 0, sizeof(int));
+  }
+  return s;
+}
+size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
+}  // namespace
+
+int num_sms() { return dev_state().sms; }
+int* device_status_word() { return dev_state().status; }
+
+extern float* g_prefill_dbg;
+
+struct PrefillWs { size_t q_sf, k_sf, v_sf, v_codes, total; };
+
+static PrefillWs prefill_ws(const rk_prefill_args& a) {
+  const size_t dch = (a.d + 127) / 128, nqt = (a.S_q + 127) / 128, nkt = (a.S_kv + 127) / 128;
+  PrefillWs w;
+  size_t off = 0;
+  w.q_sf = off; off = align_up(off + (size_t)a.B * a.H * nqt * dch * 512, 1024);
+  w.k_sf = off; off = align_up(off + (size_t)a.B * a.H_kv * nkt * dch * 512, 1024);
+  w.v_sf = off; off = align_up(off + (size_t)a.B * a.H_kv * nkt * dch * 512, 1024);
+  w.v_codes = off;
+  if (a.v_scale_axis == RK_V_SCALES_ALONG_D) off = align_up(off + (size_t)a.B * a.H_kv * a.S_kv * a.d, 1024);
+  w.total = off;
+  return w;
+}
+
+static int check_prefill_shape(const rk_prefill_args* a) {
+  if (!a) return RK_ERR_NULL_POINTER;
+  if (a->B <= 0 || a->H <= 0 || a->H_kv <= 0 || a->S_q <= 0 || a->S_kv <= 0) return RK_ERR_BAD_SHAPE;
+  if (a->d != 64 && a->d != 128 && a->d != 256) return RK_ERR_BAD_SHAPE;
+  if (a->H % a->H_kv != 0) return RK_ERR_BAD_SHAPE;
+  if (a->window < 0 || a->softcap < 0.0f || a->softmax_scale < 0.0f) return RK_ERR_BAD_SHAPE;
+  if (a->v_scale_axis != RK_V_SCALES_ALONG_KEYS && a->v_scale_axis != RK_V_SCALES_ALONG_D) return RK_ERR_BAD_FORMAT;
+  if (a->q_fmt < 0 || a->q_fmt > 3 || a->kv_fmt < 0 || a->kv_fmt > 3) return RK_ERR_BAD_FORMAT;
+  // 6-bit operands need the packed 16-in-12-bytes memory format of the tensor core; not built yet
+  if (a->q_fmt > RK_FMT_E5M2 || a->kv_fmt > RK_FMT_E5M2) return RK_ERR_UNSUPPORTED;
+  if (a->block_n != 0 && a->block_n != 128) return RK_ERR_UNSUPPORTED;
+  return RK_OK;
+}
+
+}  // namespace rk
+
+using namespace rk;
+
+extern "C" {
+
+const char* rk_error_string(int code) {
+  switch (code) {
+    case RK_OK: return "ok";
+    case RK_ERR_NULL_POINTER: return "null pointer";
+    case RK_ERR_BAD_SHAPE: return "bad shape";
+    case RK_ERR_BAD_FORMAT: return "bad element format or layout";
+    case RK_ERR_WORKSPACE: return "workspace missing, too small or misaligned";
+    case RK_ERR_MISALIGNED: return "tensor pointer not 16-byte aligned";
+    case RK_ERR_UNSUPPORTED: return "not implemented in this build";
+    case RK_ERR_NO_DEVICE: return "no usable device or driver entry point";
+    case RK_ERR_KERNEL_TIMEOUT: return "a bounded device-side wait gave up";
+    case RK_ERR_TOO_LARGE: return "request exceeds a fixed capacity";
+    default: return code > 0 ? cudaGetErrorString((cudaError_t)code) : "unknown error";
+  }
+}
+
+int rk_version(void) { return 100; }
+
+int rk_mx_quantize(const float* x, int64_t rows, int64_t cols, int fmt, uint8_t* codes, uint8_t* scales, void* stream) {
+  if (!x || !codes || !scales) return RK_ERR_NULL_POINTER;
+  if (rows < 0 || cols < 0 || cols % 32 != 0) return RK_ERR_BAD_SHAPE;
+  if (fmt < 0 || fmt > 3) return RK_ERR_BAD_FORMAT;
+  if (!aligned(x, 16) || !aligned(codes, 8)) return RK_ERR_MISALIGNED;
+  return launch_quantize_rows(x, rows, cols, fmt, codes, scales, (cudaStream_t)stream);
+}
+
+int rk_mx_quantize_keys(const float* x, int64_t batch, int64_t rows, int64_t cols, int fmt, uint8_t* codes,
+                        uint8_t* scales, void* stream) {
+  if (!x || !codes || !scales) return RK_ERR_NULL_POINTER;
+  if (batch < 0 || rows < 0 || cols < 0 || cols % 4 != 0) return RK_ERR_BAD_SHAPE;
+  if (fmt < 0 || fmt > 3) return RK_ERR_BAD_FORMAT;
+  if (!aligned(x, 16) || !aligned(codes, 4) || !aligned(scales, 4)) return RK_ERR_MISALIGNED;
+  return launch_quantize_keys(x, batch, rows, cols, fmt, codes, scales, (cudaStream_t)stream);
+}
+
+int rk_mx_rebase_v(const uint8_t* codes, const uint8_t* scales, int64_t batch, int64_t S, int64_t d, int fmt,
+                   uint8_t* out_codes, uint8_t* out_scales, void* stream) {
+  if (!codes || !scales || !out_codes || !out_scales) return RK_ERR_NULL_POINTER;
+  if (batch < 0 || S < 0 || d <= 0 || d % 32 != 0) return RK_ERR_BAD_SHAPE;
+  if (fmt < 0 || fmt > 3) return RK_ERR_BAD_FORMAT;
+  if (!aligned(codes, 4) || !aligned(out_codes, 4) || !aligned(out_scales, 4)) return RK_ERR_MISALIGNED;
+  return launch_rebase_v(codes, scales, batch, S, d, fmt, out_codes, out_scales, false, (cudaStream_t)stream);
+}
+
+int rk_attn_prefill_block_n(const rk_prefill_args* a) { (void)a; return 128; }
+
+size_t rk_attn_prefill_workspace_bytes(const rk_prefill_args* a) {
+  if (check_prefill_shape(a) != RK_OK) return 0;
+  return prefill_ws(*a).total;
+}
+
+int rk_attn_prefill(const rk_prefill_args* a, void* stream) {
+  int rc = check_prefill_shape(a);
+  if (rc != RK_OK) return rc;
+  if (!a->q || !a->k || !a->v || !a->q_scale || !a->k_scale || !a->v_scale || !a->o) return RK_ERR_NULL_POINTER;
+  if (!aligned(a->q, 16) || !aligned(a->k, 16) || !aligned(a->v, 16) || !aligned(a->o, 16)) return RK_ERR_MISALIGNED;
+  const PrefillWs w = prefill_ws(*a);
+  if (!a->workspace || a->workspace_bytes < w.total || !aligned(a->workspace, 256)) return RK_ERR_WORKSPACE;
+  cudaStream_t st = (cudaStream_t)stream;
+  uint8_t* ws = reinterpret_cast<uint8_t*>(a->workspace);
+  const int64_t bhq = (int64_t)a->B * a->H, bhkv = (int64_t)a->B * a->H_kv;
+
+  if ((rc = launch_retile_rowscales(a->q_scale, bhq, a->S_q, a->d, ws + w.q_sf, st)) != RK_OK) return rc;
+  if ((rc = launch_retile_rowscales(a->k_scale, bhkv, a->S_kv, a->d, ws + w.k_sf, st)) != RK_OK) return rc;
+  const uint8_t* v_codes = a->v;
+  if (a->v_scale_axis == RK_V_SCALES_ALONG_D) {
+    if (a->S_kv % 128 != 0 || a->d % 128 != 0) {
+      // atoms of ragged tiles keep bytes the re-blocking pass never writes: make them 2^0
+      cudaError_t e = cudaMemsetAsync(ws + w.v_sf, 0x7F, w.v_codes - w.v_sf, st);
+      if (e != cudaSuccess) return (int)e;
+    }
+    if ((rc = launch_rebase_v(a->v, a->v_scale, bhkv, a->S_kv, a->d, a->kv_fmt, ws + w.v_codes, ws + w.v_sf, true, st)) != RK_OK)
+      return rc;
+    v_codes = ws + w.v_codes;
+  } else {
+    if ((rc = launch_retile_keyscales(a->v_scale, bhkv, a->S_kv, a->d, ws + w.v_sf, st)) != RK_OK) return rc;
+  }
+  return launch_prefill(*a, v_codes, ws + w.q_sf, ws + w.k_sf, ws + w.v_sf, st);
+}
+
+size_t rk_attn_prefill_host_arena_bytes(const rk_prefill_args* a) {
+  if (check_prefill_shape(a) != RK_OK) return 0;
+  const size_t nbd = a->d / 32;
+  const size_t q = (size_t)a->B * a->H * a->S_q * a->d, kv = (size_t)a->B * a->H_kv * a->S_kv * a->d;
+  const size_t vs = a->v_scale_axis == RK_V_SCALES_ALONG_D ? kv / 32 : (size_t)a->B * a->H_kv * ((a->S_kv + 31) / 32) * a->d;
+  size_t off = 0;
+  off = align_up(off + q, 1024); off = align_up(off + kv, 1024); off = align_up(off + kv, 1024);
+  off = align_up(off + q / a->d * nbd, 1024); off = align_up(off + kv / a->d * nbd, 1024); off = align_up(off + vs, 1024);
+  off = align_up(off + q * 2, 1024); off = align_up(off + q / a->d * 4, 1024);
+  return off + prefill_ws(*a).total;
+}
+
+int rk_attn_prefill_host(const rk_prefill_args* h, void* arena, size_t arena_bytes, void* stream) {
+  int rc = check_prefill_shape(h);
+  if (rc != RK_OK) return rc;
+  if (!h->q || !h->k || !h->v || !h->q_scale || !h->k_scale || !h->v_scale || !h->o || !arena) return RK_ERR_NULL_POINTER;
+  if (arena_bytes < rk_attn_prefill_host_arena_bytes(h) || !aligned(arena, 256)) return RK_ERR_WORKSPACE;
+  cudaStream_t st = (cudaStream_t)stream;
+  const size_t nbd = h->d / 32;
+  const size_t q = (size_t)h->B * h->H * h->S_q * h->d, kv = (size_t)h->B * h->H_kv * h->S_kv * h->d;
+  const size_t qs = q / h->d * nbd, ks = kv / h->d * nbd;
+  const size_t vs = h->v_scale_axis == RK_V_SCALES_ALONG_D ? ks : (size_t)h->B * h->H_kv * ((h->S_kv + 31) / 32) * h->d;
+  uint8_t* base = reinterpret_cast<uint8_t*>(arena);
+  size_t off = 0;
+  rk_prefill_args d = *h;
+  auto take = [&](size_t bytes) { uint8_t* p = base + off; off = align_up(off + bytes, 1024); return p; };
+  uint8_t* dq = take(q); uint8_t* dk = take(kv); uint8_t* dv = take(kv);
+  uint8_t* dqs = take(qs); uint8_t* dks = take(ks); uint8_t* dvs = take(vs);
+  uint8_t* dout = take(q * 2); uint8_t* dlse = take(q / h->d * 4);
+  cudaError_t e;
+#define RK_CP(dst, src, n) if ((e = cudaMemcpyAsync(dst, src, n, cudaMemcpyHostToDevice, st)) != cudaSuccess) return (int)e
+  RK_CP(dq, h->q, q); RK_CP(dk, h->k, kv); RK_CP(dv, h->v, kv);
+  RK_CP(dqs, h->q_scale, qs); RK_CP(dks, h->k_scale, ks); RK_CP(dvs, h->v_scale, vs);
+#undef RK_CP
+  d.q = dq; d.k = dk; d.v = dv; d.q_scale = dqs; d.k_scale = dks; d.v_scale = dvs;
+  d.o = dout; d.lse = h->lse ? reinterpret_cast<float*>(dlse) : nullptr;
+  d.workspace = base + off; d.workspace_bytes = arena_bytes - off;
+  if ((rc = rk_attn_prefill(&d, stream)) != RK_OK) return rc;
+  if ((e = cudaMemcpyAsync(h->o, dout, q * 2, cudaMemcpyDeviceToHost, st)) != cudaSuccess) return (int)e;
+  if (h->lse && (e = cudaMemcpyAsync(h->lse, dlse, q / h->d * 4, cudaMemcpyDeviceToHost, st)) != cudaSuccess) return (int)e;
+  return (int)cudaStreamSynchronize(st);
+}
+
+// ------------------------------------------------------------------------------------------------
+static int check_decode_shape(const rk_decode_args* a) {
+  if (!a) return RK_ERR_NULL_POINTER;
+  if (a->B <= 0 || a->H <= 0 || a->H_kv <= 0 || a->L <= 0) return RK_ERR_BAD_SHAPE;
+  if (a->d != 128) return RK_ERR_BAD_SHAPE;
+  if (a->H % a->H_kv != 0) return RK_ERR_BAD_SHAPE;
+  const int grp = a->H / a->H_kv;
+  if (grp != 1 && grp != 2 && grp != 4 && grp != 8) return RK_ERR_BAD_SHAPE;
+  if (a->L % 4 != 0) return RK_ERR_BAD_SHAPE;   // keeps every scale-row copy a 16-byte multiple
+  if (a->kv_fmt != RK_FMT_E4M3) return RK_ERR_UNSUPPORTED;
+  if (a->num_splits < 0 || a->num_splits > 64 || a->softmax_scale < 0.0f) return RK_ERR_BAD_SHAPE;
+  return RK_OK;
+}
+
+int rk_attn_decode_num_splits(const rk_decode_args* a) {
+  if (check_decode_shape(a) != RK_OK) return 0;
+  const int tiles = (a->L + 127) / 128;
+  if (a->num_splits > 0) return a->num_splits < tiles ? a->num_splits : tiles;
+  // two CTAs fit on an SM; pick the split count (each split >= 4 key tiles) whose CTA count fills
+  // whole waves best, preferring fewer splits on ties
+  const long slots = 2L * num_sms(), units = (long)a->B * a->H_kv;
+  int best = 1; double best_eff = -1.0;
+  for (int s = 1; s <= 64 && (s == 1 || tiles / s >= 4); ++s) {
+    const long ctas = units * s, waves = (ctas + slots - 1) / slots;
+    const double eff = (double)ctas / (double)(waves * slots);
+    if (eff > best_eff + 0.02) { best_eff = eff; best = s; }
+  }
+  return best;
+}
+
+size_t rk_attn_decode_workspace_bytes(const rk_decode_args* a) {
+  const int ns = rk_attn_decode_num_splits(a);
+  if (ns <= 0) return 0;
+  return (size_t)a->B * a->H * ns * (128 + 2) * sizeof(float);
+}
+
+int rk_attn_decode(const rk_decode_args* a, void* stream) {
+  int rc = check_decode_shape(a);
+  if (rc != RK_OK) return rc;
+  if (!a->q || !a->k || !a->v || !a->k_scale || !a->v_scale || !a->o) return RK_ERR_NULL_POINTER;
+  if (!aligned(a->q, 16) || !aligned(a->k, 16) || !aligned(a->v, 16) || !aligned(a->k_scale, 16) ||
+      !aligned(a->v_scale, 16) || !aligned(a->o, 16))
+    return RK_ERR_MISALIGNED;
+  const int ns = rk_attn_decode_num_splits(a);
+  if (!a->workspace || a->workspace_bytes < rk_attn_decode_workspace_bytes(a) || !aligned(a->workspace, 16))
+    return RK_ERR_WORKSPACE;
+  return launch_decode(*a, ns, (cudaStream_t)stream);
+}
+
+int rk_last_device_status(void) {
+  int* w = device_status_word();
+  if (!w) return RK_ERR_NO_DEVICE;
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) return (int)e;
+  int v = 0;
+  if ((e = cudaMemcpy(&v, w, sizeof(int), cudaMemcpyDeviceToHost)) != cudaSuccess) return (int)e;
+  if (v != 0) cudaMemset(w, 0, sizeof(int));
+  return v;
+}
+
+/* Test hook (not in the public header): stage dump of the first query tile / first key tile of
+ * the next prefill launches into `buf` (>= 32768 floats), or NULL to switch it off. */
+RK_API void rk_debug_set_prefill_dump(float* buf) { g_prefill_dbg = buf; }
+
+}  // extern "C"

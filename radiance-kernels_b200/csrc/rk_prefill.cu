@@ -1,0 +1,519 @@
+// MX flash-attention prefill for sm_100a: TMA -> shared memory -> tcgen05
+// block-scaled MMA (kind::mxf8f6f4, E8M0 scales in TMEM) -> fp32 online softmax
+// in registers -> P re-quantized to E4M3 + E8M0 per 32 keys -> second
+// block-scaled MMA accumulating O in TMEM.
+//
+// Follows the streaming tile loop of fa_entry,
+// kernels/flash_attention_mx_gqa/kernel.cpp:91-184 (QK_j -> fused softmax+requant
+// -> scale pack -> PV_j -> rescale/accumulate -> finalize), with the stages
+// mapped onto Blackwell units:
+//   mxgemm_prefetch_tile / mxgemm_compute_tile (mesh)  -> TMA + tcgen05.mma
+//   fused_softmax_requant_tpr (one lane per row,
+//     flash_mx_impl.hpp:314-394)                       -> one thread per row, S row in registers
+//   pack_scales_to_sfmem (flash_mx_impl.hpp:625-639)   -> one st.shared per row + tcgen05.cp
+//   rescale_accumulate / finalize_O (:508-553)         -> O kept in TMEM, rescaled in place
+//
+// One CTA = one 128-row query tile of one (batch, head).  192 threads:
+//   warps 0-3  softmax: thread r owns query row r (TMEM lane r)
+//   warp  4    TMA producer (one elected lane)
+//   warp  5    MMA issuer  (one elected lane), TMEM allocation
+// Keys are walked in tiles of 128 (the online-softmax step, "block_n").
+//
+// Roofline: tensor-core bound by FLOP count (4*S_q*S_kv*d per head, half of it
+// when causal); in practice the softmax/requant ALU work per S element bounds it.
+#include <cuda.h>
+#include <cuda_bf16.h>
+
+#include "rk_common.cuh"
+#include "rk_internal.h"
+
+namespace rk {
+
+constexpr int kBlockM = 128;
+constexpr int kBlockN = 128;
+constexpr int kTileBytes = 128 * 128;      // one [128 rows][128 B] swizzled tile
+constexpr int kSfAtomBytes = 512;
+constexpr int kNumThreads = 192;
+constexpr uint32_t kTmemCols = 512;
+
+// TMEM column map
+constexpr uint32_t kColS = 0;
+constexpr uint32_t kColO = 128;
+constexpr uint32_t kColSfQ = 384;                 // + ch*4
+constexpr uint32_t kColSfK = 392;                 // + stage*8 + ch*4   (<= 3 stages)
+constexpr uint32_t kColSfP = 416;                 // + pbuf*4
+constexpr uint32_t kColSfV = 424;                 // + stage*8 + ch*4
+
+struct PrefillParams {
+  const uint8_t* q_sf;
+  const uint8_t* k_sf;
+  const uint8_t* v_sf;
+  __nv_bfloat16* o;
+  float* lse;
+  int* status;
+  float* dbg;          // optional stage dump of CTA (0,0,0), first key tile
+  int H, H_kv, S_q, S_kv, d;
+  int n_q_tiles, n_kv_tiles;
+  int q_pos0, causal, window;
+  float scale_log2;    // softmax_scale * log2(e)
+  float cap_log2;      // softcap * log2(e)
+  float inv_cap_scale; // softmax_scale / softcap
+};
+
+template <int DCH, int KV_STAGES>
+struct SmemLayout {
+  static constexpr int q_off = 0;
+  static constexpr int k_off = q_off + DCH * kTileBytes;
+  static constexpr int v_off = k_off + KV_STAGES * DCH * kTileBytes;
+  static constexpr int p_off = v_off + KV_STAGES * DCH * kTileBytes;
+  static constexpr int sfq_off = p_off + 2 * kTileBytes;
+  static constexpr int sfk_off = sfq_off + DCH * kSfAtomBytes;
+  static constexpr int sfv_off = sfk_off + KV_STAGES * DCH * kSfAtomBytes;
+  static constexpr int sfp_off = sfv_off + KV_STAGES * DCH * kSfAtomBytes;
+  static constexpr int bar_off = sfp_off + 2 * kSfAtomBytes;
+  // barriers: q_full, k_full[S], k_empty[S], v_full[S], v_empty[S], s_full, s_empty, p_full[2], pv_done[2], drain
+  static constexpr int n_bars = 1 + 4 * KV_STAGES + 2 + 4 + 1;
+  static constexpr int misc_off = bar_off + n_bars * 8;
+  static constexpr int total = misc_off + 16;
+};
+
+// ---- softmax warps -----------------------------------------------------------------------------
+template <int DCH, int KV_STAGES, bool SOFTCAP>
+__device__ __forceinline__ void softmax_rows(const PrefillParams& p, uint8_t* smem, uint64_t* bars, uint32_t tmem_base,
+                                             volatile int* abort_flag, int qt, int bh, int n_tiles) {
+  using L = SmemLayout<DCH, KV_STAGES>;
+  uint64_t* s_full = bars + 1 + 4 * KV_STAGES;
+  uint64_t* s_empty = s_full + 1;
+  uint64_t* p_full = s_empty + 1;     // [2]
+  uint64_t* pv_done = p_full + 2;     // [2]
+
+  const int row = threadIdx.x;                 // 0..127
+  const int warp = row >> 5;
+  const uint32_t lane_addr = ((uint32_t)(warp * 32)) << 16;
+  const int q_row = qt * kBlockM + row;
+  const int q_pos = p.q_pos0 + q_row;
+  const float NEG_INF = __int_as_float(0xff800000);
+
+  float m_run = NEG_INF;   // running max, log2 domain (score * log2 e)
+  float l_run = 0.0f;
+  bool ok = true;
+
+  for (int j = 0; j < n_tiles && ok; ++j) {
+    const int pb = j & 1;
+    ok = __all_sync(0xffffffffu, mbar_wait(s_full, j & 1, abort_flag, p.status, 101));
+    if (!ok) break;
+    tc_fence_after();
+
+    float s[kBlockN];
+    {
+      uint32_t* sr = reinterpret_cast<uint32_t*>(s);
+#pragma unroll
+      for (int ch = 0; ch < 4; ++ch) tmem_ld32(tmem_base + lane_addr + kColS + ch * 32, sr + ch * 32);
+      tc_wait_ld();
+    }
+    tc_fence_before();
+    mbar_arrive(s_empty);        // S may now be overwritten by the next QK^T
+
+    if (p.dbg && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && j == 0) {
+#pragma unroll
+      for (int c = 0; c < kBlockN; ++c) p.dbg[row * 128 + c] = s[c];
+    }
+
+    // ---- scale (+ soft-cap), mask, row max: everything in the log2 domain -------------------
+    const int kbase = j * kBlockN;
+    const bool tail = (kbase + kBlockN > p.S_kv);
+    const bool diag = p.causal && (kbase + kBlockN - 1 > p.q_pos0 + qt * kBlockM);
+    const bool need_mask = tail || diag || (p.window > 0);
+    int hi = p.S_kv - 1 - kbase;                             // masked iff c > hi || c <= lo
+    if (p.causal) hi = min(hi, q_pos - kbase);
+    const int lo = (p.window > 0) ? (q_pos - p.window - kbase) : -1;
+
+    float mx = NEG_INF;
+#pragma unroll
+    for (int c = 0; c < kBlockN; ++c) {
+      float x;
+      if (SOFTCAP) {
+        // cap*tanh(s*scale/cap) with tanh(y) = 1 - 2/(1 + e^(2y)); result pre-multiplied by log2 e
+        const float y2 = s[c] * (2.0f * 1.4426950408889634f * p.inv_cap_scale);
+        const float e = ex2_approx(y2);
+        x = p.cap_log2 * fmaf(-2.0f, rcp_approx(1.0f + e), 1.0f);
+      } else {
+        x = s[c] * p.scale_log2;
+      }
+      if (need_mask) x = (c > hi || c <= lo) ? NEG_INF : x;
+      s[c] = x;
+      mx = fmaxf(mx, x);
+    }
+    const float m_new = fmaxf(m_run, mx);
+    const float m_use = (m_new == NEG_INF) ? 0.0f : m_new;
+    const float corr = (m_run == NEG_INF) ? 1.0f : ex2_approx(m_run - m_new);
+    m_run = m_new;
+
+    // ---- rescale O in TMEM once the previous PV has landed ------------------------------------
+    if (j > 0) {
+      ok = __all_sync(0xffffffffu, mbar_wait(&pv_done[(j - 1) & 1], ((j - 1) >> 1) & 1, abort_flag, p.status, 102));
+      if (!ok) break;
+      tc_fence_after();
+      if (__any_sync(0xffffffffu, corr != 1.0f)) {
+#pragma unroll 1
+        for (int ch = 0; ch < DCH * 4; ++ch) {
+          uint32_t r[32];
+          tmem_ld32(tmem_base + lane_addr + kColO + ch * 32, r);
+          tc_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * corr);
+          tmem_st32(tmem_base + lane_addr + kColO + ch * 32, r);
+        }
+        tc_wait_st();
+      }
+    }
+
+    // ---- p = 2^(x - m), row sum from the unquantised p, per-32-key block requant ---------------
+    uint8_t* p_tile = smem + L::p_off + pb * kTileBytes + row * 128;
+    float lsum = 0.0f;
+    uint32_t scale_word = 0;
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      float pmax = 0.0f;
+#pragma unroll
+      for (int c = 0; c < 32; ++c) {
+        const float pv = ex2_approx(s[g * 32 + c] - m_use);
+        s[g * 32 + c] = pv;
+        lsum += pv;
+        pmax = fmaxf(pmax, pv);
+      }
+      // E8M0 code = exponent field of the block max (se = floor(log2 pmax) <= 0, all-zero block -> 0)
+      int sc = (int)(__float_as_uint(pmax) >> 23);
+      sc = min(sc, 127);
+      scale_word |= (uint32_t)sc << (8 * g);
+      const int sub = (sc - 7) * 8;          // code = (bits >> 20) - sub : exponent re-biased to E4M3, 3 mantissa bits kept
+      uint32_t w[8];
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        uint32_t word = 0;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const uint32_t bits = __float_as_uint(s[g * 32 + q * 4 + e]);
+          int t = (int)(bits >> 20) - sub;
+          // below 2^-6 of the block scale (or p == 0) -> flushed to zero, no subnormals
+          t = (t >= 8 && bits >= 0x00800000u) ? t : 0;
+          word |= (uint32_t)t << (8 * e);
+        }
+        w[q] = word;
+      }
+      // two 16-byte chunks of this row, 128-byte swizzle: chunk index XOR (row % 8)
+      const int c0 = (2 * g) ^ (row & 7), c1 = (2 * g + 1) ^ (row & 7);
+      *reinterpret_cast<uint4*>(p_tile + c0 * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+      *reinterpret_cast<uint4*>(p_tile + c1 * 16) = make_uint4(w[4], w[5], w[6], w[7]);
+    }
+    l_run = l_run * corr + lsum;
+    *reinterpret_cast<uint32_t*>(smem + L::sfp_off + pb * kSfAtomBytes + (row & 31) * 16 + (row >> 5) * 4) = scale_word;
+
+    if (p.dbg && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && j == 0) {
+      // P codes as written (un-swizzled view) and the scale word, after the 128x128 S dump
+      uint32_t* d32 = reinterpret_cast<uint32_t*>(p.dbg + 128 * 128);
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        const uint4 v4 = *reinterpret_cast<const uint4*>(p_tile + ((c ^ (row & 7)) * 16));
+        d32[row * 32 + c * 4 + 0] = v4.x; d32[row * 32 + c * 4 + 1] = v4.y;
+        d32[row * 32 + c * 4 + 2] = v4.z; d32[row * 32 + c * 4 + 3] = v4.w;
+      }
+      d32[128 * 32 + row] = scale_word;
+    }
+
+    fence_proxy_async_smem();   // make the st.shared P tile + scales visible to the tensor-core (async) proxy
+    tc_fence_before();
+    mbar_arrive(&p_full[pb]);
+  }
+
+  // ---- epilogue: O / l -> bf16 -------------------------------------------------------------------
+  if (ok) {
+    const int last = n_tiles - 1;
+    ok = __all_sync(0xffffffffu, mbar_wait(&pv_done[last & 1], (last >> 1) & 1, abort_flag, p.status, 103));
+  }
+  if (ok) {
+    tc_fence_after();
+    const float inv_l = (l_run > 0.0f) ? 1.0f / l_run : 1.0f;
+    const bool live = q_row < p.S_q;
+    __nv_bfloat16* orow = p.o + ((size_t)bh * p.S_q + q_row) * p.d;
+    const int nch = p.d / 32;
+    if (p.dbg && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
+      p.dbg[128 * 128 + 128 * 32 + 128 + row * 2 + 0] = m_run;
+      p.dbg[128 * 128 + 128 * 32 + 128 + row * 2 + 1] = l_run;
+    }
+#pragma unroll 1
+    for (int ch = 0; ch < nch; ++ch) {
+      uint32_t r[32];
+      tmem_ld32(tmem_base + lane_addr + kColO + ch * 32, r);
+      tc_wait_ld();
+      if (live) {
+        uint32_t packed[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(r[2 * i]) * inv_l, __uint_as_float(r[2 * i + 1]) * inv_l);
+          packed[i] = *reinterpret_cast<const uint32_t*>(&b2);
+        }
+        uint4* dst = reinterpret_cast<uint4*>(orow + ch * 32);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) dst[i] = make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
+      }
+    }
+    if (p.lse && live)
+      p.lse[(size_t)bh * p.S_q + q_row] = (l_run > 0.0f) ? m_run * 0.6931471805599453f + logf(l_run) : NEG_INF;
+  }
+  tc_fence_before();
+}
+
+// ---- the kernel ---------------------------------------------------------------------------------
+template <int DCH, int KV_STAGES, bool SOFTCAP>
+__global__ void __launch_bounds__(kNumThreads, 1)
+prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+               const __grid_constant__ CUtensorMap tmap_v, const PrefillParams p, const uint32_t idesc_qk,
+               const uint32_t idesc_pv) {
+  using L = SmemLayout<DCH, KV_STAGES>;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::bar_off);
+  uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(smem + L::misc_off);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::misc_off + 4);
+
+  uint64_t* q_full = bars;
+  uint64_t* k_full = bars + 1;
+  uint64_t* k_empty = k_full + KV_STAGES;
+  uint64_t* v_full = k_empty + KV_STAGES;
+  uint64_t* v_empty = v_full + KV_STAGES;
+  uint64_t* s_full = v_empty + KV_STAGES;
+  uint64_t* s_empty = s_full + 1;
+  uint64_t* p_full = s_empty + 1;
+  uint64_t* pv_done = p_full + 2;
+  uint64_t* drain = pv_done + 2;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  // an earlier launch on this device gave up on a wait: do nothing until the host has read the status
+  if (*reinterpret_cast<volatile int*>(p.status) != 0) return;
+  // heavy (late) query tiles first within a head; heads adjacent so a KV head's tiles share L2
+  const int qt = p.n_q_tiles - 1 - (int)blockIdx.x;
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int bh = b * p.H + h;
+  const int bhkv = b * p.H_kv + h / (p.H / p.H_kv);
+
+  // key tiles this query tile needs: causal tiles wholly above the diagonal are never touched
+  // (blocks_used, kernels/flash_attention_mx_gqa/flash_attention_model.py:182-186)
+  int n_tiles = p.n_kv_tiles;
+  if (p.causal) {
+    const int max_qpos = p.q_pos0 + min(qt * kBlockM + kBlockM, p.S_q) - 1;
+    n_tiles = max_qpos < 0 ? 0 : min(n_tiles, max_qpos / kBlockN + 1);
+  }
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int i = 0; i < KV_STAGES; ++i) { mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1); mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1); }
+    mbar_init(s_full, 1); mbar_init(s_empty, 128);
+    mbar_init(&p_full[0], 128); mbar_init(&p_full[1], 128);
+    mbar_init(&pv_done[0], 1); mbar_init(&pv_done[1], 1);
+    mbar_init(drain, 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 5) { tmem_alloc(tmem_ptr, kTmemCols); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_ptr;
+
+  if (n_tiles == 0) {
+    // no visible key: O = 0 (the l <= 0 guard of finalize_O, kernels/flash_attention_mx_gemma/flash_mx_impl.hpp:554-560)
+    if (warp < 4) {
+      const int q_row = qt * kBlockM + threadIdx.x;
+      if (q_row < p.S_q) {
+        __nv_bfloat16* orow = p.o + ((size_t)bh * p.S_q + q_row) * p.d;
+        for (int c = 0; c < p.d; c += 8) *reinterpret_cast<uint4*>(orow + c) = make_uint4(0, 0, 0, 0);
+        if (p.lse) p.lse[(size_t)bh * p.S_q + q_row] = __int_as_float(0xff800000);
+      }
+    }
+  } else if (warp < 4) {
+    softmax_rows<DCH, KV_STAGES, SOFTCAP>(p, smem, bars, tmem_base, abort_flag, qt, bh, n_tiles);
+  } else if (warp == 4) {
+    // ================= TMA producer =================
+    if (lane == 0) {
+      prefetch_tmap(&tmap_q); prefetch_tmap(&tmap_k); prefetch_tmap(&tmap_v);
+      mbar_arrive_expect_tx(q_full, DCH * (kTileBytes + kSfAtomBytes));
+      for (int ch = 0; ch < DCH; ++ch) {
+        tma_load_3d(smem + L::q_off + ch * kTileBytes, &tmap_q, q_full, ch * 128, qt * kBlockM, bh);
+        bulk_load_1d(smem + L::sfq_off + ch * kSfAtomBytes,
+                     p.q_sf + (((size_t)bh * p.n_q_tiles + qt) * DCH + ch) * kSfAtomBytes, kSfAtomBytes, q_full);
+      }
+      bool ok = true;
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int st = j % KV_STAGES, use = j / KV_STAGES;
+        if (use > 0) ok = mbar_wait(&k_empty[st], (use - 1) & 1, abort_flag, p.status, 201);
+        if (!ok) break;
+        mbar_arrive_expect_tx(&k_full[st], DCH * (kTileBytes + kSfAtomBytes));
+        for (int ch = 0; ch < DCH; ++ch) {
+          tma_load_3d(smem + L::k_off + (st * DCH + ch) * kTileBytes, &tmap_k, &k_full[st], ch * 128, j * kBlockN, bhkv);
+          bulk_load_1d(smem + L::sfk_off + (st * DCH + ch) * kSfAtomBytes,
+                       p.k_sf + (((size_t)bhkv * p.n_kv_tiles + j) * DCH + ch) * kSfAtomBytes, kSfAtomBytes, &k_full[st]);
+        }
+        if (use > 0) ok = mbar_wait(&v_empty[st], (use - 1) & 1, abort_flag, p.status, 202);
+        if (!ok) break;
+        mbar_arrive_expect_tx(&v_full[st], DCH * (kTileBytes + kSfAtomBytes));
+        for (int ch = 0; ch < DCH; ++ch) {
+          tma_load_3d(smem + L::v_off + (st * DCH + ch) * kTileBytes, &tmap_v, &v_full[st], ch * 128, j * kBlockN, bhkv);
+          bulk_load_1d(smem + L::sfv_off + (st * DCH + ch) * kSfAtomBytes,
+                       p.v_sf + (((size_t)bhkv * p.n_kv_tiles + j) * DCH + ch) * kSfAtomBytes, kSfAtomBytes, &v_full[st]);
+        }
+      }
+    }
+  } else {
+    // ================= MMA issuer =================
+    if (lane == 0) {
+      const uint32_t q_addr = smem_u32(smem + L::q_off), k_addr = smem_u32(smem + L::k_off);
+      const uint32_t v_addr = smem_u32(smem + L::v_off), pt_addr = smem_u32(smem + L::p_off);
+      bool ok = mbar_wait(q_full, 0, abort_flag, p.status, 301);
+      if (ok) {
+        for (int ch = 0; ch < DCH; ++ch)
+          tc_cp_32x128b_warpx4(tmem_base + kColSfQ + ch * 4,
+                               make_smem_desc(smem_u32(smem + L::sfq_off + ch * kSfAtomBytes), 0, 128, kLayoutNone));
+      }
+      auto issue_pv = [&](int i) -> bool {
+        const int pb = i & 1, st = i % KV_STAGES, use = i / KV_STAGES;
+        if (!mbar_wait(&v_full[st], use & 1, abort_flag, p.status, 303)) return false;
+        if (!mbar_wait(&p_full[pb], (i >> 1) & 1, abort_flag, p.status, 304)) return false;
+        tc_fence_after();
+        tc_cp_32x128b_warpx4(tmem_base + kColSfP + pb * 4,
+                             make_smem_desc(smem_u32(smem + L::sfp_off + pb * kSfAtomBytes), 0, 128, kLayoutNone));
+        for (int ch = 0; ch < DCH; ++ch)
+          tc_cp_32x128b_warpx4(tmem_base + kColSfV + st * 8 + ch * 4,
+                               make_smem_desc(smem_u32(smem + L::sfv_off + (st * DCH + ch) * kSfAtomBytes), 0, 128, kLayoutNone));
+        for (int ch = 0; ch < DCH; ++ch) {
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) {
+            // A = P tile, K-major: 32 keys = 32 bytes along the swizzled 128-byte row
+            const uint64_t adesc = make_smem_desc(pt_addr + pb * kTileBytes + kk * 32, 16, 1024, kLayoutSw128);
+            // B = V tile, MN-major (d contiguous): 32 keys = 32 rows of 128 bytes
+            const uint64_t bdesc = make_smem_desc(v_addr + (st * DCH + ch) * kTileBytes + kk * 4096, kTileBytes, 1024, kLayoutSw128);
+            mma_mxf8f6f4_ss(tmem_base + kColO + ch * 128, adesc, bdesc, idesc_with_sf(idesc_pv, kk, kk),
+                            tmem_base + kColSfP + pb * 4, tmem_base + kColSfV + st * 8 + ch * 4, (i > 0 || kk > 0) ? 1u : 0u);
+          }
+        }
+        tc_commit(&v_empty[st]);
+        tc_commit(&pv_done[pb]);
+        return true;
+      };
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int st = j % KV_STAGES, use = j / KV_STAGES;
+        ok = mbar_wait(&k_full[st], use & 1, abort_flag, p.status, 302);
+        if (ok && j > 0) ok = mbar_wait(s_empty, (j - 1) & 1, abort_flag, p.status, 305);
+        if (!ok) break;
+        tc_fence_after();
+        for (int ch = 0; ch < DCH; ++ch)
+          tc_cp_32x128b_warpx4(tmem_base + kColSfK + st * 8 + ch * 4,
+                               make_smem_desc(smem_u32(smem + L::sfk_off + (st * DCH + ch) * kSfAtomBytes), 0, 128, kLayoutNone));
+        for (int ch = 0; ch < DCH; ++ch) {
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) {
+            const uint64_t adesc = make_smem_desc(q_addr + ch * kTileBytes + kk * 32, 16, 1024, kLayoutSw128);
+            const uint64_t bdesc = make_smem_desc(k_addr + (st * DCH + ch) * kTileBytes + kk * 32, 16, 1024, kLayoutSw128);
+            mma_mxf8f6f4_ss(tmem_base + kColS, adesc, bdesc, idesc_with_sf(idesc_qk, kk, kk),
+                            tmem_base + kColSfQ + ch * 4, tmem_base + kColSfK + st * 8 + ch * 4, (ch > 0 || kk > 0) ? 1u : 0u);
+          }
+        }
+        tc_commit(&k_empty[st]);
+        tc_commit(s_full);
+        if (j > 0) ok = issue_pv(j - 1);
+      }
+      if (ok) ok = issue_pv(n_tiles - 1);
+      // make sure nothing issued from this thread is still running before TMEM is released
+      tc_commit(drain);
+      mbar_wait(drain, 0, abort_flag, p.status, 306);
+    }
+    __syncwarp();
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 5) { tc_fence_after(); tmem_dealloc(tmem_base, kTmemCols); }
+}
+
+// ---- host side ------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = []() -> EncodeTiledFn {
+    void* f = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &qres) != cudaSuccess ||
+        qres != cudaDriverEntryPointSuccess)
+      return nullptr;
+    return reinterpret_cast<EncodeTiledFn>(f);
+  }();
+  return fn;
+}
+
+// [BH][S][d] bytes, box = 128 bytes of d x 128 rows x 1, 128-byte swizzle, rows/cols past the edge read as 0
+int make_tmap_u8_3d(CUtensorMap* m, const void* base, int64_t BH, int64_t S, int64_t d) {
+  EncodeTiledFn enc = encode_fn();
+  if (!enc) return RK_ERR_NO_DEVICE;
+  cuuint64_t dims[3] = {(cuuint64_t)d, (cuuint64_t)S, (cuuint64_t)BH};
+  cuuint64_t strides[2] = {(cuuint64_t)d, (cuuint64_t)(S * d)};
+  cuuint32_t box[3] = {128, 128, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? RK_OK : RK_ERR_BAD_SHAPE;
+}
+
+template <int DCH, int KV_STAGES, bool SOFTCAP>
+static int launch_cfg(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const PrefillParams& p,
+                      uint32_t idesc_qk, uint32_t idesc_pv, dim3 grid, cudaStream_t st) {
+  using L = SmemLayout<DCH, KV_STAGES>;
+  const int smem_bytes = L::total + 1024;
+  auto kern = prefill_kernel<DCH, KV_STAGES, SOFTCAP>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+  if (e != cudaSuccess) return (int)e;
+  kern<<<grid, kNumThreads, smem_bytes, st>>>(tq, tk, tv, p, idesc_qk, idesc_pv);
+  return (int)cudaGetLastError();
+}
+
+float* g_prefill_dbg = nullptr;   // set by rk_debug_set_prefill_dump (tests only)
+
+int launch_prefill(const rk_prefill_args& a, const uint8_t* v_codes, const uint8_t* q_sf, const uint8_t* k_sf,
+                   const uint8_t* v_sf, cudaStream_t st) {
+  CUtensorMap tq, tk, tv;
+  int rc;
+  if ((rc = make_tmap_u8_3d(&tq, a.q, (int64_t)a.B * a.H, a.S_q, a.d)) != RK_OK) return rc;
+  if ((rc = make_tmap_u8_3d(&tk, a.k, (int64_t)a.B * a.H_kv, a.S_kv, a.d)) != RK_OK) return rc;
+  if ((rc = make_tmap_u8_3d(&tv, v_codes, (int64_t)a.B * a.H_kv, a.S_kv, a.d)) != RK_OK) return rc;
+
+  PrefillParams p;
+  p.q_sf = q_sf; p.k_sf = k_sf; p.v_sf = v_sf;
+  p.o = reinterpret_cast<__nv_bfloat16*>(a.o);
+  p.lse = a.lse;
+  p.status = device_status_word();
+  p.dbg = g_prefill_dbg;
+  p.H = a.H; p.H_kv = a.H_kv; p.S_q = a.S_q; p.S_kv = a.S_kv; p.d = a.d;
+  p.n_q_tiles = (a.S_q + kBlockM - 1) / kBlockM;
+  p.n_kv_tiles = (a.S_kv + kBlockN - 1) / kBlockN;
+  p.q_pos0 = a.q_pos0; p.causal = a.causal; p.window = a.window;
+  const float scale = a.softmax_scale > 0.0f ? a.softmax_scale : 1.0f / sqrtf((float)a.d);
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.cap_log2 = a.softcap * 1.4426950408889634f;
+  p.inv_cap_scale = a.softcap > 0.0f ? scale / a.softcap : 0.0f;
+
+  const uint32_t idesc_qk = make_idesc(a.q_fmt, a.kv_fmt, false, false, 128, 128);
+  const uint32_t idesc_pv = make_idesc(RK_FMT_E4M3, a.kv_fmt, false, true, 128, 128);
+  dim3 grid(p.n_q_tiles, a.H, a.B);
+  const bool cap = a.softcap > 0.0f;
+  if (a.d <= 128) {
+    return cap ? launch_cfg<1, 3, true>(tq, tk, tv, p, idesc_qk, idesc_pv, grid, st)
+               : launch_cfg<1, 3, false>(tq, tk, tv, p, idesc_qk, idesc_pv, grid, st);
+  }
+  return cap ? launch_cfg<2, 2, true>(tq, tk, tv, p, idesc_qk, idesc_pv, grid, st)
+             : launch_cfg<2, 2, false>(tq, tk, tv, p, idesc_qk, idesc_pv, grid, st);
+}
+
+}  // namespace rk

@@ -1,0 +1,122 @@
+"""CPU checks of the C-ABI library: it loads, exports every symbol the header declares, and rejects bad
+arguments with the documented codes before touching the GPU.  No compute is launched here."""
+import ctypes as C
+import os
+import re
+
+import pytest
+
+import radiance_kernels_b200 as rk
+from radiance_kernels_b200._lib import SYMBOLS, DecodeArgs, PrefillArgs
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def header_symbols():
+    text = open(os.path.join(ROOT, "include", "rk_mx_attn.h")).read()
+    return sorted(set(re.findall(r"RK_API\s+[\w\s\*]+?\b(rk_\w+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    L = rk.lib()
+    names = header_symbols()
+    assert len(names) >= 14
+    for n in names:
+        assert hasattr(L, n), f"{n} declared in include/rk_mx_attn.h but not exported"
+    assert sorted(SYMBOLS) == names, "python binding table and header disagree"
+
+
+def test_error_strings_and_version():
+    L = rk.lib()
+    assert L.rk_version() >= 100
+    assert L.rk_error_string(0) == b"ok"
+    for code in range(-9, 0):
+        assert L.rk_error_string(code) not in (b"", b"unknown error")
+
+
+def _pargs(**kw):
+    a = PrefillArgs()
+    a.B, a.H, a.H_kv, a.S_q, a.S_kv, a.d = 1, 4, 2, 128, 128, 128
+    a.v_scale_axis = 1
+    for k, v in kw.items():
+        setattr(a, k, v)
+    return a
+
+
+def test_prefill_argument_errors():
+    L = rk.lib()
+    assert L.rk_attn_prefill(None, None) == -1
+    assert L.rk_attn_prefill(C.byref(_pargs(d=96)), None) == -2
+    assert L.rk_attn_prefill(C.byref(_pargs(H=3)), None) == -2          # H % H_kv
+    assert L.rk_attn_prefill(C.byref(_pargs(S_kv=0)), None) == -2
+    assert L.rk_attn_prefill(C.byref(_pargs(v_scale_axis=7)), None) == -3
+    assert L.rk_attn_prefill(C.byref(_pargs(q_fmt=9)), None) == -3
+    assert L.rk_attn_prefill(C.byref(_pargs(kv_fmt=3)), None) == -6       # 6-bit operands: not built yet
+    assert L.rk_attn_prefill(C.byref(_pargs(block_n=64)), None) == -6
+    assert L.rk_attn_prefill(C.byref(_pargs()), None) == -1               # valid shape, null tensors
+    a = _pargs()
+    for f in ("q", "k", "v", "q_scale", "k_scale", "v_scale", "o"):
+        setattr(a, f, 4096)
+    a.q = 4096 + 8
+    assert L.rk_attn_prefill(C.byref(a), None) == -5                      # misaligned q
+    a.q = 4096
+    assert L.rk_attn_prefill(C.byref(a), None) == -4                      # no workspace
+    assert L.rk_attn_prefill_block_n(C.byref(a)) == 128
+
+
+def test_prefill_workspace_size():
+    # q/k/v scale atoms (512 B per 128x128 tile chunk) + re-blocked V codes, each rounded to 1 KiB
+    B, H, Hkv, S, d = 2, 4, 2, 300, 256
+    nt, dch = 3, 2
+    want = B * H * nt * dch * 512 + 2 * (B * Hkv * nt * dch * 512)
+    want += (B * Hkv * S * d + 1023) // 1024 * 1024
+    assert rk.attn_prefill_workspace_bytes(B, H, Hkv, S, S, d, rk.V_SCALES_ALONG_D) == want
+    assert rk.attn_prefill_workspace_bytes(B, H, Hkv, S, S, d, rk.V_SCALES_ALONG_KEYS) == want - (B * Hkv * S * d + 1023) // 1024 * 1024
+    assert rk.attn_prefill_workspace_bytes(B, H, Hkv, S, S, 96) == 0
+
+
+def test_decode_argument_errors():
+    L = rk.lib()
+    a = DecodeArgs()
+    a.B, a.H, a.H_kv, a.L, a.d = 2, 8, 2, 1024, 128
+    assert L.rk_attn_decode(None, None) == -1
+    assert L.rk_attn_decode(C.byref(a), None) == -1       # null tensors
+    a.d = 64
+    assert L.rk_attn_decode(C.byref(a), None) == -2
+    a.d, a.H = 128, 6                                     # group of 3
+    assert L.rk_attn_decode(C.byref(a), None) == -2
+    a.H, a.L = 8, 1022
+    assert L.rk_attn_decode(C.byref(a), None) == -2
+    a.L, a.kv_fmt = 1024, 1
+    assert L.rk_attn_decode(C.byref(a), None) == -6
+    a.kv_fmt, a.num_splits = 0, 3
+    assert L.rk_attn_decode_num_splits(C.byref(a)) == 3
+    assert L.rk_attn_decode_workspace_bytes(C.byref(a)) == 2 * 8 * 3 * 130 * 4
+    a.num_splits = 100
+    assert L.rk_attn_decode(C.byref(a), None) == -2
+
+
+def test_quantizer_argument_errors():
+    L = rk.lib()
+    assert L.rk_mx_quantize(None, 4, 32, 0, None, None, None) == -1
+    assert L.rk_mx_quantize(4096, 4, 48, 0, 4096, 4096, None) == -2
+    assert L.rk_mx_quantize(4096, 4, 64, 5, 4096, 4096, None) == -3
+    assert L.rk_mx_quantize(4100, 4, 64, 0, 4096, 4096, None) == -5
+
+
+def test_no_cpu_fallback():
+    """The product path has no CPU route: calling it with CPU tensors raises instead of computing."""
+    import torch
+    x = torch.zeros(4, 64)
+    with pytest.raises(ValueError):
+        rk.mx_quantize(x)
+
+
+def test_shard_range_covers_units_once():
+    for n in (1, 7, 16, 512):
+        for world in (1, 2, 3, 8):
+            got = []
+            for r in range(world):
+                lo, hi = rk.shard_range(n, r, world)
+                got += list(range(lo, hi))
+            assert got == list(range(n))

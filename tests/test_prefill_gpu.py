@@ -1,0 +1,123 @@
+"""Prefill attention on the GPU against the CPU oracle (same block_n, same P rule), through the C ABI."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+import radiance_kernels_b200 as rk
+from helpers import MAX_ABS, REL_L2, errors, np_, prefill_vs_oracle, quantize_inputs, randn_qkv
+
+pytestmark = pytest.mark.gpu
+
+
+def _check(r):
+    ma, rl = r["err"]
+    assert ma <= MAX_ABS and rl <= REL_L2, (ma, rl)
+
+
+def test_config1_single_head_noncausal_d64():
+    """B=1 H=1 S=256 d=64 non-causal: the reference's own CPU-runnable case."""
+    for seed in (0, 1, 2):
+        _check(prefill_vs_oracle(1, 1, 1, 256, 256, 64, causal=False, seed=seed))
+
+
+def test_single_tile_d128():
+    _check(prefill_vs_oracle(1, 1, 1, 128, 128, 128, causal=False))
+
+
+def test_causal_mha_d128():
+    _check(prefill_vs_oracle(2, 4, 4, 1024, 1024, 128, causal=True, seed=1))
+
+
+def test_causal_gqa_d128_group4():
+    _check(prefill_vs_oracle(1, 8, 2, 768, 768, 128, causal=True, seed=2))
+
+
+def test_reference_gqa_shape():
+    """The reference's GQA kernel shape: 8 query heads on 2 KV heads, Sq=64 Sk=256 d=64, q_pos0=64
+    (kernels/regen_data.sh:31-32)."""
+    _check(prefill_vs_oracle(1, 8, 2, 64, 256, 64, causal=True, q_pos0=64, seed=0))
+
+
+def test_gemma_softcap_d256():
+    _check(prefill_vs_oracle(1, 4, 2, 512, 512, 256, causal=True, softcap=50.0, mul=0.5, seed=3))
+
+
+def test_gemma_reference_style_cap_bites_window():
+    """Q scaled by 50 so the cap saturates, sliding window 128, d=256, 8:4 heads
+    (kernels/flash_attention_mx_gemma/fa_gen_data.py:77-79, kernels/regen_data.sh:33-34)."""
+    _check(prefill_vs_oracle(1, 8, 4, 256, 512, 256, causal=True, softcap=50.0, qmul=50.0, q_pos0=256, window=128))
+
+
+def test_sliding_window_d128():
+    _check(prefill_vs_oracle(1, 2, 1, 640, 640, 128, causal=True, window=200, seed=4))
+
+
+def test_ragged_lengths_and_offset():
+    _check(prefill_vs_oracle(1, 2, 2, 200, 333, 128, causal=True, q_pos0=133, seed=5))
+    _check(prefill_vs_oracle(1, 1, 1, 1, 97, 64, causal=False, seed=6))
+    _check(prefill_vs_oracle(1, 2, 1, 130, 31, 128, causal=False, seed=7))
+
+
+def test_rows_without_visible_keys_are_zero():
+    """q_pos0 < 0: the first rows see no key at all -> O = 0 (the l <= 0 guard of finalize_O)."""
+    r = prefill_vs_oracle(1, 1, 1, 256, 256, 128, causal=True, q_pos0=-130, seed=8)
+    _check(r)
+    assert np.all(r["got"][0, 0, :130] == 0.0)
+
+
+def test_v_scales_along_keys_reference_layout():
+    _check(prefill_vs_oracle(1, 2, 1, 384, 384, 128, causal=True, v_axis=rk.V_SCALES_ALONG_KEYS, seed=9))
+    _check(prefill_vs_oracle(1, 1, 1, 256, 200, 64, causal=False, v_axis=rk.V_SCALES_ALONG_KEYS, seed=10))
+
+
+def test_e5m2_operands():
+    _check(prefill_vs_oracle(1, 2, 1, 256, 256, 128, causal=True, fmt=rk.E5M2, seed=11))
+
+
+def test_lse_output():
+    r = prefill_vs_oracle(1, 2, 1, 256, 256, 128, causal=True, want_lse=True, seed=12)
+    _check(r)
+    assert np.abs(r["lse"] - r["ref"]["lse"]).max() < 1e-3
+
+
+def test_bit_identical_across_runs():
+    """Race check borrowed from the reference ("bit-identical O across 13 runs",
+    kernels/flash_attention_mx/kernel.cpp:158-160)."""
+    Q, K, V = randn_qkv(2, 4, 2, 1024, 1024, 128, seed=13)
+    qc, qs, kc, ks, vc, vs = quantize_inputs(Q, K, V)
+    first = rk.attn_prefill(qc, kc, vc, qs, ks, vs, causal=True)
+    for _ in range(5):
+        again = rk.attn_prefill(qc, kc, vc, qs, ks, vs, causal=True)
+        assert torch.equal(first, again)
+    assert rk.last_device_status() == 0
+
+
+def test_host_buffer_entry_point_matches_device_one():
+    Q, K, V = randn_qkv(1, 4, 2, 512, 512, 128, seed=14)
+    qc, qs, kc, ks, vc, vs = quantize_inputs(Q, K, V)
+    dev = rk.attn_prefill(qc, kc, vc, qs, ks, vs, causal=True)
+    host = rk.attn_prefill_host(*[t.cpu().pin_memory() for t in (qc, kc, vc, qs, ks, vs)], causal=True)
+    assert torch.equal(dev.cpu(), host)
+
+
+def test_full_size_head_slices_match_oracle():
+    """B=8 H=16 S=4096 d=128 causal (the benchmark workload): the whole tensor runs on the GPU, two
+    (batch, head) slices are checked against the oracle, and every row is checked for the size-independent
+    property that O is a convex combination of V rows (|O| <= max|V| per column block)."""
+    B, H, S, d = 8, 16, 4096, 128
+    Q, K, V = randn_qkv(B, H, H, S, S, d, seed=15)
+    qc, qs, kc, ks, vc, vs = quantize_inputs(Q, K, V)
+    del Q, K
+    o = rk.attn_prefill(qc, kc, vc, qs, ks, vs, causal=True)
+    torch.cuda.synchronize()
+    assert rk.last_device_status() == 0
+    assert torch.isfinite(o.float()).all()
+    assert o.float().abs().max() <= V.abs().max() * 1.01
+    for sl in (0, B * H - 1):
+        b, h = divmod(sl, H)
+        ref = oracle.attn_prefill(np_(qc[b:b + 1, h:h + 1]), np_(kc[b:b + 1, h:h + 1]), np_(vc[b:b + 1, h:h + 1]),
+                                  np_(qs[b:b + 1, h:h + 1]), np_(ks[b:b + 1, h:h + 1]), np_(vs[b:b + 1, h:h + 1]),
+                                  causal=True, softmax_scale=d ** -0.5, block_n=128)
+        ma, rl = errors(np_(o[b, h].float()), ref["o_f32"][0, 0])
+        assert ma <= MAX_ABS and rl <= REL_L2, (sl, ma, rl)

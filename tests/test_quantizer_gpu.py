@@ -1,0 +1,109 @@
+"""MX block quantizer on the GPU: bit-exact against the oracle, the reference's known-answer test and
+golden.py vectors, through the C ABI."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+import radiance_kernels_b200 as rk
+from helpers import np_
+
+pytestmark = pytest.mark.gpu
+G = os.path.join(os.path.dirname(__file__), "golden")
+
+
+def test_simt_quant_known_answer_on_gpu():
+    kat = np.load(os.path.join(G, "simt_quant_kat.npz"))
+    x = torch.from_numpy(kat["X_raw"]).cuda()
+    codes, scales = rk.mx_quantize(x)
+    packed = np_(codes).reshape(-1, 4).astype(np.uint32)
+    words = packed[:, 0] | (packed[:, 1] << 8) | (packed[:, 2] << 16) | (packed[:, 3] << 24)
+    assert np.array_equal(words, kat["gold_all"][:8192])
+    assert np.array_equal(np_(scales).reshape(-1).astype(np.uint32), kat["gold_all"][8192:])
+
+
+def test_golden_py_encode_vectors_on_gpu():
+    """Each golden.py fp8_code_rshift vector becomes element 0 of a block whose amax is exactly 448*2^0 wide,
+    so the block scale is 2^0 and the code must equal the vector's code."""
+    v = np.load(os.path.join(G, "golden_py_vectors.npz"))
+    xin = v["enc_in"]
+    keep = np.isfinite(xin) & (np.abs(xin) <= 448.0)
+    xin, want = xin[keep], v["enc_codes"][keep]
+    x = np.zeros((xin.size, 32), np.float32)
+    x[:, 0] = xin
+    x[:, 1] = 448.0          # pins e = 0
+    codes, scales = rk.mx_quantize(torch.from_numpy(x).cuda())
+    assert np.all(np_(scales) == 127)
+    assert np.array_equal(np_(codes)[:, 0], want)
+
+
+@pytest.mark.parametrize("fmt", [rk.E4M3, rk.E5M2, rk.E2M3, rk.E3M2])
+def test_quantize_rows_bit_exact(fmt):
+    g = torch.Generator(device="cuda").manual_seed(11 + fmt)
+    x = torch.randn(512, 1024, generator=g, device="cuda")
+    x = x * torch.exp2(torch.randint(-20, 20, (512, 32), generator=g, device="cuda").float()).repeat_interleave(32, 1)
+    x[3, 64:96] = 0.0                       # all-zero block
+    x[4, 0:32] = -0.0
+    x[5, 7] = float("inf")
+    x[6, 9] = 3e38
+    x[7, 0:32] = 1e-41                      # denormal amax
+    codes, scales = rk.mx_quantize(x, fmt)
+    oc, os_ = oracle.quantize(np_(x), fmt)
+    assert np.array_equal(np_(codes), oc)
+    assert np.array_equal(np_(scales), os_)
+
+
+def test_quantize_exhaustive_bf16_inputs():
+    """Every finite bf16 pattern as an input element (the reference validates its fp6 encoder the same way,
+    kernels/flash_attention_mx_fp6/README.md:14-18), in blocks whose scale is pinned to 2^0."""
+    bits = np.arange(65536, dtype=np.uint32)
+    vals = (bits << 16).view(np.float32)
+    keep = np.isfinite(vals) & (np.abs(vals) <= 448.0)
+    vals = vals[keep]
+    x = np.zeros((vals.size, 32), np.float32)
+    x[:, 0] = vals
+    x[:, 1] = 448.0
+    codes, scales = rk.mx_quantize(torch.from_numpy(x).cuda())
+    oc, os_ = oracle.quantize(x)
+    assert np.array_equal(np_(codes), oc) and np.array_equal(np_(scales), os_)
+
+
+def test_quantize_keys_and_rebase_bit_exact():
+    g = torch.Generator(device="cuda").manual_seed(5)
+    x = torch.randn(3, 200, 128, generator=g, device="cuda") * 3.0       # ragged: 200 rows = 6 blocks + 8
+    ck, sk = rk.mx_quantize_keys(x)
+    for b in range(3):
+        oc, os_ = oracle.quantize(np_(x[b]), axis=0)
+        assert np.array_equal(np_(ck[b]), oc) and np.array_equal(np_(sk[b]), os_)
+    c, s = rk.mx_quantize(x)
+    rc, rs = rk.mx_rebase_v(c, s)
+    for b in range(3):
+        oc, os_ = oracle.rebase_v(np_(c[b]), np_(s[b]))
+        assert np.array_equal(np_(rc[b]), oc) and np.array_equal(np_(rs[b]), os_)
+
+
+def test_rebase_is_nearly_lossless():
+    """Re-blocking V along the keys changes the decoded values only where an element sits more than 2^14 below
+    its new block's amax."""
+    g = torch.Generator(device="cuda").manual_seed(6)
+    x = torch.randn(1, 4096, 128, generator=g, device="cuda")
+    c, s = rk.mx_quantize(x)
+    rc, rs = rk.mx_rebase_v(c, s)
+    a = oracle.dequant(np_(c[0]), np_(s[0]))
+    b = oracle.dequant(np_(rc[0]), np_(rs[0]), axis=0)
+    assert np.linalg.norm(a - b) / np.linalg.norm(a) < 1e-5
+
+
+def test_quantize_full_size_idempotent():
+    """At the benchmark's tensor size: quantize(dequant(quantize(x))) reproduces codes and scales (a
+    size-independent property checked without the CPU oracle)."""
+    n_rows, d = 8 * 16 * 4096 // 8, 128          # one eighth of the B8 H16 S4096 d128 tensor
+    g = torch.Generator(device="cuda").manual_seed(1)
+    x = torch.randn(n_rows, d, generator=g, device="cuda")
+    c1, s1 = rk.mx_quantize(x)
+    lut = torch.tensor([oracle.lib().rko_decode_elem(i, 0) for i in range(256)], device="cuda")
+    deq = lut[c1.long()] * torch.exp2(s1.float() - 127.0).repeat_interleave(32, 1)
+    c2, s2 = rk.mx_quantize(deq)
+    assert torch.equal(c1, c2) and torch.equal(s1, s2)
