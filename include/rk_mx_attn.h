@@ -165,6 +165,12 @@ RK_API int rk_attn_decode_num_splits(const rk_decode_args* a);
 RK_API size_t rk_attn_decode_workspace_bytes(const rk_decode_args* a);
 RK_API int rk_attn_decode(const rk_decode_args* a, void* stream);
 
+/* Profiling aid (no reference counterpart): when both are non-NULL, the next rk_attn_prefill /
+ * rk_attn_decode calls record cudaEvent_t `before` right before their main kernel (the tiled
+ * attention kernel / the split-KV kernel) and `after` right after it, on the call's stream, so a
+ * caller can time that kernel apart from the preparation passes.  Pass NULLs to switch it off. */
+RK_API void rk_profile_set_events(void* before, void* after);
+
 /* Status word of the last kernel that ran on the current device: 0 = clean;
  * non-zero = a bounded wait inside a kernel gave up (the code says which) and
  * the output of that launch is not valid.  Synchronises the device. */

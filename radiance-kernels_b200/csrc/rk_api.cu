@@ -34,6 +34,7 @@ int num_sms() { return dev_state().sms; }
 int* device_status_word() { return dev_state().status; }
 
 extern float* g_prefill_dbg;
+cudaEvent_t g_ev_before = nullptr, g_ev_after = nullptr;
 
 struct PrefillWs { size_t q_sf, k_sf, v_sf, v_codes, total; };
 
@@ -252,6 +253,8 @@ int rk_last_device_status(void) {
   if (v != 0) cudaMemset(w, 0, sizeof(int));
   return v;
 }
+
+void rk_profile_set_events(void* before, void* after) { g_ev_before = (cudaEvent_t)before; g_ev_after = (cudaEvent_t)after; }
 
 /* Test hook (not in the public header): stage dump of the first query tile / first key tile of
  * the next prefill launches into `buf` (>= 32768 floats), or NULL to switch it off. */

@@ -391,7 +391,9 @@ int launch_decode(const rk_decode_args& a, int nsplit, cudaStream_t st) {
   cudaError_t e = cudaFuncSetAttribute(decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDecSmemBytes);
   if (e != cudaSuccess) return (int)e;
   dim3 grid(nsplit, a.H_kv, a.B);
+  if (g_ev_before && g_ev_after) cudaEventRecord(g_ev_before, st);
   decode_kernel<<<grid, kDecThreads, kDecSmemBytes, st>>>(tk, tv, p);
+  if (g_ev_before && g_ev_after) cudaEventRecord(g_ev_after, st);
   if ((e = cudaGetLastError()) != cudaSuccess) return (int)e;
   const int warps_per_cta = 4;
   decode_combine_kernel<<<(int)((BH + warps_per_cta - 1) / warps_per_cta), warps_per_cta * 32, 0, st>>>(

@@ -7,6 +7,7 @@
 
 namespace rk {
 
+extern cudaEvent_t g_ev_before, g_ev_after;   // optional profiling events around the main kernels
 int num_sms();                 // SM count of the current device (cached per device)
 int* device_status_word();     // per-device int in global memory, zeroed at creation; kernels CAS error codes into it
 
@@ -16,20 +17,6 @@ int launch_rebase_v(const uint8_t* codes, const uint8_t* scales, int64_t batch, 
                     uint8_t* out_codes, uint8_t* out_scales, bool tiled, cudaStream_t st);
 int launch_retile_rowscales(const uint8_t* in, int64_t batch, int64_t S, int64_t d, uint8_t* out, cudaStream_t st);
 int launch_retile_keyscales(const uint8_t* in, int64_t batch, int64_t S, int64_t d, uint8_t* out, cudaStream_t st);
-
-// Prefill kernel operands after preparation (all device pointers).
-struct PrefillLaunch {
-  const void* tmap_q;   // CUtensorMap* in device-visible (grid constant) form is passed by value, see rk_prefill.cu
-  const uint8_t* q_sf;  // scale atoms [B*H][q tiles][d chunks][512]
-  const uint8_t* k_sf;  // [B*H_kv][kv tiles][d chunks][512]
-  const uint8_t* v_sf;  // [B*H_kv][kv tiles][d chunks][512]
-  void* o;
-  float* lse;
-  int B, H, H_kv, S_q, S_kv, d;
-  int q_pos0, causal, window;
-  float softcap, softmax_scale;
-  int q_fmt, kv_fmt;
-};
 
 int launch_prefill(const rk_prefill_args& a, const uint8_t* v_codes, const uint8_t* q_sf, const uint8_t* k_sf,
                    const uint8_t* v_sf, cudaStream_t st);

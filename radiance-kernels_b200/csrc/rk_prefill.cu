@@ -475,7 +475,9 @@ static int launch_cfg(const CUtensorMap& tq, const CUtensorMap& tk, const CUtens
   auto kern = prefill_kernel<DCH, KV_STAGES, SOFTCAP>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
   if (e != cudaSuccess) return (int)e;
+  if (g_ev_before && g_ev_after) cudaEventRecord(g_ev_before, st);
   kern<<<grid, kNumThreads, smem_bytes, st>>>(tq, tk, tv, p, idesc_qk, idesc_pv);
+  if (g_ev_before && g_ev_after) cudaEventRecord(g_ev_after, st);
   return (int)cudaGetLastError();
 }
 

@@ -97,13 +97,19 @@ def test_rebase_is_nearly_lossless():
 
 
 def test_quantize_full_size_idempotent():
-    """At the benchmark's tensor size: quantize(dequant(quantize(x))) reproduces codes and scales (a
-    size-independent property checked without the CPU oracle)."""
+    """At the benchmark's tensor size: dequant(quantize(dequant(quantize(x)))) == dequant(quantize(x)) -- every
+    decoded value is exactly representable again (a size-independent property checked without the CPU oracle).
+    Codes may differ: a block whose amax rounded down can pick a smaller scale the second time."""
     n_rows, d = 8 * 16 * 4096 // 8, 128          # one eighth of the B8 H16 S4096 d128 tensor
     g = torch.Generator(device="cuda").manual_seed(1)
     x = torch.randn(n_rows, d, generator=g, device="cuda")
-    c1, s1 = rk.mx_quantize(x)
     lut = torch.tensor([oracle.lib().rko_decode_elem(i, 0) for i in range(256)], device="cuda")
-    deq = lut[c1.long()] * torch.exp2(s1.float() - 127.0).repeat_interleave(32, 1)
-    c2, s2 = rk.mx_quantize(deq)
-    assert torch.equal(c1, c2) and torch.equal(s1, s2)
+
+    def deq(c, s):
+        return lut[c.long()] * torch.exp2(s.float() - 127.0).repeat_interleave(32, 1)
+
+    c1, s1 = rk.mx_quantize(x)
+    d1 = deq(c1, s1)
+    c2, s2 = rk.mx_quantize(d1)
+    assert torch.equal(d1, deq(c2, s2))
+    assert (s2 <= s1).all()
