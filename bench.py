@@ -166,6 +166,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-decode", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--case", default="full", choices=["full", "small"],
+                    help="small: a reduced batch of the same shapes, for profiler captures only (not a bench number)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -202,6 +204,9 @@ def main():
 
     L = rk.lib()
     peaks = measured_peaks()
+    if args.case == "small":
+        PREFILL.update(B=4)
+        DECODE.update(B=8)
     c = PREFILL
     B, H, Hkv, S, d = c["B"], c["H"], c["H_kv"], c["S"], c["d"]
     g = torch.Generator(device=dev).manual_seed(1000 + rank)
@@ -337,7 +342,7 @@ def main():
     line = {"metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "mxfp8_e4m3 (e8m0 block scales, fp32 accumulate, bf16 out)", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "per_gpu_batch": "B=8 H=16 (128 independent (batch, head) units per GPU)",
+            "config": {"workload": WORKLOAD if args.case == "full" else "REDUCED BATCH (profiling case, not a bench number): " + WORKLOAD, "per_gpu_batch": "B=8 H=16 (128 independent (batch, head) units per GPU)",
                        "parallelism": f"units sharded over {world} GPU(s), no collective on the data path",
                        "l2": "inputs + output (335 MB) exceed the 126 MB L2; no flush between steps"},
             "roofline": roofline, "e2e": e2e, "gpu_launches": launches, "clocks": clocks, "decode": decode}

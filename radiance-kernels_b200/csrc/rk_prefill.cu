@@ -9,14 +9,14 @@
 // mapped onto Blackwell units:
 //   mxgemm_prefetch_tile / mxgemm_compute_tile (mesh)  -> TMA + tcgen05.mma
 //   fused_softmax_requant_tpr (one lane per row,
-//     flash_mx_impl.hpp:314-394)                       -> one thread per row, S row in registers
+//     flash_mx_impl.hpp:314-394)                       -> two threads per row, S half-rows in registers
 //   pack_scales_to_sfmem (flash_mx_impl.hpp:625-639)   -> one st.shared per row + tcgen05.cp
 //   rescale_accumulate / finalize_O (:508-553)         -> O kept in TMEM, rescaled in place
 //
-// One CTA = one 128-row query tile of one (batch, head).  192 threads:
-//   warps 0-3  softmax: thread r owns query row r (TMEM lane r)
-//   warp  4    TMA producer (one elected lane)
-//   warp  5    MMA issuer  (one elected lane), TMEM allocation
+// One CTA = one 128-row query tile of one (batch, head).  320 threads:
+//   warps 0-7  softmax: two threads per query row (TMEM lane = row), 64 keys of the tile each
+//   warp  8    TMA producer (one elected lane)
+//   warp  9    MMA issuer  (one elected lane), TMEM allocation
 // Keys are walked in tiles of 128 (the online-softmax step, "block_n").
 //
 // Roofline: tensor-core bound by FLOP count (4*S_q*S_kv*d per head, half of it
@@ -33,7 +33,8 @@ constexpr int kBlockM = 128;
 constexpr int kBlockN = 128;
 constexpr int kTileBytes = 128 * 128;      // one [128 rows][128 B] swizzled tile
 constexpr int kSfAtomBytes = 512;
-constexpr int kNumThreads = 192;
+constexpr int kNumSoftmaxWarps = 8;
+constexpr int kNumThreads = (kNumSoftmaxWarps + 2) * 32;
 constexpr uint32_t kTmemCols = 512;
 
 // TMEM column map
@@ -71,13 +72,24 @@ struct SmemLayout {
   static constexpr int sfv_off = sfk_off + KV_STAGES * DCH * kSfAtomBytes;
   static constexpr int sfp_off = sfv_off + KV_STAGES * DCH * kSfAtomBytes;
   static constexpr int bar_off = sfp_off + 2 * kSfAtomBytes;
-  // barriers: q_full, k_full[S], k_empty[S], v_full[S], v_empty[S], s_full, s_empty, p_full[2], pv_done[2], drain
-  static constexpr int n_bars = 1 + 4 * KV_STAGES + 2 + 4 + 1;
+  // barriers: q_full, k_full[S], k_empty[S], v_full[S], v_empty[S], s_full, s_empty, p_full[2], pv_done[2], drain, pair[4]
+  static constexpr int n_bars = 1 + 4 * KV_STAGES + 2 + 4 + 1 + 4;
   static constexpr int misc_off = bar_off + n_bars * 8;
-  static constexpr int total = misc_off + 16;
+  static constexpr int xchg_off = misc_off + 16;          // row-max / row-sum exchange: 3 x 2 x 128 floats
+  static constexpr int total = xchg_off + 3 * 2 * 128 * 4;
 };
 
 // ---- softmax warps -----------------------------------------------------------------------------
+// 8 warps: warp w serves TMEM lane quadrant q = w & 3 (rows 32q..32q+31) and column half h = w >> 2
+// (keys 64h..64h+63 of the tile).  The two threads of a row exchange their partial row max through
+// shared memory (one 64-thread named barrier per tile and quadrant); everything else is private.
+RK_DEVINL float fmax3(float a, float b, float c) { float d; asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c)); return d; }
+RK_DEVINL float mul_ftz(float a, float b) { float d; asm("mul.rn.ftz.f32 %0, %1, %2;" : "=f"(d) : "f"(a), "f"(b)); return d; }
+// two ints (0..255 each) into bytes 1:0 of the result, bytes 3:2 taken from the low half of c
+RK_DEVINL uint32_t pack_u8x2(uint32_t hi, uint32_t lo, uint32_t c) {
+  uint32_t d; asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(hi), "r"(lo), "r"(c)); return d;
+}
+
 template <int DCH, int KV_STAGES, bool SOFTCAP>
 __device__ __forceinline__ void softmax_rows(const PrefillParams& p, uint8_t* smem, uint64_t* bars, uint32_t tmem_base,
                                              volatile int* abort_flag, int qt, int bh, int n_tiles) {
@@ -86,16 +98,21 @@ __device__ __forceinline__ void softmax_rows(const PrefillParams& p, uint8_t* sm
   uint64_t* s_empty = s_full + 1;
   uint64_t* p_full = s_empty + 1;     // [2]
   uint64_t* pv_done = p_full + 2;     // [2]
+  uint64_t* pair = pv_done + 3;       // [4]: the two warps of a lane quadrant meet here (bounded, unlike bar.sync)
+  float* xchg = reinterpret_cast<float*>(smem + L::xchg_off);   // [2 parities][2 halves][128 rows]
 
-  const int row = threadIdx.x;                 // 0..127
-  const int warp = row >> 5;
-  const uint32_t lane_addr = ((uint32_t)(warp * 32)) << 16;
+  const int warp = threadIdx.x >> 5;           // 0..7
+  const int quad = warp & 3, half = warp >> 2;
+  const int row = quad * 32 + (threadIdx.x & 31);
+  const uint32_t lane_addr = ((uint32_t)(quad * 32)) << 16;
   const int q_row = qt * kBlockM + row;
   const int q_pos = p.q_pos0 + q_row;
   const float NEG_INF = __int_as_float(0xff800000);
+  constexpr int kHalfN = kBlockN / 2;          // 64 keys per thread and tile
+  constexpr int kOCh = DCH * 2;                // 32-column chunks of O owned by this thread
 
   float m_run = NEG_INF;   // running max, log2 domain (score * log2 e)
-  float l_run = 0.0f;
+  float l_run = 0.0f;      // this thread's half of the row sum
   bool ok = true;
 
   for (int j = 0; j < n_tiles && ok; ++j) {
@@ -104,11 +121,11 @@ __device__ __forceinline__ void softmax_rows(const PrefillParams& p, uint8_t* sm
     if (!ok) break;
     tc_fence_after();
 
-    float s[kBlockN];
+    float s[kHalfN];
     {
       uint32_t* sr = reinterpret_cast<uint32_t*>(s);
-#pragma unroll
-      for (int ch = 0; ch < 4; ++ch) tmem_ld32(tmem_base + lane_addr + kColS + ch * 32, sr + ch * 32);
+      tmem_ld32(tmem_base + lane_addr + kColS + half * kHalfN, sr);
+      tmem_ld32(tmem_base + lane_addr + kColS + half * kHalfN + 32, sr + 32);
       tc_wait_ld();
     }
     tc_fence_before();
@@ -116,53 +133,74 @@ __device__ __forceinline__ void softmax_rows(const PrefillParams& p, uint8_t* sm
 
     if (p.dbg && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && j == 0) {
 #pragma unroll
-      for (int c = 0; c < kBlockN; ++c) p.dbg[row * 128 + c] = s[c];
+      for (int c = 0; c < kHalfN; ++c) p.dbg[row * 128 + half * kHalfN + c] = s[c];
     }
 
-    // ---- scale (+ soft-cap), mask, row max: everything in the log2 domain -------------------
-    const int kbase = j * kBlockN;
-    const bool tail = (kbase + kBlockN > p.S_kv);
-    const bool diag = p.causal && (kbase + kBlockN - 1 > p.q_pos0 + qt * kBlockM);
+    // ---- (soft-cap,) mask, partial row max --------------------------------------------------------
+    // Without a cap the max is taken on the raw scores (the scale is positive) and the scale is folded
+    // into the exponent's FMA; with a cap s[] is replaced by the capped score in the log2 domain.
+    const int kbase = j * kBlockN + half * kHalfN;
+    const bool tail = (j * kBlockN + kBlockN > p.S_kv);
+    const bool diag = p.causal && (j * kBlockN + kBlockN - 1 > p.q_pos0 + qt * kBlockM);
     const bool need_mask = tail || diag || (p.window > 0);
-    int hi = p.S_kv - 1 - kbase;                             // masked iff c > hi || c <= lo
-    if (p.causal) hi = min(hi, q_pos - kbase);
-    const int lo = (p.window > 0) ? (q_pos - p.window - kbase) : -1;
-
-    float mx = NEG_INF;
+    if (SOFTCAP) {
 #pragma unroll
-    for (int c = 0; c < kBlockN; ++c) {
-      float x;
-      if (SOFTCAP) {
-        // cap*tanh(s*scale/cap) with tanh(y) = 1 - 2/(1 + e^(2y)); result pre-multiplied by log2 e
-        const float y2 = s[c] * (2.0f * 1.4426950408889634f * p.inv_cap_scale);
-        const float e = ex2_approx(y2);
-        x = p.cap_log2 * fmaf(-2.0f, rcp_approx(1.0f + e), 1.0f);
-      } else {
-        x = s[c] * p.scale_log2;
+      for (int c = 0; c < kHalfN; ++c) {
+        // cap*tanh(s*scale/cap), tanh(y) = 1 - 2/(1 + e^(2y)); result pre-multiplied by log2 e
+        const float e = ex2_approx(s[c] * (2.0f * 1.4426950408889634f * p.inv_cap_scale));
+        s[c] = p.cap_log2 * fmaf(-2.0f, rcp_approx(1.0f + e), 1.0f);
       }
-      if (need_mask) x = (c > hi || c <= lo) ? NEG_INF : x;
-      s[c] = x;
-      mx = fmaxf(mx, x);
     }
-    const float m_new = fmaxf(m_run, mx);
-    const float m_use = (m_new == NEG_INF) ? 0.0f : m_new;
+    if (need_mask) {
+      int hi = p.S_kv - 1 - kbase;                             // masked iff c > hi || c <= lo
+      if (p.causal) hi = min(hi, q_pos - kbase);
+      const int lo = (p.window > 0) ? (q_pos - p.window - kbase) : -1;
+#pragma unroll
+      for (int c = 0; c < kHalfN; ++c) s[c] = (c > hi || c <= lo) ? NEG_INF : s[c];
+    }
+    float bm0[2], bm1[2];   // per 32-key block: two interleaved partial maxima
+#pragma unroll
+    for (int g = 0; g < 2; ++g) {
+      float a0 = fmax3(s[g * 32 + 0], s[g * 32 + 1], s[g * 32 + 2]);
+      float a1 = fmax3(s[g * 32 + 3], s[g * 32 + 4], s[g * 32 + 5]);
+#pragma unroll
+      for (int c = 6; c < 30; c += 4) { a0 = fmax3(a0, s[g * 32 + c], s[g * 32 + c + 1]); a1 = fmax3(a1, s[g * 32 + c + 2], s[g * 32 + c + 3]); }
+      bm0[g] = fmax3(a0, s[g * 32 + 30], s[g * 32 + 31]);
+      bm1[g] = a1;
+    }
+    const float bmax0 = fmaxf(bm0[0], bm1[0]), bmax1 = fmaxf(bm0[1], bm1[1]);   // block maxima (raw / capped domain)
+    float mx = fmaxf(bmax0, bmax1);
+    // exchange with the thread that owns the other 64 keys of this row
+    xchg[(pb * 2 + half) * 128 + row] = mx;
+    mbar_arrive(&pair[quad]);
+    ok = __all_sync(0xffffffffu, mbar_wait(&pair[quad], j & 1, abort_flag, p.status, 104));
+    if (!ok) break;
+    mx = fmaxf(mx, xchg[(pb * 2 + (half ^ 1)) * 128 + row]);
+    const float sc_mul = SOFTCAP ? 1.0f : p.scale_log2;
+    const float m_new = fmaxf(m_run, mx * sc_mul);            // -inf * positive stays -inf
+    // The exponent is formed as fma(s, scale, -m): for the row-max element that leaves the rounding
+    // residue of s*scale (up to half an ulp of m) instead of exactly 0, and a p a hair below 1 would
+    // drop the block scale by a binade.  Lowering the subtracted max by 2^-21 |m| keeps that p in
+    // [1, 1 + 1e-5); the common factor cancels in O = sum(p v) / sum(p).
+    const float m_use = (m_new == NEG_INF) ? 0.0f : (SOFTCAP ? m_new : fmaf(-fabsf(m_new), 4.76837158203125e-7f, m_new));
     const float corr = (m_run == NEG_INF) ? 1.0f : ex2_approx(m_run - m_new);
     m_run = m_new;
 
-    // ---- rescale O in TMEM once the previous PV has landed ------------------------------------
+    // ---- rescale this thread's half of O in TMEM once the previous PV has landed ------------------
     if (j > 0) {
       ok = __all_sync(0xffffffffu, mbar_wait(&pv_done[(j - 1) & 1], ((j - 1) >> 1) & 1, abort_flag, p.status, 102));
       if (!ok) break;
       tc_fence_after();
       if (__any_sync(0xffffffffu, corr != 1.0f)) {
 #pragma unroll 1
-        for (int ch = 0; ch < DCH * 4; ++ch) {
+        for (int ch = 0; ch < kOCh; ++ch) {
           uint32_t r[32];
-          tmem_ld32(tmem_base + lane_addr + kColO + ch * 32, r);
+          const uint32_t addr = tmem_base + lane_addr + kColO + (half * kOCh + ch) * 32;
+          tmem_ld32(addr, r);
           tc_wait_ld();
 #pragma unroll
           for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * corr);
-          tmem_st32(tmem_base + lane_addr + kColO + ch * 32, r);
+          tmem_st32(addr, r);
         }
         tc_wait_st();
       }
@@ -170,55 +208,75 @@ __device__ __forceinline__ void softmax_rows(const PrefillParams& p, uint8_t* sm
 
     // ---- p = 2^(x - m), row sum from the unquantised p, per-32-key block requant ---------------
     uint8_t* p_tile = smem + L::p_off + pb * kTileBytes + row * 128;
-    float lsum = 0.0f;
-    uint32_t scale_word = 0;
+    float ls0 = 0.0f, ls1 = 0.0f, ls2 = 0.0f, ls3 = 0.0f;
+    uint32_t scale_half = 0;
 #pragma unroll
-    for (int g = 0; g < 4; ++g) {
-      float pmax = 0.0f;
+    for (int g = 0; g < 2; ++g) {
 #pragma unroll
-      for (int c = 0; c < 32; ++c) {
-        const float pv = ex2_approx(s[g * 32 + c] - m_use);
-        s[g * 32 + c] = pv;
-        lsum += pv;
-        pmax = fmaxf(pmax, pv);
+      for (int c = 0; c < 32; c += 4) {
+        const float p0 = ex2_approx(fmaf(s[g * 32 + c + 0], sc_mul, -m_use));
+        const float p1 = ex2_approx(fmaf(s[g * 32 + c + 1], sc_mul, -m_use));
+        const float p2 = ex2_approx(fmaf(s[g * 32 + c + 2], sc_mul, -m_use));
+        const float p3 = ex2_approx(fmaf(s[g * 32 + c + 3], sc_mul, -m_use));
+        s[g * 32 + c + 0] = p0; s[g * 32 + c + 1] = p1; s[g * 32 + c + 2] = p2; s[g * 32 + c + 3] = p3;
+        ls0 += p0; ls1 += p1; ls2 += p2; ls3 += p3;
       }
-      // E8M0 code = exponent field of the block max (se = floor(log2 pmax) <= 0, all-zero block -> 0)
+      // block max of p = 2^(block max of x - m): exp2 is monotone, so it is the p of the arg-max element
+      const float pmax = ex2_approx(fmaf(g == 0 ? bmax0 : bmax1, sc_mul, -m_use));
+      // E8M0 code = exponent field of the block max (se = floor(log2 pmax) <= 0; an all-zero block gives 0)
       int sc = (int)(__float_as_uint(pmax) >> 23);
       sc = min(sc, 127);
-      scale_word |= (uint32_t)sc << (8 * g);
-      const int sub = (sc - 7) * 8;          // code = (bits >> 20) - sub : exponent re-biased to E4M3, 3 mantissa bits kept
+      scale_half |= (uint32_t)sc << (8 * g);
       uint32_t w[8];
+      if (sc >= 7) {
+        // y = p * 2^(7-sc) has exponent field E - se + 7 = the E4M3 exponent field and keeps the mantissa,
+        // so the truncated code is y's bits [20,27); .ftz zeroes everything below 2^-6 of the block scale.
+        const float f = __uint_as_float((uint32_t)(134 - sc) << 23);
 #pragma unroll
-      for (int q = 0; q < 8; ++q) {
-        uint32_t word = 0;
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const uint32_t bits = __float_as_uint(s[g * 32 + q * 4 + e]);
-          int t = (int)(bits >> 20) - sub;
-          // below 2^-6 of the block scale (or p == 0) -> flushed to zero, no subnormals
-          t = (t >= 8 && bits >= 0x00800000u) ? t : 0;
-          word |= (uint32_t)t << (8 * e);
+        for (int q = 0; q < 8; ++q) {
+          const uint32_t c0 = __float_as_uint(mul_ftz(s[g * 32 + q * 4 + 0], f)) >> 20;
+          const uint32_t c1 = __float_as_uint(mul_ftz(s[g * 32 + q * 4 + 1], f)) >> 20;
+          const uint32_t c2 = __float_as_uint(mul_ftz(s[g * 32 + q * 4 + 2], f)) >> 20;
+          const uint32_t c3 = __float_as_uint(mul_ftz(s[g * 32 + q * 4 + 3], f)) >> 20;
+          w[q] = pack_u8x2(c1, c0, pack_u8x2(c3, c2, 0u));
         }
-        w[q] = word;
+      } else {
+        // block max below 2^-120 (or zero): exact integer form of the same rule
+        const int sub = (sc - 7) * 8;
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          uint32_t word = 0;
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const uint32_t bits = __float_as_uint(s[g * 32 + q * 4 + e]);
+            int t = (int)(bits >> 20) - sub;
+            t = (t >= 8 && bits >= 0x00800000u) ? t : 0;
+            word |= (uint32_t)t << (8 * e);
+          }
+          w[q] = word;
+        }
       }
       // two 16-byte chunks of this row, 128-byte swizzle: chunk index XOR (row % 8)
-      const int c0 = (2 * g) ^ (row & 7), c1 = (2 * g + 1) ^ (row & 7);
+      const int blk = half * 2 + g;
+      const int c0 = (2 * blk) ^ (row & 7), c1 = (2 * blk + 1) ^ (row & 7);
       *reinterpret_cast<uint4*>(p_tile + c0 * 16) = make_uint4(w[0], w[1], w[2], w[3]);
       *reinterpret_cast<uint4*>(p_tile + c1 * 16) = make_uint4(w[4], w[5], w[6], w[7]);
     }
-    l_run = l_run * corr + lsum;
-    *reinterpret_cast<uint32_t*>(smem + L::sfp_off + pb * kSfAtomBytes + (row & 31) * 16 + (row >> 5) * 4) = scale_word;
+    l_run = l_run * corr + ((ls0 + ls1) + (ls2 + ls3));
+    *reinterpret_cast<uint16_t*>(smem + L::sfp_off + pb * kSfAtomBytes + (row & 31) * 16 + (row >> 5) * 4 + half * 2) =
+        (uint16_t)scale_half;
 
     if (p.dbg && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && j == 0) {
-      // P codes as written (un-swizzled view) and the scale word, after the 128x128 S dump
+      // P codes as written (un-swizzled view) and the scale bytes, after the 128x128 S dump
       uint32_t* d32 = reinterpret_cast<uint32_t*>(p.dbg + 128 * 128);
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {
-        const uint4 v4 = *reinterpret_cast<const uint4*>(p_tile + ((c ^ (row & 7)) * 16));
-        d32[row * 32 + c * 4 + 0] = v4.x; d32[row * 32 + c * 4 + 1] = v4.y;
-        d32[row * 32 + c * 4 + 2] = v4.z; d32[row * 32 + c * 4 + 3] = v4.w;
+      for (int c = 0; c < 4; ++c) {
+        const int lc = half * 4 + c;
+        const uint4 v4 = *reinterpret_cast<const uint4*>(p_tile + ((lc ^ (row & 7)) * 16));
+        d32[row * 32 + lc * 4 + 0] = v4.x; d32[row * 32 + lc * 4 + 1] = v4.y;
+        d32[row * 32 + lc * 4 + 2] = v4.z; d32[row * 32 + lc * 4 + 3] = v4.w;
       }
-      d32[128 * 32 + row] = scale_word;
+      reinterpret_cast<uint16_t*>(d32 + 128 * 32)[row * 2 + half] = (uint16_t)scale_half;
     }
 
     fence_proxy_async_smem();   // make the st.shared P tile + scales visible to the tensor-core (async) proxy
@@ -226,25 +284,34 @@ __device__ __forceinline__ void softmax_rows(const PrefillParams& p, uint8_t* sm
     mbar_arrive(&p_full[pb]);
   }
 
-  // ---- epilogue: O / l -> bf16 -------------------------------------------------------------------
+  // ---- epilogue: O / l -> bf16, each thread its half of the columns --------------------------------
+  // the row sum is the sum of the two halves
+  float l_tot = l_run;
+  if (ok) {
+    xchg[(2 * 2 + half) * 128 + row] = l_run;
+    mbar_arrive(&pair[quad]);
+    ok = __all_sync(0xffffffffu, mbar_wait(&pair[quad], n_tiles & 1, abort_flag, p.status, 105));
+    if (ok) l_tot += xchg[(2 * 2 + (half ^ 1)) * 128 + row];
+  }
   if (ok) {
     const int last = n_tiles - 1;
     ok = __all_sync(0xffffffffu, mbar_wait(&pv_done[last & 1], (last >> 1) & 1, abort_flag, p.status, 103));
   }
   if (ok) {
     tc_fence_after();
-    const float inv_l = (l_run > 0.0f) ? 1.0f / l_run : 1.0f;
+    const float inv_l = (l_tot > 0.0f) ? 1.0f / l_tot : 1.0f;
     const bool live = q_row < p.S_q;
     __nv_bfloat16* orow = p.o + ((size_t)bh * p.S_q + q_row) * p.d;
-    const int nch = p.d / 32;
-    if (p.dbg && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
+    const int nch = p.d / 64;                      // 32-column chunks per thread
+    if (p.dbg && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && half == 0) {
       p.dbg[128 * 128 + 128 * 32 + 128 + row * 2 + 0] = m_run;
-      p.dbg[128 * 128 + 128 * 32 + 128 + row * 2 + 1] = l_run;
+      p.dbg[128 * 128 + 128 * 32 + 128 + row * 2 + 1] = l_tot;
     }
 #pragma unroll 1
     for (int ch = 0; ch < nch; ++ch) {
       uint32_t r[32];
-      tmem_ld32(tmem_base + lane_addr + kColO + ch * 32, r);
+      const int col0 = (half * nch + ch) * 32;
+      tmem_ld32(tmem_base + lane_addr + kColO + col0, r);
       tc_wait_ld();
       if (live) {
         uint32_t packed[16];
@@ -253,13 +320,13 @@ __device__ __forceinline__ void softmax_rows(const PrefillParams& p, uint8_t* sm
           const __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(r[2 * i]) * inv_l, __uint_as_float(r[2 * i + 1]) * inv_l);
           packed[i] = *reinterpret_cast<const uint32_t*>(&b2);
         }
-        uint4* dst = reinterpret_cast<uint4*>(orow + ch * 32);
+        uint4* dst = reinterpret_cast<uint4*>(orow + col0);
 #pragma unroll
         for (int i = 0; i < 4; ++i) dst[i] = make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
       }
     }
-    if (p.lse && live)
-      p.lse[(size_t)bh * p.S_q + q_row] = (l_run > 0.0f) ? m_run * 0.6931471805599453f + logf(l_run) : NEG_INF;
+    if (p.lse && live && half == 0)
+      p.lse[(size_t)bh * p.S_q + q_row] = (l_tot > 0.0f) ? m_run * 0.6931471805599453f + logf(l_tot) : NEG_INF;
   }
   tc_fence_before();
 }
@@ -309,14 +376,15 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
     for (int i = 0; i < KV_STAGES; ++i) { mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1); mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1); }
-    mbar_init(s_full, 1); mbar_init(s_empty, 128);
-    mbar_init(&p_full[0], 128); mbar_init(&p_full[1], 128);
+    mbar_init(s_full, 1); mbar_init(s_empty, kNumSoftmaxWarps * 32);
+    mbar_init(&p_full[0], kNumSoftmaxWarps * 32); mbar_init(&p_full[1], kNumSoftmaxWarps * 32);
     mbar_init(&pv_done[0], 1); mbar_init(&pv_done[1], 1);
     mbar_init(drain, 1);
+    for (int i = 0; i < 4; ++i) mbar_init(&drain[1 + i], 64);
     *abort_flag = 0;
     fence_barrier_init();
   }
-  if (warp == 5) { tmem_alloc(tmem_ptr, kTmemCols); tmem_relinquish(); }
+  if (warp == kNumSoftmaxWarps + 1) { tmem_alloc(tmem_ptr, kTmemCols); tmem_relinquish(); }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -332,9 +400,9 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         if (p.lse) p.lse[(size_t)bh * p.S_q + q_row] = __int_as_float(0xff800000);
       }
     }
-  } else if (warp < 4) {
+  } else if (warp < kNumSoftmaxWarps) {
     softmax_rows<DCH, KV_STAGES, SOFTCAP>(p, smem, bars, tmem_base, abort_flag, qt, bh, n_tiles);
-  } else if (warp == 4) {
+  } else if (warp == kNumSoftmaxWarps) {
     // ================= TMA producer =================
     if (lane == 0) {
       prefetch_tmap(&tmap_q); prefetch_tmap(&tmap_k); prefetch_tmap(&tmap_v);
@@ -433,7 +501,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) { tc_fence_after(); tmem_dealloc(tmem_base, kTmemCols); }
+  if (warp == kNumSoftmaxWarps + 1) { tc_fence_after(); tmem_dealloc(tmem_base, kTmemCols); }
 }
 
 // ---- host side ------------------------------------------------------------------------------------
