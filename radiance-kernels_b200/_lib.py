@@ -76,6 +76,8 @@ def lib():
             fn = getattr(L, name)   # AttributeError if the header and the library disagree
             fn.restype = res
             fn.argtypes = args
+        L.rk_debug_verify_encoder.restype = C.c_int
+        L.rk_debug_verify_encoder.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]
         L.rk_debug_set_prefill_dump.restype = None
         L.rk_debug_set_prefill_dump.argtypes = [C.c_void_p]
         _LIB = L

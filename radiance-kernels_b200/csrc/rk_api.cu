@@ -256,6 +256,14 @@ int rk_last_device_status(void) {
 
 void rk_profile_set_events(void* before, void* after) { g_ev_before = (cudaEvent_t)before; g_ev_after = (cudaEvent_t)after; }
 
+/* Test hook (not in the public header): sweeps all 2^32 fp32 bit patterns and counts the inputs on which the
+ * hardware element converter and the reference's integer encoder disagree (device outputs: a 64-bit count and
+ * the smallest offending bit pattern, which the caller initialises to 0 and 0xFFFFFFFF). */
+RK_API int rk_debug_verify_encoder(int fmt, unsigned long long* mismatches, uint32_t* first_bad, void* stream) {
+  if (!mismatches || !first_bad) return RK_ERR_NULL_POINTER;
+  return launch_verify_encoder(fmt, mismatches, first_bad, (cudaStream_t)stream);
+}
+
 /* Test hook (not in the public header): stage dump of the first query tile / first key tile of
  * the next prefill launches into `buf` (>= 32768 floats), or NULL to switch it off. */
 RK_API void rk_debug_set_prefill_dump(float* buf) { g_prefill_dbg = buf; }

@@ -16,6 +16,7 @@ int launch_quantize_keys(const float* x, int64_t batch, int64_t rows, int64_t co
 int launch_rebase_v(const uint8_t* codes, const uint8_t* scales, int64_t batch, int64_t S, int64_t d, int fmt,
                     uint8_t* out_codes, uint8_t* out_scales, bool tiled, cudaStream_t st);
 int launch_retile_rowscales(const uint8_t* in, int64_t batch, int64_t S, int64_t d, uint8_t* out, cudaStream_t st);
+int launch_verify_encoder(int fmt, unsigned long long* mismatches, uint32_t* first_bad, cudaStream_t st);
 int launch_retile_keyscales(const uint8_t* in, int64_t batch, int64_t S, int64_t d, uint8_t* out, cudaStream_t st);
 
 int launch_prefill(const rk_prefill_args& a, const uint8_t* v_codes, const uint8_t* q_sf, const uint8_t* k_sf,

@@ -1,9 +1,9 @@
 // MX block quantizer kernels (HBM-bound streaming kernels, no tensor cores).
 //
 //  quantize_rows   fp32 [rows][cols] -> codes + one E8M0 scale per 32 contiguous
-//                  elements.  Bit-exact restatement of quantize_one_block,
+//                  elements.  Same results as quantize_one_block,
 //                  kernels/simt_quant/kernel.cpp:95-129 (golden:
-//                  lib/golden/golden.py:118-170), vectorised: 4 lanes share a
+//                  lib/golden/golden.py:118-170), bit for bit.  4 lanes share a
 //                  block, each lane loads 2 x float4 and stores 8 packed codes.
 //                  Algorithmic traffic 4 B in + 1 B + 1/32 B out per element.
 //  quantize_keys   same rule with the blocks running down the rows (the key
@@ -13,16 +13,59 @@
 //                  along the keys.  Writes the scales either row-major
 //                  [ceil(S/32)][d] or directly in the 512-byte scale-factor
 //                  atoms the attention kernel copies into TMEM.
-//  retile_scales   row-major [rows][d/32] scales -> scale-factor atoms.
+//  retile_*scales  row-major scales -> scale-factor atoms.
+//
+// Element encoding: the reference's integer round-shift encoder (rk::encode_rne)
+// defines the result.  The hot loops use the hardware converter
+// cvt.rn.satfinite.<fmt>x2.f32 instead, which verify_encoder_kernel proves equal
+// to it on every finite fp32 input (all 2^32 bit patterns are swept in the GPU
+// tests); blocks that hold a NaN or an infinity take the integer encoder.
 #include "rk_common.cuh"
 #include "rk_internal.h"
 
 namespace rk {
 
+// four floats -> four packed element codes (byte k = code of v[k]); finite inputs only
+template <int FMT> RK_DEVINL uint32_t hw_encode4(float a, float b, float c, float d) {
+  uint32_t r;
+  if (FMT == 0)
+    asm("{\n\t.reg .b16 lo, hi;\n\tcvt.rn.satfinite.e4m3x2.f32 lo, %2, %1;\n\tcvt.rn.satfinite.e4m3x2.f32 hi, %4, %3;\n\tmov.b32 %0, {lo, hi};\n\t}"
+        : "=r"(r) : "f"(a), "f"(b), "f"(c), "f"(d));
+  else if (FMT == 1)
+    asm("{\n\t.reg .b16 lo, hi;\n\tcvt.rn.satfinite.e5m2x2.f32 lo, %2, %1;\n\tcvt.rn.satfinite.e5m2x2.f32 hi, %4, %3;\n\tmov.b32 %0, {lo, hi};\n\t}"
+        : "=r"(r) : "f"(a), "f"(b), "f"(c), "f"(d));
+  else if (FMT == 2)
+    asm("{\n\t.reg .b16 lo, hi;\n\tcvt.rn.satfinite.e2m3x2.f32 lo, %2, %1;\n\tcvt.rn.satfinite.e2m3x2.f32 hi, %4, %3;\n\tmov.b32 %0, {lo, hi};\n\t}"
+        : "=r"(r) : "f"(a), "f"(b), "f"(c), "f"(d));
+  else
+    asm("{\n\t.reg .b16 lo, hi;\n\tcvt.rn.satfinite.e3m2x2.f32 lo, %2, %1;\n\tcvt.rn.satfinite.e3m2x2.f32 hi, %4, %3;\n\tmov.b32 %0, {lo, hi};\n\t}"
+        : "=r"(r) : "f"(a), "f"(b), "f"(c), "f"(d));
+  return r;
+}
+template <int FMT> RK_DEVINL uint32_t ref_encode4(float a, float b, float c, float d) {
+  return encode_rne<FMT>(a) | (encode_rne<FMT>(b) << 8) | (encode_rne<FMT>(c) << 16) | (encode_rne<FMT>(d) << 24);
+}
+
+// Sweeps fp32 bit patterns [first, first + count): counts inputs on which the hardware converter and the
+// reference's integer encoder disagree (NaNs excluded: the kernels never hand one to the converter).
+template <int FMT>
+__global__ void verify_encoder_kernel(uint64_t first, uint64_t count, unsigned long long* mismatches, uint32_t* first_bad) {
+  unsigned long long bad = 0;
+  for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += (uint64_t)gridDim.x * blockDim.x) {
+    const uint32_t bits = (uint32_t)(first + i);
+    if ((bits & 0x7FFFFFFFu) > 0x7F800000u) continue;
+    const float x = __uint_as_float(bits);
+    const uint32_t hw = hw_encode4<FMT>(x, 0.0f, 0.0f, 0.0f) & 0xFFu;
+    const uint32_t rf = encode_rne<FMT>(x);
+    if (hw != rf) { if (bad == 0) atomicMin(first_bad, bits); ++bad; }
+  }
+  if (bad) atomicAdd(mismatches, bad);
+}
+
 template <int FMT>
 __global__ void __launch_bounds__(256) quantize_rows_kernel(const float4* __restrict__ x, int64_t nchunks,
                                                             uint2* __restrict__ codes, uint8_t* __restrict__ scales) {
-  // chunk = 8 consecutive elements; 4 consecutive lanes = one 32-element block
+  // chunk = 8 consecutive elements; 4 consecutive lanes = one 32-element block.
   // Warp-uniform loop bound: all 32 lanes run the shuffles even when the last
   // chunks of the array end inside this warp (nchunks is a multiple of 4, so a
   // 4-lane group is either wholly live or wholly idle).
@@ -32,23 +75,25 @@ __global__ void __launch_bounds__(256) quantize_rows_kernel(const float4* __rest
     const bool live = c < nchunks;
     float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
     if (live) { a = __ldcs(x + 2 * c); b = __ldcs(x + 2 * c + 1); }
-    float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
-    float amax = 0.0f;
+    const float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+    float amax = 0.0f, nonfinite = 0.0f;
 #pragma unroll
     for (int j = 0; j < 8; j++) {
-      const float av = fabsf(v[j]);
-      if (av > amax) amax = av;    // NaN never wins, as in the reference loop
+      amax = fmaxf(amax, fabsf(v[j]));          // a NaN never wins, as in the reference's compare loop
+      nonfinite = fmaf(v[j], 0.0f, nonfinite);  // stays 0 unless an element is NaN or +-inf
     }
-    float o = __shfl_xor_sync(0xffffffffu, amax, 1); if (o > amax) amax = o;
-    o = __shfl_xor_sync(0xffffffffu, amax, 2); if (o > amax) amax = o;
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
     if (!live) continue;
     uint32_t scode = 0; float p2 = 1.0f;
     if (amax > 0.0f) block_scale<FMT>(amax, scode, p2);
-    uint32_t w0 = 0, w1 = 0;
-#pragma unroll
-    for (int j = 0; j < 4; j++) {
-      w0 |= encode_rne<FMT>(v[j] * p2) << (8 * j);
-      w1 |= encode_rne<FMT>(v[4 + j] * p2) << (8 * j);
+    uint32_t w0, w1;
+    if (nonfinite == 0.0f) {
+      w0 = hw_encode4<FMT>(v[0] * p2, v[1] * p2, v[2] * p2, v[3] * p2);
+      w1 = hw_encode4<FMT>(v[4] * p2, v[5] * p2, v[6] * p2, v[7] * p2);
+    } else {
+      w0 = ref_encode4<FMT>(v[0] * p2, v[1] * p2, v[2] * p2, v[3] * p2);
+      w1 = ref_encode4<FMT>(v[4] * p2, v[5] * p2, v[6] * p2, v[7] * p2);
     }
     __stcs(codes + c, make_uint2(w0, w1));
     if ((c & 3) == 0) scales[c >> 2] = (uint8_t)scode;
@@ -68,11 +113,12 @@ __global__ void __launch_bounds__(128) quantize_keys_kernel(const float* __restr
     const int n = (int)min((int64_t)32, rows - r0);
     const float* xb = x + (bt * rows + r0) * cols + c4 * 4;
     float amax[4] = {0.f, 0.f, 0.f, 0.f};
+    float nonfinite = 0.0f;
     for (int j = 0; j < n; j++) {
       const float4 v = *reinterpret_cast<const float4*>(xb + (int64_t)j * cols);
-      const float av[4] = {fabsf(v.x), fabsf(v.y), fabsf(v.z), fabsf(v.w)};
-#pragma unroll
-      for (int q = 0; q < 4; q++) if (av[q] > amax[q]) amax[q] = av[q];
+      amax[0] = fmaxf(amax[0], fabsf(v.x)); amax[1] = fmaxf(amax[1], fabsf(v.y));
+      amax[2] = fmaxf(amax[2], fabsf(v.z)); amax[3] = fmaxf(amax[3], fabsf(v.w));
+      nonfinite = fmaf(v.x, 0.0f, fmaf(v.y, 0.0f, fmaf(v.z, 0.0f, fmaf(v.w, 0.0f, nonfinite))));
     }
     uint32_t sc[4]; float p2[4];
 #pragma unroll
@@ -80,8 +126,8 @@ __global__ void __launch_bounds__(128) quantize_keys_kernel(const float* __restr
     uint8_t* cb = codes + (bt * rows + r0) * cols + c4 * 4;
     for (int j = 0; j < n; j++) {
       const float4 v = *reinterpret_cast<const float4*>(xb + (int64_t)j * cols);
-      const uint32_t w = encode_rne<FMT>(v.x * p2[0]) | (encode_rne<FMT>(v.y * p2[1]) << 8) |
-                         (encode_rne<FMT>(v.z * p2[2]) << 16) | (encode_rne<FMT>(v.w * p2[3]) << 24);
+      const uint32_t w = (nonfinite == 0.0f) ? hw_encode4<FMT>(v.x * p2[0], v.y * p2[1], v.z * p2[2], v.w * p2[3])
+                                             : ref_encode4<FMT>(v.x * p2[0], v.y * p2[1], v.z * p2[2], v.w * p2[3]);
       *reinterpret_cast<uint32_t*>(cb + (int64_t)j * cols) = w;
     }
     *reinterpret_cast<uint32_t*>(scales + (bt * nkb + kb) * cols + c4 * 4) = sc[0] | (sc[1] << 8) | (sc[2] << 16) | (sc[3] << 24);
@@ -94,6 +140,48 @@ __global__ void __launch_bounds__(128) quantize_keys_kernel(const float* __restr
 // columns (lane = r%32, column = r/32, byte = kb).
 __host__ __device__ inline int sf_atom_offset(int r, int kb) { return (r & 31) * 16 + (r >> 5) * 4 + kb; }
 
+// Exact value of element code `c` times 2^(s-127) as an fp32.  Normal codes under ordinary scales are
+// placed by integer arithmetic (E4M3: bits = (mag + 8 s - 56) << 20); everything else (subnormal codes,
+// scale codes near the ends of the range, the other formats) takes the generic multiply.
+template <int FMT> RK_DEVINL float decode_scaled(uint32_t c, uint32_t s) {
+  if (FMT == 0) {
+    const uint32_t mag = c & 0x7Fu;
+    if (mag >= 8u && s >= 16u && s <= 240u) return __uint_as_float(((c & 0x80u) << 24) | ((mag + 8u * s - 56u) << 20));
+  }
+  return decode_elem<FMT>(c) * e8m0_to_f32(s);
+}
+
+// Generic re-blocking of one (4 columns x up to 32 keys) block through fp32: decode every element exactly,
+// block rule down each column, encode.  Used for formats other than E4M3 and for E4M3 blocks that hold
+// subnormal codes or extreme scale codes.
+template <int FMT>
+__device__ __noinline__ void rebase_block_generic(const uint8_t* cb, const uint8_t* sb, int n, int64_t d, int64_t nbd,
+                                                  uint8_t* ob, uint32_t (&sc)[4]) {
+  float amax[4] = {0.f, 0.f, 0.f, 0.f};
+  for (int j = 0; j < n; j++) {
+    const uint32_t cw = *reinterpret_cast<const uint32_t*>(cb + (int64_t)j * d);
+    const uint32_t sj = sb[(int64_t)j * nbd];
+#pragma unroll
+    for (int q = 0; q < 4; q++) amax[q] = fmaxf(amax[q], fabsf(decode_scaled<FMT>((cw >> (8 * q)) & 0xFFu, sj)));
+  }
+  float p2[4];
+#pragma unroll
+  for (int q = 0; q < 4; q++) { sc[q] = 0; p2[q] = 1.0f; if (amax[q] > 0.0f) block_scale<FMT>(amax[q], sc[q], p2[q]); }
+  for (int j = 0; j < n; j++) {
+    const uint32_t cw = *reinterpret_cast<const uint32_t*>(cb + (int64_t)j * d);
+    const uint32_t sj = sb[(int64_t)j * nbd];
+    *reinterpret_cast<uint32_t*>(ob + (int64_t)j * d) =
+        ref_encode4<FMT>(decode_scaled<FMT>(cw & 0xFFu, sj) * p2[0], decode_scaled<FMT>((cw >> 8) & 0xFFu, sj) * p2[1],
+                         decode_scaled<FMT>((cw >> 16) & 0xFFu, sj) * p2[2], decode_scaled<FMT>(cw >> 24, sj) * p2[3]);
+  }
+}
+
+// One thread = 4 adjacent columns x one 32-key block.
+// E4M3 fast path, all integer: a normal code c under scale code s has value (1 + m/8) * 2^(L/8 - 134) with
+// L = (c & 0x7F) + 8 s, so the block's amax is the largest L, the block rule gives the new scale code
+// s' = L_max/8 - 15 (+1 when the mantissa of the max is 7, i.e. above 1.75), and an element's new code is
+// sign | (L - 8 s') whenever that is a normal code; smaller ones are rounded to nearest-even into the
+// subnormal range.  Identical to decoding to fp32 and re-quantizing (which the generic path does).
 template <int FMT, bool TILED>
 __global__ void __launch_bounds__(128) rebase_v_kernel(const uint8_t* __restrict__ codes, const uint8_t* __restrict__ scales,
                                                        int64_t batch, int64_t S, int64_t d,
@@ -107,36 +195,57 @@ __global__ void __launch_bounds__(128) rebase_v_kernel(const uint8_t* __restrict
     const int n = (int)min((int64_t)32, S - r0);
     const uint8_t* cb = codes + (bt * S + r0) * d + c4 * 4;
     const uint8_t* sb = scales + (bt * S + r0) * nbd + (c4 * 4) / 32;
-    float val[32][4];
-    float amax[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-    for (int j = 0; j < 32; j++) {
-      if (j < n) {
-        const uint32_t w = *reinterpret_cast<const uint32_t*>(cb + (int64_t)j * d);
-        const float sf = e8m0_to_f32(sb[(int64_t)j * nbd]);
+    uint8_t* ob = out_codes + (bt * S + r0) * d + c4 * 4;
+    uint32_t sc[4];
+    bool fast = (FMT == 0);
+    if (FMT == 0) {
+      // pass 1: largest L per column (the block is small enough to be re-read from L1 in pass 2)
+      int lmax[4] = {0, 0, 0, 0};
+#pragma unroll 4
+      for (int j = 0; j < n; j++) {
+        const uint32_t cw = *reinterpret_cast<const uint32_t*>(cb + (int64_t)j * d);
+        const int sj = sb[(int64_t)j * nbd];
+        fast = fast && (sj >= 16) && (sj <= 240);
 #pragma unroll
         for (int q = 0; q < 4; q++) {
-          val[j][q] = decode_elem<FMT>((w >> (8 * q)) & 0xFFu) * sf;
-          const float av = fabsf(val[j][q]);
-          if (av > amax[q]) amax[q] = av;
+          const int mag = (int)((cw >> (8 * q)) & 0x7Fu);
+          fast = fast && (mag == 0 || mag >= 8);                 // a subnormal code sends the block to the generic path
+          lmax[q] = max(lmax[q], mag >= 8 ? mag + 8 * sj : 0);
         }
-      } else {
+      }
+      if (fast) {
+        int sub[4];
 #pragma unroll
-        for (int q = 0; q < 4; q++) val[j][q] = 0.0f;
+        for (int q = 0; q < 4; q++) {
+          const int s_new = lmax[q] == 0 ? 0 : (lmax[q] >> 3) - 15 + ((lmax[q] & 7) == 7 ? 1 : 0);
+          sc[q] = (uint32_t)s_new;
+          sub[q] = 8 * s_new;
+        }
+#pragma unroll 4
+        for (int j = 0; j < n; j++) {
+          const uint32_t cw = *reinterpret_cast<const uint32_t*>(cb + (int64_t)j * d);
+          const int sj8 = 8 * (int)sb[(int64_t)j * nbd];
+          uint32_t out = 0;
+#pragma unroll
+          for (int q = 0; q < 4; q++) {
+            const uint32_t c = (cw >> (8 * q)) & 0xFFu;
+            const int mag = (int)(c & 0x7Fu);
+            const int tt = mag + sj8 - sub[q];                  // new exponent field * 8 + mantissa
+            uint32_t code;
+            if (mag == 0) code = 0;                             // +-0 keeps only its sign
+            else if (tt >= 8) code = (uint32_t)tt;
+            else {                                              // below the smallest normal: RNE into the subnormal grid
+              const int sh = 1 - (tt >> 3);                     // >= 1
+              const uint32_t sig = 8u | (uint32_t)(tt & 7);
+              code = sh > 5 ? 0u : round_shift(sig, sh);
+            }
+            out |= ((c & 0x80u) | code) << (8 * q);
+          }
+          *reinterpret_cast<uint32_t*>(ob + (int64_t)j * d) = out;
+        }
       }
     }
-    uint32_t sc[4]; float p2[4];
-#pragma unroll
-    for (int q = 0; q < 4; q++) { sc[q] = 0; p2[q] = 1.0f; if (amax[q] > 0.0f) block_scale<FMT>(amax[q], sc[q], p2[q]); }
-    uint8_t* ob = out_codes + (bt * S + r0) * d + c4 * 4;
-#pragma unroll
-    for (int j = 0; j < 32; j++) {
-      if (j < n) {
-        const uint32_t w = encode_rne<FMT>(val[j][0] * p2[0]) | (encode_rne<FMT>(val[j][1] * p2[1]) << 8) |
-                           (encode_rne<FMT>(val[j][2] * p2[2]) << 16) | (encode_rne<FMT>(val[j][3] * p2[3]) << 24);
-        *reinterpret_cast<uint32_t*>(ob + (int64_t)j * d) = w;
-      }
-    }
+    if (!fast) rebase_block_generic<FMT>(cb, sb, n, d, nbd, ob, sc);
     if (TILED) {
       const int64_t kt = kb / 4;
       const int kbi = (int)(kb % 4);
@@ -231,7 +340,7 @@ int launch_rebase_v(const uint8_t* codes, const uint8_t* scales, int64_t batch, 
                     uint8_t* out_codes, uint8_t* out_scales, bool tiled, cudaStream_t st) {
   const int64_t total = batch * ((S + 31) / 32) * (d / 4);
   if (total == 0) return RK_OK;
-  const int grid = grid_for(total, 128, 8);
+  const int grid = grid_for(total, 128, 16);
   if (tiled) { RK_DISPATCH_FMT(fmt, (rebase_v_kernel<F, true><<<grid, 128, 0, st>>>(codes, scales, batch, S, d, out_codes, out_scales))); }
   else       { RK_DISPATCH_FMT(fmt, (rebase_v_kernel<F, false><<<grid, 128, 0, st>>>(codes, scales, batch, S, d, out_codes, out_scales))); }
   return (int)cudaGetLastError();
@@ -248,6 +357,13 @@ int launch_retile_keyscales(const uint8_t* in, int64_t batch, int64_t S, int64_t
   const int64_t total = batch * ((S + 127) / 128) * ((d + 127) / 128) * 128;
   if (total == 0) return RK_OK;
   retile_keyscales_kernel<<<grid_for(total, 256, 8), 256, 0, st>>>(in, batch, S, d, out);
+  return (int)cudaGetLastError();
+}
+
+// Runs the exhaustive encoder check for one format over all 2^32 fp32 bit patterns.
+int launch_verify_encoder(int fmt, unsigned long long* mismatches, uint32_t* first_bad, cudaStream_t st) {
+  const int grid = num_sms() * 8;
+  RK_DISPATCH_FMT(fmt, (verify_encoder_kernel<F><<<grid, 256, 0, st>>>(0ull, 1ull << 32, mismatches, first_bad)));
   return (int)cudaGetLastError();
 }
 

@@ -40,6 +40,20 @@ def test_golden_py_encode_vectors_on_gpu():
 
 
 @pytest.mark.parametrize("fmt", [rk.E4M3, rk.E5M2, rk.E2M3, rk.E3M2])
+def test_hardware_converter_equals_reference_encoder_on_every_fp32(fmt):
+    """All 2^32 fp32 bit patterns (NaNs aside, which the kernels route to the integer encoder): the hardware
+    converter used in the hot loops gives the code of the reference's round-shift encoder
+    (kernels/simt_quant/kernel.cpp:56-81)."""
+    import ctypes as C
+    count = torch.zeros(1, dtype=torch.int64, device="cuda")
+    first = torch.full((1,), -1, dtype=torch.int32, device="cuda")
+    rc = rk.lib().rk_debug_verify_encoder(fmt, C.c_void_p(count.data_ptr()), C.c_void_p(first.data_ptr()), None)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert int(count.item()) == 0, f"{int(count.item())} mismatches, first at bits {int(first.item()) & 0xFFFFFFFF:#010x}"
+
+
+@pytest.mark.parametrize("fmt", [rk.E4M3, rk.E5M2, rk.E2M3, rk.E3M2])
 def test_quantize_rows_bit_exact(fmt):
     g = torch.Generator(device="cuda").manual_seed(11 + fmt)
     x = torch.randn(512, 1024, generator=g, device="cuda")
@@ -49,6 +63,8 @@ def test_quantize_rows_bit_exact(fmt):
     x[5, 7] = float("inf")
     x[6, 9] = 3e38
     x[7, 0:32] = 1e-41                      # denormal amax
+    x[8, 3] = float("nan")
+    x[9, 40] = float("-inf")
     codes, scales = rk.mx_quantize(x, fmt)
     oc, os_ = oracle.quantize(np_(x), fmt)
     assert np.array_equal(np_(codes), oc)
