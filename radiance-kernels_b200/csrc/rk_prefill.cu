@@ -9,14 +9,14 @@
 // mapped onto Blackwell units:
 //   mxgemm_prefetch_tile / mxgemm_compute_tile (mesh)  -> TMA + tcgen05.mma
 //   fused_softmax_requant_tpr (one lane per row,
-//     flash_mx_impl.hpp:314-394)                       -> two threads per row, S half-rows in registers
+//     flash_mx_impl.hpp:314-394)                       -> four threads per row, one 32-key block each in registers
 //   pack_scales_to_sfmem (flash_mx_impl.hpp:625-639)   -> one st.shared per row + tcgen05.cp
 //   rescale_accumulate / finalize_O (:508-553)         -> O kept in TMEM, rescaled in place
 //
-// One CTA = one 128-row query tile of one (batch, head).  320 threads:
-//   warps 0-7  softmax: two threads per query row (TMEM lane = row), 64 keys of the tile each
-//   warp  8    TMA producer (one elected lane)
-//   warp  9    MMA issuer  (one elected lane), TMEM allocation
+// One CTA = one 128-row query tile of one (batch, head).  576 threads:
+//   warps 0-15  softmax: four threads per query row (TMEM lane = row), one 32-key block of the tile each
+//   warp  16    TMA producer (one elected lane)
+//   warp  17    MMA issuer  (one elected lane), TMEM allocation
 // Keys are walked in tiles of 128 (the online-softmax step, "block_n").
 //
 // Roofline: tensor-core bound by FLOP count (4*S_q*S_kv*d per head, half of it
@@ -33,7 +33,8 @@ constexpr int kBlockM = 128;
 constexpr int kBlockN = 128;
 constexpr int kTileBytes = 128 * 128;      // one [128 rows][128 B] swizzled tile
 constexpr int kSfAtomBytes = 512;
-constexpr int kNumSoftmaxWarps = 8;
+constexpr int kParts = 4;                       // threads per query row (each owns 128 / kParts keys of a tile)
+constexpr int kNumSoftmaxWarps = 4 * kParts;
 constexpr int kNumThreads = (kNumSoftmaxWarps + 2) * 32;
 constexpr uint32_t kTmemCols = 512;
 
@@ -75,20 +76,40 @@ struct SmemLayout {
   // barriers: q_full, k_full[S], k_empty[S], v_full[S], v_empty[S], s_full, s_empty, p_full[2], pv_done[2], drain, pair[4]
   static constexpr int n_bars = 1 + 4 * KV_STAGES + 2 + 4 + 1 + 4;
   static constexpr int misc_off = bar_off + n_bars * 8;
-  static constexpr int xchg_off = misc_off + 16;          // row-max / row-sum exchange: 3 x 2 x 128 floats
-  static constexpr int total = xchg_off + 3 * 2 * 128 * 4;
+  static constexpr int xchg_off = misc_off + 16;          // row-max / row-sum exchange: 3 x kParts x 128 floats
+  static constexpr int total = xchg_off + 3 * kParts * 128 * 4;
 };
 
 // ---- softmax warps -----------------------------------------------------------------------------
-// 8 warps: warp w serves TMEM lane quadrant q = w & 3 (rows 32q..32q+31) and column half h = w >> 2
-// (keys 64h..64h+63 of the tile).  The two threads of a row exchange their partial row max through
-// shared memory (one 64-thread named barrier per tile and quadrant); everything else is private.
+// 4 * kParts warps: warp w serves TMEM lane quadrant q = w & 3 (rows 32q..32q+31) and the 32-key block
+// w >> 2 of the tile, so a thread's keys are exactly one MX block of P.  The kParts threads of a row
+// exchange their block maxima through shared memory (one bounded mbarrier per quadrant, one arrival per
+// warp); everything else is private.
 RK_DEVINL float fmax3(float a, float b, float c) { float d; asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c)); return d; }
-RK_DEVINL float mul_ftz(float a, float b) { float d; asm("mul.rn.ftz.f32 %0, %1, %2;" : "=f"(d) : "f"(a), "f"(b)); return d; }
+// packed fp32 pairs (two lanes per instruction on the FMA pipe)
+RK_DEVINL void fma2(float a0, float a1, float b, float c, float& d0, float& d1) {      // d = a * b + c
+  asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %4};\n\tmov.b64 rc, {%5, %5};\n\t"
+      "fma.rn.f32x2 rd, ra, rb, rc;\n\tmov.b64 {%0, %1}, rd;\n\t}" : "=f"(d0), "=f"(d1) : "f"(a0), "f"(a1), "f"(b), "f"(c));
+}
+RK_DEVINL void add2(float& a0, float& a1, float b0, float b1) {                          // a += b
+  asm("{\n\t.reg .b64 ra, rb;\n\tmov.b64 ra, {%0, %1};\n\tmov.b64 rb, {%2, %3};\n\tadd.rn.f32x2 ra, ra, rb;\n\tmov.b64 {%0, %1}, ra;\n\t}"
+      : "+f"(a0), "+f"(a1) : "f"(b0), "f"(b1));
+}
+RK_DEVINL void mul2_ftz(float a0, float a1, float b, float& d0, float& d1) {           // d = a * b, subnormal results -> 0
+  asm("{\n\t.reg .b64 ra, rb, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %4};\n\tmul.rn.ftz.f32x2 rd, ra, rb;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d0), "=f"(d1) : "f"(a0), "f"(a1), "f"(b));
+}
 // two ints (0..255 each) into bytes 1:0 of the result, bytes 3:2 taken from the low half of c
 RK_DEVINL uint32_t pack_u8x2(uint32_t hi, uint32_t lo, uint32_t c) {
   uint32_t d; asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(hi), "r"(lo), "r"(c)); return d;
 }
+
+#ifdef RK_X_STAMPS
+#define RK_STAMP(slot, j, k) do { if (p.dbg && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (j) < 32) \
+    reinterpret_cast<unsigned*>(p.dbg)[24576 + (slot) * 512 + (j) * 8 + (k)] = (unsigned)clock64(); } while (0)
+#else
+#define RK_STAMP(slot, j, k) do {} while (0)
+#endif
 
 template <int DCH, int KV_STAGES, bool SOFTCAP>
 __device__ __forceinline__ void softmax_rows(const PrefillParams& p, uint8_t* smem, uint64_t* bars, uint32_t tmem_base,
@@ -98,84 +119,104 @@ __device__ __forceinline__ void softmax_rows(const PrefillParams& p, uint8_t* sm
   uint64_t* s_empty = s_full + 1;
   uint64_t* p_full = s_empty + 1;     // [2]
   uint64_t* pv_done = p_full + 2;     // [2]
-  uint64_t* pair = pv_done + 3;       // [4]: the two warps of a lane quadrant meet here (bounded, unlike bar.sync)
-  float* xchg = reinterpret_cast<float*>(smem + L::xchg_off);   // [2 parities][2 halves][128 rows]
+  uint64_t* quadbar = pv_done + 3;    // [4]: the kParts warps of a lane quadrant meet here (bounded, unlike bar.sync)
+  float* xchg = reinterpret_cast<float*>(smem + L::xchg_off);   // [3][kParts][128 rows]
 
-  const int warp = threadIdx.x >> 5;           // 0..7
-  const int quad = warp & 3, half = warp >> 2;
-  const int row = quad * 32 + (threadIdx.x & 31);
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int quad = warp & 3, part = warp >> 2;             // TMEM lane quadrant, 32-key block of the tile
+  const int row = quad * 32 + lane;
   const uint32_t lane_addr = ((uint32_t)(quad * 32)) << 16;
   const int q_row = qt * kBlockM + row;
   const int q_pos = p.q_pos0 + q_row;
   const float NEG_INF = __int_as_float(0xff800000);
-  constexpr int kHalfN = kBlockN / 2;          // 64 keys per thread and tile
-  constexpr int kOCh = DCH * 2;                // 32-column chunks of O owned by this thread
+  constexpr int kOCols = DCH * 128 / kParts;               // O columns this thread rescales (32 or 64)
 
   float m_run = NEG_INF;   // running max, log2 domain (score * log2 e)
-  float l_run = 0.0f;      // this thread's half of the row sum
+  float l_run = 0.0f;      // this thread's share of the row sum
   bool ok = true;
 
   for (int j = 0; j < n_tiles && ok; ++j) {
     const int pb = j & 1;
+    const int sslot = (warp == 0) ? 0 : (warp == 15 ? 1 : 7);
+    if (lane == 0 && sslot < 2) RK_STAMP(sslot, j, 0);
     ok = __all_sync(0xffffffffu, mbar_wait(s_full, j & 1, abort_flag, p.status, 101));
     if (!ok) break;
     tc_fence_after();
+    if (lane == 0 && sslot < 2) RK_STAMP(sslot, j, 1);
 
-    float s[kHalfN];
-    {
-      uint32_t* sr = reinterpret_cast<uint32_t*>(s);
-      tmem_ld32(tmem_base + lane_addr + kColS + half * kHalfN, sr);
-      tmem_ld32(tmem_base + lane_addr + kColS + half * kHalfN + 32, sr + 32);
-      tc_wait_ld();
-    }
-    tc_fence_before();
-    mbar_arrive(s_empty);        // S may now be overwritten by the next QK^T
-
-    if (p.dbg && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && j == 0) {
-#pragma unroll
-      for (int c = 0; c < kHalfN; ++c) p.dbg[row * 128 + half * kHalfN + c] = s[c];
-    }
-
-    // ---- (soft-cap,) mask, partial row max --------------------------------------------------------
-    // Without a cap the max is taken on the raw scores (the scale is positive) and the scale is folded
-    // into the exponent's FMA; with a cap s[] is replaced by the capped score in the log2 domain.
-    const int kbase = j * kBlockN + half * kHalfN;
+    // mask bounds relative to the tile's first key: key column c is masked iff c > hi || c <= lo
     const bool tail = (j * kBlockN + kBlockN > p.S_kv);
     const bool diag = p.causal && (j * kBlockN + kBlockN - 1 > p.q_pos0 + qt * kBlockM);
     const bool need_mask = tail || diag || (p.window > 0);
+    int hi = p.S_kv - 1 - j * kBlockN;
+    if (p.causal) hi = min(hi, q_pos - j * kBlockN);
+    const int lo = (p.window > 0) ? (q_pos - p.window - j * kBlockN) : -1;
+
+    float s[32];
+    tmem_ld32(tmem_base + lane_addr + kColS + part * 32, reinterpret_cast<uint32_t*>(s));
+    tc_wait_ld();
+    float mx_others = NEG_INF;
+    if (!SOFTCAP) {
+      // Row max without talking to the other warps: read the row's other three 32-key blocks as well
+      // (TMEM reads are cheap) and reduce them here.  The warps of a row then never wait for each other.
+#pragma unroll 1
+      for (int o = 1; o < kParts; ++o) {
+        const int blk = (part + o) & (kParts - 1);
+        float t[32];
+        tmem_ld32(tmem_base + lane_addr + kColS + blk * 32, reinterpret_cast<uint32_t*>(t));
+        tc_wait_ld();
+        if (need_mask) {
+#pragma unroll
+          for (int c = 0; c < 32; ++c) t[c] = (blk * 32 + c > hi || blk * 32 + c <= lo) ? NEG_INF : t[c];
+        }
+        float b0 = fmax3(t[0], t[1], t[2]), b1 = fmax3(t[3], t[4], t[5]);
+#pragma unroll
+        for (int c = 6; c < 30; c += 4) { b0 = fmax3(b0, t[c], t[c + 1]); b1 = fmax3(b1, t[c + 2], t[c + 3]); }
+        mx_others = fmax3(mx_others, fmax3(b0, b1, t[30]), t[31]);
+      }
+    }
+    tc_fence_before();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(s_empty);        // one arrival per warp: S may be overwritten once all 16 have read
+    if (lane == 0 && sslot < 2) RK_STAMP(sslot, j, 2);
+
+    if (p.dbg && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && j == 0) {
+#pragma unroll
+      for (int c = 0; c < 32; ++c) p.dbg[row * 128 + part * 32 + c] = s[c];
+    }
+
+    // ---- (soft-cap,) mask, block max ---------------------------------------------------------------
+    // Without a cap the max is taken on the raw scores (the scale is positive) and the scale is folded
+    // into the exponent's FMA; with a cap s[] is replaced by the capped score in the log2 domain.
     if (SOFTCAP) {
 #pragma unroll
-      for (int c = 0; c < kHalfN; ++c) {
+      for (int c = 0; c < 32; ++c) {
         // cap*tanh(s*scale/cap), tanh(y) = 1 - 2/(1 + e^(2y)); result pre-multiplied by log2 e
         const float e = ex2_approx(s[c] * (2.0f * 1.4426950408889634f * p.inv_cap_scale));
         s[c] = p.cap_log2 * fmaf(-2.0f, rcp_approx(1.0f + e), 1.0f);
       }
     }
     if (need_mask) {
-      int hi = p.S_kv - 1 - kbase;                             // masked iff c > hi || c <= lo
-      if (p.causal) hi = min(hi, q_pos - kbase);
-      const int lo = (p.window > 0) ? (q_pos - p.window - kbase) : -1;
 #pragma unroll
-      for (int c = 0; c < kHalfN; ++c) s[c] = (c > hi || c <= lo) ? NEG_INF : s[c];
+      for (int c = 0; c < 32; ++c) s[c] = (part * 32 + c > hi || part * 32 + c <= lo) ? NEG_INF : s[c];
     }
-    float bm0[2], bm1[2];   // per 32-key block: two interleaved partial maxima
+    float a0 = fmax3(s[0], s[1], s[2]), a1 = fmax3(s[3], s[4], s[5]);
 #pragma unroll
-    for (int g = 0; g < 2; ++g) {
-      float a0 = fmax3(s[g * 32 + 0], s[g * 32 + 1], s[g * 32 + 2]);
-      float a1 = fmax3(s[g * 32 + 3], s[g * 32 + 4], s[g * 32 + 5]);
+    for (int c = 6; c < 30; c += 4) { a0 = fmax3(a0, s[c], s[c + 1]); a1 = fmax3(a1, s[c + 2], s[c + 3]); }
+    const float bmax = fmax3(a0, a1, fmaxf(s[30], s[31]));     // this block's max (raw / capped domain)
+    float mx = fmaxf(bmax, mx_others);
+    if (SOFTCAP) {
+      // the capped scores cost two MUFU ops each, so here the four threads of a row exchange block maxima
+      xchg[(pb * kParts + part) * 128 + row] = bmax;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&quadbar[quad]);
+      ok = __all_sync(0xffffffffu, mbar_wait(&quadbar[quad], j & 1, abort_flag, p.status, 104));
+      if (!ok) break;
 #pragma unroll
-      for (int c = 6; c < 30; c += 4) { a0 = fmax3(a0, s[g * 32 + c], s[g * 32 + c + 1]); a1 = fmax3(a1, s[g * 32 + c + 2], s[g * 32 + c + 3]); }
-      bm0[g] = fmax3(a0, s[g * 32 + 30], s[g * 32 + 31]);
-      bm1[g] = a1;
+      for (int o = 1; o < kParts; ++o) mx = fmaxf(mx, xchg[(pb * kParts + ((part + o) & (kParts - 1))) * 128 + row]);
     }
-    const float bmax0 = fmaxf(bm0[0], bm1[0]), bmax1 = fmaxf(bm0[1], bm1[1]);   // block maxima (raw / capped domain)
-    float mx = fmaxf(bmax0, bmax1);
-    // exchange with the thread that owns the other 64 keys of this row
-    xchg[(pb * 2 + half) * 128 + row] = mx;
-    mbar_arrive(&pair[quad]);
-    ok = __all_sync(0xffffffffu, mbar_wait(&pair[quad], j & 1, abort_flag, p.status, 104));
-    if (!ok) break;
-    mx = fmaxf(mx, xchg[(pb * 2 + (half ^ 1)) * 128 + row]);
+    if (lane == 0 && sslot < 2) RK_STAMP(sslot, j, 3);
     const float sc_mul = SOFTCAP ? 1.0f : p.scale_log2;
     const float m_new = fmaxf(m_run, mx * sc_mul);            // -inf * positive stays -inf
     // The exponent is formed as fma(s, scale, -m): for the row-max element that leaves the rounding
@@ -186,16 +227,88 @@ __device__ __forceinline__ void softmax_rows(const PrefillParams& p, uint8_t* sm
     const float corr = (m_run == NEG_INF) ? 1.0f : ex2_approx(m_run - m_new);
     m_run = m_new;
 
-    // ---- rescale this thread's half of O in TMEM once the previous PV has landed ------------------
+    // ---- p = 2^(x - m), row sum from the unquantised p, requant of this 32-key block ---------------
+    uint8_t* p_tile = smem + L::p_off + pb * kTileBytes + row * 128;
+    float ls0 = 0.0f, ls1 = 0.0f, ls2 = 0.0f, ls3 = 0.0f;
+#pragma unroll
+    for (int c = 0; c < 32; c += 4) {
+      // two packed FMAs form the four exponents; the exponentials themselves go to the MUFU one by one
+      float x0, x1, x2, x3;
+      fma2(s[c + 0], s[c + 1], sc_mul, -m_use, x0, x1);
+      fma2(s[c + 2], s[c + 3], sc_mul, -m_use, x2, x3);
+      const float p0 = ex2_approx(x0), p1 = ex2_approx(x1), p2 = ex2_approx(x2), p3 = ex2_approx(x3);
+      s[c + 0] = p0; s[c + 1] = p1; s[c + 2] = p2; s[c + 3] = p3;
+      add2(ls0, ls1, p0, p1);
+      add2(ls2, ls3, p2, p3);
+    }
+    // block max of p = 2^(block max of x - m): exp2 is monotone, so it is the p of the arg-max element
+    const float pmax = ex2_approx(fmaf(bmax, sc_mul, -m_use));
+    // E8M0 code = exponent field of the block max (se = floor(log2 pmax) <= 0; an all-zero block gives 0)
+    int sc = (int)(__float_as_uint(pmax) >> 23);
+    sc = min(sc, 127);
+    uint32_t w[8];
+    if (sc >= 7) {
+      // y = p * 2^(7-sc) has exponent field E - se + 7 = the E4M3 exponent field and keeps the mantissa,
+      // so the truncated code is y's bits [20,27); .ftz zeroes everything below 2^-6 of the block scale.
+      const float f = __uint_as_float((uint32_t)(134 - sc) << 23);
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        float y0, y1, y2, y3;
+        mul2_ftz(s[q * 4 + 0], s[q * 4 + 1], f, y0, y1);
+        mul2_ftz(s[q * 4 + 2], s[q * 4 + 3], f, y2, y3);
+        w[q] = pack_u8x2(__float_as_uint(y1) >> 20, __float_as_uint(y0) >> 20,
+                         pack_u8x2(__float_as_uint(y3) >> 20, __float_as_uint(y2) >> 20, 0u));
+      }
+    } else {
+      // block max below 2^-120 (or zero): exact integer form of the same rule
+      const int sub = (sc - 7) * 8;
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        uint32_t word = 0;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const uint32_t bits = __float_as_uint(s[q * 4 + e]);
+          int t = (int)(bits >> 20) - sub;
+          t = (t >= 8 && bits >= 0x00800000u) ? t : 0;
+          word |= (uint32_t)t << (8 * e);
+        }
+        w[q] = word;
+      }
+    }
+    {
+      // two 16-byte chunks of this row, 128-byte swizzle: chunk index XOR (row % 8)
+      const int c0 = (2 * part) ^ (row & 7), c1 = (2 * part + 1) ^ (row & 7);
+      *reinterpret_cast<uint4*>(p_tile + c0 * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+      *reinterpret_cast<uint4*>(p_tile + c1 * 16) = make_uint4(w[4], w[5], w[6], w[7]);
+    }
+    l_run = l_run * corr + ((ls0 + ls1) + (ls2 + ls3));
+    smem[L::sfp_off + pb * kSfAtomBytes + (row & 31) * 16 + (row >> 5) * 4 + part] = (uint8_t)sc;
+
+    if (p.dbg && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && j == 0) {
+      // P codes as written (un-swizzled view) and the scale bytes, after the 128x128 S dump
+      uint32_t* d32 = reinterpret_cast<uint32_t*>(p.dbg + 128 * 128);
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        const int lc = part * 2 + c;
+        const uint4 v4 = *reinterpret_cast<const uint4*>(p_tile + ((lc ^ (row & 7)) * 16));
+        d32[row * 32 + lc * 4 + 0] = v4.x; d32[row * 32 + lc * 4 + 1] = v4.y;
+        d32[row * 32 + lc * 4 + 2] = v4.z; d32[row * 32 + lc * 4 + 3] = v4.w;
+      }
+      reinterpret_cast<uint8_t*>(d32 + 128 * 32)[row * 4 + part] = (uint8_t)sc;
+    }
+
+    if (lane == 0 && sslot < 2) RK_STAMP(sslot, j, 4);
+    // ---- rescale this thread's share of O in TMEM once the previous PV has landed (it had the whole
+    //      exp/requant phase above to finish, so this wait is normally free) ----------------------------
     if (j > 0) {
       ok = __all_sync(0xffffffffu, mbar_wait(&pv_done[(j - 1) & 1], ((j - 1) >> 1) & 1, abort_flag, p.status, 102));
       if (!ok) break;
       tc_fence_after();
       if (__any_sync(0xffffffffu, corr != 1.0f)) {
 #pragma unroll 1
-        for (int ch = 0; ch < kOCh; ++ch) {
+        for (int ch = 0; ch < kOCols / 32; ++ch) {
           uint32_t r[32];
-          const uint32_t addr = tmem_base + lane_addr + kColO + (half * kOCh + ch) * 32;
+          const uint32_t addr = tmem_base + lane_addr + kColO + part * kOCols + ch * 32;
           tmem_ld32(addr, r);
           tc_wait_ld();
 #pragma unroll
@@ -205,93 +318,25 @@ __device__ __forceinline__ void softmax_rows(const PrefillParams& p, uint8_t* sm
         tc_wait_st();
       }
     }
-
-    // ---- p = 2^(x - m), row sum from the unquantised p, per-32-key block requant ---------------
-    uint8_t* p_tile = smem + L::p_off + pb * kTileBytes + row * 128;
-    float ls0 = 0.0f, ls1 = 0.0f, ls2 = 0.0f, ls3 = 0.0f;
-    uint32_t scale_half = 0;
-#pragma unroll
-    for (int g = 0; g < 2; ++g) {
-#pragma unroll
-      for (int c = 0; c < 32; c += 4) {
-        const float p0 = ex2_approx(fmaf(s[g * 32 + c + 0], sc_mul, -m_use));
-        const float p1 = ex2_approx(fmaf(s[g * 32 + c + 1], sc_mul, -m_use));
-        const float p2 = ex2_approx(fmaf(s[g * 32 + c + 2], sc_mul, -m_use));
-        const float p3 = ex2_approx(fmaf(s[g * 32 + c + 3], sc_mul, -m_use));
-        s[g * 32 + c + 0] = p0; s[g * 32 + c + 1] = p1; s[g * 32 + c + 2] = p2; s[g * 32 + c + 3] = p3;
-        ls0 += p0; ls1 += p1; ls2 += p2; ls3 += p3;
-      }
-      // block max of p = 2^(block max of x - m): exp2 is monotone, so it is the p of the arg-max element
-      const float pmax = ex2_approx(fmaf(g == 0 ? bmax0 : bmax1, sc_mul, -m_use));
-      // E8M0 code = exponent field of the block max (se = floor(log2 pmax) <= 0; an all-zero block gives 0)
-      int sc = (int)(__float_as_uint(pmax) >> 23);
-      sc = min(sc, 127);
-      scale_half |= (uint32_t)sc << (8 * g);
-      uint32_t w[8];
-      if (sc >= 7) {
-        // y = p * 2^(7-sc) has exponent field E - se + 7 = the E4M3 exponent field and keeps the mantissa,
-        // so the truncated code is y's bits [20,27); .ftz zeroes everything below 2^-6 of the block scale.
-        const float f = __uint_as_float((uint32_t)(134 - sc) << 23);
-#pragma unroll
-        for (int q = 0; q < 8; ++q) {
-          const uint32_t c0 = __float_as_uint(mul_ftz(s[g * 32 + q * 4 + 0], f)) >> 20;
-          const uint32_t c1 = __float_as_uint(mul_ftz(s[g * 32 + q * 4 + 1], f)) >> 20;
-          const uint32_t c2 = __float_as_uint(mul_ftz(s[g * 32 + q * 4 + 2], f)) >> 20;
-          const uint32_t c3 = __float_as_uint(mul_ftz(s[g * 32 + q * 4 + 3], f)) >> 20;
-          w[q] = pack_u8x2(c1, c0, pack_u8x2(c3, c2, 0u));
-        }
-      } else {
-        // block max below 2^-120 (or zero): exact integer form of the same rule
-        const int sub = (sc - 7) * 8;
-#pragma unroll
-        for (int q = 0; q < 8; ++q) {
-          uint32_t word = 0;
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const uint32_t bits = __float_as_uint(s[g * 32 + q * 4 + e]);
-            int t = (int)(bits >> 20) - sub;
-            t = (t >= 8 && bits >= 0x00800000u) ? t : 0;
-            word |= (uint32_t)t << (8 * e);
-          }
-          w[q] = word;
-        }
-      }
-      // two 16-byte chunks of this row, 128-byte swizzle: chunk index XOR (row % 8)
-      const int blk = half * 2 + g;
-      const int c0 = (2 * blk) ^ (row & 7), c1 = (2 * blk + 1) ^ (row & 7);
-      *reinterpret_cast<uint4*>(p_tile + c0 * 16) = make_uint4(w[0], w[1], w[2], w[3]);
-      *reinterpret_cast<uint4*>(p_tile + c1 * 16) = make_uint4(w[4], w[5], w[6], w[7]);
-    }
-    l_run = l_run * corr + ((ls0 + ls1) + (ls2 + ls3));
-    *reinterpret_cast<uint16_t*>(smem + L::sfp_off + pb * kSfAtomBytes + (row & 31) * 16 + (row >> 5) * 4 + half * 2) =
-        (uint16_t)scale_half;
-
-    if (p.dbg && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && j == 0) {
-      // P codes as written (un-swizzled view) and the scale bytes, after the 128x128 S dump
-      uint32_t* d32 = reinterpret_cast<uint32_t*>(p.dbg + 128 * 128);
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        const int lc = half * 4 + c;
-        const uint4 v4 = *reinterpret_cast<const uint4*>(p_tile + ((lc ^ (row & 7)) * 16));
-        d32[row * 32 + lc * 4 + 0] = v4.x; d32[row * 32 + lc * 4 + 1] = v4.y;
-        d32[row * 32 + lc * 4 + 2] = v4.z; d32[row * 32 + lc * 4 + 3] = v4.w;
-      }
-      reinterpret_cast<uint16_t*>(d32 + 128 * 32)[row * 2 + half] = (uint16_t)scale_half;
-    }
-
+    if (lane == 0 && sslot < 2) RK_STAMP(sslot, j, 5);
     fence_proxy_async_smem();   // make the st.shared P tile + scales visible to the tensor-core (async) proxy
     tc_fence_before();
-    mbar_arrive(&p_full[pb]);
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&p_full[pb]);
+    if (lane == 0 && sslot < 2) RK_STAMP(sslot, j, 6);
   }
 
-  // ---- epilogue: O / l -> bf16, each thread its half of the columns --------------------------------
-  // the row sum is the sum of the two halves
+  // ---- epilogue: O / l -> bf16, each thread d / kParts of the columns -------------------------------
   float l_tot = l_run;
   if (ok) {
-    xchg[(2 * 2 + half) * 128 + row] = l_run;
-    mbar_arrive(&pair[quad]);
-    ok = __all_sync(0xffffffffu, mbar_wait(&pair[quad], n_tiles & 1, abort_flag, p.status, 105));
-    if (ok) l_tot += xchg[(2 * 2 + (half ^ 1)) * 128 + row];
+    xchg[(2 * kParts + part) * 128 + row] = l_run;
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&quadbar[quad]);
+    ok = __all_sync(0xffffffffu, mbar_wait(&quadbar[quad], SOFTCAP ? (n_tiles & 1) : 0, abort_flag, p.status, 105));
+    if (ok) {
+#pragma unroll
+      for (int o = 1; o < kParts; ++o) l_tot += xchg[(2 * kParts + ((part + o) & (kParts - 1))) * 128 + row];
+    }
   }
   if (ok) {
     const int last = n_tiles - 1;
@@ -302,30 +347,30 @@ __device__ __forceinline__ void softmax_rows(const PrefillParams& p, uint8_t* sm
     const float inv_l = (l_tot > 0.0f) ? 1.0f / l_tot : 1.0f;
     const bool live = q_row < p.S_q;
     __nv_bfloat16* orow = p.o + ((size_t)bh * p.S_q + q_row) * p.d;
-    const int nch = p.d / 64;                      // 32-column chunks per thread
-    if (p.dbg && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && half == 0) {
+    const int ncols = p.d / kParts;                 // 16, 32 or 64 output columns per thread
+    if (p.dbg && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && part == 0) {
       p.dbg[128 * 128 + 128 * 32 + 128 + row * 2 + 0] = m_run;
       p.dbg[128 * 128 + 128 * 32 + 128 + row * 2 + 1] = l_tot;
     }
 #pragma unroll 1
-    for (int ch = 0; ch < nch; ++ch) {
-      uint32_t r[32];
-      const int col0 = (half * nch + ch) * 32;
-      tmem_ld32(tmem_base + lane_addr + kColO + col0, r);
+    for (int c16 = 0; c16 < ncols / 16; ++c16) {
+      uint32_t r[16];
+      const int col0 = part * ncols + c16 * 16;
+      tmem_ld16(tmem_base + lane_addr + kColO + col0, r);
       tc_wait_ld();
       if (live) {
-        uint32_t packed[16];
+        uint32_t packed[8];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
+        for (int i = 0; i < 8; ++i) {
           const __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(r[2 * i]) * inv_l, __uint_as_float(r[2 * i + 1]) * inv_l);
           packed[i] = *reinterpret_cast<const uint32_t*>(&b2);
         }
         uint4* dst = reinterpret_cast<uint4*>(orow + col0);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) dst[i] = make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
+        dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+        dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
       }
     }
-    if (p.lse && live && half == 0)
+    if (p.lse && live && part == 0)
       p.lse[(size_t)bh * p.S_q + q_row] = (l_tot > 0.0f) ? m_run * 0.6931471805599453f + logf(l_tot) : NEG_INF;
   }
   tc_fence_before();
@@ -376,11 +421,11 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
     for (int i = 0; i < KV_STAGES; ++i) { mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1); mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1); }
-    mbar_init(s_full, 1); mbar_init(s_empty, kNumSoftmaxWarps * 32);
-    mbar_init(&p_full[0], kNumSoftmaxWarps * 32); mbar_init(&p_full[1], kNumSoftmaxWarps * 32);
+    mbar_init(s_full, 1); mbar_init(s_empty, kNumSoftmaxWarps);
+    mbar_init(&p_full[0], kNumSoftmaxWarps); mbar_init(&p_full[1], kNumSoftmaxWarps);
     mbar_init(&pv_done[0], 1); mbar_init(&pv_done[1], 1);
     mbar_init(drain, 1);
-    for (int i = 0; i < 4; ++i) mbar_init(&drain[1 + i], 64);
+    for (int i = 0; i < 4; ++i) mbar_init(&drain[1 + i], kParts);
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -447,8 +492,10 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
       auto issue_pv = [&](int i) -> bool {
         const int pb = i & 1, st = i % KV_STAGES, use = i / KV_STAGES;
         if (!mbar_wait(&v_full[st], use & 1, abort_flag, p.status, 303)) return false;
+        RK_STAMP(2, i + 1, 4);
         if (!mbar_wait(&p_full[pb], (i >> 1) & 1, abort_flag, p.status, 304)) return false;
         tc_fence_after();
+        RK_STAMP(2, i + 1, 5);
         tc_cp_32x128b_warpx4(tmem_base + kColSfP + pb * 4,
                              make_smem_desc(smem_u32(smem + L::sfp_off + pb * kSfAtomBytes), 0, 128, kLayoutNone));
         for (int ch = 0; ch < DCH; ++ch)
@@ -471,10 +518,13 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
       };
       for (int j = 0; j < n_tiles && ok; ++j) {
         const int st = j % KV_STAGES, use = j / KV_STAGES;
+        RK_STAMP(2, j, 0);
         ok = mbar_wait(&k_full[st], use & 1, abort_flag, p.status, 302);
+        RK_STAMP(2, j, 1);
         if (ok && j > 0) ok = mbar_wait(s_empty, (j - 1) & 1, abort_flag, p.status, 305);
         if (!ok) break;
         tc_fence_after();
+        RK_STAMP(2, j, 2);
         for (int ch = 0; ch < DCH; ++ch)
           tc_cp_32x128b_warpx4(tmem_base + kColSfK + st * 8 + ch * 4,
                                make_smem_desc(smem_u32(smem + L::sfk_off + (st * DCH + ch) * kSfAtomBytes), 0, 128, kLayoutNone));
@@ -489,7 +539,9 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         }
         tc_commit(&k_empty[st]);
         tc_commit(s_full);
+        RK_STAMP(2, j, 3);
         if (j > 0) ok = issue_pv(j - 1);
+        RK_STAMP(2, j, 6);
       }
       if (ok) ok = issue_pv(n_tiles - 1);
       // make sure nothing issued from this thread is still running before TMEM is released
