@@ -36,7 +36,6 @@ constexpr int kDecStages = 3;
 constexpr int kDecD = 128;
 constexpr int kDecStageBytes = 2 * kDecTileKeys * kDecD + 2 * kDecTileKeys * 4;   // K, V, K scales, V scales
 constexpr int kDecSmemBytes = kDecStages * kDecStageBytes + 64 + 1024;
-constexpr int kMaxGroup = 8;
 
 struct DecodeParams {
   const __nv_bfloat16* q;

@@ -26,41 +26,9 @@
 
 #include "rk_common.cuh"
 #include "rk_internal.h"
+#include "rk_prefill.cuh"
 
 namespace rk {
-
-constexpr int kBlockM = 128;
-constexpr int kBlockN = 128;
-constexpr int kTileBytes = 128 * 128;      // one [128 rows][128 B] swizzled tile
-constexpr int kSfAtomBytes = 512;
-constexpr int kParts = 4;                       // threads per query row (each owns 128 / kParts keys of a tile)
-constexpr int kNumSoftmaxWarps = 4 * kParts;
-constexpr int kNumThreads = (kNumSoftmaxWarps + 2) * 32;
-constexpr uint32_t kTmemCols = 512;
-
-// TMEM column map
-constexpr uint32_t kColS = 0;
-constexpr uint32_t kColO = 128;
-constexpr uint32_t kColSfQ = 384;                 // + ch*4
-constexpr uint32_t kColSfK = 392;                 // + stage*8 + ch*4   (<= 3 stages)
-constexpr uint32_t kColSfP = 416;                 // + pbuf*4
-constexpr uint32_t kColSfV = 424;                 // + stage*8 + ch*4
-
-struct PrefillParams {
-  const uint8_t* q_sf;
-  const uint8_t* k_sf;
-  const uint8_t* v_sf;
-  __nv_bfloat16* o;
-  float* lse;
-  int* status;
-  float* dbg;          // optional stage dump of CTA (0,0,0), first key tile
-  int H, H_kv, S_q, S_kv, d;
-  int n_q_tiles, n_kv_tiles;
-  int q_pos0, causal, window;
-  float scale_log2;    // softmax_scale * log2(e)
-  float cap_log2;      // softcap * log2(e)
-  float inv_cap_scale; // softmax_scale / softcap
-};
 
 template <int DCH, int KV_STAGES>
 struct SmemLayout {
@@ -85,32 +53,6 @@ struct SmemLayout {
 // w >> 2 of the tile, so a thread's keys are exactly one MX block of P.  The kParts threads of a row
 // exchange their block maxima through shared memory (one bounded mbarrier per quadrant, one arrival per
 // warp); everything else is private.
-RK_DEVINL float fmax3(float a, float b, float c) { float d; asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c)); return d; }
-// packed fp32 pairs (two lanes per instruction on the FMA pipe)
-RK_DEVINL void fma2(float a0, float a1, float b, float c, float& d0, float& d1) {      // d = a * b + c
-  asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %4};\n\tmov.b64 rc, {%5, %5};\n\t"
-      "fma.rn.f32x2 rd, ra, rb, rc;\n\tmov.b64 {%0, %1}, rd;\n\t}" : "=f"(d0), "=f"(d1) : "f"(a0), "f"(a1), "f"(b), "f"(c));
-}
-RK_DEVINL void add2(float& a0, float& a1, float b0, float b1) {                          // a += b
-  asm("{\n\t.reg .b64 ra, rb;\n\tmov.b64 ra, {%0, %1};\n\tmov.b64 rb, {%2, %3};\n\tadd.rn.f32x2 ra, ra, rb;\n\tmov.b64 {%0, %1}, ra;\n\t}"
-      : "+f"(a0), "+f"(a1) : "f"(b0), "f"(b1));
-}
-RK_DEVINL void mul2_ftz(float a0, float a1, float b, float& d0, float& d1) {           // d = a * b, subnormal results -> 0
-  asm("{\n\t.reg .b64 ra, rb, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %4};\n\tmul.rn.ftz.f32x2 rd, ra, rb;\n\tmov.b64 {%0, %1}, rd;\n\t}"
-      : "=f"(d0), "=f"(d1) : "f"(a0), "f"(a1), "f"(b));
-}
-// two ints (0..255 each) into bytes 1:0 of the result, bytes 3:2 taken from the low half of c
-RK_DEVINL uint32_t pack_u8x2(uint32_t hi, uint32_t lo, uint32_t c) {
-  uint32_t d; asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(hi), "r"(lo), "r"(c)); return d;
-}
-
-#ifdef RK_X_STAMPS
-#define RK_STAMP(slot, j, k) do { if (p.dbg && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (j) < 32) \
-    reinterpret_cast<unsigned*>(p.dbg)[24576 + (slot) * 512 + (j) * 8 + (k)] = (unsigned)clock64(); } while (0)
-#else
-#define RK_STAMP(slot, j, k) do {} while (0)
-#endif
-
 template <int DCH, int KV_STAGES, bool SOFTCAP>
 __device__ __forceinline__ void softmax_rows(const PrefillParams& p, uint8_t* smem, uint64_t* bars, uint32_t tmem_base,
                                              volatile int* abort_flag, int qt, int bh, int n_tiles) {
@@ -630,10 +572,7 @@ int launch_prefill(const rk_prefill_args& a, const uint8_t* v_codes, const uint8
   const uint32_t idesc_pv = make_idesc(RK_FMT_E4M3, a.kv_fmt, false, true, 128, 128);
   dim3 grid(p.n_q_tiles, a.H, a.B);
   const bool cap = a.softcap > 0.0f;
-  if (a.d <= 128) {
-    return cap ? launch_cfg<1, 3, true>(tq, tk, tv, p, idesc_qk, idesc_pv, grid, st)
-               : launch_cfg<1, 3, false>(tq, tk, tv, p, idesc_qk, idesc_pv, grid, st);
-  }
+  if (a.d <= 128) return launch_prefill2q(tq, tk, tv, p, idesc_qk, idesc_pv, cap, a.B, st);   // two query tiles per CTA
   return cap ? launch_cfg<2, 2, true>(tq, tk, tv, p, idesc_qk, idesc_pv, grid, st)
              : launch_cfg<2, 2, false>(tq, tk, tv, p, idesc_qk, idesc_pv, grid, st);
 }

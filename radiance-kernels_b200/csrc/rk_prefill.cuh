@@ -1,0 +1,78 @@
+// Definitions shared by the two prefill kernels (one 128-row query tile per CTA / two of them).
+#pragma once
+#include <cuda.h>
+#include <cuda_bf16.h>
+
+#include "rk_common.cuh"
+#include "rk_internal.h"
+
+namespace rk {
+
+constexpr int kBlockM = 128;
+constexpr int kBlockN = 128;
+constexpr int kTileBytes = 128 * 128;      // one [128 rows][128 B] swizzled tile
+constexpr int kSfAtomBytes = 512;
+constexpr int kParts = 4;                       // threads per query row (each owns 128 / kParts keys of a tile)
+constexpr int kNumSoftmaxWarps = 4 * kParts;
+constexpr int kNumThreads = (kNumSoftmaxWarps + 2) * 32;
+constexpr uint32_t kTmemCols = 512;
+
+// TMEM column map
+constexpr uint32_t kColS = 0;
+constexpr uint32_t kColO = 128;
+constexpr uint32_t kColSfQ = 384;                 // + ch*4
+constexpr uint32_t kColSfK = 392;                 // + stage*8 + ch*4   (<= 3 stages)
+constexpr uint32_t kColSfP = 416;                 // + pbuf*4
+constexpr uint32_t kColSfV = 424;                 // + stage*8 + ch*4
+
+struct PrefillParams {
+  const uint8_t* q_sf;
+  const uint8_t* k_sf;
+  const uint8_t* v_sf;
+  __nv_bfloat16* o;
+  float* lse;
+  int* status;
+  float* dbg;          // optional stage dump of CTA (0,0,0), first key tile
+  int H, H_kv, S_q, S_kv, d;
+  int n_q_tiles, n_kv_tiles;
+  int q_pos0, causal, window;
+  float scale_log2;    // softmax_scale * log2(e)
+  float cap_log2;      // softcap * log2(e)
+  float inv_cap_scale; // softmax_scale / softcap
+};
+
+RK_DEVINL float fmax3(float a, float b, float c) { float d; asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c)); return d; }
+// packed fp32 pairs (two lanes per instruction on the FMA pipe)
+RK_DEVINL void fma2(float a0, float a1, float b, float c, float& d0, float& d1) {      // d = a * b + c
+  asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %4};\n\tmov.b64 rc, {%5, %5};\n\t"
+      "fma.rn.f32x2 rd, ra, rb, rc;\n\tmov.b64 {%0, %1}, rd;\n\t}" : "=f"(d0), "=f"(d1) : "f"(a0), "f"(a1), "f"(b), "f"(c));
+}
+RK_DEVINL void add2(float& a0, float& a1, float b0, float b1) {                          // a += b
+  asm("{\n\t.reg .b64 ra, rb;\n\tmov.b64 ra, {%0, %1};\n\tmov.b64 rb, {%2, %3};\n\tadd.rn.f32x2 ra, ra, rb;\n\tmov.b64 {%0, %1}, ra;\n\t}"
+      : "+f"(a0), "+f"(a1) : "f"(b0), "f"(b1));
+}
+RK_DEVINL void mul2_ftz(float a0, float a1, float b, float& d0, float& d1) {           // d = a * b, subnormal results -> 0
+  asm("{\n\t.reg .b64 ra, rb, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %4};\n\tmul.rn.ftz.f32x2 rd, ra, rb;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d0), "=f"(d1) : "f"(a0), "f"(a1), "f"(b));
+}
+// two ints (0..255 each) into bytes 1:0 of the result, bytes 3:2 taken from the low half of c
+RK_DEVINL uint32_t pack_u8x2(uint32_t hi, uint32_t lo, uint32_t c) {
+  uint32_t d; asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(hi), "r"(lo), "r"(c)); return d;
+}
+
+#ifdef RK_X_STAMPS
+#define RK_STAMP(slot, j, k) do { if (p.dbg && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (j) < 32) \
+    reinterpret_cast<unsigned*>(p.dbg)[24576 + (slot) * 512 + (j) * 8 + (k)] = (unsigned)clock64(); } while (0)
+#else
+#define RK_STAMP(slot, j, k) do {} while (0)
+#endif
+
+
+int make_tmap_u8_3d(CUtensorMap* m, const void* base, int64_t BH, int64_t S, int64_t d);
+extern float* g_prefill_dbg;
+
+// Two 128-row query tiles per CTA (d <= 128); defined in rk_prefill2q.cu.
+int launch_prefill2q(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const PrefillParams& p,
+                     uint32_t idesc_qk, uint32_t idesc_pv, bool softcap, int B, cudaStream_t st);
+
+}  // namespace rk
