@@ -165,6 +165,27 @@ RK_API int rk_attn_decode_num_splits(const rk_decode_args* a);
 RK_API size_t rk_attn_decode_workspace_bytes(const rk_decode_args* a);
 RK_API int rk_attn_decode(const rk_decode_args* a, void* stream);
 
+/* Decode for callers that cannot allocate device memory at the call site -- a plugin running inside a
+ * memory pool it does not own, a serving loop whose allocator is locked while a step is in flight, a
+ * host that must leave a caching allocator's bookkeeping untouched.  It has no counterpart in the
+ * reference.  Same arguments and results as rk_attn_decode, except that `workspace` / `workspace_bytes`
+ * are ignored: the split partials go to a fixed array of RK_DECODE_NOALLOC_SCRATCH_BYTES (5 MiB) inside
+ * the library image (every GPU that loads the library holds it until exit).
+ * The call allocates nothing, neither directly nor through a library.
+ *   - B * H * splits * 130 floats must fit the array.  With num_splits == 0 the split count is lowered
+ *     until it fits; if even one split does not fit, or a requested num_splits does not, the call
+ *     returns RK_ERR_TOO_LARGE and launches nothing.
+ *   - The first call on each device looks up the array's device address (no allocation, but a runtime
+ *     query): make that first call outside any stream capture.
+ *   - All calls on a device share the array.  Nothing in it has to start at zero (every slot a launch
+ *     reads it has written first), but two calls that overlap on the GPU (different streams) would
+ *     overwrite each other's partials: serialise them.
+ *   - A bounded wait that gives up is recorded in a status word of its own inside the library image
+ *     (rk_last_device_status() does not see it); it is sticky: later no-allocation launches on that
+ *     device return without computing. */
+#define RK_DECODE_NOALLOC_SCRATCH_BYTES (5u << 20)
+RK_API int rk_attn_decode_noalloc(const rk_decode_args* a, void* stream);
+
 /* Profiling aid (no reference counterpart): when both are non-NULL, the next rk_attn_prefill /
  * rk_attn_decode calls record cudaEvent_t `before` right before their main kernel (the tiled
  * attention kernel / the split-KV kernel) and `after` right after it, on the call's stream, so a

@@ -51,6 +51,7 @@ SYMBOLS = {
     "rk_attn_decode_num_splits": (C.c_int, [C.POINTER(DecodeArgs)]),
     "rk_attn_decode_workspace_bytes": (C.c_size_t, [C.POINTER(DecodeArgs)]),
     "rk_attn_decode": (C.c_int, [C.POINTER(DecodeArgs), C.c_void_p]),
+    "rk_attn_decode_noalloc": (C.c_int, [C.POINTER(DecodeArgs), C.c_void_p]),
     "rk_profile_set_events": (None, [C.c_void_p, C.c_void_p]),
     "rk_last_device_status": (C.c_int, []),
 }

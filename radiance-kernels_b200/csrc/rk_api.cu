@@ -243,6 +243,16 @@ int rk_attn_decode(const rk_decode_args* a, void* stream) {
   return launch_decode(*a, ns, (cudaStream_t)stream);
 }
 
+int rk_attn_decode_noalloc(const rk_decode_args* a, void* stream) {
+  int rc = check_decode_shape(a);
+  if (rc != RK_OK) return rc;
+  if (!a->q || !a->k || !a->v || !a->k_scale || !a->v_scale || !a->o) return RK_ERR_NULL_POINTER;
+  if (!aligned(a->q, 16) || !aligned(a->k, 16) || !aligned(a->v, 16) || !aligned(a->k_scale, 16) ||
+      !aligned(a->v_scale, 16) || !aligned(a->o, 16))
+    return RK_ERR_MISALIGNED;
+  return launch_decode_noalloc(*a, (cudaStream_t)stream);
+}
+
 int rk_last_device_status(void) {
   int* w = device_status_word();
   if (!w) return RK_ERR_NO_DEVICE;

@@ -24,6 +24,8 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <mutex>
+
 #include "rk_common.cuh"
 #include "rk_internal.h"
 
@@ -397,6 +399,81 @@ int launch_decode(const rk_decode_args& a, int nsplit, cudaStream_t st) {
   const int warps_per_cta = 4;
   decode_combine_kernel<<<(int)((BH + warps_per_cta - 1) / warps_per_cta), warps_per_cta * 32, 0, st>>>(
       p.part_o, p.part_ml, nsplit, (int)BH, reinterpret_cast<__nv_bfloat16*>(a.o), a.lse);
+  return (int)cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------------------------------
+// Decode without any allocation.  Some hosts may not allocate device memory where they call us: a
+// serving loop that runs inside a memory pool it does not own, a plugin loaded into a process whose
+// allocator is locked while a step is in flight, or code that must not perturb a caching allocator's
+// bookkeeping.  For them the split partials live in a fixed array that is part of the library image
+// on every GPU that loads it, instead of in a caller-provided workspace.
+constexpr size_t kNoAllocScratchFloats = RK_DECODE_NOALLOC_SCRATCH_BYTES / sizeof(float);   // e.g. batch 64 x 32 heads x 4 splits x 130 floats
+static __device__ __align__(256) float g_noalloc_scratch[kNoAllocScratchFloats];
+static __device__ int g_noalloc_status;               // zero at load; a kernel's bounded wait records its code here
+
+namespace {
+struct NoAllocDev { bool ready = false; float* scratch = nullptr; int* status = nullptr; int sms = 0; };
+NoAllocDev g_noalloc_dev[64];
+std::mutex g_noalloc_mu;
+}  // namespace
+
+int launch_decode_noalloc(const rk_decode_args& a, cudaStream_t st) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  NoAllocDev nd;
+  {
+    std::lock_guard<std::mutex> lk(g_noalloc_mu);
+    NoAllocDev& slot = g_noalloc_dev[dev & 63];
+    if (!slot.ready) {
+      // In host code the array's name is only a stand-in; the device address comes from the runtime,
+      // once per device, with that device current.
+      void* ptr = nullptr;
+      if ((e = cudaGetSymbolAddress(&ptr, g_noalloc_scratch)) != cudaSuccess) return (int)e;
+      slot.scratch = static_cast<float*>(ptr);
+      if ((e = cudaGetSymbolAddress(&ptr, g_noalloc_status)) != cudaSuccess) return (int)e;
+      slot.status = static_cast<int*>(ptr);
+      if ((e = cudaDeviceGetAttribute(&slot.sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return (int)e;
+      slot.ready = true;
+    }
+    nd = slot;
+  }
+  // split count: the caller's, or the one that fills whole waves of 2 CTAs per SM best, shrunk to fit the array
+  const int tiles = (a.L + kDecTileKeys - 1) / kDecTileKeys;
+  const size_t BH = (size_t)a.B * a.H;
+  int nsplit;
+  if (a.num_splits > 0) {
+    nsplit = a.num_splits < tiles ? a.num_splits : tiles;
+    if (BH * nsplit * 130 > kNoAllocScratchFloats) return RK_ERR_TOO_LARGE;
+  } else {
+    const long slots = 2L * nd.sms, units = (long)a.B * a.H_kv;
+    nsplit = 1; double best_eff = -1.0;
+    for (int s = 1; s <= 64 && (s == 1 || tiles / s >= 4) && BH * s * 130 <= kNoAllocScratchFloats; ++s) {
+      const long ctas = units * s, waves = (ctas + slots - 1) / slots;
+      const double eff = (double)ctas / (double)(waves * slots);
+      if (eff > best_eff + 0.02) { best_eff = eff; nsplit = s; }
+    }
+    if (BH * nsplit * 130 > kNoAllocScratchFloats) return RK_ERR_TOO_LARGE;
+  }
+  CUtensorMap tk, tv;
+  int rc;
+  if ((rc = make_tmap_u8_3d(&tk, a.k, (int64_t)a.B * a.H_kv, a.L, a.d)) != RK_OK) return rc;
+  if ((rc = make_tmap_u8_3d(&tv, a.v, (int64_t)a.B * a.H_kv, a.L, a.d)) != RK_OK) return rc;
+  DecodeParams p;
+  p.q = reinterpret_cast<const __nv_bfloat16*>(a.q);
+  p.k_scale = a.k_scale; p.v_scale = a.v_scale; p.kv_len = a.kv_len;
+  p.part_o = nd.scratch;
+  p.part_ml = nd.scratch + BH * nsplit * 128;
+  p.status = nd.status;
+  p.B = a.B; p.H = a.H; p.H_kv = a.H_kv; p.L = a.L; p.grp = a.H / a.H_kv; p.nsplit = nsplit;
+  const float scale = a.softmax_scale > 0.0f ? a.softmax_scale : 1.0f / sqrtf((float)a.d);
+  p.scale_log2 = scale * 1.4426950408889634f;
+  if ((e = cudaFuncSetAttribute(decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDecSmemBytes)) != cudaSuccess) return (int)e;
+  decode_kernel<<<dim3(nsplit, a.H_kv, a.B), kDecThreads, kDecSmemBytes, st>>>(tk, tv, p);
+  if ((e = cudaGetLastError()) != cudaSuccess) return (int)e;
+  decode_combine_kernel<<<(int)((BH + 3) / 4), 128, 0, st>>>(p.part_o, p.part_ml, nsplit, (int)BH,
+                                                            reinterpret_cast<__nv_bfloat16*>(a.o), a.lse);
   return (int)cudaGetLastError();
 }
 

@@ -23,5 +23,6 @@ int launch_prefill(const rk_prefill_args& a, const uint8_t* v_codes, const uint8
                    const uint8_t* v_sf, cudaStream_t st);
 
 int launch_decode(const rk_decode_args& a, int num_splits, cudaStream_t st);
+int launch_decode_noalloc(const rk_decode_args& a, cudaStream_t st);
 
 }  // namespace rk
