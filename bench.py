@@ -250,7 +250,7 @@ def main():
     fp8_peak = 2.0 * peaks["bf16_sustained"]
     roofline = {"bound": "tensor", "achieved": flops / (kern_ms * 1e-3) / 1e12, "peak": fp8_peak, "unit": "TFLOP/s",
                 "frac": flops / (kern_ms * 1e-3) / 1e12 / fp8_peak, "traffic": None,
-                "kernel": "prefill_kernel<1,3,false>", "kernel_ms": kern_ms,
+                "kernel": "prefill2q_kernel<false>", "kernel_ms": kern_ms,
                 "peak_note": f"2 x {peaks['source']} sustained cuBLAS bf16 ({peaks['bf16_sustained']} TF/s) as the dense "
                              f"MXFP8 proxy; nominal dense FP8 is 4500 TF/s (frac of nominal {flops / (kern_ms * 1e-3) / 1e12 / 4500.0:.4f})"}
 

@@ -59,6 +59,11 @@ RK_DEVINL void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t 
   asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
+// E8M0 byte `blk` of the packed scale word -> 2^(code-127) as fp32 (code 0 -> 0: such a block holds zeros only)
+RK_DEVINL float e8m0_byte_to_f32(uint32_t word, int blk) {
+  const uint32_t sh = blk < 3 ? (word << (23 - 8 * blk)) : (word >> 1);
+  return __uint_as_float(sh & 0x7F800000u);
+}
 // two packed E4M3 (low 16 bits of x) -> f16x2, exact
 RK_DEVINL uint32_t e4m3x2_to_f16x2(uint32_t x) {
   uint32_t r;
@@ -223,8 +228,8 @@ decode_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant_
               const uint32_t w = *reinterpret_cast<const uint32_t*>(rowp + ((i ^ (krow & 7)) << 4) + 4 * t);
               mma_f16_16816(c, qa[i][0], 0u, qa[i][1], 0u, e4m3x2_to_f16x2(w), e4m3x2_hi_to_f16x2(w));
             }
-            s0 = fmaf(c[0], e8m0_to_f32((ksc >> (8 * blk)) & 0xFFu), s0);
-            s1 = fmaf(c[1], e8m0_to_f32((ksc1 >> (8 * blk)) & 0xFFu), s1);
+            s0 = fmaf(c[0], e8m0_byte_to_f32(ksc, blk), s0);
+            s1 = fmaf(c[1], e8m0_byte_to_f32(ksc1, blk), s1);
           }
           sacc[nt][0] = s0 * qscale;     // log2 domain
           sacc[nt][1] = s1 * qscale;
