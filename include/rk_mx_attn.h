@@ -114,7 +114,8 @@ typedef struct rk_prefill_args {
   int32_t window;          /* >0: also mask key_pos <= q_pos - window (FA_WINDOW); 0 = off */
   float softcap;           /* >0: s <- cap*tanh(s/cap) after the softmax scale, before mask/max; 0 = off */
   float softmax_scale;     /* FA_SOFTMAX_SCALE; 0 selects 1/sqrt(d) */
-  int32_t q_fmt, kv_fmt;   /* RK_FMT_*; P is always E4M3 as in the reference */
+  int32_t q_fmt, kv_fmt;   /* RK_FMT_*; 6-bit codes (E2M3 / E3M2) come one per byte and are packed into the
+                              workspace for the tensor core; P is always E4M3 as in the reference */
   int32_t v_scale_axis;    /* RK_V_SCALES_ALONG_KEYS | RK_V_SCALES_ALONG_D */
   int32_t block_n;         /* keys per online-softmax step; 0 = default.  On return from
                               rk_attn_prefill_block_n() the value the kernel uses (128). */

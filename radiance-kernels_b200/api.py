@@ -83,10 +83,10 @@ def _prefill_args(q, k, v, q_scale, k_scale, v_scale, o, lse, causal, softmax_sc
     return a
 
 
-def attn_prefill_workspace_bytes(B, H, H_kv, S_q, S_kv, d, v_scale_axis=V_SCALES_ALONG_D):
+def attn_prefill_workspace_bytes(B, H, H_kv, S_q, S_kv, d, v_scale_axis=V_SCALES_ALONG_D, q_fmt=E4M3, kv_fmt=E4M3):
     a = PrefillArgs()
     a.B, a.H, a.H_kv, a.S_q, a.S_kv, a.d = B, H, H_kv, S_q, S_kv, d
-    a.v_scale_axis = v_scale_axis
+    a.v_scale_axis, a.q_fmt, a.kv_fmt = v_scale_axis, q_fmt, kv_fmt
     return lib().rk_attn_prefill_workspace_bytes(C.byref(a))
 
 

@@ -36,7 +36,7 @@ int* device_status_word() { return dev_state().status; }
 extern float* g_prefill_dbg;
 cudaEvent_t g_ev_before = nullptr, g_ev_after = nullptr;
 
-struct PrefillWs { size_t q_sf, k_sf, v_sf, v_codes, total; };
+struct PrefillWs { size_t q_sf, k_sf, v_sf, v_codes, q6, k6, v6t, total; };
 
 static PrefillWs prefill_ws(const rk_prefill_args& a) {
   const size_t dch = (a.d + 127) / 128, nqt = (a.S_q + 127) / 128, nkt = (a.S_kv + 127) / 128;
@@ -47,6 +47,14 @@ static PrefillWs prefill_ws(const rk_prefill_args& a) {
   w.v_sf = off; off = align_up(off + (size_t)a.B * a.H_kv * nkt * dch * 512, 1024);
   w.v_codes = off;
   if (a.v_scale_axis == RK_V_SCALES_ALONG_D) off = align_up(off + (size_t)a.B * a.H_kv * a.S_kv * a.d, 1024);
+  // 6-bit operands: densely packed copies (Q, K along d; V transposed, along the keys), rows padded to 128 codes
+  const size_t dp = dch * 128, skp = nkt * 128;
+  w.q6 = off;
+  if (a.q_fmt >= RK_FMT_E2M3) off = align_up(off + (size_t)a.B * a.H * a.S_q * dp * 3 / 4, 1024);
+  w.k6 = off;
+  if (a.kv_fmt >= RK_FMT_E2M3) off = align_up(off + (size_t)a.B * a.H_kv * a.S_kv * dp * 3 / 4, 1024);
+  w.v6t = off;
+  if (a.kv_fmt >= RK_FMT_E2M3) off = align_up(off + (size_t)a.B * a.H_kv * a.d * skp * 3 / 4, 1024);
   w.total = off;
   return w;
 }
@@ -59,8 +67,6 @@ static int check_prefill_shape(const rk_prefill_args* a) {
   if (a->window < 0 || a->softcap < 0.0f || a->softmax_scale < 0.0f) return RK_ERR_BAD_SHAPE;
   if (a->v_scale_axis != RK_V_SCALES_ALONG_KEYS && a->v_scale_axis != RK_V_SCALES_ALONG_D) return RK_ERR_BAD_FORMAT;
   if (a->q_fmt < 0 || a->q_fmt > 3 || a->kv_fmt < 0 || a->kv_fmt > 3) return RK_ERR_BAD_FORMAT;
-  // 6-bit operands need the packed 16-in-12-bytes memory format of the tensor core; not built yet
-  if (a->q_fmt > RK_FMT_E5M2 || a->kv_fmt > RK_FMT_E5M2) return RK_ERR_UNSUPPORTED;
   if (a->block_n != 0 && a->block_n != 128) return RK_ERR_UNSUPPORTED;
   return RK_OK;
 }
@@ -148,7 +154,19 @@ int rk_attn_prefill(const rk_prefill_args* a, void* stream) {
   } else {
     if ((rc = launch_retile_keyscales(a->v_scale, bhkv, a->S_kv, a->d, ws + w.v_sf, st)) != RK_OK) return rc;
   }
-  return launch_prefill(*a, v_codes, ws + w.q_sf, ws + w.k_sf, ws + w.v_sf, st);
+  const uint8_t* q_codes = a->q;
+  const uint8_t* k_codes = a->k;
+  if (a->q_fmt >= RK_FMT_E2M3) {
+    if ((rc = launch_pack6_rows(a->q, bhq * a->S_q, a->d, ws + w.q6, st)) != RK_OK) return rc;
+    q_codes = ws + w.q6;
+  }
+  if (a->kv_fmt >= RK_FMT_E2M3) {
+    if ((rc = launch_pack6_rows(a->k, bhkv * a->S_kv, a->d, ws + w.k6, st)) != RK_OK) return rc;
+    k_codes = ws + w.k6;
+    if ((rc = launch_pack6_transpose(v_codes, bhkv, a->S_kv, a->d, ws + w.v6t, st)) != RK_OK) return rc;
+    v_codes = ws + w.v6t;
+  }
+  return launch_prefill(*a, q_codes, k_codes, v_codes, ws + w.q_sf, ws + w.k_sf, ws + w.v_sf, st);
 }
 
 size_t rk_attn_prefill_host_arena_bytes(const rk_prefill_args* a) {

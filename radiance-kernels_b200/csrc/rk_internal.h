@@ -16,11 +16,15 @@ int launch_quantize_keys(const float* x, int64_t batch, int64_t rows, int64_t co
 int launch_rebase_v(const uint8_t* codes, const uint8_t* scales, int64_t batch, int64_t S, int64_t d, int fmt,
                     uint8_t* out_codes, uint8_t* out_scales, bool tiled, cudaStream_t st);
 int launch_retile_rowscales(const uint8_t* in, int64_t batch, int64_t S, int64_t d, uint8_t* out, cudaStream_t st);
+int launch_pack6_rows(const uint8_t* in, int64_t rows, int64_t d, uint8_t* out, cudaStream_t st);
+int launch_pack6_transpose(const uint8_t* in, int64_t batch, int64_t S, int64_t d, uint8_t* out, cudaStream_t st);
 int launch_verify_encoder(int fmt, unsigned long long* mismatches, uint32_t* first_bad, cudaStream_t st);
 int launch_retile_keyscales(const uint8_t* in, int64_t batch, int64_t S, int64_t d, uint8_t* out, cudaStream_t st);
 
-int launch_prefill(const rk_prefill_args& a, const uint8_t* v_codes, const uint8_t* q_sf, const uint8_t* k_sf,
-                   const uint8_t* v_sf, cudaStream_t st);
+// q/k/v_codes: byte codes as the caller gave them, or -- for 6-bit formats -- the packed copies made by
+// launch_pack6_rows (Q, K) and launch_pack6_transpose (V, stored [d][keys]).
+int launch_prefill(const rk_prefill_args& a, const uint8_t* q_codes, const uint8_t* k_codes, const uint8_t* v_codes,
+                   const uint8_t* q_sf, const uint8_t* k_sf, const uint8_t* v_sf, cudaStream_t st);
 
 int launch_decode(const rk_decode_args& a, int num_splits, cudaStream_t st);
 int launch_decode_noalloc(const rk_decode_args& a, cudaStream_t st);

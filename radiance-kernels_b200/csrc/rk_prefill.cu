@@ -393,7 +393,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
     // ================= TMA producer =================
     if (lane == 0) {
       prefetch_tmap(&tmap_q); prefetch_tmap(&tmap_k); prefetch_tmap(&tmap_v);
-      mbar_arrive_expect_tx(q_full, DCH * (kTileBytes + kSfAtomBytes));
+      mbar_arrive_expect_tx(q_full, DCH * (p.q_tile_tx + kSfAtomBytes));
       for (int ch = 0; ch < DCH; ++ch) {
         tma_load_3d(smem + L::q_off + ch * kTileBytes, &tmap_q, q_full, ch * 128, qt * kBlockM, bh);
         bulk_load_1d(smem + L::sfq_off + ch * kSfAtomBytes,
@@ -404,7 +404,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         const int st = j % KV_STAGES, use = j / KV_STAGES;
         if (use > 0) ok = mbar_wait(&k_empty[st], (use - 1) & 1, abort_flag, p.status, 201);
         if (!ok) break;
-        mbar_arrive_expect_tx(&k_full[st], DCH * (kTileBytes + kSfAtomBytes));
+        mbar_arrive_expect_tx(&k_full[st], DCH * (p.kv_tile_tx + kSfAtomBytes));
         for (int ch = 0; ch < DCH; ++ch) {
           tma_load_3d(smem + L::k_off + (st * DCH + ch) * kTileBytes, &tmap_k, &k_full[st], ch * 128, j * kBlockN, bhkv);
           bulk_load_1d(smem + L::sfk_off + (st * DCH + ch) * kSfAtomBytes,
@@ -412,9 +412,12 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         }
         if (use > 0) ok = mbar_wait(&v_empty[st], (use - 1) & 1, abort_flag, p.status, 202);
         if (!ok) break;
-        mbar_arrive_expect_tx(&v_full[st], DCH * (kTileBytes + kSfAtomBytes));
+        mbar_arrive_expect_tx(&v_full[st], DCH * (p.kv_tile_tx + kSfAtomBytes));
         for (int ch = 0; ch < DCH; ++ch) {
-          tma_load_3d(smem + L::v_off + (st * DCH + ch) * kTileBytes, &tmap_v, &v_full[st], ch * 128, j * kBlockN, bhkv);
+          if (p.v_transposed)
+            tma_load_3d(smem + L::v_off + (st * DCH + ch) * kTileBytes, &tmap_v, &v_full[st], j * kBlockN, ch * 128, bhkv);
+          else
+            tma_load_3d(smem + L::v_off + (st * DCH + ch) * kTileBytes, &tmap_v, &v_full[st], ch * 128, j * kBlockN, bhkv);
           bulk_load_1d(smem + L::sfv_off + (st * DCH + ch) * kSfAtomBytes,
                        p.v_sf + (((size_t)bhkv * p.n_kv_tiles + j) * DCH + ch) * kSfAtomBytes, kSfAtomBytes, &v_full[st]);
         }
@@ -449,7 +452,10 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
             // A = P tile, K-major: 32 keys = 32 bytes along the swizzled 128-byte row
             const uint64_t adesc = make_smem_desc(pt_addr + pb * kTileBytes + kk * 32, 16, 1024, kLayoutSw128);
             // B = V tile, MN-major (d contiguous): 32 keys = 32 rows of 128 bytes
-            const uint64_t bdesc = make_smem_desc(v_addr + (st * DCH + ch) * kTileBytes + kk * 4096, kTileBytes, 1024, kLayoutSw128);
+            // (6-bit V is stored transposed, [d][keys]: K-major like the K tile of QK^T)
+            const uint64_t bdesc = p.v_transposed
+                ? make_smem_desc(v_addr + (st * DCH + ch) * kTileBytes + kk * 32, 16, 1024, kLayoutSw128)
+                : make_smem_desc(v_addr + (st * DCH + ch) * kTileBytes + kk * 4096, kTileBytes, 1024, kLayoutSw128);
             mma_mxf8f6f4_ss(tmem_base + kColO + ch * 128, adesc, bdesc, idesc_with_sf(idesc_pv, kk, kk),
                             tmem_base + kColSfP + pb * 4, tmem_base + kColSfV + st * 8 + ch * 4, (i > 0 || kk > 0) ? 1u : 0u);
           }
@@ -529,6 +535,22 @@ int make_tmap_u8_3d(CUtensorMap* m, const void* base, int64_t BH, int64_t S, int
   return r == CUDA_SUCCESS ? RK_OK : RK_ERR_BAD_SHAPE;
 }
 
+// Packed 6-bit tensor [BH][rows][cols_padded codes], cols_padded a multiple of 128; a box is 128 codes x 128 rows
+// and lands in shared memory as 128 bytes per row (16 codes in 12 bytes + 4 bytes of padding, 128-byte swizzle).
+int make_tmap_u6_3d(CUtensorMap* m, const void* base, int64_t BH, int64_t rows, int64_t cols_padded) {
+  EncodeTiledFn enc = encode_fn();
+  if (!enc) return RK_ERR_NO_DEVICE;
+  const cuuint64_t row_bytes = (cuuint64_t)cols_padded * 3 / 4;
+  cuuint64_t dims[3] = {(cuuint64_t)cols_padded, (cuuint64_t)rows, (cuuint64_t)BH};
+  cuuint64_t strides[2] = {row_bytes, row_bytes * (cuuint64_t)rows};
+  cuuint32_t box[3] = {128, 128, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_16U6_ALIGN16B, 3, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? RK_OK : RK_ERR_BAD_SHAPE;
+}
+
 template <int DCH, int KV_STAGES, bool SOFTCAP>
 static int launch_cfg(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const PrefillParams& p,
                       uint32_t idesc_qk, uint32_t idesc_pv, dim3 grid, cudaStream_t st) {
@@ -545,13 +567,18 @@ static int launch_cfg(const CUtensorMap& tq, const CUtensorMap& tk, const CUtens
 
 float* g_prefill_dbg = nullptr;   // set by rk_debug_set_prefill_dump (tests only)
 
-int launch_prefill(const rk_prefill_args& a, const uint8_t* v_codes, const uint8_t* q_sf, const uint8_t* k_sf,
-                   const uint8_t* v_sf, cudaStream_t st) {
+int launch_prefill(const rk_prefill_args& a, const uint8_t* q_codes, const uint8_t* k_codes, const uint8_t* v_codes,
+                   const uint8_t* q_sf, const uint8_t* k_sf, const uint8_t* v_sf, cudaStream_t st) {
   CUtensorMap tq, tk, tv;
   int rc;
-  if ((rc = make_tmap_u8_3d(&tq, a.q, (int64_t)a.B * a.H, a.S_q, a.d)) != RK_OK) return rc;
-  if ((rc = make_tmap_u8_3d(&tk, a.k, (int64_t)a.B * a.H_kv, a.S_kv, a.d)) != RK_OK) return rc;
-  if ((rc = make_tmap_u8_3d(&tv, v_codes, (int64_t)a.B * a.H_kv, a.S_kv, a.d)) != RK_OK) return rc;
+  const bool q6 = a.q_fmt >= RK_FMT_E2M3, kv6 = a.kv_fmt >= RK_FMT_E2M3;
+  const int64_t dp = (a.d + 127) / 128 * 128, skp = ((int64_t)a.S_kv + 127) / 128 * 128;
+  rc = q6 ? make_tmap_u6_3d(&tq, q_codes, (int64_t)a.B * a.H, a.S_q, dp) : make_tmap_u8_3d(&tq, q_codes, (int64_t)a.B * a.H, a.S_q, a.d);
+  if (rc != RK_OK) return rc;
+  rc = kv6 ? make_tmap_u6_3d(&tk, k_codes, (int64_t)a.B * a.H_kv, a.S_kv, dp) : make_tmap_u8_3d(&tk, k_codes, (int64_t)a.B * a.H_kv, a.S_kv, a.d);
+  if (rc != RK_OK) return rc;
+  rc = kv6 ? make_tmap_u6_3d(&tv, v_codes, (int64_t)a.B * a.H_kv, a.d, skp) : make_tmap_u8_3d(&tv, v_codes, (int64_t)a.B * a.H_kv, a.S_kv, a.d);
+  if (rc != RK_OK) return rc;
 
   PrefillParams p;
   p.q_sf = q_sf; p.k_sf = k_sf; p.v_sf = v_sf;
@@ -563,13 +590,16 @@ int launch_prefill(const rk_prefill_args& a, const uint8_t* v_codes, const uint8
   p.n_q_tiles = (a.S_q + kBlockM - 1) / kBlockM;
   p.n_kv_tiles = (a.S_kv + kBlockN - 1) / kBlockN;
   p.q_pos0 = a.q_pos0; p.causal = a.causal; p.window = a.window;
+  p.v_transposed = kv6 ? 1 : 0;
+  p.q_tile_tx = q6 ? kTileBytes * 3 / 4 : kTileBytes;
+  p.kv_tile_tx = kv6 ? kTileBytes * 3 / 4 : kTileBytes;
   const float scale = a.softmax_scale > 0.0f ? a.softmax_scale : 1.0f / sqrtf((float)a.d);
   p.scale_log2 = scale * 1.4426950408889634f;
   p.cap_log2 = a.softcap * 1.4426950408889634f;
   p.inv_cap_scale = a.softcap > 0.0f ? scale / a.softcap : 0.0f;
 
   const uint32_t idesc_qk = make_idesc(a.q_fmt, a.kv_fmt, false, false, 128, 128);
-  const uint32_t idesc_pv = make_idesc(RK_FMT_E4M3, a.kv_fmt, false, true, 128, 128);
+  const uint32_t idesc_pv = make_idesc(RK_FMT_E4M3, a.kv_fmt, false, /*B MN-major*/ !kv6, 128, 128);
   dim3 grid(p.n_q_tiles, a.H, a.B);
   const bool cap = a.softcap > 0.0f;
   if (a.d <= 128) return launch_prefill2q(tq, tk, tv, p, idesc_qk, idesc_pv, cap, a.B, st);   // two query tiles per CTA

@@ -36,6 +36,9 @@ struct PrefillParams {
   int H, H_kv, S_q, S_kv, d;
   int n_q_tiles, n_kv_tiles;
   int q_pos0, causal, window;
+  int q_tile_tx, kv_tile_tx;   // bytes one Q / K / V tile load adds to its mbarrier: 16384, or 12288 for 6-bit tensors
+                               // (the transaction counts the packed source bytes, not the padded shared-memory image)
+  int v_transposed;    // V tiles are [d][keys] (K-major B operand; 6-bit V) instead of [keys][d]
   float scale_log2;    // softmax_scale * log2(e)
   float cap_log2;      // softcap * log2(e)
   float inv_cap_scale; // softmax_scale / softcap
@@ -69,6 +72,7 @@ RK_DEVINL uint32_t pack_u8x2(uint32_t hi, uint32_t lo, uint32_t c) {
 
 
 int make_tmap_u8_3d(CUtensorMap* m, const void* base, int64_t BH, int64_t S, int64_t d);
+int make_tmap_u6_3d(CUtensorMap* m, const void* base, int64_t BH, int64_t rows, int64_t cols_padded);
 extern float* g_prefill_dbg;
 
 // Two 128-row query tiles per CTA (d <= 128); defined in rk_prefill2q.cu.

@@ -353,7 +353,7 @@ prefill2q_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     if (lane == 0 && n_all > 0) {
       prefetch_tmap(&tmap_q); prefetch_tmap(&tmap_k); prefetch_tmap(&tmap_v);
       const int nq = (2 * qp + 1 < p.n_q_tiles) ? 2 : 1;
-      mbar_arrive_expect_tx(&bars[bQ], nq * (kTileBytes + kSfAtomBytes));
+      mbar_arrive_expect_tx(&bars[bQ], nq * (p.q_tile_tx + kSfAtomBytes));
       for (int g = 0; g < nq; ++g) {
         tma_load_3d(smem + q_off + g * kTileBytes, &tmap_q, &bars[bQ], 0, (2 * qp + g) * kBlockM, bh);
         bulk_load_1d(smem + sfq_off + g * kSfAtomBytes, p.q_sf + ((size_t)bh * p.n_q_tiles + 2 * qp + g) * kSfAtomBytes,
@@ -364,14 +364,15 @@ prefill2q_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         const int st = j % kStages, use = j / kStages;
         if (use > 0) ok = mbar_wait(&bars[bKE + st], (use - 1) & 1, abort_flag, p.status, 201);
         if (!ok) break;
-        mbar_arrive_expect_tx(&bars[bKF + st], kTileBytes + kSfAtomBytes);
+        mbar_arrive_expect_tx(&bars[bKF + st], p.kv_tile_tx + kSfAtomBytes);
         tma_load_3d(smem + k_off + st * kTileBytes, &tmap_k, &bars[bKF + st], 0, j * kBlockN, bhkv);
         bulk_load_1d(smem + sfk_off + st * kSfAtomBytes, p.k_sf + ((size_t)bhkv * p.n_kv_tiles + j) * kSfAtomBytes,
                      kSfAtomBytes, &bars[bKF + st]);
         if (use > 0) ok = mbar_wait(&bars[bVE + st], (use - 1) & 1, abort_flag, p.status, 202);
         if (!ok) break;
-        mbar_arrive_expect_tx(&bars[bVF + st], kTileBytes + kSfAtomBytes);
-        tma_load_3d(smem + v_off + st * kTileBytes, &tmap_v, &bars[bVF + st], 0, j * kBlockN, bhkv);
+        mbar_arrive_expect_tx(&bars[bVF + st], p.kv_tile_tx + kSfAtomBytes);
+        if (p.v_transposed) tma_load_3d(smem + v_off + st * kTileBytes, &tmap_v, &bars[bVF + st], j * kBlockN, 0, bhkv);
+        else tma_load_3d(smem + v_off + st * kTileBytes, &tmap_v, &bars[bVF + st], 0, j * kBlockN, bhkv);
         bulk_load_1d(smem + sfv_off + st * kSfAtomBytes, p.v_sf + ((size_t)bhkv * p.n_kv_tiles + j) * kSfAtomBytes,
                      kSfAtomBytes, &bars[bVF + st]);
       }
@@ -414,7 +415,9 @@ prefill2q_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk) {
           const uint64_t adesc = make_smem_desc(pt_addr + (g * 2 + pb) * kTileBytes + kk * 32, 16, 1024, kLayoutSw128);
-          const uint64_t bdesc = make_smem_desc(v_addr + st * kTileBytes + kk * 4096, kTileBytes, 1024, kLayoutSw128);
+          // V tile [keys][d] is the MN-major B operand; a 6-bit V is stored transposed and is K-major like K
+          const uint64_t bdesc = p.v_transposed ? make_smem_desc(v_addr + st * kTileBytes + kk * 32, 16, 1024, kLayoutSw128)
+                                                : make_smem_desc(v_addr + st * kTileBytes + kk * 4096, kTileBytes, 1024, kLayoutSw128);
           mma_mxf8f6f4_ss(tmem_base + cO + g * 128, adesc, bdesc, idesc_with_sf(idesc_pv, kk, kk),
                           tmem_base + cSfP + (g * 2 + pb) * 4, tmem_base + cSfV + st * 4, (i > 0 || kk > 0) ? 1u : 0u);
         }

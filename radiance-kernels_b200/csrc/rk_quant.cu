@@ -302,6 +302,62 @@ __global__ void retile_rowscales_kernel(const uint8_t* __restrict__ in, int64_t 
   }
 }
 
+
+// ---- 6-bit operands ---------------------------------------------------------------------------------
+// The tensor core reads 6-bit elements from shared memory as 16 codes in 12 bytes + 4 bytes of padding;
+// TMA (data type 16U6_ALIGN16B) produces that from a densely packed global tensor whose rows hold a multiple
+// of 128 codes: code i of a row sits at bits [6i, 6i+6) of the row's little-endian bit stream.
+RK_DEVINL void pack16x6(const uint32_t (&c)[16], uint32_t (&w)[3]) {
+  uint64_t lo = 0, hi = 0;     // 96 bits
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const uint64_t v = c[i] & 0x3Fu;
+    const int bit = 6 * i;
+    if (bit < 64) { lo |= v << bit; if (bit + 6 > 64) hi |= v >> (64 - bit); }
+    else hi |= v << (bit - 64);
+  }
+  w[0] = (uint32_t)lo; w[1] = (uint32_t)(lo >> 32); w[2] = (uint32_t)hi;
+}
+
+// byte codes [rows][d] -> packed [rows][dp * 3/4 bytes], dp = d rounded up to 128, padding codes 0
+__global__ void pack6_rows_kernel(const uint8_t* __restrict__ in, int64_t rows, int64_t d, int64_t dp, uint8_t* __restrict__ out) {
+  const int64_t groups = dp / 16, total = rows * groups;
+  for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = t / groups, gidx = t % groups;
+    uint32_t c[16], w[3];
+    if (gidx * 16 < d) {
+      const uint4 v = *reinterpret_cast<const uint4*>(in + r * d + gidx * 16);
+      const uint32_t ww[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int i = 0; i < 16; ++i) c[i] = (ww[i >> 2] >> (8 * (i & 3))) & 0xFFu;
+    } else {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) c[i] = 0;
+    }
+    pack16x6(c, w);
+    uint32_t* o = reinterpret_cast<uint32_t*>(out + r * (dp * 3 / 4) + gidx * 12);
+    o[0] = w[0]; o[1] = w[1]; o[2] = w[2];
+  }
+}
+
+// byte codes [batch][S][d] -> packed transposed [batch][d][Sp * 3/4 bytes], Sp = S rounded up to 128
+__global__ void pack6_transpose_kernel(const uint8_t* __restrict__ in, int64_t batch, int64_t S, int64_t d, int64_t Sp,
+                                       uint8_t* __restrict__ out) {
+  const int64_t groups = Sp / 16, total = batch * groups * d;      // consecutive threads = consecutive d (coalesced reads)
+  for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t col = t % d, gidx = (t / d) % groups, bt = t / (d * groups);
+    uint32_t c[16], w[3];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const int64_t key = gidx * 16 + i;
+      c[i] = key < S ? in[(bt * S + key) * d + col] : 0u;
+    }
+    pack16x6(c, w);
+    uint32_t* o = reinterpret_cast<uint32_t*>(out + (bt * d + col) * (Sp * 3 / 4) + gidx * 12);
+    o[0] = w[0]; o[1] = w[1]; o[2] = w[2];
+  }
+}
+
 static int grid_for(int64_t work_items, int threads, int per_sm) {
   const int64_t want = (work_items + threads - 1) / threads;
   const int64_t cap = (int64_t)num_sms() * per_sm;
@@ -357,6 +413,20 @@ int launch_retile_keyscales(const uint8_t* in, int64_t batch, int64_t S, int64_t
   const int64_t total = batch * ((S + 127) / 128) * ((d + 127) / 128) * 128;
   if (total == 0) return RK_OK;
   retile_keyscales_kernel<<<grid_for(total, 256, 8), 256, 0, st>>>(in, batch, S, d, out);
+  return (int)cudaGetLastError();
+}
+
+int launch_pack6_rows(const uint8_t* in, int64_t rows, int64_t d, uint8_t* out, cudaStream_t st) {
+  const int64_t dp = (d + 127) / 128 * 128, total = rows * (dp / 16);
+  if (total == 0) return RK_OK;
+  pack6_rows_kernel<<<grid_for(total, 256, 8), 256, 0, st>>>(in, rows, d, dp, out);
+  return (int)cudaGetLastError();
+}
+
+int launch_pack6_transpose(const uint8_t* in, int64_t batch, int64_t S, int64_t d, uint8_t* out, cudaStream_t st) {
+  const int64_t Sp = (S + 127) / 128 * 128, total = batch * (Sp / 16) * d;
+  if (total == 0) return RK_OK;
+  pack6_transpose_kernel<<<grid_for(total, 256, 8), 256, 0, st>>>(in, batch, S, d, Sp, out);
   return (int)cudaGetLastError();
 }
 

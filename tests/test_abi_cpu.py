@@ -51,7 +51,6 @@ def test_prefill_argument_errors():
     assert L.rk_attn_prefill(C.byref(_pargs(S_kv=0)), None) == -2
     assert L.rk_attn_prefill(C.byref(_pargs(v_scale_axis=7)), None) == -3
     assert L.rk_attn_prefill(C.byref(_pargs(q_fmt=9)), None) == -3
-    assert L.rk_attn_prefill(C.byref(_pargs(kv_fmt=3)), None) == -6       # 6-bit operands: not built yet
     assert L.rk_attn_prefill(C.byref(_pargs(block_n=64)), None) == -6
     assert L.rk_attn_prefill(C.byref(_pargs()), None) == -1               # valid shape, null tensors
     a = _pargs()

@@ -75,6 +75,25 @@ def test_e5m2_operands():
     _check(prefill_vs_oracle(1, 2, 1, 256, 256, 128, causal=True, fmt=rk.E5M2, seed=11))
 
 
+def test_mxfp6_operands_e2m3_q_e3m2_kv():
+    """MXFP6 variant: E2M3 queries, E3M2 keys and values (P stays E4M3), 6-bit codes packed for the tensor core."""
+    import oracle
+    for (B, H, Hkv, Sq, Skv, d, axis) in ((1, 2, 1, 256, 256, 128, rk.V_SCALES_ALONG_D), (1, 4, 2, 200, 333, 64, rk.V_SCALES_ALONG_KEYS),
+                                          (1, 2, 1, 384, 384, 256, rk.V_SCALES_ALONG_D)):
+        Q, K, V = randn_qkv(B, H, Hkv, Sq, Skv, d, seed=31, mul=0.5)
+        qc, qs = rk.mx_quantize(Q, rk.E2M3)
+        kc, ks = rk.mx_quantize(K, rk.E3M2)
+        vc, vs = rk.mx_quantize(V, rk.E3M2) if axis == rk.V_SCALES_ALONG_D else rk.mx_quantize_keys(V, rk.E3M2)
+        o = rk.attn_prefill(qc, kc, vc, qs, ks, vs, causal=True, softcap=50.0 if d == 256 else 0.0, q_fmt=rk.E2M3, kv_fmt=rk.E3M2,
+                            v_scale_axis=axis)
+        torch.cuda.synchronize()
+        assert rk.last_device_status() == 0
+        ref = oracle.attn_prefill(np_(qc), np_(kc), np_(vc), np_(qs), np_(ks), np_(vs), causal=True, softmax_scale=d ** -0.5,
+                                  softcap=50.0 if d == 256 else 0.0, q_fmt=rk.E2M3, kv_fmt=rk.E3M2, v_scale_axis=axis, block_n=128)
+        ma, rl = errors(np_(o.float()), ref["o_f32"])
+        assert ma <= MAX_ABS and rl <= REL_L2, (d, ma, rl)
+
+
 def test_lse_output():
     r = prefill_vs_oracle(1, 2, 1, 256, 256, 128, causal=True, want_lse=True, seed=12)
     _check(r)
