@@ -217,7 +217,11 @@ __device__ __forceinline__ void softmax_group(const PrefillParams& p, uint8_t* s
           tmem_ld32(tmem_base + lane_addr + o_col + ch * 32, r);
           tc_wait_ld();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * corr);
+          for (int i = 0; i < 32; i += 2) {
+            float a, b;
+            mul2_ftz(__uint_as_float(r[i]), __uint_as_float(r[i + 1]), corr, a, b);
+            r[i] = __float_as_uint(a); r[i + 1] = __float_as_uint(b);
+          }
           tmem_st32(tmem_base + lane_addr + o_col + ch * 32, r);
         }
         tc_wait_st();

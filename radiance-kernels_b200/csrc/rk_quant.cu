@@ -201,7 +201,7 @@ __global__ void __launch_bounds__(128) rebase_v_kernel(const uint8_t* __restrict
     if (FMT == 0) {
       // pass 1: largest L per column (the block is small enough to be re-read from L1 in pass 2)
       int lmax[4] = {0, 0, 0, 0};
-#pragma unroll 4
+#pragma unroll 16
       for (int j = 0; j < n; j++) {
         const uint32_t cw = *reinterpret_cast<const uint32_t*>(cb + (int64_t)j * d);
         const int sj = sb[(int64_t)j * nbd];
@@ -221,7 +221,7 @@ __global__ void __launch_bounds__(128) rebase_v_kernel(const uint8_t* __restrict
           sc[q] = (uint32_t)s_new;
           sub[q] = 8 * s_new;
         }
-#pragma unroll 4
+#pragma unroll 8
         for (int j = 0; j < n; j++) {
           const uint32_t cw = *reinterpret_cast<const uint32_t*>(cb + (int64_t)j * d);
           const int sj8 = 8 * (int)sb[(int64_t)j * nbd];
