@@ -38,6 +38,18 @@ def prefill_flops(c):
     return 4.0 * c["B"] * c["H"] * c["S"] * c["S"] * c["d"] * 0.5      # causal: half the tiles counted
 
 
+def prefill_algorithmic_bytes(c):
+    """Q, K, V codes + E8M0 scales read once, bf16 O and fp32 LSE written once."""
+    qkv = (c["B"] * c["H"] * c["S"] + 2 * c["B"] * c["H_kv"] * c["S"]) * c["d"] * (1 + 1 / 32)
+    return int(qkv + c["B"] * c["H"] * c["S"] * (2 * c["d"] + 4))
+
+
+# DRAM traffic of one launch from the ncu captures summarised under profiles/ (dram__bytes_read.sum +
+# dram__bytes_write.sum), per unit of work; both kernels' traffic is proportional to the unit count.
+NCU_PREFILL_DRAM_BYTES_PER_HEAD = (103.966976e6 + 34.787584e6) / 64        # S=4096, d=128, causal
+NCU_DECODE_DRAM_BYTES_PER_SEQUENCE = (554.994176e6 + 17.266688e6) / 8      # H_kv=8, L=32768, d=128
+
+
 def decode_bytes(c):
     return 2.0 * c["B"] * c["H_kv"] * c["L"] * c["d"] * (1 + 1 / 32) + 2 * c["B"] * c["H"] * c["d"] * 2
 
@@ -249,7 +261,10 @@ def main():
     value = flops * world / (ms_step * 1e-3) / 1e12
     fp8_peak = 2.0 * peaks["bf16_sustained"]
     roofline = {"bound": "tensor", "achieved": flops / (kern_ms * 1e-3) / 1e12, "peak": fp8_peak, "unit": "TFLOP/s",
-                "frac": flops / (kern_ms * 1e-3) / 1e12 / fp8_peak, "traffic": None,
+                "frac": flops / (kern_ms * 1e-3) / 1e12 / fp8_peak,
+                "traffic": NCU_PREFILL_DRAM_BYTES_PER_HEAD * c["B"] * c["H"] if (c["S"], c["d"]) == (4096, 128) else None,
+                "traffic_note": "ncu dram read+write of one launch at B=4 (138.75 MB for 64 (batch, head) units), scaled by "
+                                "the unit count; algorithmic bytes per launch: %d" % prefill_algorithmic_bytes(c),
                 "kernel": "prefill2q_kernel<false>", "kernel_ms": kern_ms,
                 "peak_note": f"2 x {peaks['source']} sustained cuBLAS bf16 ({peaks['bf16_sustained']} TF/s) as the dense "
                              f"MXFP8 proxy; nominal dense FP8 is 4500 TF/s (frac of nominal {flops / (kern_ms * 1e-3) / 1e12 / 4500.0:.4f})"}
@@ -321,7 +336,10 @@ def main():
                   "ms_per_step": dms, "workload": "batch 64, 32 query heads / 8 KV heads, d=128, KV length 32768, MXFP8 cache",
                   "num_splits": rk.attn_decode_num_splits(Bd, Hd, Hkd, Ld, dd),
                   "roofline": {"bound": "hbm", "achieved": by / (dk * 1e-3) / 1e9, "peak": peaks["hbm"], "unit": "GB/s",
-                               "frac": by / (dk * 1e-3) / 1e9 / peaks["hbm"], "traffic": None, "kernel": "decode_kernel",
+                               "frac": by / (dk * 1e-3) / 1e9 / peaks["hbm"],
+                               "traffic": NCU_DECODE_DRAM_BYTES_PER_SEQUENCE * Bd if (Hkd, Ld, dd) == (8, 32768, 128) else None,
+                               "traffic_note": "ncu dram read+write of one launch at B=8 (572.26 MB), scaled by B",
+                               "kernel": "decode_kernel",
                                "kernel_ms": dk, "peak_note": f"{peaks['source']} HBM copy bandwidth; nominal 8000 GB/s"}}
         if rk.last_device_status() != 0:
             raise SystemExit("device status non-zero after the decode leg")
