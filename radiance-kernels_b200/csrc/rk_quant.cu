@@ -176,87 +176,194 @@ __device__ __noinline__ void rebase_block_generic(const uint8_t* cb, const uint8
   }
 }
 
-// One thread = 4 adjacent columns x one 32-key block.
-// E4M3 fast path, all integer: a normal code c under scale code s has value (1 + m/8) * 2^(L/8 - 134) with
-// L = (c & 0x7F) + 8 s, so the block's amax is the largest L, the block rule gives the new scale code
-// s' = L_max/8 - 15 (+1 when the mantissa of the max is 7, i.e. above 1.75), and an element's new code is
-// sign | (L - 8 s') whenever that is a normal code; smaller ones are rounded to nearest-even into the
-// subnormal range.  Identical to decoding to fp32 and re-quantizing (which the generic path does).
-template <int FMT, bool TILED>
-__global__ void __launch_bounds__(128) rebase_v_kernel(const uint8_t* __restrict__ codes, const uint8_t* __restrict__ scales,
-                                                       int64_t batch, int64_t S, int64_t d,
-                                                       uint8_t* __restrict__ out_codes, uint8_t* __restrict__ out_scales) {
-  const int64_t c4n = d / 4, nkb = (S + 31) / 32, nbd = d / 32;
-  const int64_t total = batch * nkb * c4n;
-  const int64_t ntile = (S + 127) / 128, dch = (d + 127) / 128;   // atom grid of the TILED layout
-  for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t c4 = t % c4n, kb = (t / c4n) % nkb, bt = t / (c4n * nkb);
-    const int64_t r0 = kb * 32;
-    const int n = (int)min((int64_t)32, S - r0);
-    const uint8_t* cb = codes + (bt * S + r0) * d + c4 * 4;
-    const uint8_t* sb = scales + (bt * S + r0) * nbd + (c4 * 4) / 32;
-    uint8_t* ob = out_codes + (bt * S + r0) * d + c4 * 4;
-    uint32_t sc[4];
-    bool fast = (FMT == 0);
-    if (FMT == 0) {
-      // pass 1: largest L per column (the block is small enough to be re-read from L1 in pass 2)
-      int lmax[4] = {0, 0, 0, 0};
-#pragma unroll 16
-      for (int j = 0; j < n; j++) {
-        const uint32_t cw = *reinterpret_cast<const uint32_t*>(cb + (int64_t)j * d);
-        const int sj = sb[(int64_t)j * nbd];
-        fast = fast && (sj >= 16) && (sj <= 240);
+// ---- E4M3 re-blocking in integer arithmetic ---------------------------------------------------------------
+// A normal code c (magnitude bits mag = c & 0x7F >= 8) under scale code s has the value
+// (1 + m/8) * 2^(L/8 - 134) with L = mag + 8 s (m = L & 7), so the largest |value| of a block is the largest
+// L, the block rule gives the new scale code s' = L_max/8 - 15 (+1 when the mantissa of the maximum is 7,
+// i.e. above 1.75 = 448/256), and an element's new code is sign | (L - 8 s') whenever that is a normal code;
+// smaller ones are rounded to nearest-even into the subnormal grid.  A subnormal input (mag 1..7) is first
+// normalised to the same (1 + m/8) * 2^x form, which gives it a (possibly negative) pseudo-magnitude.
+// Identical to decoding to fp32 and re-quantizing (which the generic path does).
+// Two elements ride in one register as 16-bit lanes (L < 4096), maxima by max.u16x2.
+RK_DEVINL uint32_t max_u16x2(uint32_t a, uint32_t b) {
+  uint32_t r;
+  asm("max.u16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+// pseudo-magnitude of a subnormal E4M3 code, mag in 1..7: value = mag * 2^-9 = (1 + m'/8) * 2^(e' - 7)
+RK_DEVINL int e4m3_subnormal_mag(int mag) {
+  const int p = 31 - __clz(mag);                       // 0..2
+  return ((mag << (3 - p)) & 7) + 8 * (p - 2);
+}
+// new code (without sign) of an element with L - 8 s' = tt
+RK_DEVINL uint32_t e4m3_code_from_tt(int tt) {
+  if (tt >= 8) return (uint32_t)tt;
+  const int sh = 1 - (tt >> 3);                        // >= 1: below the smallest normal
+  return sh > 5 ? 0u : round_shift(8u | (uint32_t)(tt & 7), sh);
+}
+// non-zero when some byte of w has a zero exponent field (zero or subnormal code)
+RK_DEVINL uint32_t e4m3_exp0_bits(uint32_t w) {
+  const uint32_t e = w & 0x78787878u;
+  return (e - 0x08080808u) & ~e & 0x80808080u;
+}
+RK_DEVINL uint32_t addmax_u16x2(uint32_t a, uint32_t b, uint32_t c) {   // max(a + b, c) in both 16-bit lanes
+  uint32_t r;
+  asm("{ .reg .b32 t; add.u16x2 t, %1, %2; max.u16x2 %0, t, %3; }" : "=r"(r) : "r"(a), "r"(b), "r"(c));
+  return r;
+}
+
+// Rare rows (a zero or subnormal code among the four): per-byte L, packed as lanes (0, 2) and (1, 3).
+__device__ __noinline__ uint2 e4m3_rare_l(uint32_t cw, int sj) {
+  uint32_t l[4];
 #pragma unroll
-        for (int q = 0; q < 4; q++) {
-          const int mag = (int)((cw >> (8 * q)) & 0x7Fu);
-          fast = fast && (mag == 0 || mag >= 8);                 // a subnormal code sends the block to the generic path
-          lmax[q] = max(lmax[q], mag >= 8 ? mag + 8 * sj : 0);
+  for (int q = 0; q < 4; q++) {
+    const int mag = (int)((cw >> (8 * q)) & 0x7Fu);
+    l[q] = mag == 0 ? 0u : (uint32_t)((mag >= 8 ? mag : e4m3_subnormal_mag(mag)) + 8 * sj) & 0xFFFFu;
+  }
+  return make_uint2(l[0] | (l[2] << 16), l[1] | (l[3] << 16));
+}
+// Rare rows of the second pass: some lane leaves the normal range, or an input was zero / subnormal.
+// sub02 / sub13 carry 8 s' of columns (0, 2) and (1, 3) as 16-bit lanes.
+__device__ __noinline__ uint32_t e4m3_rare_recode(uint32_t cw, int sj, uint32_t sub02, uint32_t sub13) {
+  uint32_t out = cw & 0x80808080u;
+#pragma unroll
+  for (int q = 0; q < 4; q++) {
+    const int mag = (int)((cw >> (8 * q)) & 0x7Fu);
+    const int sub = (int)((((q & 1) ? sub13 : sub02) >> (16 * (q >> 1))) & 0xFFFFu);
+    if (mag != 0) out |= e4m3_code_from_tt((mag >= 8 ? mag : e4m3_subnormal_mag(mag)) + 8 * sj - sub) << (8 * q);
+  }
+  return out;
+}
+
+// Four lanes share one unit = 16 adjacent columns x one 32-key block: lane "rg" holds rows 8 rg .. 8 rg + 7 as
+// eight 16-byte words in registers between the two passes (all loads of a thread in flight together), the
+// column maxima meet by two shuffles.  A warp covers 8 adjacent units, so each 16-byte access of a warp touches
+// four full 128-byte lines.  Formats other than E4M3, and E4M3 blocks with scale codes outside [18, 240], go
+// through the generic fp32 path, each lane taking 4 of the unit's 16 columns over all 32 keys.
+template <int FMT, bool TILED>
+__global__ void __launch_bounds__(128, 4) rebase_v_kernel(const uint8_t* __restrict__ codes, const uint8_t* __restrict__ scales,
+                                                          int64_t batch, int64_t S, int64_t d,
+                                                          uint8_t* __restrict__ out_codes, uint8_t* __restrict__ out_scales) {
+  const int64_t c16n = d / 16, nkb = (S + 31) / 32, nbd = d / 32;
+  const int64_t units = batch * nkb * c16n;
+  const int64_t ntile = (S + 127) / 128, dch = (d + 127) / 128;   // atom grid of the TILED layout
+  const int64_t warps_total = (units + 7) / 8;
+  const int lane = threadIdx.x & 31, rg = lane >> 3;
+  for (int64_t w = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; w < warps_total;
+       w += ((int64_t)gridDim.x * blockDim.x) >> 5) {
+    const int64_t u = w * 8 + (lane & 7);
+    const bool valid = u < units;
+    const int64_t uu = valid ? u : 0;
+    const int64_t c16 = uu % c16n, kb = (uu / c16n) % nkb, bt = uu / (c16n * nkb);
+    const int64_t r0 = kb * 32;
+    const int n = valid ? (int)min((int64_t)32, S - r0) : 0;      // keys of this block that exist
+    const uint8_t* cb = codes + (bt * S + r0) * d + c16 * 16;
+    const uint8_t* sb = scales + (bt * S + r0) * nbd + c16 / 2;
+    uint8_t* ob = out_codes + (bt * S + r0) * d + c16 * 16;
+    uint32_t sc[4];                                               // new scale codes of columns 4 rg .. 4 rg + 3
+    uint32_t bad = (FMT == 0) ? 0u : 1u;
+    if (FMT == 0) {
+      // rows past a ragged end read as zero codes under a mid-range scale: they change nothing
+      uint4 cw[8];
+      uint32_t s8[8];
+#pragma unroll
+      for (int i = 0; i < 8; i++) {
+        const int j = rg * 8 + i;
+        const bool in = j < n;
+        cw[i] = in ? __ldg(reinterpret_cast<const uint4*>(cb + (int64_t)j * d)) : make_uint4(0u, 0u, 0u, 0u);
+        s8[i] = in ? (uint32_t)__ldg(sb + (int64_t)j * nbd) : 127u;
+      }
+      // pass 1: largest L per column; word x of a row holds columns 4x .. 4x+3, lanes (0, 2) in lo[x], (1, 3) in hi[x]
+      uint32_t lo[4] = {0u, 0u, 0u, 0u}, hi[4] = {0u, 0u, 0u, 0u};
+#pragma unroll
+      for (int i = 0; i < 8; i++) {
+        bad |= (s8[i] - 18u > 222u) ? 1u : 0u;
+        s8[i] *= 0x00080008u;
+        const uint32_t wv[4] = {cw[i].x, cw[i].y, cw[i].z, cw[i].w};
+        // one test per row: does any of its 16 codes have a zero exponent field (zero or subnormal)?
+        if ((e4m3_exp0_bits(wv[0]) | e4m3_exp0_bits(wv[1]) | e4m3_exp0_bits(wv[2]) | e4m3_exp0_bits(wv[3])) == 0u) {
+#pragma unroll
+          for (int x = 0; x < 4; x++) {
+            lo[x] = addmax_u16x2(wv[x] & 0x007F007Fu, s8[i], lo[x]);
+            hi[x] = addmax_u16x2((wv[x] >> 8) & 0x007F007Fu, s8[i], hi[x]);
+          }
+        } else {
+#pragma unroll
+          for (int x = 0; x < 4; x++) {
+            uint2 l = make_uint2((wv[x] & 0x007F007Fu) + s8[i], ((wv[x] >> 8) & 0x007F007Fu) + s8[i]);
+            if (e4m3_exp0_bits(wv[x]) != 0u) l = e4m3_rare_l(wv[x], (int)((s8[i] & 0xFFFFu) >> 3));
+            lo[x] = max_u16x2(lo[x], l.x);
+            hi[x] = max_u16x2(hi[x], l.y);
+          }
         }
       }
-      if (fast) {
-        int sub[4];
 #pragma unroll
-        for (int q = 0; q < 4; q++) {
-          const int s_new = lmax[q] == 0 ? 0 : (lmax[q] >> 3) - 15 + ((lmax[q] & 7) == 7 ? 1 : 0);
-          sc[q] = (uint32_t)s_new;
-          sub[q] = 8 * s_new;
-        }
-#pragma unroll 8
-        for (int j = 0; j < n; j++) {
-          const uint32_t cw = *reinterpret_cast<const uint32_t*>(cb + (int64_t)j * d);
-          const int sj8 = 8 * (int)sb[(int64_t)j * nbd];
-          uint32_t out = 0;
+      for (int x = 0; x < 4; x++) {
+        lo[x] = max_u16x2(lo[x], __shfl_xor_sync(0xFFFFFFFFu, lo[x], 8));
+        hi[x] = max_u16x2(hi[x], __shfl_xor_sync(0xFFFFFFFFu, hi[x], 8));
+        lo[x] = max_u16x2(lo[x], __shfl_xor_sync(0xFFFFFFFFu, lo[x], 16));
+        hi[x] = max_u16x2(hi[x], __shfl_xor_sync(0xFFFFFFFFu, hi[x], 16));
+      }
+      bad |= __shfl_xor_sync(0xFFFFFFFFu, bad, 8);
+      bad |= __shfl_xor_sync(0xFFFFFFFFu, bad, 16);
+      if (bad == 0u) {
+        // s' = L_max / 8 - 15 (+1 when the mantissa bits are 7) in both 16-bit lanes at once; all-zero columns
+        // (L_max = 0) get scale code 0
+        uint32_t sub_lo[4], sub_hi[4];
 #pragma unroll
-          for (int q = 0; q < 4; q++) {
-            const uint32_t c = (cw >> (8 * q)) & 0xFFu;
-            const int mag = (int)(c & 0x7Fu);
-            const int tt = mag + sj8 - sub[q];                  // new exponent field * 8 + mantissa
-            uint32_t code;
-            if (mag == 0) code = 0;                             // +-0 keeps only its sign
-            else if (tt >= 8) code = (uint32_t)tt;
-            else {                                              // below the smallest normal: RNE into the subnormal grid
-              const int sh = 1 - (tt >> 3);                     // >= 1
-              const uint32_t sig = 8u | (uint32_t)(tt & 7);
-              code = sh > 5 ? 0u : round_shift(sig, sh);
-            }
-            out |= ((c & 0x80u) | code) << (8 * q);
+        for (int x = 0; x < 4; x++) {
+          uint32_t v[2] = {lo[x], hi[x]};
+#pragma unroll
+          for (int h = 0; h < 2; h++) {
+            uint32_t sn = ((v[h] >> 3) & 0x1FFF1FFFu) + ((((v[h] & 0x00070007u) + 0x00010001u) >> 3) & 0x00010001u);
+            if ((v[h] & 0xFFFFu) == 0u) sn |= 0x0000000Fu;          // an all-zero column: 15 - 15 = scale code 0
+            if ((v[h] >> 16) == 0u) sn |= 0x000F0000u;
+            v[h] = sn - 0x000F000Fu;
           }
-          *reinterpret_cast<uint32_t*>(ob + (int64_t)j * d) = out;
+          sub_lo[x] = v[0] << 3;
+          sub_hi[x] = v[1] << 3;
+          if (x == rg) {
+            sc[0] = v[0] & 0xFFFFu; sc[1] = v[1] & 0xFFFFu; sc[2] = v[0] >> 16; sc[3] = v[1] >> 16;
+          }
+        }
+        // pass 2: lanes carry tt + 0x4000 (tt = L - 8 s') so that they stay non-negative
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+          const uint32_t wv[4] = {cw[i].x, cw[i].y, cw[i].z, cw[i].w};
+          uint32_t ov[4];
+          // lanes that leave the normal range (tt < 8) set bit 15 of their half; zero / subnormal inputs set bit 7
+          uint32_t rare[4];
+#pragma unroll
+          for (int x = 0; x < 4; x++) {
+            const uint32_t t_lo = (wv[x] & 0x007F007Fu) + s8[i] + (0x40004000u - sub_lo[x]);
+            const uint32_t t_hi = ((wv[x] >> 8) & 0x007F007Fu) + s8[i] + (0x40004000u - sub_hi[x]);
+            ov[x] = (wv[x] & 0x80808080u) | (t_lo & 0x007F007Fu) | ((t_hi & 0x007F007Fu) << 8);
+            rare[x] = (((t_lo - 0x40084008u) | (t_hi - 0x40084008u)) & 0x80008000u) | e4m3_exp0_bits(wv[x]);
+          }
+          if ((rare[0] | rare[1] | rare[2] | rare[3]) != 0u) {      // one branch per row in the common case
+#pragma unroll
+            for (int x = 0; x < 4; x++)
+              if (rare[x] != 0u) ov[x] = e4m3_rare_recode(wv[x], (int)((s8[i] & 0xFFFFu) >> 3), sub_lo[x], sub_hi[x]);
+          }
+          const int j = rg * 8 + i;
+          if (j < n) *reinterpret_cast<uint4*>(ob + (int64_t)j * d) = make_uint4(ov[0], ov[1], ov[2], ov[3]);
         }
       }
     }
-    if (!fast) rebase_block_generic<FMT>(cb, sb, n, d, nbd, ob, sc);
+    if (!valid) continue;
+    if (bad != 0u) rebase_block_generic<FMT>(cb + rg * 4, sb, n, d, nbd, ob + rg * 4, sc);
+    const int64_t col0 = c16 * 16 + rg * 4;
     if (TILED) {
       const int64_t kt = kb / 4;
       const int kbi = (int)(kb % 4);
 #pragma unroll
       for (int q = 0; q < 4; q++) {
-        const int64_t col = c4 * 4 + q;
+        const int64_t col = col0 + q;
         const int64_t atom = (bt * ntile + kt) * dch + col / 128;
         out_scales[atom * 512 + sf_atom_offset((int)(col % 128), kbi)] = (uint8_t)sc[q];
       }
     } else {
-      *reinterpret_cast<uint32_t*>(out_scales + (bt * nkb + kb) * d + c4 * 4) = sc[0] | (sc[1] << 8) | (sc[2] << 16) | (sc[3] << 24);
+      *reinterpret_cast<uint32_t*>(out_scales + (bt * nkb + kb) * d + col0) = sc[0] | (sc[1] << 8) | (sc[2] << 16) | (sc[3] << 24);
     }
   }
 }
@@ -394,9 +501,9 @@ int launch_quantize_keys(const float* x, int64_t batch, int64_t rows, int64_t co
 
 int launch_rebase_v(const uint8_t* codes, const uint8_t* scales, int64_t batch, int64_t S, int64_t d, int fmt,
                     uint8_t* out_codes, uint8_t* out_scales, bool tiled, cudaStream_t st) {
-  const int64_t total = batch * ((S + 31) / 32) * (d / 4);
+  const int64_t total = ((batch * ((S + 31) / 32) * (d / 16) + 7) / 8) * 32;     // 4 lanes per 16-column unit, whole warps
   if (total == 0) return RK_OK;
-  const int grid = grid_for(total, 128, 16);
+  const int grid = grid_for(total, 128, 8);
   if (tiled) { RK_DISPATCH_FMT(fmt, (rebase_v_kernel<F, true><<<grid, 128, 0, st>>>(codes, scales, batch, S, d, out_codes, out_scales))); }
   else       { RK_DISPATCH_FMT(fmt, (rebase_v_kernel<F, false><<<grid, 128, 0, st>>>(codes, scales, batch, S, d, out_codes, out_scales))); }
   return (int)cudaGetLastError();
