@@ -110,13 +110,25 @@ RK_DEVINL void mbar_arrive(uint64_t* bar) {
 RK_DEVINL void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
+// One poll of an mbarrier phase.  HINT_NS > 0 lets the hardware keep the thread suspended for up to that many
+// ns before it reports "not yet": a warp that waits long (a TMA producer) then issues few instructions and
+// leaves the issue slots of its scheduler to the working warps; 0 = the hardware default, quickest wake-up.
+template <uint32_t HINT_NS = 0>
 RK_DEVINL bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  if (HINT_NS > 0) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity), "r"(HINT_NS) : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  }
   return ok != 0;
 }
 RK_DEVINL uint64_t global_timer_ns() {
@@ -126,12 +138,13 @@ RK_DEVINL uint64_t global_timer_ns() {
 // CTA's abort flag or the device status word is set by someone else), records
 // `code` in *status and returns false; the caller then skips its work so the
 // kernel drains and exits instead of hanging the GPU.
+template <uint32_t HINT_NS = 0>
 RK_DEVINL bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status, int code,
                          uint64_t limit_ns = 2000000000ull) {
-  if (mbar_try_wait(bar, parity)) return true;
+  if (mbar_try_wait<HINT_NS>(bar, parity)) return true;
   const uint64_t t0 = global_timer_ns();
   for (uint32_t it = 1;; ++it) {
-    if (mbar_try_wait(bar, parity)) return true;
+    if (mbar_try_wait<HINT_NS>(bar, parity)) return true;
     if ((it & 255u) == 0u) {
       if (*abort_flag || *reinterpret_cast<volatile int*>(status) != 0) { *abort_flag = 1; return false; }
       if (global_timer_ns() - t0 > limit_ns) break;

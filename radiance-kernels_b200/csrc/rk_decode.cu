@@ -144,7 +144,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant_
       prefetch_tmap(&tmap_k); prefetch_tmap(&tmap_v);
       for (int j = 0; j < n_tiles; ++j) {
         if (j >= kDecStages &&
-            !mbar_wait(&empty[j % kDecStages], ((j / kDecStages) - 1) & 1, abort_flag, p.status, 402)) break;
+            !mbar_wait<20000>(&empty[j % kDecStages], ((j / kDecStages) - 1) & 1, abort_flag, p.status, 402)) break;
         issue_stage(j);
       }
     }
@@ -200,7 +200,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant_
 
     for (int j = 0; j < n_tiles && ok; ++j) {
       const int st = j % kDecStages;
-      ok = __all_sync(0xffffffffu, mbar_wait(&full[st], (j / kDecStages) & 1, abort_flag, p.status, 401));
+      ok = __all_sync(0xffffffffu, mbar_wait<20000>(&full[st], (j / kDecStages) & 1, abort_flag, p.status, 401));
       if (!ok) break;
       const uint8_t* sk = smem + st * kDecStageBytes;
       const uint8_t* sv = sk + kDecTileKeys * kDecD;

@@ -254,7 +254,7 @@ __device__ __forceinline__ void softmax_rows(const PrefillParams& p, uint8_t* sm
           tmem_ld32(addr, r);
           tc_wait_ld();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * corr);
+          for (int i = 0; i < 32; i += 2) mul2_ftz_inplace(r[i], r[i + 1], corr);
           tmem_st32(addr, r);
         }
         tc_wait_st();

@@ -54,6 +54,10 @@ RK_DEVINL void add2(float& a0, float& a1, float b0, float b1) {                 
   asm("{\n\t.reg .b64 ra, rb;\n\tmov.b64 ra, {%0, %1};\n\tmov.b64 rb, {%2, %3};\n\tadd.rn.f32x2 ra, ra, rb;\n\tmov.b64 {%0, %1}, ra;\n\t}"
       : "+f"(a0), "+f"(a1) : "f"(b0), "f"(b1));
 }
+RK_DEVINL void mul2_ftz_inplace(uint32_t& a0, uint32_t& a1, float b) {                 // a *= b on two fp32 bit patterns, in their registers
+  asm("{\n\t.reg .b64 ra, rb;\n\tmov.b64 ra, {%0, %1};\n\tmov.b64 rb, {%2, %2};\n\tmul.rn.ftz.f32x2 ra, ra, rb;\n\tmov.b64 {%0, %1}, ra;\n\t}"
+      : "+r"(a0), "+r"(a1) : "f"(b));
+}
 RK_DEVINL void mul2_ftz(float a0, float a1, float b, float& d0, float& d1) {           // d = a * b, subnormal results -> 0
   asm("{\n\t.reg .b64 ra, rb, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %4};\n\tmul.rn.ftz.f32x2 rd, ra, rb;\n\tmov.b64 {%0, %1}, rd;\n\t}"
       : "=f"(d0), "=f"(d1) : "f"(a0), "f"(a1), "f"(b));

@@ -217,11 +217,7 @@ __device__ __forceinline__ void softmax_group(const PrefillParams& p, uint8_t* s
           tmem_ld32(tmem_base + lane_addr + o_col + ch * 32, r);
           tc_wait_ld();
 #pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            float a, b;
-            mul2_ftz(__uint_as_float(r[i]), __uint_as_float(r[i + 1]), corr, a, b);
-            r[i] = __float_as_uint(a); r[i + 1] = __float_as_uint(b);
-          }
+          for (int i = 0; i < 32; i += 2) mul2_ftz_inplace(r[i], r[i + 1], corr);
           tmem_st32(tmem_base + lane_addr + o_col + ch * 32, r);
         }
         tc_wait_st();
