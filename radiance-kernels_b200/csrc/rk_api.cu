@@ -232,7 +232,7 @@ int rk_attn_decode_num_splits(const rk_decode_args* a) {
   if (a->num_splits > 0) return a->num_splits < tiles ? a->num_splits : tiles;
   // two CTAs fit on an SM; pick the split count (each split >= 4 key tiles) whose CTA count fills
   // whole waves best, preferring fewer splits on ties
-  const long slots = 2L * num_sms(), units = (long)a->B * a->H_kv;
+  const long slots = (long)decode_ctas_per_sm(*a) * num_sms(), units = (long)a->B * a->H_kv;
   int best = 1; double best_eff = -1.0;
   for (int s = 1; s <= 64 && (s == 1 || tiles / s >= 4); ++s) {
     const long ctas = units * s, waves = (ctas + slots - 1) / slots;
@@ -295,5 +295,8 @@ RK_API int rk_debug_verify_encoder(int fmt, unsigned long long* mismatches, uint
 /* Test hook (not in the public header): stage dump of the first query tile / first key tile of
  * the next prefill launches into `buf` (>= 32768 floats), or NULL to switch it off. */
 RK_API void rk_debug_set_prefill_dump(float* buf) { g_prefill_dbg = buf; }
+
+/* Test hook (not in the public header): 0 = choose the decode kernel by shape, 1 = always the mma.sync kernel. */
+RK_API void rk_debug_set_decode_path(int path) { g_decode_path = path; }
 
 }  // extern "C"

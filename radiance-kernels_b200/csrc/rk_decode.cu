@@ -379,6 +379,20 @@ __global__ void decode_combine_kernel(const float* __restrict__ part_o, const fl
 
 int make_tmap_u8_3d(CUtensorMap* m, const void* base, int64_t BH, int64_t S, int64_t d);   // defined beside the prefill kernel
 
+}  // namespace rk
+#include "rk_decode_tc.cuh"
+namespace rk {
+
+// Which kernel serves a call: the tcgen05 kernel handles d = 128 with up to 4 query heads per KV head; everything
+// else (and a forced choice through the test hook: 1 = mma.sync kernel, 2 = tcgen05 kernel) takes the mma.sync kernel.
+int g_decode_path = 0;
+bool decode_uses_tc(const rk_decode_args& a) {
+  const bool can = a.d == 128 && a.H_kv > 0 && a.H / a.H_kv <= dtc::kMaxGrp;
+  if (g_decode_path == 1) return false;
+  return can;
+}
+int decode_ctas_per_sm(const rk_decode_args& a) { return decode_uses_tc(a) ? 1 : 2; }
+
 int launch_decode(const rk_decode_args& a, int nsplit, cudaStream_t st) {
   CUtensorMap tk, tv;
   int rc;
@@ -394,12 +408,26 @@ int launch_decode(const rk_decode_args& a, int nsplit, cudaStream_t st) {
   p.B = a.B; p.H = a.H; p.H_kv = a.H_kv; p.L = a.L; p.grp = a.H / a.H_kv; p.nsplit = nsplit;
   const float scale = a.softmax_scale > 0.0f ? a.softmax_scale : 1.0f / sqrtf((float)a.d);
   p.scale_log2 = scale * 1.4426950408889634f;
-  cudaError_t e = cudaFuncSetAttribute(decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDecSmemBytes);
-  if (e != cudaSuccess) return (int)e;
+  cudaError_t e;
   dim3 grid(nsplit, a.H_kv, a.B);
-  if (g_ev_before && g_ev_after) cudaEventRecord(g_ev_before, st);
-  decode_kernel<<<grid, kDecThreads, kDecSmemBytes, st>>>(tk, tv, p);
-  if (g_ev_before && g_ev_after) cudaEventRecord(g_ev_after, st);
+  if (decode_uses_tc(a)) {
+    DecodeTcParams t;
+    t.q = p.q; t.k_scale = p.k_scale; t.v_scale = p.v_scale; t.kv_len = p.kv_len;
+    t.part_o = p.part_o; t.part_ml = p.part_ml; t.status = p.status;
+    t.B = p.B; t.H = p.H; t.H_kv = p.H_kv; t.L = p.L; t.grp = p.grp; t.nsplit = p.nsplit; t.scale_log2 = p.scale_log2;
+    const int smem_bytes = dtc::total + 1024;
+    if ((e = cudaFuncSetAttribute(decode_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes)) != cudaSuccess) return (int)e;
+    const uint32_t idesc_qk = make_idesc(0, 0, false, false, 128, dtc::kNq);
+    const uint32_t idesc_pv = make_idesc(0, 0, true, false, 128, dtc::kNp);
+    if (g_ev_before && g_ev_after) cudaEventRecord(g_ev_before, st);
+    decode_tc_kernel<<<grid, dtc::kThreads, smem_bytes, st>>>(tk, tv, t, idesc_qk, idesc_pv);
+    if (g_ev_before && g_ev_after) cudaEventRecord(g_ev_after, st);
+  } else {
+    if ((e = cudaFuncSetAttribute(decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDecSmemBytes)) != cudaSuccess) return (int)e;
+    if (g_ev_before && g_ev_after) cudaEventRecord(g_ev_before, st);
+    decode_kernel<<<grid, kDecThreads, kDecSmemBytes, st>>>(tk, tv, p);
+    if (g_ev_before && g_ev_after) cudaEventRecord(g_ev_after, st);
+  }
   if ((e = cudaGetLastError()) != cudaSuccess) return (int)e;
   const int warps_per_cta = 4;
   decode_combine_kernel<<<(int)((BH + warps_per_cta - 1) / warps_per_cta), warps_per_cta * 32, 0, st>>>(

@@ -28,5 +28,8 @@ int launch_prefill(const rk_prefill_args& a, const uint8_t* q_codes, const uint8
 
 int launch_decode(const rk_decode_args& a, int num_splits, cudaStream_t st);
 int launch_decode_noalloc(const rk_decode_args& a, cudaStream_t st);
+extern int g_decode_path;                                   // test hook: 0 = by shape, 1 = mma.sync kernel only
+bool decode_uses_tc(const rk_decode_args& a);                // true when the tcgen05 decode kernel serves this call
+int decode_ctas_per_sm(const rk_decode_args& a);             // resident CTAs per SM of the kernel that serves it
 
 }  // namespace rk

@@ -66,3 +66,87 @@ def test_lse_and_large_v_scale():
 def test_full_length_one_sequence():
     """KV length 32768 (the benchmark's per-sequence length) for one sequence, all 8 KV heads."""
     run(1, 32, 8, 32768, seed=9)
+
+
+def _quantized_cache(B, Hkv, L, seed, kmul=1.0, vscale_spread=0):
+    d = 128
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    K = torch.randn(B, Hkv, L, d, generator=g, device="cuda") * kmul
+    V = torch.randn(B, Hkv, L, d, generator=g, device="cuda")
+    if vscale_spread:       # per-key magnitudes spread over 2^+-spread: block scales differ widely inside a 32-key block
+        e = torch.randint(-vscale_spread, vscale_spread + 1, (B, Hkv, L, 1), generator=g, device="cuda").float()
+        V = V * torch.exp2(e)
+    kc, ks = rk.mx_quantize(K)
+    vc, vs = rk.mx_quantize(V)
+    return kc, ks, vc, vs
+
+
+def _check(q, kc, ks, vc, vs, lens=None, num_splits=0):
+    d = 128
+    kl = None if lens is None else torch.tensor(lens, dtype=torch.int32, device="cuda")
+    ref = oracle.attn_decode(np_(q.view(torch.uint16)), np_(kc), np_(vc), np_(ks), np_(vs), softmax_scale=d ** -0.5,
+                             kv_len=None if lens is None else np.array(lens, np.int32))
+    outs = []
+    for path in (1, 0):                       # 1 = the mma.sync kernel, 0 = chosen by shape (tcgen05 for these shapes)
+        rk.lib().rk_debug_set_decode_path(path)
+        try:
+            o = rk.attn_decode(q, kc, vc, ks, vs, kv_len=kl, num_splits=num_splits)
+            torch.cuda.synchronize()
+        finally:
+            rk.lib().rk_debug_set_decode_path(0)
+        assert rk.last_device_status() == 0
+        got = np_(o.float())
+        assert np.isfinite(got).all(), f"path {path}: non-finite output"
+        ma, rl = errors(got, ref["o_f32"])
+        # the absolute bound is stated for outputs of order one; scale it with the reference's magnitude
+        assert ma <= MAX_ABS * max(1.0, float(np.abs(ref["o_f32"]).max())) and rl <= REL_L2, (path, ma, rl)
+        outs.append(got)
+    return outs, ref
+
+
+def test_both_decode_kernels_match_the_oracle():
+    g = torch.Generator(device="cuda").manual_seed(21)
+    q = torch.randn(2, 8, 128, generator=g, device="cuda").bfloat16()
+    kc, ks, vc, vs = _quantized_cache(2, 2, 2048, seed=22)
+    (legacy, tc), ref = _check(q, kc, ks, vc, vs)
+    assert np.abs(legacy - tc).max() < 4e-3
+
+
+def test_tc_decode_peaked_rows_and_growing_maxima():
+    """Large logits: a few keys dominate, the running maximum keeps growing along the sequence (keys scaled up
+    towards the end), so O is rescaled several times and most p are far below the block maximum."""
+    g = torch.Generator(device="cuda").manual_seed(23)
+    q = (torch.randn(1, 4, 128, generator=g, device="cuda") * 4.0).bfloat16()
+    kc, ks, vc, vs = _quantized_cache(1, 1, 4096, seed=24)
+    K = torch.randn(1, 1, 4096, 128, generator=g, device="cuda") * torch.linspace(0.2, 3.0, 4096, device="cuda").view(1, 1, -1, 1)
+    kc, ks = rk.mx_quantize(K)
+    _check(q, kc, ks, vc, vs, num_splits=1)
+    _check(q, kc, ks, vc, vs, num_splits=4)
+
+
+def test_tc_decode_v_scales_spread_inside_a_block():
+    g = torch.Generator(device="cuda").manual_seed(25)
+    q = torch.randn(1, 8, 128, generator=g, device="cuda").bfloat16()
+    kc, ks, vc, vs = _quantized_cache(1, 2, 1024, seed=26, vscale_spread=12)
+    _check(q, kc, ks, vc, vs)
+
+
+def test_decode_ignores_poisoned_cache_past_kv_len():
+    """Keys at and beyond kv_len hold NaN codes and NaN scales (0x7F / 0xFF): they must not reach the result."""
+    g = torch.Generator(device="cuda").manual_seed(27)
+    q = torch.randn(2, 8, 128, generator=g, device="cuda").bfloat16()
+    kc, ks, vc, vs = _quantized_cache(2, 2, 1024, seed=28)
+    lens = [700, 130]
+    clean = [t.clone() for t in (kc, ks, vc, vs)]
+    for b, n in enumerate(lens):
+        kc[b, :, n:] = 0x7F; vc[b, :, n:] = 0x7F; ks[b, :, n:] = 0xFF; vs[b, :, n:] = 0xFF
+    kl = torch.tensor(lens, dtype=torch.int32, device="cuda")
+    ref = oracle.attn_decode(np_(q.view(torch.uint16)), np_(clean[0]), np_(clean[2]), np_(clean[1]), np_(clean[3]),
+                             softmax_scale=128 ** -0.5, kv_len=np.array(lens, np.int32))
+    o = rk.attn_decode(q, kc, vc, ks, vs, kv_len=kl)
+    torch.cuda.synchronize()
+    assert rk.last_device_status() == 0
+    got = np_(o.float())
+    assert np.isfinite(got).all()
+    ma, rl = errors(got, ref["o_f32"])
+    assert ma <= MAX_ABS and rl <= REL_L2, (ma, rl)
