@@ -391,7 +391,7 @@ bool decode_uses_tc(const rk_decode_args& a) {
   if (g_decode_path == 1) return false;
   return can;
 }
-int decode_ctas_per_sm(const rk_decode_args& a) { return decode_uses_tc(a) ? 1 : 2; }
+int decode_ctas_per_sm(const rk_decode_args& a) { return decode_uses_tc(a) ? dtc::kCtasPerSm : 2; }
 
 int launch_decode(const rk_decode_args& a, int nsplit, cudaStream_t st) {
   CUtensorMap tk, tv;

@@ -41,7 +41,11 @@ constexpr int kWorkers = 4;                       // worker warps
 constexpr int kThreads = (kWorkers + 2) * 32;     // + TMA warp + MMA warp
 constexpr int kTile = 128;                        // keys per stage
 constexpr int kD = 128;
-constexpr int kStages = 6;
+#ifndef RK_X_DTC_STAGES
+#define RK_X_DTC_STAGES 3
+#endif
+constexpr int kStages = RK_X_DTC_STAGES;
+constexpr int kCtasPerSm = kStages <= 3 ? 2 : 1;
 constexpr int kMaxGrp = 4;                        // query heads per KV head handled by this kernel
 constexpr int kNq = 16;                           // B rows of the QK^T MMA: (term, head) = term * 4 + h, rows 8..15 zero
 constexpr int kNp = 32;                           // B rows of the PV MMA: term * 16 + h * 4 + g
@@ -56,8 +60,8 @@ constexpr int q_off = p_off + 2 * 4096;           // [16 rows][128 B], K-major S
 constexpr int sfp_off = q_off + 2048;             // 2 x 512-byte scale atoms for P
 constexpr int sfq_off = sfp_off + 2 * 512;        // scale atom of the query terms
 constexpr int one_off = sfq_off + 512;            // scale atom of ones (code 127) for V
-constexpr int xchg_off = one_off + 512;           // [2][4 warps][4 heads] floats (tile maxima), then [4][128] l partials
-constexpr int bar_off = xchg_off + 2 * 16 * 4 + 4 * 128 * 4;
+constexpr int xchg_off = one_off + 512;           // [2][4 warps][4 heads] floats (tile maxima)
+constexpr int bar_off = xchg_off + 2 * 16 * 4;
 enum { bFull = 0, bEmpty = bFull + kStages, bSF = bEmpty + kStages, bSE = bSF + 2, bPF = bSE + 2, bPV = bPF + 2,
        bMX = bPV + 2, bDrain = bMX + 2, nBars = bDrain + 1 };
 constexpr int misc_off = bar_off + nBars * 8;     // tmem base, abort flag
@@ -121,7 +125,7 @@ RK_DEVINL float pow2i(int e) {
   return __uint_as_float(f <= 0 ? 0u : ((uint32_t)(f > 254 ? 254 : f) << 23));
 }
 
-__global__ void __launch_bounds__(dtc::kThreads, 1)
+__global__ void __launch_bounds__(dtc::kThreads, dtc::kCtasPerSm)
 decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
                  const DecodeTcParams p, const uint32_t idesc_qk, const uint32_t idesc_pv) {
   using namespace dtc;
@@ -447,7 +451,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_consta
         }
       }
     }
-    float* lsum = xchg + 32;                                        // [4 heads][128 threads]
+    float* lsum = reinterpret_cast<float*>(smem + p_off);           // [4 heads][128 threads]: the P tiles are free now
 #pragma unroll
     for (int h = 0; h < 4; ++h) lsum[h * 128 + kt] = l_part[h];
     asm volatile("bar.sync 1, 128;" ::: "memory");                  // workers only; every worker reaches this point
