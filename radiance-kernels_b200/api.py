@@ -112,14 +112,15 @@ class PrefillHostRunner:
     pinned host memory, the device arena is allocated once and reused."""
 
     def __init__(self, q, k, v, q_scale, k_scale, v_scale, *, causal, softmax_scale=0.0, q_pos0=0, window=0,
-                 softcap=0.0, q_fmt=E4M3, kv_fmt=E4M3, v_scale_axis=V_SCALES_ALONG_D, device="cuda"):
+                 softcap=0.0, q_fmt=E4M3, kv_fmt=E4M3, v_scale_axis=V_SCALES_ALONG_D, want_lse=False, device="cuda"):
         for t in (q, k, v, q_scale, k_scale, v_scale):
             if t.is_cuda or not t.is_contiguous():
                 raise ValueError("host runner takes contiguous CPU tensors (pinned for full copy speed)")
         self.keep = (q, k, v, q_scale, k_scale, v_scale)
         B, H, S_q, d = q.shape
         self.o = torch.empty((B, H, S_q, d), dtype=torch.bfloat16).pin_memory()
-        self.args = _prefill_args(q, k, v, q_scale, k_scale, v_scale, self.o, None, causal, softmax_scale, q_pos0,
+        self.lse = torch.empty((B, H, S_q), dtype=torch.float32).pin_memory() if want_lse else None
+        self.args = _prefill_args(q, k, v, q_scale, k_scale, v_scale, self.o, self.lse, causal, softmax_scale, q_pos0,
                                   window, softcap, q_fmt, kv_fmt, v_scale_axis)
         need = lib().rk_attn_prefill_host_arena_bytes(C.byref(self.args))
         self.arena = torch.empty(need + 1024, dtype=torch.uint8, device=device)

@@ -3,6 +3,7 @@
 // include/rk_mx_attn.h for the contract of every function.
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <mutex>
 
 #include "rk_internal.h"
@@ -181,6 +182,36 @@ size_t rk_attn_prefill_host_arena_bytes(const rk_prefill_args* a) {
   return off + prefill_ws(*a).total;
 }
 
+// Copy streams and events of the host-buffer entry point, one set per device, made on first use.
+namespace {
+constexpr int kHostMaxChunks = 16;
+struct HostPipe {
+  bool ready = false;
+  cudaStream_t h2d = nullptr, d2h = nullptr;
+  cudaEvent_t start = nullptr, end = nullptr, in[kHostMaxChunks] = {}, out[kHostMaxChunks] = {};
+};
+HostPipe g_host_pipe[64];
+std::mutex g_host_pipe_mu;
+
+int host_pipe_init(HostPipe& hp) {
+  if (hp.ready) return RK_OK;
+  cudaError_t e;
+  if ((e = cudaStreamCreateWithFlags(&hp.h2d, cudaStreamNonBlocking)) != cudaSuccess) return (int)e;
+  if ((e = cudaStreamCreateWithFlags(&hp.d2h, cudaStreamNonBlocking)) != cudaSuccess) return (int)e;
+  if ((e = cudaEventCreateWithFlags(&hp.start, cudaEventDisableTiming)) != cudaSuccess) return (int)e;
+  if ((e = cudaEventCreateWithFlags(&hp.end, cudaEventDisableTiming)) != cudaSuccess) return (int)e;
+  for (int i = 0; i < kHostMaxChunks; ++i) {
+    if ((e = cudaEventCreateWithFlags(&hp.in[i], cudaEventDisableTiming)) != cudaSuccess) return (int)e;
+    if ((e = cudaEventCreateWithFlags(&hp.out[i], cudaEventDisableTiming)) != cudaSuccess) return (int)e;
+  }
+  hp.ready = true;
+  return RK_OK;
+}
+}  // namespace
+
+// Host buffers in, host buffer out.  The (batch, KV head) units are independent, so the call is cut into up to
+// 16 chunks of whole units and pipelined: chunk c+1 crosses PCIe on a copy stream while chunk c is computed on
+// the caller's stream and the output of chunk c-1 goes back on a second copy stream.
 int rk_attn_prefill_host(const rk_prefill_args* h, void* arena, size_t arena_bytes, void* stream) {
   int rc = check_prefill_shape(h);
   if (rc != RK_OK) return rc;
@@ -190,25 +221,71 @@ int rk_attn_prefill_host(const rk_prefill_args* h, void* arena, size_t arena_byt
   const size_t nbd = h->d / 32;
   const size_t q = (size_t)h->B * h->H * h->S_q * h->d, kv = (size_t)h->B * h->H_kv * h->S_kv * h->d;
   const size_t qs = q / h->d * nbd, ks = kv / h->d * nbd;
-  const size_t vs = h->v_scale_axis == RK_V_SCALES_ALONG_D ? ks : (size_t)h->B * h->H_kv * ((h->S_kv + 31) / 32) * h->d;
+  const bool v_along_d = h->v_scale_axis == RK_V_SCALES_ALONG_D;
+  const size_t vs_head = v_along_d ? (size_t)h->S_kv * nbd : (size_t)((h->S_kv + 31) / 32) * h->d;   // V scale bytes per KV head
+  const size_t vs = (size_t)h->B * h->H_kv * vs_head;
   uint8_t* base = reinterpret_cast<uint8_t*>(arena);
   size_t off = 0;
-  rk_prefill_args d = *h;
   auto take = [&](size_t bytes) { uint8_t* p = base + off; off = align_up(off + bytes, 1024); return p; };
   uint8_t* dq = take(q); uint8_t* dk = take(kv); uint8_t* dv = take(kv);
   uint8_t* dqs = take(qs); uint8_t* dks = take(ks); uint8_t* dvs = take(vs);
   uint8_t* dout = take(q * 2); uint8_t* dlse = take(q / h->d * 4);
+  uint8_t* ws = base + off;
+  const size_t ws_bytes = arena_bytes - off;
+
+  int dev = 0;
   cudaError_t e;
-#define RK_CP(dst, src, n) if ((e = cudaMemcpyAsync(dst, src, n, cudaMemcpyHostToDevice, st)) != cudaSuccess) return (int)e
-  RK_CP(dq, h->q, q); RK_CP(dk, h->k, kv); RK_CP(dv, h->v, kv);
-  RK_CP(dqs, h->q_scale, qs); RK_CP(dks, h->k_scale, ks); RK_CP(dvs, h->v_scale, vs);
+  if ((e = cudaGetDevice(&dev)) != cudaSuccess) return (int)e;
+  std::lock_guard<std::mutex> lk(g_host_pipe_mu);      // one pipelined call per process at a time: the streams are shared
+  HostPipe& hp = g_host_pipe[dev & 63];
+  if ((rc = host_pipe_init(hp)) != RK_OK) return rc;
+
+  // chunks: whole batches when there are many, ranges of KV heads inside a batch when there are few
+  const int grp = h->H / h->H_kv;
+  const int batches_per_chunk = h->B >= 8 ? (h->B + 7) / 8 : 1;
+  const int chunks_per_batch = h->B >= 8 ? 1 : std::max(1, std::min(h->H_kv, 8 / h->B));
+  const int kv_per_chunk = (h->H_kv + chunks_per_batch - 1) / chunks_per_batch;
+
+  if ((e = cudaEventRecord(hp.start, st)) != cudaSuccess) return (int)e;
+  if ((e = cudaStreamWaitEvent(hp.h2d, hp.start, 0)) != cudaSuccess) return (int)e;
+  if ((e = cudaStreamWaitEvent(hp.d2h, hp.start, 0)) != cudaSuccess) return (int)e;
+  int c = 0;
+  for (int b0 = 0; b0 < h->B; b0 += batches_per_chunk) {
+    const int nb = std::min(batches_per_chunk, h->B - b0);
+    for (int kv0 = 0; kv0 < h->H_kv; kv0 += kv_per_chunk, ++c) {
+      const int nkv = std::min(kv_per_chunk, h->H_kv - kv0);
+      // first (batch, head) of the chunk; a chunk of several batches always spans all heads (kv0 = 0)
+      const size_t qh = (size_t)b0 * h->H + (size_t)kv0 * grp, kh = (size_t)b0 * h->H_kv + kv0;
+      const size_t nqh = (size_t)nb * nkv * grp, nkh = (size_t)nb * nkv;
+      const size_t q_row = (size_t)h->S_q * h->d, k_row = (size_t)h->S_kv * h->d;
+#define RK_CP(dst, src, o, n) if ((e = cudaMemcpyAsync((dst) + (o), reinterpret_cast<const uint8_t*>(src) + (o), n, cudaMemcpyHostToDevice, hp.h2d)) != cudaSuccess) return (int)e
+      RK_CP(dq, h->q, qh * q_row, nqh * q_row);
+      RK_CP(dk, h->k, kh * k_row, nkh * k_row);
+      RK_CP(dv, h->v, kh * k_row, nkh * k_row);
+      RK_CP(dqs, h->q_scale, qh * q_row / 32, nqh * q_row / 32);
+      RK_CP(dks, h->k_scale, kh * k_row / 32, nkh * k_row / 32);
+      RK_CP(dvs, h->v_scale, kh * vs_head, nkh * vs_head);
 #undef RK_CP
-  d.q = dq; d.k = dk; d.v = dv; d.q_scale = dqs; d.k_scale = dks; d.v_scale = dvs;
-  d.o = dout; d.lse = h->lse ? reinterpret_cast<float*>(dlse) : nullptr;
-  d.workspace = base + off; d.workspace_bytes = arena_bytes - off;
-  if ((rc = rk_attn_prefill(&d, stream)) != RK_OK) return rc;
-  if ((e = cudaMemcpyAsync(h->o, dout, q * 2, cudaMemcpyDeviceToHost, st)) != cudaSuccess) return (int)e;
-  if (h->lse && (e = cudaMemcpyAsync(h->lse, dlse, q / h->d * 4, cudaMemcpyDeviceToHost, st)) != cudaSuccess) return (int)e;
+      if ((e = cudaEventRecord(hp.in[c], hp.h2d)) != cudaSuccess) return (int)e;
+      if ((e = cudaStreamWaitEvent(st, hp.in[c], 0)) != cudaSuccess) return (int)e;
+      rk_prefill_args d = *h;
+      d.B = nb; d.H = nkv * grp; d.H_kv = nkv;
+      d.q = dq + qh * q_row; d.k = dk + kh * k_row; d.v = dv + kh * k_row;
+      d.q_scale = dqs + qh * q_row / 32; d.k_scale = dks + kh * k_row / 32; d.v_scale = dvs + kh * vs_head;
+      d.o = dout + qh * q_row * 2;
+      d.lse = h->lse ? reinterpret_cast<float*>(dlse) + qh * h->S_q : nullptr;
+      d.workspace = ws; d.workspace_bytes = ws_bytes;       // chunks run one after the other on `st`: one workspace serves all
+      if ((rc = rk_attn_prefill(&d, stream)) != RK_OK) return rc;
+      if ((e = cudaEventRecord(hp.out[c], st)) != cudaSuccess) return (int)e;
+      if ((e = cudaStreamWaitEvent(hp.d2h, hp.out[c], 0)) != cudaSuccess) return (int)e;
+      if ((e = cudaMemcpyAsync(reinterpret_cast<uint8_t*>(h->o) + qh * q_row * 2, dout + qh * q_row * 2, nqh * q_row * 2,
+                               cudaMemcpyDeviceToHost, hp.d2h)) != cudaSuccess) return (int)e;
+      if (h->lse && (e = cudaMemcpyAsync(h->lse + qh * h->S_q, reinterpret_cast<float*>(dlse) + qh * h->S_q,
+                                         nqh * h->S_q * 4, cudaMemcpyDeviceToHost, hp.d2h)) != cudaSuccess) return (int)e;
+    }
+  }
+  if ((e = cudaEventRecord(hp.end, hp.d2h)) != cudaSuccess) return (int)e;
+  if ((e = cudaStreamWaitEvent(st, hp.end, 0)) != cudaSuccess) return (int)e;
   return (int)cudaStreamSynchronize(st);
 }
 

@@ -120,6 +120,25 @@ def test_host_buffer_entry_point_matches_device_one():
     assert torch.equal(dev.cpu(), host)
 
 
+@pytest.mark.parametrize("B,H,Hkv,S,axis", [(3, 6, 3, 256, 1), (10, 2, 2, 128, 0), (2, 8, 8, 160, 1), (9, 4, 1, 128, 1)])
+def test_host_entry_point_chunking(B, H, Hkv, S, axis):
+    """The host entry point cuts the call into chunks of whole (batch, KV head) units (ranges of KV heads when
+    the batch is small, groups of batches when it is large): every chunking gives the device call's bits, for O
+    and for the log-sum-exp, with either V scale layout and a ragged sequence length."""
+    Q, K, V = randn_qkv(B, H, Hkv, S, S, 128, seed=40 + B)
+    qc, qs = rk.mx_quantize(Q); kc, ks = rk.mx_quantize(K)
+    vc, vs = rk.mx_quantize(V) if axis == 1 else rk.mx_quantize_keys(V)
+    lse = torch.empty(B, H, S, dtype=torch.float32, device="cuda")
+    dev = rk.attn_prefill(qc, kc, vc, qs, ks, vs, causal=True, v_scale_axis=axis, lse=lse)
+    runner = rk.PrefillHostRunner(*[t.cpu().pin_memory() for t in (qc, kc, vc, qs, ks, vs)], causal=True,
+                                  v_scale_axis=axis, want_lse=True)
+    for _ in range(2):                      # twice: the shared copy streams and events are reused
+        host = runner.run()
+        assert torch.equal(dev.cpu(), host)
+        assert torch.equal(lse.cpu(), runner.lse)
+    assert rk.last_device_status() == 0
+
+
 def test_full_size_head_slices_match_oracle():
     """B=8 H=16 S=4096 d=128 causal (the benchmark workload): the whole tensor runs on the GPU, two
     (batch, head) slices are checked against the oracle, and every row is checked for the size-independent
