@@ -170,6 +170,17 @@ RK_API int rk_attn_decode_num_splits(const rk_decode_args* a);
 RK_API size_t rk_attn_decode_workspace_bytes(const rk_decode_args* a);
 RK_API int rk_attn_decode(const rk_decode_args* a, void* stream);
 
+/* Append one token to an MXFP8 / MXFP6 KV cache so that decode can run in a loop: for every batch b and KV
+ * head, the new K row and the new V row (fp32 [B][H_kv][d], device memory) are quantized in blocks of 32
+ * along d with the rule of rk_mx_quantize and stored as row pos[b] of the cache (codes [B][H_kv][L][d],
+ * scales [B][H_kv][L][d/32]; pos is a device array of B int32).  A position outside [0, L) leaves that
+ * sequence untouched.  The reference has no KV cache (its attention kernels read link-time arrays,
+ * kernels/flash_attention_mx_gemma/fa_gen_data.py:148-192); the quantization is that of
+ * kernels/simt_quant/kernel.cpp:95-129 applied to one row. */
+RK_API int rk_kv_cache_append(const float* k_new, const float* v_new, int32_t B, int32_t H_kv, int32_t L, int32_t d,
+                              const int32_t* pos, int32_t fmt, uint8_t* k_codes, uint8_t* k_scales,
+                              uint8_t* v_codes, uint8_t* v_scales, void* stream);
+
 /* Decode for callers that cannot allocate device memory at the call site -- a plugin running inside a
  * memory pool it does not own, a serving loop whose allocator is locked while a step is in flight, a
  * host that must leave a caching allocator's bookkeeping untouched.  It has no counterpart in the

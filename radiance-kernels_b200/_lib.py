@@ -52,6 +52,8 @@ SYMBOLS = {
     "rk_attn_decode_workspace_bytes": (C.c_size_t, [C.POINTER(DecodeArgs)]),
     "rk_attn_decode": (C.c_int, [C.POINTER(DecodeArgs), C.c_void_p]),
     "rk_attn_decode_noalloc": (C.c_int, [C.POINTER(DecodeArgs), C.c_void_p]),
+    "rk_kv_cache_append": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_int32,
+                                     C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "rk_profile_set_events": (None, [C.c_void_p, C.c_void_p]),
     "rk_last_device_status": (C.c_int, []),
 }
@@ -81,6 +83,8 @@ def lib():
         L.rk_debug_verify_encoder.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]
         L.rk_debug_set_prefill_dump.restype = None
         L.rk_debug_set_prefill_dump.argtypes = [C.c_void_p]
+        L.rk_debug_set_decode_path.restype = None
+        L.rk_debug_set_decode_path.argtypes = [C.c_int]
         _LIB = L
     return _LIB
 

@@ -148,6 +148,17 @@ def _decode_args(q, k, v, k_scale, v_scale, kv_len, o, lse, softmax_scale, kv_fm
     return a
 
 
+def kv_cache_append(k_new, v_new, pos, k_codes, k_scales, v_codes, v_scales, fmt=E4M3):
+    """Quantize one new K row and V row per (batch, KV head) (fp32 [B,H_kv,d]) into row pos[b] of the cache
+    (codes [B,H_kv,L,d], scales [B,H_kv,L,d/32]); pos is an int32 CUDA tensor [B]."""
+    _need_cuda(k_new, v_new, pos, k_codes, k_scales, v_codes, v_scales)
+    if k_new.dtype != torch.float32 or v_new.dtype != torch.float32 or pos.dtype != torch.int32:
+        raise ValueError("kv_cache_append takes float32 rows and int32 positions")
+    B, H_kv, L, d = k_codes.shape
+    check(lib().rk_kv_cache_append(_ptr(k_new), _ptr(v_new), B, H_kv, L, d, _ptr(pos), fmt, _ptr(k_codes), _ptr(k_scales),
+                                   _ptr(v_codes), _ptr(v_scales), _stream()), "rk_kv_cache_append")
+
+
 def attn_decode_num_splits(B, H, H_kv, L, d=128, num_splits=0):
     a = DecodeArgs()
     a.B, a.H, a.H_kv, a.L, a.d, a.num_splits = B, H, H_kv, L, d, num_splits

@@ -303,6 +303,16 @@ static int check_decode_shape(const rk_decode_args* a) {
   return RK_OK;
 }
 
+int rk_kv_cache_append(const float* k_new, const float* v_new, int32_t B, int32_t H_kv, int32_t L, int32_t d,
+                       const int32_t* pos, int32_t fmt, uint8_t* k_codes, uint8_t* k_scales, uint8_t* v_codes,
+                       uint8_t* v_scales, void* stream) {
+  if (!k_new || !v_new || !pos || !k_codes || !k_scales || !v_codes || !v_scales) return RK_ERR_NULL_POINTER;
+  if (B < 0 || H_kv < 0 || L <= 0 || d <= 0 || d % 32 != 0) return RK_ERR_BAD_SHAPE;
+  if (fmt < 0 || fmt > 3) return RK_ERR_UNSUPPORTED;
+  if (!aligned(k_new, 16) || !aligned(v_new, 16) || !aligned(k_codes, 8) || !aligned(v_codes, 8)) return RK_ERR_MISALIGNED;
+  return launch_kv_append(k_new, v_new, B, H_kv, L, d, pos, fmt, k_codes, k_scales, v_codes, v_scales, (cudaStream_t)stream);
+}
+
 int rk_attn_decode_num_splits(const rk_decode_args* a) {
   if (check_decode_shape(a) != RK_OK) return 0;
   const int tiles = (a->L + 127) / 128;

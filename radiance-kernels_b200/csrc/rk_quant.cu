@@ -100,6 +100,52 @@ __global__ void __launch_bounds__(256) quantize_rows_kernel(const float4* __rest
   }
 }
 
+// Append one token to a KV cache: row pos[b] of every (batch, KV head) of K and of V is quantized (blocks of 32
+// along d, same rule and same code path as quantize_rows_kernel) and written in place.  chunk = 8 consecutive
+// elements of one new row; 4 consecutive lanes = one block.  A position outside [0, L) is skipped.
+template <int FMT>
+__global__ void __launch_bounds__(128) kv_append_kernel(const float* __restrict__ k_new, const float* __restrict__ v_new,
+                                                        int B, int H_kv, int L, int d, const int32_t* __restrict__ pos,
+                                                        uint8_t* __restrict__ k_codes, uint8_t* __restrict__ k_scales,
+                                                        uint8_t* __restrict__ v_codes, uint8_t* __restrict__ v_scales) {
+  const int cpr = d / 8;                                     // chunks per row (a multiple of 4)
+  const int64_t rows = (int64_t)B * H_kv, nchunks = 2 * rows * cpr;
+  const int lane = threadIdx.x & 31;
+  for (int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; c - lane < nchunks; c += (int64_t)gridDim.x * blockDim.x) {
+    const bool live = c < nchunks;
+    const int64_t cc = live ? c : 0;
+    const int which = (int)(cc / (rows * cpr));              // 0 = K, 1 = V
+    const int64_t row = (cc / cpr) % rows;
+    const int col = (int)(cc % cpr) * 8;
+    const float* src = (which ? v_new : k_new) + row * d + col;
+    float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b4 = a;
+    if (live) { a = *reinterpret_cast<const float4*>(src); b4 = *reinterpret_cast<const float4*>(src + 4); }
+    const float v[8] = {a.x, a.y, a.z, a.w, b4.x, b4.y, b4.z, b4.w};
+    float amax = 0.0f, nonfinite = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 8; j++) { amax = fmaxf(amax, fabsf(v[j])); nonfinite = fmaf(v[j], 0.0f, nonfinite); }
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    if (!live) continue;
+    const int bidx = (int)(row / H_kv);
+    const int at = pos[bidx];
+    if (at < 0 || at >= L) continue;
+    uint32_t scode = 0; float p2 = 1.0f;
+    if (amax > 0.0f) block_scale<FMT>(amax, scode, p2);
+    uint32_t w0, w1;
+    if (nonfinite == 0.0f) {
+      w0 = hw_encode4<FMT>(v[0] * p2, v[1] * p2, v[2] * p2, v[3] * p2);
+      w1 = hw_encode4<FMT>(v[4] * p2, v[5] * p2, v[6] * p2, v[7] * p2);
+    } else {
+      w0 = ref_encode4<FMT>(v[0] * p2, v[1] * p2, v[2] * p2, v[3] * p2);
+      w1 = ref_encode4<FMT>(v[4] * p2, v[5] * p2, v[6] * p2, v[7] * p2);
+    }
+    const int64_t crow = row * L + at;                        // row of the cache
+    *reinterpret_cast<uint2*>((which ? v_codes : k_codes) + crow * d + col) = make_uint2(w0, w1);
+    if ((col & 31) == 0) (which ? v_scales : k_scales)[crow * (d / 32) + col / 32] = (uint8_t)scode;
+  }
+}
+
 // One thread = 4 adjacent columns x one 32-row block.
 template <int FMT>
 __global__ void __launch_bounds__(128) quantize_keys_kernel(const float* __restrict__ x, int64_t batch, int64_t rows,
@@ -496,6 +542,15 @@ int launch_quantize_keys(const float* x, int64_t batch, int64_t rows, int64_t co
   if (total == 0) return RK_OK;
   const int grid = grid_for(total, 128, 16);
   RK_DISPATCH_FMT(fmt, (quantize_keys_kernel<F><<<grid, 128, 0, st>>>(x, batch, rows, cols, codes, scales)));
+  return (int)cudaGetLastError();
+}
+
+int launch_kv_append(const float* k_new, const float* v_new, int B, int H_kv, int L, int d, const int32_t* pos, int fmt,
+                     uint8_t* k_codes, uint8_t* k_scales, uint8_t* v_codes, uint8_t* v_scales, cudaStream_t st) {
+  const int64_t total = 2LL * B * H_kv * (d / 8);
+  if (total == 0) return RK_OK;
+  const int grid = grid_for(total, 128, 8);
+  RK_DISPATCH_FMT(fmt, (kv_append_kernel<F><<<grid, 128, 0, st>>>(k_new, v_new, B, H_kv, L, d, pos, k_codes, k_scales, v_codes, v_scales)));
   return (int)cudaGetLastError();
 }
 
