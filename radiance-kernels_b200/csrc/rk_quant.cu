@@ -493,21 +493,36 @@ __global__ void pack6_rows_kernel(const uint8_t* __restrict__ in, int64_t rows, 
   }
 }
 
-// byte codes [batch][S][d] -> packed transposed [batch][d][Sp * 3/4 bytes], Sp = S rounded up to 128
-__global__ void pack6_transpose_kernel(const uint8_t* __restrict__ in, int64_t batch, int64_t S, int64_t d, int64_t Sp,
-                                       uint8_t* __restrict__ out) {
-  const int64_t groups = Sp / 16, total = batch * groups * d;      // consecutive threads = consecutive d (coalesced reads)
-  for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t col = t % d, gidx = (t / d) % groups, bt = t / (d * groups);
-    uint32_t c[16], w[3];
-#pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      const int64_t key = gidx * 16 + i;
-      c[i] = key < S ? in[(bt * S + key) * d + col] : 0u;
+// byte codes [batch][S][d] -> packed transposed [batch][d][Sp * 3/4 bytes], Sp = S rounded up to 128.
+// One CTA = one tile of 128 keys x 128 columns through shared memory: coalesced 16-byte reads along d, then each
+// thread packs 16 keys of one column and the 8 threads of a column write 96 contiguous bytes.
+__global__ void __launch_bounds__(256) pack6_transpose_kernel(const uint8_t* __restrict__ in, int64_t batch, int64_t S, int64_t d,
+                                                              int64_t Sp, uint8_t* __restrict__ out) {
+  __shared__ uint8_t tile[128][128 + 4];                       // [key][col], rows padded by one word against bank conflicts
+  const int64_t ktiles = Sp / 128, ctiles = (d + 127) / 128;
+  const int64_t ntiles = batch * ktiles * ctiles;
+  for (int64_t tix = blockIdx.x; tix < ntiles; tix += gridDim.x) {
+    const int64_t ct = tix % ctiles, kt = (tix / ctiles) % ktiles, bt = tix / (ctiles * ktiles);
+    const int64_t key0 = kt * 128, col0 = ct * 128;
+    __syncthreads();                                           // the previous tile has been read out
+    for (int i = threadIdx.x; i < 128 * 8; i += 256) {         // 128 rows x 8 chunks of 16 columns
+      const int r = i >> 3, ch = i & 7;
+      uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      if (key0 + r < S && col0 + ch * 16 < d) v = *reinterpret_cast<const uint4*>(in + (bt * S + key0 + r) * d + col0 + ch * 16);
+      uint32_t* dst = reinterpret_cast<uint32_t*>(&tile[r][ch * 16]);
+      dst[0] = v.x; dst[1] = v.y; dst[2] = v.z; dst[3] = v.w;
     }
-    pack16x6(c, w);
-    uint32_t* o = reinterpret_cast<uint32_t*>(out + (bt * d + col) * (Sp * 3 / 4) + gidx * 12);
-    o[0] = w[0]; o[1] = w[1]; o[2] = w[2];
+    __syncthreads();
+    for (int i = threadIdx.x; i < 128 * 8; i += 256) {         // 128 columns x 8 groups of 16 keys
+      const int col = i >> 3, gi = i & 7;
+      if (col0 + col >= d) continue;
+      uint32_t c[16], w[3];
+#pragma unroll
+      for (int k = 0; k < 16; ++k) c[k] = tile[gi * 16 + k][col];
+      pack16x6(c, w);
+      uint32_t* o = reinterpret_cast<uint32_t*>(out + (bt * d + col0 + col) * (Sp * 3 / 4) + (kt * 8 + gi) * 12);
+      o[0] = w[0]; o[1] = w[1]; o[2] = w[2];
+    }
   }
 }
 
@@ -586,9 +601,9 @@ int launch_pack6_rows(const uint8_t* in, int64_t rows, int64_t d, uint8_t* out, 
 }
 
 int launch_pack6_transpose(const uint8_t* in, int64_t batch, int64_t S, int64_t d, uint8_t* out, cudaStream_t st) {
-  const int64_t Sp = (S + 127) / 128 * 128, total = batch * (Sp / 16) * d;
-  if (total == 0) return RK_OK;
-  pack6_transpose_kernel<<<grid_for(total, 256, 8), 256, 0, st>>>(in, batch, S, d, Sp, out);
+  const int64_t Sp = (S + 127) / 128 * 128, tiles = batch * (Sp / 128) * ((d + 127) / 128);
+  if (tiles == 0) return RK_OK;
+  pack6_transpose_kernel<<<(int)min(tiles, (int64_t)num_sms() * 8), 256, 0, st>>>(in, batch, S, d, Sp, out);
   return (int)cudaGetLastError();
 }
 
