@@ -170,6 +170,17 @@ RK_API int rk_attn_decode_num_splits(const rk_decode_args* a);
 RK_API size_t rk_attn_decode_workspace_bytes(const rk_decode_args* a);
 RK_API int rk_attn_decode(const rk_decode_args* a, void* stream);
 
+/* RoPE fused with the block quantizer: the producer step right before attention, without the fp32 round trip of
+ * the rotated tensor through HBM.  x is fp32 [rows][d] (rows = any flattening of batch, head, token; d a
+ * multiple of 64); row r is rotated with row pos[r] of the half-width caches cos_half / sin_half [n_pos][d/2]
+ * (pos a device array, entries in [0, n_pos)), or with row pos0 + r % seq_len when pos is NULL (the layout
+ * [batch][head][seq_len][d]).  Rotation is the rotate-half form of lib/golden/golden.py:229-236 (rope_apply, the
+ * golden of kernels/rope_qkv_fused), every product and sum rounded to fp32 on its own; quantization as
+ * rk_mx_quantize.  Outputs: codes [rows][d], scales [rows][d/32]. */
+RK_API int rk_rope_mx_quantize(const float* x, int64_t rows, int32_t d, const int32_t* pos, int32_t seq_len, int32_t pos0,
+                               const float* cos_half, const float* sin_half, int32_t n_pos, int32_t fmt,
+                               uint8_t* codes, uint8_t* scales, void* stream);
+
 /* Append one token to an MXFP8 / MXFP6 KV cache so that decode can run in a loop: for every batch b and KV
  * head, the new K row and the new V row (fp32 [B][H_kv][d], device memory) are quantized in blocks of 32
  * along d with the rule of rk_mx_quantize and stored as row pos[b] of the cache (codes [B][H_kv][L][d],

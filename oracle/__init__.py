@@ -77,6 +77,8 @@ def lib():
         for n in ("rko_dequant_rows", "rko_dequant_cols"):
             getattr(L, n).restype = None
             getattr(L, n).argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int, C.c_void_p]
+        L.rko_rope_rows.restype = None
+        L.rko_rope_rows.argtypes = [C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
         L.rko_rebase_v.restype = None
         L.rko_rebase_v.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int, C.c_void_p, C.c_void_p]
         L.rko_attn_prefill.restype = C.c_int
@@ -115,6 +117,18 @@ def _p(a):
 
 def hardware_threads():
     return lib().rko_hardware_threads()
+
+
+def rope(x, pos, cos_half, sin_half):
+    """RoPE (rotate-half) of fp32 rows [rows, d]; row r uses cache row pos[r] of cos_half / sin_half [n_pos, d/2]."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    pos = np.ascontiguousarray(pos, dtype=np.int32)
+    c = np.ascontiguousarray(cos_half, dtype=np.float32)
+    s = np.ascontiguousarray(sin_half, dtype=np.float32)
+    rows, d = x.shape
+    out = np.empty_like(x)
+    lib().rko_rope_rows(_p(x), rows, d, _p(pos), _p(c), _p(s), _p(out))
+    return out
 
 
 def quantize(x, fmt=E4M3, axis=-1, nthreads=1):

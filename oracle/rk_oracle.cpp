@@ -258,6 +258,24 @@ void rko_quantize_cols(const float* x, int64_t rows, int64_t cols, int fmt,
 }
 
 // codes [rows][cols] + scales [rows][cols/32] -> fp32 (code * 2^(s-127), one fp32 multiply)
+// RoPE, HF Llama rotate-half form with half-width caches (lib/golden/golden.py:229-236, rope_apply):
+// out[:, :half] = c0 * cos - c1 * sin, out[:, half:] = c1 * cos + c0 * sin, every product and sum rounded to
+// fp32 on its own (numpy float32 arithmetic: no fused multiply-add).  Row r uses cache row pos[r].
+void rko_rope_rows(const float* x, int64_t rows, int64_t d, const int32_t* pos, const float* cos_h,
+                   const float* sin_h, float* out) {
+  const int64_t half = d / 2;
+  for (int64_t r = 0; r < rows; r++) {
+    const float* c = cos_h + (int64_t)pos[r] * half;
+    const float* s = sin_h + (int64_t)pos[r] * half;
+    for (int64_t i = 0; i < half; i++) {
+      const volatile float c0 = x[r * d + i], c1 = x[r * d + half + i];
+      const volatile float a = c0 * c[i], b = c1 * s[i], e = c1 * c[i], f = c0 * s[i];   // volatile: no contraction
+      out[r * d + i] = a - b;
+      out[r * d + half + i] = e + f;
+    }
+  }
+}
+
 void rko_dequant_rows(const uint8_t* codes, const uint8_t* scales, int64_t rows, int64_t cols,
                       int fmt, float* out) {
   const Fmt& f = kFmt[fmt];

@@ -9,6 +9,6 @@ from .api import (  # noqa: F401
     E4M3, E5M2, E2M3, E3M2, V_SCALES_ALONG_KEYS, V_SCALES_ALONG_D,
     mx_quantize, mx_quantize_keys, mx_rebase_v,
     attn_prefill, attn_prefill_workspace_bytes, attn_prefill_host, PrefillHostRunner,
-    attn_decode, attn_decode_workspace_bytes, attn_decode_num_splits, kv_cache_append,
+    attn_decode, attn_decode_workspace_bytes, attn_decode_num_splits, kv_cache_append, rope_mx_quantize,
     last_device_status, shard_range,
 )

@@ -52,6 +52,8 @@ SYMBOLS = {
     "rk_attn_decode_workspace_bytes": (C.c_size_t, [C.POINTER(DecodeArgs)]),
     "rk_attn_decode": (C.c_int, [C.POINTER(DecodeArgs), C.c_void_p]),
     "rk_attn_decode_noalloc": (C.c_int, [C.POINTER(DecodeArgs), C.c_void_p]),
+    "rk_rope_mx_quantize": (C.c_int, [C.c_void_p, C.c_int64, C.c_int32, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p,
+                                      C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p]),
     "rk_kv_cache_append": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_int32,
                                      C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "rk_profile_set_events": (None, [C.c_void_p, C.c_void_p]),

@@ -43,6 +43,21 @@ def mx_quantize(x, fmt=E4M3):
     return codes, scales
 
 
+def rope_mx_quantize(x, cos_half, sin_half, *, pos=None, pos0=0, fmt=E4M3):
+    """RoPE (rotate-half) then MX quantization along d.  x fp32 [..., S, d]; caches fp32 [n_pos, d/2]; rows use cache
+    row pos0 + s, or pos[row] (int32 tensor with one entry per row) when given.  Returns (codes, scales)."""
+    _need_cuda(x, cos_half, sin_half, pos)
+    if x.dtype != torch.float32 or cos_half.dtype != torch.float32 or sin_half.dtype != torch.float32:
+        raise ValueError("rope_mx_quantize takes float32")
+    S, d = x.shape[-2], x.shape[-1]
+    rows = x.numel() // max(d, 1)
+    codes = torch.empty(x.shape, dtype=torch.uint8, device=x.device)
+    scales = torch.empty(x.shape[:-1] + (d // 32,), dtype=torch.uint8, device=x.device)
+    check(lib().rk_rope_mx_quantize(_ptr(x), rows, d, _ptr(pos), S, pos0, _ptr(cos_half), _ptr(sin_half),
+                                    cos_half.shape[0], fmt, _ptr(codes), _ptr(scales), _stream()), "rk_rope_mx_quantize")
+    return codes, scales
+
+
 def mx_quantize_keys(x, fmt=E4M3):
     """fp32 [..., rows, cols] -> codes same shape, scales [..., ceil(rows/32), cols]; blocks run down the rows."""
     _need_cuda(x)

@@ -303,6 +303,17 @@ static int check_decode_shape(const rk_decode_args* a) {
   return RK_OK;
 }
 
+int rk_rope_mx_quantize(const float* x, int64_t rows, int32_t d, const int32_t* pos, int32_t seq_len, int32_t pos0,
+                        const float* cos_half, const float* sin_half, int32_t n_pos, int32_t fmt, uint8_t* codes,
+                        uint8_t* scales, void* stream) {
+  if (!x || !cos_half || !sin_half || !codes || !scales) return RK_ERR_NULL_POINTER;
+  if (rows < 0 || d <= 0 || d % 64 != 0 || n_pos <= 0) return RK_ERR_BAD_SHAPE;      // both halves are whole blocks
+  if (!pos && (seq_len <= 0 || pos0 < 0 || (int64_t)pos0 + seq_len > n_pos)) return RK_ERR_BAD_SHAPE;
+  if (fmt < 0 || fmt > 3) return RK_ERR_UNSUPPORTED;
+  if (!aligned(x, 16) || !aligned(cos_half, 16) || !aligned(sin_half, 16) || !aligned(codes, 8)) return RK_ERR_MISALIGNED;
+  return launch_rope_quantize_rows(x, rows, d, pos, seq_len, pos0, cos_half, sin_half, fmt, codes, scales, (cudaStream_t)stream);
+}
+
 int rk_kv_cache_append(const float* k_new, const float* v_new, int32_t B, int32_t H_kv, int32_t L, int32_t d,
                        const int32_t* pos, int32_t fmt, uint8_t* k_codes, uint8_t* k_scales, uint8_t* v_codes,
                        uint8_t* v_scales, void* stream) {

@@ -26,6 +26,8 @@ int launch_retile_keyscales(const uint8_t* in, int64_t batch, int64_t S, int64_t
 int launch_prefill(const rk_prefill_args& a, const uint8_t* q_codes, const uint8_t* k_codes, const uint8_t* v_codes,
                    const uint8_t* q_sf, const uint8_t* k_sf, const uint8_t* v_sf, cudaStream_t st);
 
+int launch_rope_quantize_rows(const float* x, int64_t rows, int d, const int32_t* pos, int seq_len, int pos0, const float* cos_h,
+                              const float* sin_h, int fmt, uint8_t* codes, uint8_t* scales, cudaStream_t st);
 int launch_kv_append(const float* k_new, const float* v_new, int B, int H_kv, int L, int d, const int32_t* pos, int fmt,
                      uint8_t* k_codes, uint8_t* k_scales, uint8_t* v_codes, uint8_t* v_scales, cudaStream_t st);
 int launch_decode(const rk_decode_args& a, int num_splits, cudaStream_t st);

@@ -100,6 +100,77 @@ __global__ void __launch_bounds__(256) quantize_rows_kernel(const float4* __rest
   }
 }
 
+// RoPE fused with the block quantizer, so that rotated Q / K never exist in HBM as fp32: rotate-half form with
+// half-width caches (lib/golden/golden.py:229-236): out[:half] = c0 cos - c1 sin, out[half:] = c1 cos + c0 sin,
+// every product and sum rounded on its own (no fused multiply-add, as numpy float32 does), then the lib/golden block
+// rule along d.  chunk = 8 consecutive elements of the first half and their 8 partners of the second half; 4 lanes
+// = one 32-element block in each half.  Row r uses cache row pos[r], or pos0 + r % seq_len when pos is null.
+template <int FMT>
+__global__ void __launch_bounds__(256) rope_quantize_rows_kernel(const float* __restrict__ x, int64_t rows, int d,
+                                                                 const int32_t* __restrict__ pos, int seq_len, int pos0,
+                                                                 const float* __restrict__ cos_h, const float* __restrict__ sin_h,
+                                                                 uint8_t* __restrict__ codes, uint8_t* __restrict__ scales) {
+  const int half = d / 2, cpr = half / 8;                     // chunks per row (a multiple of 4)
+  const int64_t nchunks = rows * cpr;
+  const int lane = threadIdx.x & 31;
+  for (int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; c - lane < nchunks; c += (int64_t)gridDim.x * blockDim.x) {
+    const bool live = c < nchunks;
+    const int64_t cc = live ? c : 0;
+    const int64_t r = cc / cpr;
+    const int i0 = (int)(cc % cpr) * 8;
+    float o0[8], o1[8];
+#pragma unroll
+    for (int j = 0; j < 8; j++) { o0[j] = 0.0f; o1[j] = 0.0f; }
+    if (live) {
+      const int64_t at = pos ? (int64_t)pos[r] : (int64_t)pos0 + (r % seq_len);
+      const float* xr = x + r * d;
+      const float4 a0 = __ldcs(reinterpret_cast<const float4*>(xr + i0)), a1 = __ldcs(reinterpret_cast<const float4*>(xr + i0 + 4));
+      const float4 b0 = __ldcs(reinterpret_cast<const float4*>(xr + half + i0)), b1 = __ldcs(reinterpret_cast<const float4*>(xr + half + i0 + 4));
+      const float4 c0 = *reinterpret_cast<const float4*>(cos_h + at * half + i0), c1 = *reinterpret_cast<const float4*>(cos_h + at * half + i0 + 4);
+      const float4 s0 = *reinterpret_cast<const float4*>(sin_h + at * half + i0), s1 = *reinterpret_cast<const float4*>(sin_h + at * half + i0 + 4);
+      const float lo[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+      const float hi[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+      const float cs[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+      const float sn[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+#pragma unroll
+      for (int j = 0; j < 8; j++) {
+        o0[j] = __fsub_rn(__fmul_rn(lo[j], cs[j]), __fmul_rn(hi[j], sn[j]));
+        o1[j] = __fadd_rn(__fmul_rn(hi[j], cs[j]), __fmul_rn(lo[j], sn[j]));
+      }
+    }
+    float am0 = 0.0f, am1 = 0.0f, nf = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+      am0 = fmaxf(am0, fabsf(o0[j])); am1 = fmaxf(am1, fabsf(o1[j]));
+      nf = fmaf(o0[j], 0.0f, nf); nf = fmaf(o1[j], 0.0f, nf);
+    }
+    am0 = fmaxf(am0, __shfl_xor_sync(0xffffffffu, am0, 1)); am1 = fmaxf(am1, __shfl_xor_sync(0xffffffffu, am1, 1));
+    am0 = fmaxf(am0, __shfl_xor_sync(0xffffffffu, am0, 2)); am1 = fmaxf(am1, __shfl_xor_sync(0xffffffffu, am1, 2));
+    if (!live) continue;
+    uint32_t sc0 = 0, sc1 = 0; float p0 = 1.0f, p1 = 1.0f;
+    if (am0 > 0.0f) block_scale<FMT>(am0, sc0, p0);
+    if (am1 > 0.0f) block_scale<FMT>(am1, sc1, p1);
+    uint32_t w[4];
+    if (nf == 0.0f) {
+      w[0] = hw_encode4<FMT>(o0[0] * p0, o0[1] * p0, o0[2] * p0, o0[3] * p0);
+      w[1] = hw_encode4<FMT>(o0[4] * p0, o0[5] * p0, o0[6] * p0, o0[7] * p0);
+      w[2] = hw_encode4<FMT>(o1[0] * p1, o1[1] * p1, o1[2] * p1, o1[3] * p1);
+      w[3] = hw_encode4<FMT>(o1[4] * p1, o1[5] * p1, o1[6] * p1, o1[7] * p1);
+    } else {
+      w[0] = ref_encode4<FMT>(o0[0] * p0, o0[1] * p0, o0[2] * p0, o0[3] * p0);
+      w[1] = ref_encode4<FMT>(o0[4] * p0, o0[5] * p0, o0[6] * p0, o0[7] * p0);
+      w[2] = ref_encode4<FMT>(o1[0] * p1, o1[1] * p1, o1[2] * p1, o1[3] * p1);
+      w[3] = ref_encode4<FMT>(o1[4] * p1, o1[5] * p1, o1[6] * p1, o1[7] * p1);
+    }
+    __stcs(reinterpret_cast<uint2*>(codes + r * d + i0), make_uint2(w[0], w[1]));
+    __stcs(reinterpret_cast<uint2*>(codes + r * d + half + i0), make_uint2(w[2], w[3]));
+    if ((i0 & 31) == 0) {
+      scales[r * (d / 32) + i0 / 32] = (uint8_t)sc0;
+      scales[r * (d / 32) + (half + i0) / 32] = (uint8_t)sc1;
+    }
+  }
+}
+
 // Append one token to a KV cache: row pos[b] of every (batch, KV head) of K and of V is quantized (blocks of 32
 // along d, same rule and same code path as quantize_rows_kernel) and written in place.  chunk = 8 consecutive
 // elements of one new row; 4 consecutive lanes = one block.  A position outside [0, L) is skipped.
@@ -557,6 +628,15 @@ int launch_quantize_keys(const float* x, int64_t batch, int64_t rows, int64_t co
   if (total == 0) return RK_OK;
   const int grid = grid_for(total, 128, 16);
   RK_DISPATCH_FMT(fmt, (quantize_keys_kernel<F><<<grid, 128, 0, st>>>(x, batch, rows, cols, codes, scales)));
+  return (int)cudaGetLastError();
+}
+
+int launch_rope_quantize_rows(const float* x, int64_t rows, int d, const int32_t* pos, int seq_len, int pos0, const float* cos_h,
+                              const float* sin_h, int fmt, uint8_t* codes, uint8_t* scales, cudaStream_t st) {
+  const int64_t nchunks = rows * (d / 16);
+  if (nchunks == 0) return RK_OK;
+  const int grid = grid_for(nchunks, 256, 8);
+  RK_DISPATCH_FMT(fmt, (rope_quantize_rows_kernel<F><<<grid, 256, 0, st>>>(x, rows, d, pos, seq_len, pos0, cos_h, sin_h, codes, scales)));
   return (int)cudaGetLastError();
 }
 

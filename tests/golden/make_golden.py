@@ -18,6 +18,9 @@ reference tree is read-only) and stores only input/output vectors:
                           edge-case inputs chosen here: fp8_code_rshift (ties,
                           subnormals, saturation, signed zero, inf), block_exp /
                           pow2_neg_e, softcap (fp64 tanh reference).
+  rope_vectors.npz        lib/golden/golden.py rope_caches + rope_apply (HF Llama
+                          rotate-half) on seeded inputs for head dims 64, 128, 256:
+                          X, the half-width cos / sin caches and the rotated output.
 """
 import argparse
 import importlib.util
@@ -96,9 +99,24 @@ def make_golden_py_vectors(ref):
     print("golden_py_vectors.npz:", xin.size, "encode cases,", amax_bits.size, "block_exp cases")
 
 
+def make_rope_vectors(ref):
+    G = load_golden(ref)
+    rng = np.random.default_rng(777)
+    out = {}
+    for d in (64, 128, 256):
+        M = 40
+        X = (rng.standard_normal((M, d)) * np.exp2(rng.integers(-3, 4, (M, 1)))).astype(np.float32)
+        cos_h, sin_h, _, _ = G.rope_caches(M, d)
+        Y = G.rope_apply(X, cos_h, sin_h)
+        out[f"x{d}"] = X; out[f"cos{d}"] = cos_h; out[f"sin{d}"] = sin_h; out[f"y{d}"] = Y.astype(np.float32)
+    np.savez_compressed(HERE / "rope_vectors.npz", **out)
+    print("rope_vectors.npz:", {k: v.shape for k, v in out.items() if k.startswith("y")})
+
+
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--ref", default="/root/reference")
     ref = pathlib.Path(ap.parse_args().ref)
     make_simt_quant_kat(ref)
     make_golden_py_vectors(ref)
+    make_rope_vectors(ref)

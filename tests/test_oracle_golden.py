@@ -87,3 +87,17 @@ def test_rne_encoder_agrees_with_reference_fp8_to_code_on_normals():
     xs = xs[np.abs(xs) >= 2.0 ** -6]
     for x in xs:
         assert L.rko_encode_elem_rne(float(x), oracle.E4M3) == R.ref_fp8_e4m3_to_code(float(x))
+
+
+def test_rope_matches_reference_rope_apply():
+    """oracle.rope against lib/golden/golden.py rope_caches + rope_apply outputs (tests/golden/rope_vectors.npz),
+    bit for bit, for head dims 64, 128 and 256."""
+    z = np.load(os.path.join(G, "rope_vectors.npz"))
+    for d in (64, 128, 256):
+        x, c, s, y = z[f"x{d}"], z[f"cos{d}"], z[f"sin{d}"], z[f"y{d}"]
+        got = oracle.rope(x, np.arange(x.shape[0], dtype=np.int32), c, s)
+        assert np.array_equal(got.view(np.uint32), y.view(np.uint32)), d
+        # a permuted position list picks the matching cache rows
+        perm = np.random.default_rng(d).permutation(x.shape[0]).astype(np.int32)
+        got = oracle.rope(x[perm], perm, c, s)
+        assert np.array_equal(got.view(np.uint32), y[perm].view(np.uint32)), d

@@ -158,3 +158,39 @@ def test_quantize_full_size_idempotent():
     c2, s2 = rk.mx_quantize(d1)
     assert torch.equal(d1, deq(c2, s2))
     assert (s2 <= s1).all()
+
+
+@pytest.mark.parametrize("fmt", [0, 1, 2, 3])
+def test_rope_quantize_bit_exact_against_reference_rope_golden(fmt):
+    """The fused RoPE + quantizer: codes and scales equal oracle.quantize of the reference's own rope_apply output
+    (tests/golden/rope_vectors.npz, made by lib/golden/golden.py), for head dims 64 / 128 / 256 and every format."""
+    z = np.load(os.path.join(os.path.dirname(__file__), "golden", "rope_vectors.npz"))
+    for d in (64, 128, 256):
+        x, c, s, y = z[f"x{d}"], z[f"cos{d}"], z[f"sin{d}"], z[f"y{d}"]
+        codes, scales = rk.rope_mx_quantize(torch.from_numpy(x).cuda(), torch.from_numpy(c).cuda(), torch.from_numpy(s).cuda(), fmt=fmt)
+        oc, os_ = oracle.quantize(y, fmt=fmt)
+        assert np.array_equal(np_(codes), oc) and np.array_equal(np_(scales), os_), (fmt, d)
+
+
+def test_rope_quantize_positions_and_layouts():
+    """[batch][head][S][d] input with an offset into the caches, and an explicit per-row position list; compared
+    with the oracle's rope + quantize.  Includes a row of zeros, a NaN and an inf (integer encoder path)."""
+    rng = np.random.default_rng(5)
+    B, H, S, d, npos = 2, 3, 50, 128, 80
+    x = rng.standard_normal((B, H, S, d)).astype(np.float32)
+    x[0, 0, 3] = 0.0
+    x[1, 2, 7, 5] = np.nan
+    x[1, 1, 9, 100] = np.inf
+    ang = np.arange(npos)[:, None] * (10000.0 ** (-(np.arange(d // 2) * 2.0 / d)))[None, :]
+    c, s = np.cos(ang).astype(np.float32), np.sin(ang).astype(np.float32)
+    xt, ct, st = torch.from_numpy(x).cuda(), torch.from_numpy(c).cuda(), torch.from_numpy(s).cuda()
+    codes, scales = rk.rope_mx_quantize(xt, ct, st, pos0=11)
+    pos = np.tile(np.arange(11, 11 + S, dtype=np.int32), B * H)
+    y = oracle.rope(x.reshape(-1, d), pos, c, s)
+    oc, os_ = oracle.quantize(y)
+    assert np.array_equal(np_(codes).reshape(-1, d), oc) and np.array_equal(np_(scales).reshape(-1, d // 32), os_)
+    pos2 = rng.integers(0, npos, size=B * H * S).astype(np.int32)
+    codes, scales = rk.rope_mx_quantize(xt, ct, st, pos=torch.from_numpy(pos2).cuda())
+    y = oracle.rope(x.reshape(-1, d), pos2, c, s)
+    oc, os_ = oracle.quantize(y)
+    assert np.array_equal(np_(codes).reshape(-1, d), oc) and np.array_equal(np_(scales).reshape(-1, d // 32), os_)
