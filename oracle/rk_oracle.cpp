@@ -11,6 +11,8 @@
 //     reference's own lib/golden/mx_fp_math.h (compiled from the reference
 //     tree) and against golden vectors produced by the reference's
 //     lib/golden/golden.py and kernels/simt_quant/gen_quant.py.
+//   * RoPE (rko_rope_rows) and the tanh soft-cap: PINNED against vectors made by
+//     importing rope_caches / rope_apply / softcap from lib/golden/golden.py.
 //   * attention (prefill, decode): PARITY UNPINNED.  The reference commits no
 //     attention golden vectors and its Python attention model imports a module
 //     (fp8_matmul_model, from the un-vendored submodule lib/mxgemmini ->
