@@ -159,3 +159,37 @@ def test_full_size_head_slices_match_oracle():
                                   causal=True, softmax_scale=d ** -0.5, block_n=128)
         ma, rl = errors(np_(o[b, h].float()), ref["o_f32"][0, 0])
         assert ma <= MAX_ABS and rl <= REL_L2, (sl, ma, rl)
+
+
+@pytest.mark.parametrize("d,qmul", [(128, 1.0), (128, 6.0), (64, 1.0)])
+def test_stage_parity_s_and_requantized_p(d, qmul):
+    """Stage-level parity on the first key tile of the last query tile (the kernels' debug dump): S = Q K^T within
+    fp32 reassociation error, and the requantized P -- E4M3 codes and E8M0 block scales -- equal to the oracle's.
+    A code may differ by one step where the fp32 p sits on a truncation boundary; such elements are counted and
+    must stay below 0.05 %."""
+    import ctypes as C
+    Sq = Skv = 256
+    Q, K, V = randn_qkv(1, 1, 1, Sq, Skv, d, seed=50, qmul=qmul)
+    qc, qs, kc, ks, vc, vs = quantize_inputs(Q, K, V)
+    dbg = torch.zeros(32768, dtype=torch.float32, device="cuda")
+    rk.lib().rk_debug_set_prefill_dump(C.c_void_p(dbg.data_ptr()))
+    try:
+        rk.attn_prefill(qc, kc, vc, qs, ks, vs, causal=True)
+        torch.cuda.synchronize()
+    finally:
+        rk.lib().rk_debug_set_prefill_dump(None)
+    assert rk.last_device_status() == 0
+    scale = d ** -0.5
+    r = oracle.attn_prefill(np_(qc), np_(kc), np_(vc), np_(qs), np_(ks), np_(vs), causal=True, softmax_scale=scale,
+                            block_n=128, dump_slice=0)
+    dd = np_(dbg)
+    rows = slice(128, 256)                                    # the dump is the last query tile, key tile 0
+    s_gpu = dd[:128 * 128].reshape(128, 128)
+    s_ref = r["s"][rows, :128] / scale
+    assert np.abs(s_gpu - s_ref).max() <= 1e-5 * np.abs(s_ref).max() + 1e-6
+    pcodes = dd[128 * 128: 128 * 128 + 128 * 32].view(np.uint8).reshape(128, 128)
+    pscale = dd[128 * 128 + 128 * 32: 128 * 128 + 128 * 32 + 128].view(np.uint8).reshape(128, 4)
+    assert np.array_equal(pscale, r["p_scales"][rows, :4])
+    diff = pcodes.astype(np.int32) - r["p_codes"][rows, :128].astype(np.int32)
+    bad = np.count_nonzero(diff)
+    assert np.abs(diff).max() <= 1 and bad <= 0.0005 * diff.size, (bad, int(np.abs(diff).max()))
