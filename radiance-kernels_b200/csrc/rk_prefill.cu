@@ -55,7 +55,7 @@ struct SmemLayout {
 // warp); everything else is private.
 template <int DCH, int KV_STAGES, bool SOFTCAP>
 __device__ __forceinline__ void softmax_rows(const PrefillParams& p, uint8_t* smem, uint64_t* bars, uint32_t tmem_base,
-                                             volatile int* abort_flag, int qt, int bh, int n_tiles) {
+                                             volatile int* abort_flag, int qt, int bh, int n_tiles, int j0) {
   using L = SmemLayout<DCH, KV_STAGES>;
   uint64_t* s_full = bars + 1 + 4 * KV_STAGES;
   uint64_t* s_empty = s_full + 1;
@@ -88,12 +88,13 @@ __device__ __forceinline__ void softmax_rows(const PrefillParams& p, uint8_t* sm
     if (lane == 0 && sslot < 2) RK_STAMP(sslot, j, 1);
 
     // mask bounds relative to the tile's first key: key column c is masked iff c > hi || c <= lo
-    const bool tail = (j * kBlockN + kBlockN > p.S_kv);
-    const bool diag = p.causal && (j * kBlockN + kBlockN - 1 > p.q_pos0 + qt * kBlockM);
+    const int key0 = (j + j0) * kBlockN;                      // first key of this tile (j counts from the first tile inside the window)
+    const bool tail = (key0 + kBlockN > p.S_kv);
+    const bool diag = p.causal && (key0 + kBlockN - 1 > p.q_pos0 + qt * kBlockM);
     const bool need_mask = tail || diag || (p.window > 0);
-    int hi = p.S_kv - 1 - j * kBlockN;
-    if (p.causal) hi = min(hi, q_pos - j * kBlockN);
-    const int lo = (p.window > 0) ? (q_pos - p.window - j * kBlockN) : -1;
+    int hi = p.S_kv - 1 - key0;
+    if (p.causal) hi = min(hi, q_pos - key0);
+    const int lo = (p.window > 0) ? (q_pos - p.window - key0) : -1;
 
     float s[32];
     tmem_ld32(tmem_base + lane_addr + kColS + part * 32, reinterpret_cast<uint32_t*>(s));
@@ -359,6 +360,13 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
     const int max_qpos = p.q_pos0 + min(qt * kBlockM + kBlockM, p.S_q) - 1;
     n_tiles = max_qpos < 0 ? 0 : min(n_tiles, max_qpos / kBlockN + 1);
   }
+  // sliding window: key tiles wholly below the window of the tile's first row are masked for every row of it
+  int j0 = 0;
+  if (p.window > 0) {
+    const int first_key = p.q_pos0 + qt * kBlockM - p.window + 1;      // lowest key the first row may see
+    j0 = min(max(first_key, 0) / kBlockN, max(n_tiles - 1, 0));
+    n_tiles -= j0;                                                      // tiles j0 .. j0 + n_tiles - 1 are visited
+  }
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
@@ -388,7 +396,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
       }
     }
   } else if (warp < kNumSoftmaxWarps) {
-    softmax_rows<DCH, KV_STAGES, SOFTCAP>(p, smem, bars, tmem_base, abort_flag, qt, bh, n_tiles);
+    softmax_rows<DCH, KV_STAGES, SOFTCAP>(p, smem, bars, tmem_base, abort_flag, qt, bh, n_tiles, j0);
   } else if (warp == kNumSoftmaxWarps) {
     // ================= TMA producer =================
     if (lane == 0) {
@@ -406,20 +414,20 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         if (!ok) break;
         mbar_arrive_expect_tx(&k_full[st], DCH * (p.kv_tile_tx + kSfAtomBytes));
         for (int ch = 0; ch < DCH; ++ch) {
-          tma_load_3d(smem + L::k_off + (st * DCH + ch) * kTileBytes, &tmap_k, &k_full[st], ch * 128, j * kBlockN, bhkv);
+          tma_load_3d(smem + L::k_off + (st * DCH + ch) * kTileBytes, &tmap_k, &k_full[st], ch * 128, (j + j0) * kBlockN, bhkv);
           bulk_load_1d(smem + L::sfk_off + (st * DCH + ch) * kSfAtomBytes,
-                       p.k_sf + (((size_t)bhkv * p.n_kv_tiles + j) * DCH + ch) * kSfAtomBytes, kSfAtomBytes, &k_full[st]);
+                       p.k_sf + (((size_t)bhkv * p.n_kv_tiles + j + j0) * DCH + ch) * kSfAtomBytes, kSfAtomBytes, &k_full[st]);
         }
         if (use > 0) ok = mbar_wait(&v_empty[st], (use - 1) & 1, abort_flag, p.status, 202);
         if (!ok) break;
         mbar_arrive_expect_tx(&v_full[st], DCH * (p.kv_tile_tx + kSfAtomBytes));
         for (int ch = 0; ch < DCH; ++ch) {
           if (p.v_transposed)
-            tma_load_3d(smem + L::v_off + (st * DCH + ch) * kTileBytes, &tmap_v, &v_full[st], j * kBlockN, ch * 128, bhkv);
+            tma_load_3d(smem + L::v_off + (st * DCH + ch) * kTileBytes, &tmap_v, &v_full[st], (j + j0) * kBlockN, ch * 128, bhkv);
           else
-            tma_load_3d(smem + L::v_off + (st * DCH + ch) * kTileBytes, &tmap_v, &v_full[st], ch * 128, j * kBlockN, bhkv);
+            tma_load_3d(smem + L::v_off + (st * DCH + ch) * kTileBytes, &tmap_v, &v_full[st], ch * 128, (j + j0) * kBlockN, bhkv);
           bulk_load_1d(smem + L::sfv_off + (st * DCH + ch) * kSfAtomBytes,
-                       p.v_sf + (((size_t)bhkv * p.n_kv_tiles + j) * DCH + ch) * kSfAtomBytes, kSfAtomBytes, &v_full[st]);
+                       p.v_sf + (((size_t)bhkv * p.n_kv_tiles + j + j0) * DCH + ch) * kSfAtomBytes, kSfAtomBytes, &v_full[st]);
         }
       }
     }

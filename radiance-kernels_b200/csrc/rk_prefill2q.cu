@@ -44,7 +44,7 @@ constexpr int total = xchg_off + 2 * 3 * 2 * 128 * 4;
 
 template <bool SOFTCAP>
 __device__ __forceinline__ void softmax_group(const PrefillParams& p, uint8_t* smem, uint64_t* bars, uint32_t tmem_base,
-                                              volatile int* abort_flag, int grp, int qt, int bh, int n_tiles) {
+                                              volatile int* abort_flag, int grp, int qt, int bh, int n_tiles, int j0) {
   using namespace q2;
   uint64_t* s_full = bars + bSF + grp;
   uint64_t* s_empty = bars + bSE + grp;
@@ -91,8 +91,9 @@ __device__ __forceinline__ void softmax_group(const PrefillParams& p, uint8_t* s
     }
 
     // ---- (soft-cap,) mask, block maxima ----------------------------------------------------------------
-    const bool tail = (j * kBlockN + kBlockN > p.S_kv);
-    const bool diag = p.causal && (j * kBlockN + kBlockN - 1 > p.q_pos0 + qt * kBlockM);
+    const int key0 = (j + j0) * kBlockN;                      // first key of this tile (j counts from the first tile inside the window)
+    const bool tail = (key0 + kBlockN > p.S_kv);
+    const bool diag = p.causal && (key0 + kBlockN - 1 > p.q_pos0 + qt * kBlockM);
     const bool need_mask = tail || diag || (p.window > 0);
     if (SOFTCAP) {
 #pragma unroll
@@ -102,7 +103,7 @@ __device__ __forceinline__ void softmax_group(const PrefillParams& p, uint8_t* s
       }
     }
     if (need_mask) {
-      const int kb = j * kBlockN + half * 64;
+      const int kb = key0 + half * 64;
       int hi = p.S_kv - 1 - kb;                               // masked iff c > hi || c <= lo
       if (p.causal) hi = min(hi, q_pos - kb);
       const int lo = (p.window > 0) ? (q_pos - p.window - kb) : -1;
@@ -311,6 +312,14 @@ prefill2q_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     }
     nt[g] = n;
   }
+  // sliding window: key tiles wholly below the window of the pair's first row are masked for every row of both tiles
+  int j0 = 0;
+  if (p.window > 0) {
+    const int first_key = p.q_pos0 + 2 * qp * kBlockM - p.window + 1;  // lowest key the first row may see
+    j0 = min(max(first_key, 0) / kBlockN, max(min(nt[0], nt[1] > 0 ? nt[1] : nt[0]) - 1, 0));
+    nt[0] = max(nt[0] - j0, 0);                                         // tiles j0 .. j0 + nt - 1 are visited
+    nt[1] = max(nt[1] - j0, 0);
+  }
   const int n_all = max(nt[0], nt[1]);
 
   if (threadIdx.x == 0) {
@@ -335,7 +344,7 @@ prefill2q_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     const int grp = warp / kGroupWarps;
     const int qt = 2 * qp + grp;
     if (nt[grp] > 0) {
-      softmax_group<SOFTCAP>(p, smem, bars, tmem_base, abort_flag, grp, qt, bh, nt[grp]);
+      softmax_group<SOFTCAP>(p, smem, bars, tmem_base, abort_flag, grp, qt, bh, nt[grp], j0);
     } else if (qt < p.n_q_tiles) {
       // no visible key: O = 0 (the l <= 0 guard of finalize_O, kernels/flash_attention_mx_gemma/flash_mx_impl.hpp:554-560)
       const int t = threadIdx.x - grp * kGroupWarps * 32;
@@ -365,15 +374,15 @@ prefill2q_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         if (use > 0) ok = mbar_wait(&bars[bKE + st], (use - 1) & 1, abort_flag, p.status, 201);
         if (!ok) break;
         mbar_arrive_expect_tx(&bars[bKF + st], p.kv_tile_tx + kSfAtomBytes);
-        tma_load_3d(smem + k_off + st * kTileBytes, &tmap_k, &bars[bKF + st], 0, j * kBlockN, bhkv);
-        bulk_load_1d(smem + sfk_off + st * kSfAtomBytes, p.k_sf + ((size_t)bhkv * p.n_kv_tiles + j) * kSfAtomBytes,
+        tma_load_3d(smem + k_off + st * kTileBytes, &tmap_k, &bars[bKF + st], 0, (j + j0) * kBlockN, bhkv);
+        bulk_load_1d(smem + sfk_off + st * kSfAtomBytes, p.k_sf + ((size_t)bhkv * p.n_kv_tiles + j + j0) * kSfAtomBytes,
                      kSfAtomBytes, &bars[bKF + st]);
         if (use > 0) ok = mbar_wait(&bars[bVE + st], (use - 1) & 1, abort_flag, p.status, 202);
         if (!ok) break;
         mbar_arrive_expect_tx(&bars[bVF + st], p.kv_tile_tx + kSfAtomBytes);
-        if (p.v_transposed) tma_load_3d(smem + v_off + st * kTileBytes, &tmap_v, &bars[bVF + st], j * kBlockN, 0, bhkv);
-        else tma_load_3d(smem + v_off + st * kTileBytes, &tmap_v, &bars[bVF + st], 0, j * kBlockN, bhkv);
-        bulk_load_1d(smem + sfv_off + st * kSfAtomBytes, p.v_sf + ((size_t)bhkv * p.n_kv_tiles + j) * kSfAtomBytes,
+        if (p.v_transposed) tma_load_3d(smem + v_off + st * kTileBytes, &tmap_v, &bars[bVF + st], (j + j0) * kBlockN, 0, bhkv);
+        else tma_load_3d(smem + v_off + st * kTileBytes, &tmap_v, &bars[bVF + st], 0, (j + j0) * kBlockN, bhkv);
+        bulk_load_1d(smem + sfv_off + st * kSfAtomBytes, p.v_sf + ((size_t)bhkv * p.n_kv_tiles + j + j0) * kSfAtomBytes,
                      kSfAtomBytes, &bars[bVF + st]);
       }
     }

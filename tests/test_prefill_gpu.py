@@ -53,6 +53,15 @@ def test_sliding_window_d128():
     _check(prefill_vs_oracle(1, 2, 1, 640, 640, 128, causal=True, window=200, seed=4))
 
 
+@pytest.mark.parametrize("d,S,window,q_pos0,softcap", [(128, 1536, 300, 0, 0.0), (128, 1100, 128, 700, 0.0),
+                                                      (256, 1280, 200, 0, 50.0), (128, 900, 1, 0, 0.0)])
+def test_sliding_window_skips_key_tiles_below_the_window(d, S, window, q_pos0, softcap):
+    """Long sequences with a short window: most key tiles lie wholly below the window and are never loaded; the
+    result must equal the oracle's, which masks them (both kernels: d = 128 pairs of query tiles, d = 256)."""
+    _check(prefill_vs_oracle(1, 2, 1, S, S + q_pos0, d, causal=True, window=window, q_pos0=q_pos0, softcap=softcap,
+                             mul=0.5 if d == 256 else 1.0, seed=60 + window))
+
+
 def test_ragged_lengths_and_offset():
     _check(prefill_vs_oracle(1, 2, 2, 200, 333, 128, causal=True, q_pos0=133, seed=5))
     _check(prefill_vs_oracle(1, 1, 1, 1, 97, 64, causal=False, seed=6))
