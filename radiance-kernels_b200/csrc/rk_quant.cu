@@ -293,35 +293,50 @@ __device__ __noinline__ void rebase_block_generic(const uint8_t* cb, const uint8
   }
 }
 
-// ---- E4M3 re-blocking in integer arithmetic ---------------------------------------------------------------
-// A normal code c (magnitude bits mag = c & 0x7F >= 8) under scale code s has the value
-// (1 + m/8) * 2^(L/8 - 134) with L = mag + 8 s (m = L & 7), so the largest |value| of a block is the largest
-// L, the block rule gives the new scale code s' = L_max/8 - 15 (+1 when the mantissa of the maximum is 7,
-// i.e. above 1.75 = 448/256), and an element's new code is sign | (L - 8 s') whenever that is a normal code;
-// smaller ones are rounded to nearest-even into the subnormal grid.  A subnormal input (mag 1..7) is first
+// ---- re-blocking in integer arithmetic ------------------------------------------------------------------------
+// Written out for E4M3 (the other formats differ in the constants of RebaseT): a normal code c (magnitude bits
+// mag = c & 0x7F >= 8) under scale code s has the value (1 + m/8) * 2^(L/8 - 134) with L = mag + 8 s (m = L & 7),
+// so the largest |value| of a block is the largest L, the block rule gives the new scale code
+// s' = L_max/8 - 15 (+1 when the mantissa of the maximum is 7, i.e. above 1.75 = 448/256; only E4M3 has a top
+// mantissa that its largest normal lacks), and an element's new code is sign | (L - 8 s') whenever that is a
+// normal code; smaller ones are rounded to nearest-even into the subnormal grid.  A subnormal input is first
 // normalised to the same (1 + m/8) * 2^x form, which gives it a (possibly negative) pseudo-magnitude.
 // Identical to decoding to fp32 and re-quantizing (which the generic path does).
 // Two elements ride in one register as 16-bit lanes (L < 4096), maxima by max.u16x2.
+template <int FMT> struct RebaseT {
+  static constexpr int MB = FmtT<FMT>::mbits;                                        // mantissa bits
+  static constexpr uint32_t MAG = (1u << (FmtT<FMT>::ebits + FmtT<FMT>::mbits)) - 1u;   // magnitude bits of a code
+  static constexpr uint32_t SIGN = MAG + 1u;
+  static constexpr int ONE = 1 << MB;                                                // smallest normal magnitude
+  static constexpr int OFF = FmtT<FMT>::bias + FmtT<FMT>::emax;                      // s' = L_max / ONE - OFF
+  static constexpr bool PLUS1 = (FmtT<FMT>::max_mant != ONE - 1);                    // the block rule's "+1" can fire
+  static constexpr uint32_t S_LO = OFF + MB + 1;                                     // scale codes the integer path takes
+  static constexpr uint32_t MAG2 = MAG | (MAG << 16), SIGN4 = SIGN * 0x01010101u;
+  static constexpr uint32_t EXP4 = (MAG & ~(uint32_t)(ONE - 1)) * 0x01010101u, LOW4 = (uint32_t)ONE * 0x01010101u;
+};
 RK_DEVINL uint32_t max_u16x2(uint32_t a, uint32_t b) {
   uint32_t r;
   asm("max.u16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
   return r;
 }
-// pseudo-magnitude of a subnormal E4M3 code, mag in 1..7: value = mag * 2^-9 = (1 + m'/8) * 2^(e' - 7)
-RK_DEVINL int e4m3_subnormal_mag(int mag) {
-  const int p = 31 - __clz(mag);                       // 0..2
-  return ((mag << (3 - p)) & 7) + 8 * (p - 2);
+// pseudo-magnitude of a subnormal code, mag in 1 .. ONE-1: value = mag * 2^x = (1 + m'/ONE) * 2^(x')
+template <int FMT> RK_DEVINL int rb_subnormal_mag(int mag) {
+  using R = RebaseT<FMT>;
+  const int p = 31 - __clz(mag);                       // 0 .. MB-1
+  return ((mag << (R::MB - p)) & (R::ONE - 1)) + R::ONE * (p - R::MB + 1);
 }
-// new code (without sign) of an element with L - 8 s' = tt
-RK_DEVINL uint32_t e4m3_code_from_tt(int tt) {
-  if (tt >= 8) return (uint32_t)tt;
-  const int sh = 1 - (tt >> 3);                        // >= 1: below the smallest normal
-  return sh > 5 ? 0u : round_shift(8u | (uint32_t)(tt & 7), sh);
+// new code (without sign) of an element with L - ONE s' = tt
+template <int FMT> RK_DEVINL uint32_t rb_code_from_tt(int tt) {
+  using R = RebaseT<FMT>;
+  if (tt >= R::ONE) return (uint32_t)tt;
+  const int sh = 1 - (tt >> R::MB);                    // >= 1: below the smallest normal
+  return sh > R::MB + 2 ? 0u : round_shift((uint32_t)R::ONE | (uint32_t)(tt & (R::ONE - 1)), sh);
 }
 // non-zero when some byte of w has a zero exponent field (zero or subnormal code)
-RK_DEVINL uint32_t e4m3_exp0_bits(uint32_t w) {
-  const uint32_t e = w & 0x78787878u;
-  return (e - 0x08080808u) & ~e & 0x80808080u;
+template <int FMT> RK_DEVINL uint32_t rb_exp0_bits(uint32_t w) {
+  using R = RebaseT<FMT>;
+  const uint32_t e = w & R::EXP4;
+  return (e - R::LOW4) & ~e & 0x80808080u;
 }
 RK_DEVINL uint32_t addmax_u16x2(uint32_t a, uint32_t b, uint32_t c) {   // max(a + b, c) in both 16-bit lanes
   uint32_t r;
@@ -330,24 +345,26 @@ RK_DEVINL uint32_t addmax_u16x2(uint32_t a, uint32_t b, uint32_t c) {   // max(a
 }
 
 // Rare rows (a zero or subnormal code among the four): per-byte L, packed as lanes (0, 2) and (1, 3).
-__device__ __noinline__ uint2 e4m3_rare_l(uint32_t cw, int sj) {
+template <int FMT> __device__ __noinline__ uint2 rb_rare_l(uint32_t cw, int sj) {
+  using R = RebaseT<FMT>;
   uint32_t l[4];
 #pragma unroll
   for (int q = 0; q < 4; q++) {
-    const int mag = (int)((cw >> (8 * q)) & 0x7Fu);
-    l[q] = mag == 0 ? 0u : (uint32_t)((mag >= 8 ? mag : e4m3_subnormal_mag(mag)) + 8 * sj) & 0xFFFFu;
+    const int mag = (int)((cw >> (8 * q)) & R::MAG);
+    l[q] = mag == 0 ? 0u : (uint32_t)((mag >= R::ONE ? mag : rb_subnormal_mag<FMT>(mag)) + R::ONE * sj) & 0xFFFFu;
   }
   return make_uint2(l[0] | (l[2] << 16), l[1] | (l[3] << 16));
 }
 // Rare rows of the second pass: some lane leaves the normal range, or an input was zero / subnormal.
-// sub02 / sub13 carry 8 s' of columns (0, 2) and (1, 3) as 16-bit lanes.
-__device__ __noinline__ uint32_t e4m3_rare_recode(uint32_t cw, int sj, uint32_t sub02, uint32_t sub13) {
-  uint32_t out = cw & 0x80808080u;
+// sub02 / sub13 carry ONE * s' of columns (0, 2) and (1, 3) as 16-bit lanes.
+template <int FMT> __device__ __noinline__ uint32_t rb_rare_recode(uint32_t cw, int sj, uint32_t sub02, uint32_t sub13) {
+  using R = RebaseT<FMT>;
+  uint32_t out = cw & R::SIGN4;
 #pragma unroll
   for (int q = 0; q < 4; q++) {
-    const int mag = (int)((cw >> (8 * q)) & 0x7Fu);
+    const int mag = (int)((cw >> (8 * q)) & R::MAG);
     const int sub = (int)((((q & 1) ? sub13 : sub02) >> (16 * (q >> 1))) & 0xFFFFu);
-    if (mag != 0) out |= e4m3_code_from_tt((mag >= 8 ? mag : e4m3_subnormal_mag(mag)) + 8 * sj - sub) << (8 * q);
+    if (mag != 0) out |= rb_code_from_tt<FMT>((mag >= R::ONE ? mag : rb_subnormal_mag<FMT>(mag)) + R::ONE * sj - sub) << (8 * q);
   }
   return out;
 }
@@ -355,8 +372,8 @@ __device__ __noinline__ uint32_t e4m3_rare_recode(uint32_t cw, int sj, uint32_t 
 // Four lanes share one unit = 16 adjacent columns x one 32-key block: lane "rg" holds rows 8 rg .. 8 rg + 7 as
 // eight 16-byte words in registers between the two passes (all loads of a thread in flight together), the
 // column maxima meet by two shuffles.  A warp covers 8 adjacent units, so each 16-byte access of a warp touches
-// four full 128-byte lines.  Formats other than E4M3, and E4M3 blocks with scale codes outside [18, 240], go
-// through the generic fp32 path, each lane taking 4 of the unit's 16 columns over all 32 keys.
+// four full 128-byte lines.  Blocks with scale codes outside [S_LO, 240] go through the generic fp32 path, each
+// lane taking 4 of the unit's 16 columns over all 32 keys.
 template <int FMT, bool TILED>
 __global__ void __launch_bounds__(128, 4) rebase_v_kernel(const uint8_t* __restrict__ codes, const uint8_t* __restrict__ scales,
                                                           int64_t batch, int64_t S, int64_t d,
@@ -378,8 +395,9 @@ __global__ void __launch_bounds__(128, 4) rebase_v_kernel(const uint8_t* __restr
     const uint8_t* sb = scales + (bt * S + r0) * nbd + c16 / 2;
     uint8_t* ob = out_codes + (bt * S + r0) * d + c16 * 16;
     uint32_t sc[4];                                               // new scale codes of columns 4 rg .. 4 rg + 3
-    uint32_t bad = (FMT == 0) ? 0u : 1u;
-    if (FMT == 0) {
+    using R = RebaseT<FMT>;
+    uint32_t bad = 0u;
+    {
       // rows past a ragged end read as zero codes under a mid-range scale: they change nothing
       uint4 cw[8];
       uint32_t s8[8];
@@ -394,21 +412,21 @@ __global__ void __launch_bounds__(128, 4) rebase_v_kernel(const uint8_t* __restr
       uint32_t lo[4] = {0u, 0u, 0u, 0u}, hi[4] = {0u, 0u, 0u, 0u};
 #pragma unroll
       for (int i = 0; i < 8; i++) {
-        bad |= (s8[i] - 18u > 222u) ? 1u : 0u;
-        s8[i] *= 0x00080008u;
+        bad |= (s8[i] - R::S_LO > 240u - R::S_LO) ? 1u : 0u;
+        s8[i] *= (uint32_t)R::ONE * 0x00010001u;
         const uint32_t wv[4] = {cw[i].x, cw[i].y, cw[i].z, cw[i].w};
         // one test per row: does any of its 16 codes have a zero exponent field (zero or subnormal)?
-        if ((e4m3_exp0_bits(wv[0]) | e4m3_exp0_bits(wv[1]) | e4m3_exp0_bits(wv[2]) | e4m3_exp0_bits(wv[3])) == 0u) {
+        if ((rb_exp0_bits<FMT>(wv[0]) | rb_exp0_bits<FMT>(wv[1]) | rb_exp0_bits<FMT>(wv[2]) | rb_exp0_bits<FMT>(wv[3])) == 0u) {
 #pragma unroll
           for (int x = 0; x < 4; x++) {
-            lo[x] = addmax_u16x2(wv[x] & 0x007F007Fu, s8[i], lo[x]);
-            hi[x] = addmax_u16x2((wv[x] >> 8) & 0x007F007Fu, s8[i], hi[x]);
+            lo[x] = addmax_u16x2(wv[x] & R::MAG2, s8[i], lo[x]);
+            hi[x] = addmax_u16x2((wv[x] >> 8) & R::MAG2, s8[i], hi[x]);
           }
         } else {
 #pragma unroll
           for (int x = 0; x < 4; x++) {
-            uint2 l = make_uint2((wv[x] & 0x007F007Fu) + s8[i], ((wv[x] >> 8) & 0x007F007Fu) + s8[i]);
-            if (e4m3_exp0_bits(wv[x]) != 0u) l = e4m3_rare_l(wv[x], (int)((s8[i] & 0xFFFFu) >> 3));
+            uint2 l = make_uint2((wv[x] & R::MAG2) + s8[i], ((wv[x] >> 8) & R::MAG2) + s8[i]);
+            if (rb_exp0_bits<FMT>(wv[x]) != 0u) l = rb_rare_l<FMT>(wv[x], (int)((s8[i] & 0xFFFFu) >> R::MB));
             lo[x] = max_u16x2(lo[x], l.x);
             hi[x] = max_u16x2(hi[x], l.y);
           }
@@ -432,13 +450,15 @@ __global__ void __launch_bounds__(128, 4) rebase_v_kernel(const uint8_t* __restr
           uint32_t v[2] = {lo[x], hi[x]};
 #pragma unroll
           for (int h = 0; h < 2; h++) {
-            uint32_t sn = ((v[h] >> 3) & 0x1FFF1FFFu) + ((((v[h] & 0x00070007u) + 0x00010001u) >> 3) & 0x00010001u);
-            if ((v[h] & 0xFFFFu) == 0u) sn |= 0x0000000Fu;          // an all-zero column: 15 - 15 = scale code 0
-            if ((v[h] >> 16) == 0u) sn |= 0x000F0000u;
-            v[h] = sn - 0x000F000Fu;
+            constexpr uint32_t M2 = (uint32_t)(R::ONE - 1) * 0x00010001u, Q2 = (0xFFFFu >> R::MB) * 0x00010001u;
+            uint32_t sn = (v[h] >> R::MB) & Q2;
+            if (R::PLUS1) sn += (((v[h] & M2) + 0x00010001u) >> R::MB) & 0x00010001u;
+            if ((v[h] & 0xFFFFu) == 0u) sn = (sn & 0xFFFF0000u) | (uint32_t)R::OFF;          // an all-zero column: scale code 0
+            if ((v[h] >> 16) == 0u) sn = (sn & 0x0000FFFFu) | ((uint32_t)R::OFF << 16);
+            v[h] = sn - (uint32_t)R::OFF * 0x00010001u;
           }
-          sub_lo[x] = v[0] << 3;
-          sub_hi[x] = v[1] << 3;
+          sub_lo[x] = v[0] << R::MB;
+          sub_hi[x] = v[1] << R::MB;
           if (x == rg) {
             sc[0] = v[0] & 0xFFFFu; sc[1] = v[1] & 0xFFFFu; sc[2] = v[0] >> 16; sc[3] = v[1] >> 16;
           }
@@ -452,15 +472,15 @@ __global__ void __launch_bounds__(128, 4) rebase_v_kernel(const uint8_t* __restr
           uint32_t rare[4];
 #pragma unroll
           for (int x = 0; x < 4; x++) {
-            const uint32_t t_lo = (wv[x] & 0x007F007Fu) + s8[i] + (0x40004000u - sub_lo[x]);
-            const uint32_t t_hi = ((wv[x] >> 8) & 0x007F007Fu) + s8[i] + (0x40004000u - sub_hi[x]);
-            ov[x] = (wv[x] & 0x80808080u) | (t_lo & 0x007F007Fu) | ((t_hi & 0x007F007Fu) << 8);
-            rare[x] = (((t_lo - 0x40084008u) | (t_hi - 0x40084008u)) & 0x80008000u) | e4m3_exp0_bits(wv[x]);
+            const uint32_t t_lo = (wv[x] & R::MAG2) + s8[i] + (0x40004000u - sub_lo[x]);
+            const uint32_t t_hi = ((wv[x] >> 8) & R::MAG2) + s8[i] + (0x40004000u - sub_hi[x]);
+            ov[x] = (wv[x] & R::SIGN4) | (t_lo & R::MAG2) | ((t_hi & R::MAG2) << 8);
+            rare[x] = (((t_lo - (0x40004000u + (uint32_t)R::ONE * 0x00010001u)) | (t_hi - (0x40004000u + (uint32_t)R::ONE * 0x00010001u))) & 0x80008000u) | rb_exp0_bits<FMT>(wv[x]);
           }
           if ((rare[0] | rare[1] | rare[2] | rare[3]) != 0u) {      // one branch per row in the common case
 #pragma unroll
             for (int x = 0; x < 4; x++)
-              if (rare[x] != 0u) ov[x] = e4m3_rare_recode(wv[x], (int)((s8[i] & 0xFFFFu) >> 3), sub_lo[x], sub_hi[x]);
+              if (rare[x] != 0u) ov[x] = rb_rare_recode<FMT>(wv[x], (int)((s8[i] & 0xFFFFu) >> R::MB), sub_lo[x], sub_hi[x]);
           }
           const int j = rg * 8 + i;
           if (j < n) *reinterpret_cast<uint4*>(ob + (int64_t)j * d) = make_uint4(ov[0], ov[1], ov[2], ov[3]);

@@ -100,31 +100,36 @@ def test_quantize_keys_and_rebase_bit_exact():
         assert np.array_equal(np_(rc[b]), oc) and np.array_equal(np_(rs[b]), os_)
 
 
+@pytest.mark.parametrize("fmt", [0, 1, 2, 3])
 @pytest.mark.parametrize("S,d", [(32 * 7 + 5, 256), (96, 64), (40, 128), (32, 32)])
-def test_rebase_bit_exact_on_adversarial_codes(S, d):
-    """Every branch of the integer re-blocking: random raw E4M3 codes (zeros, subnormals, both signs; the NaN
-    encodings replaced) under scale codes that vary row to row by up to 2^24, extreme scale codes that must take
-    the generic path, all-zero columns, ragged tails, and widths where a warp spans several key blocks."""
-    rng = np.random.default_rng(11)
+def test_rebase_bit_exact_on_adversarial_codes(S, d, fmt):
+    """Every branch of the integer re-blocking, for all four element formats: random raw codes (zeros, subnormals,
+    both signs; the E4M3 NaN encodings replaced) under scale codes that vary row to row by up to 2^24, extreme
+    scale codes that must take the generic path, all-zero columns, ragged tails, and widths where a warp spans
+    several key blocks."""
+    rng = np.random.default_rng(11 + fmt)
     nb = d // 32
-    codes = rng.integers(0, 256, size=(4, S, d), dtype=np.uint8)
-    codes[(codes & 0x7F) == 0x7F] = 0x7E
+    nbits = 8 if fmt < 2 else 6
+    sign, mant_bits = 1 << (nbits - 1), (3 if fmt in (0, 2) else 2)
+    codes = rng.integers(0, 1 << nbits, size=(4, S, d), dtype=np.uint8)
+    if fmt == 0:
+        codes[(codes & 0x7F) == 0x7F] = 0x7E
     codes[0, :, 0:4] = 0                                   # all-zero columns
-    codes[0, :, 4:8] = 0x80                                # all negative zero
+    codes[0, :, 4:8] = sign                                # all negative zero
     codes[0, :, 9] = 0                                     # a zero column beside ordinary ones
-    codes[1, :, :] &= 0x87                                 # a slice of subnormals and zeros only
+    codes[1, :, :] &= sign | ((1 << mant_bits) - 1)        # a slice of subnormals and zeros only
     scales = rng.integers(115, 140, size=(4, S, nb), dtype=np.uint8)
     scales[2] = rng.integers(100, 124, size=(S, nb), dtype=np.uint8)
     scales[3, :, 0] = rng.integers(0, 256, size=S, dtype=np.uint8)       # extreme scale codes: generic path
     if nb > 2:
         scales[3, :, 1] = rng.integers(236, 246, size=S, dtype=np.uint8)
-        scales[3, :, 2] = rng.integers(14, 22, size=S, dtype=np.uint8)
+        scales[3, :, 2] = rng.integers(4, 40, size=S, dtype=np.uint8)
     scales[3][scales[3] == 255] = 254
     c = torch.from_numpy(codes).cuda()
     s = torch.from_numpy(scales).cuda()
-    rc, rs = rk.mx_rebase_v(c, s)
+    rc, rs = rk.mx_rebase_v(c, s, fmt)
     for b in range(4):
-        oc, os_ = oracle.rebase_v(codes[b], scales[b])
+        oc, os_ = oracle.rebase_v(codes[b], scales[b], fmt)
         assert np.array_equal(np_(rs[b]), os_), f"scales differ in slice {b}"
         assert np.array_equal(np_(rc[b]), oc), f"codes differ in slice {b}"
 
