@@ -77,6 +77,10 @@ RK_API int rk_version(void);
  * ------------------------------------------------------------------------- */
 RK_API int rk_mx_quantize(const float* x, int64_t rows, int64_t cols, int fmt,
                    uint8_t* codes, uint8_t* scales, void* stream);
+/* Same as rk_mx_quantize with a bf16 input [rows][cols] (the dtype projections usually produce): each value is
+ * widened exactly to fp32 and takes the same path, at 2 instead of 4 input bytes per element. */
+RK_API int rk_mx_quantize_bf16(const void* x_bf16, int64_t rows, int64_t cols, int fmt,
+                               uint8_t* codes, uint8_t* scales, void* stream);
 RK_API int rk_mx_quantize_keys(const float* x, int64_t batch, int64_t rows, int64_t cols, int fmt,
                         uint8_t* codes, uint8_t* scales, void* stream);
 

@@ -22,8 +22,9 @@ def build(force=False):
     src = _HERE / "rk_oracle.cpp"
     if force or not so.exists() or so.stat().st_mtime < src.stat().st_mtime:
         subprocess.run(["make", "-C", str(_HERE), "liboracle.so"], check=True, stdout=subprocess.DEVNULL)
-    if os.path.isdir("/root/reference") and (force or not (_HERE / "_ref" / "libref_codec.so").exists()):
-        subprocess.run(["make", "-C", str(_HERE), "ref"], check=True, stdout=subprocess.DEVNULL)
+    ref = os.environ.get("RK_REFERENCE_DIR", "/root/reference")
+    if os.path.isdir(ref) and (force or not (_HERE / "_ref" / "libref_codec.so").exists()):
+        subprocess.run(["make", "-C", str(_HERE), "ref", "REF=" + ref], check=True, stdout=subprocess.DEVNULL)
 
 
 class PrefillArgs(C.Structure):

@@ -41,6 +41,7 @@ SYMBOLS = {
     "rk_error_string": (C.c_char_p, [C.c_int]),
     "rk_version": (C.c_int, []),
     "rk_mx_quantize": (C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "rk_mx_quantize_bf16": (C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]),
     "rk_mx_quantize_keys": (C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]),
     "rk_mx_rebase_v": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]),
     "rk_attn_prefill_block_n": (C.c_int, [C.POINTER(PrefillArgs)]),

@@ -31,15 +31,16 @@ def _need_cuda(*ts):
 
 
 def mx_quantize(x, fmt=E4M3):
-    """fp32 [..., cols] -> (codes uint8 [..., cols], scales uint8 [..., cols/32]); blocks along the last axis."""
+    """fp32 or bf16 [..., cols] -> (codes uint8 [..., cols], scales uint8 [..., cols/32]); blocks along the last axis."""
     _need_cuda(x)
-    if x.dtype != torch.float32:
-        raise ValueError("mx_quantize takes float32")
+    if x.dtype not in (torch.float32, torch.bfloat16):
+        raise ValueError("mx_quantize takes float32 or bfloat16")
     cols = x.shape[-1]
     rows = x.numel() // max(cols, 1)
     codes = torch.empty(x.shape, dtype=torch.uint8, device=x.device)
     scales = torch.empty(x.shape[:-1] + (cols // 32,), dtype=torch.uint8, device=x.device)
-    check(lib().rk_mx_quantize(_ptr(x), rows, cols, fmt, _ptr(codes), _ptr(scales), _stream()), "rk_mx_quantize")
+    fn = lib().rk_mx_quantize if x.dtype == torch.float32 else lib().rk_mx_quantize_bf16
+    check(fn(_ptr(x), rows, cols, fmt, _ptr(codes), _ptr(scales), _stream()), "rk_mx_quantize")
     return codes, scales
 
 

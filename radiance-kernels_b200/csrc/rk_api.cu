@@ -104,6 +104,14 @@ int rk_mx_quantize(const float* x, int64_t rows, int64_t cols, int fmt, uint8_t*
   return launch_quantize_rows(x, rows, cols, fmt, codes, scales, (cudaStream_t)stream);
 }
 
+int rk_mx_quantize_bf16(const void* x, int64_t rows, int64_t cols, int fmt, uint8_t* codes, uint8_t* scales, void* stream) {
+  if (!x || !codes || !scales) return RK_ERR_NULL_POINTER;
+  if (rows < 0 || cols < 0 || cols % 32 != 0) return RK_ERR_BAD_SHAPE;
+  if (fmt < 0 || fmt > 3) return RK_ERR_BAD_FORMAT;
+  if (!aligned(x, 16) || !aligned(codes, 8)) return RK_ERR_MISALIGNED;
+  return launch_quantize_rows_bf16(x, rows, cols, fmt, codes, scales, (cudaStream_t)stream);
+}
+
 int rk_mx_quantize_keys(const float* x, int64_t batch, int64_t rows, int64_t cols, int fmt, uint8_t* codes,
                         uint8_t* scales, void* stream) {
   if (!x || !codes || !scales) return RK_ERR_NULL_POINTER;

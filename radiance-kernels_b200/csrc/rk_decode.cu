@@ -415,12 +415,14 @@ int launch_decode(const rk_decode_args& a, int nsplit, cudaStream_t st) {
     t.q = p.q; t.k_scale = p.k_scale; t.v_scale = p.v_scale; t.kv_len = p.kv_len;
     t.part_o = p.part_o; t.part_ml = p.part_ml; t.status = p.status;
     t.B = p.B; t.H = p.H; t.H_kv = p.H_kv; t.L = p.L; t.grp = p.grp; t.nsplit = p.nsplit; t.scale_log2 = p.scale_log2;
-    const int smem_bytes = dtc::total + 1024;
-    if ((e = cudaFuncSetAttribute(decode_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes)) != cudaSuccess) return (int)e;
+    const bool eight = p.grp > 4;                        // head capacity 4 (two P buffers) or 8 (one)
+    const int smem_bytes = (eight ? dtc::Lay<8>::total : dtc::Lay<4>::total) + 1024;
+    auto kern = eight ? decode_tc_kernel<8> : decode_tc_kernel<4>;
+    if ((e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes)) != cudaSuccess) return (int)e;
     const uint32_t idesc_qk = make_idesc(0, 0, false, false, 128, dtc::kNq);
-    const uint32_t idesc_pv = make_idesc(0, 0, true, false, 128, dtc::kNp);
+    const uint32_t idesc_pv = make_idesc(0, 0, true, false, 128, eight ? dtc::Lay<8>::kNp : dtc::Lay<4>::kNp);
     if (g_ev_before && g_ev_after) cudaEventRecord(g_ev_before, st);
-    decode_tc_kernel<<<grid, dtc::kThreads, smem_bytes, st>>>(tk, tv, t, idesc_qk, idesc_pv);
+    kern<<<grid, dtc::kThreads, smem_bytes, st>>>(tk, tv, t, idesc_qk, idesc_pv);
     if (g_ev_before && g_ev_after) cudaEventRecord(g_ev_after, st);
   } else {
     if ((e = cudaFuncSetAttribute(decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDecSmemBytes)) != cudaSuccess) return (int)e;

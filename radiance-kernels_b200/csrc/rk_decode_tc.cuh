@@ -46,32 +46,39 @@ constexpr int kD = 128;
 #endif
 constexpr int kStages = RK_X_DTC_STAGES;
 constexpr int kCtasPerSm = kStages <= 3 ? 2 : 1;
-constexpr int kMaxGrp = 4;                        // query heads per KV head handled by this kernel
-constexpr int kNq = 16;                           // B rows of the QK^T MMA: (term, head) = term * 4 + h, rows 8..15 zero
-constexpr int kNp = 32;                           // B rows of the PV MMA: term * 16 + h * 4 + g
+constexpr int kMaxGrp = 8;                        // query heads per KV head handled by this kernel (HH = 4 or 8 rows of capacity)
+constexpr int kNq = 16;                           // B rows of the QK^T MMA: term * HH + h (rows past 2 HH stay zero)
 constexpr int kTileBytes = kTile * kD;            // 16384
 constexpr int kStageBytes = 2 * kTileBytes + 2 * 512;   // K, V, K scales [128][4], V scales [128][4]
 constexpr float kLazyLog2 = 8.0f;                 // rescale O when a running maximum grew by more than this
 
-// shared-memory map (offsets from a 1024-byte aligned base)
-constexpr int stage_off = 0;
-constexpr int p_off = kStages * kStageBytes;      // 2 x [32 rows][128 B], K-major SW128
-constexpr int q_off = p_off + 2 * 4096;           // [16 rows][128 B], K-major SW128
-constexpr int sfp_off = q_off + 2048;             // 2 x 512-byte scale atoms for P
-constexpr int sfq_off = sfp_off + 2 * 512;        // scale atom of the query terms
-constexpr int one_off = sfq_off + 512;            // scale atom of ones (code 127) for V
-constexpr int xchg_off = one_off + 512;           // [2][4 warps][4 heads] floats (tile maxima)
-constexpr int bar_off = xchg_off + 2 * 16 * 4;
+// Per head capacity HH: B rows of the PV MMA = term * 4 HH + h * 4 + g; with 8 heads one P buffer instead of two keeps
+// the CTA inside the shared memory that lets two CTAs share an SM.
+template <int HH> struct Lay {
+  static constexpr int kNp = 8 * HH;
+  static constexpr int kPBufs = HH == 4 ? 2 : 1;
+  static constexpr int kPBytes = kNp * 128;       // one P tile: [kNp rows][128 B], K-major SW128
+  // shared-memory map (offsets from a 1024-byte aligned base)
+  static constexpr int stage_off = 0;
+  static constexpr int p_off = kStages * kStageBytes;
+  static constexpr int q_off = p_off + kPBufs * kPBytes;       // [16 rows][128 B], K-major SW128
+  static constexpr int sfp_off = q_off + 2048;                 // 2 x 512-byte scale atoms for P
+  static constexpr int sfq_off = sfp_off + 2 * 512;            // scale atom of the query terms
+  static constexpr int one_off = sfq_off + 512;                // scale atom of ones (code 127) for V
+  static constexpr int xchg_off = one_off + 512;               // [2][4 warps][8 heads] floats (tile maxima)
+  static constexpr int bar_off = xchg_off + 2 * 32 * 4;
+  static constexpr int misc_off = bar_off + 32 * 8;            // tmem base, abort flag
+  static constexpr int total = misc_off + 16;
+  static_assert(kStageBytes % 1024 == 0 && p_off % 1024 == 0 && q_off % 1024 == 0, "swizzled tiles need 1024-byte alignment");
+};
 enum { bFull = 0, bEmpty = bFull + kStages, bSF = bEmpty + kStages, bSE = bSF + 2, bPF = bSE + 2, bPV = bPF + 2,
        bMX = bPV + 2, bDrain = bMX + 2, nBars = bDrain + 1 };
-constexpr int misc_off = bar_off + nBars * 8;     // tmem base, abort flag
-constexpr int total = misc_off + 16;
-static_assert(stage_off % 1024 == 0 && kStageBytes % 1024 == 0 && p_off % 1024 == 0 && q_off % 1024 == 0, "swizzled tiles need 1024-byte alignment");
+static_assert(nBars <= 32, "barrier slots");
 
 // TMEM columns
 constexpr uint32_t cS = 0;          // 2 x 16
-constexpr uint32_t cO = 32;         // 32
-constexpr uint32_t cSfK = 64;       // 4 per stage
+constexpr uint32_t cO = 32;         // up to 64
+constexpr uint32_t cSfK = 96;       // 4 per stage
 constexpr uint32_t cSfQ = cSfK + 4 * kStages;
 constexpr uint32_t cSfP = cSfQ + 4; // 2 x 4
 constexpr uint32_t cSfOne = cSfP + 8;
@@ -125,16 +132,18 @@ RK_DEVINL float pow2i(int e) {
   return __uint_as_float(f <= 0 ? 0u : ((uint32_t)(f > 254 ? 254 : f) << 23));
 }
 
+template <int HH>
 __global__ void __launch_bounds__(dtc::kThreads, dtc::kCtasPerSm)
 decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
                  const DecodeTcParams p, const uint32_t idesc_qk, const uint32_t idesc_pv) {
   using namespace dtc;
+  using L = Lay<HH>;
   extern __shared__ __align__(1024) uint8_t dtc_smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(dtc_smem_raw) + 1023) & ~(uintptr_t)1023);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + bar_off);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + misc_off);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + misc_off + 4);
-  float* xchg = reinterpret_cast<float*>(smem + xchg_off);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::bar_off);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::misc_off);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::misc_off + 4);
+  float* xchg = reinterpret_cast<float*>(smem + L::xchg_off);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (*reinterpret_cast<volatile int*>(p.status) != 0) return;   // an earlier launch gave up on a wait
@@ -162,39 +171,41 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_consta
   if (warp < kWorkers) {
     const int t = threadIdx.x;                                    // 0..127
     // P tiles: rows of heads that do not exist stay zero for ever; scale atoms start as ones (code 127)
-    for (int i = t; i < 2 * 4096 / 16; i += 128) reinterpret_cast<uint4*>(smem + p_off)[i] = make_uint4(0u, 0u, 0u, 0u);
-    for (int i = t; i < 2048 / 16; i += 128) reinterpret_cast<uint4*>(smem + sfp_off)[i] = make_uint4(0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu);
-    // rows 8..15 of the query tile are never written below
-    reinterpret_cast<uint4*>(smem + q_off + 1024)[t & 63] = make_uint4(0u, 0u, 0u, 0u);
+    for (int i = t; i < L::kPBufs * L::kPBytes / 16; i += 128) reinterpret_cast<uint4*>(smem + L::p_off)[i] = make_uint4(0u, 0u, 0u, 0u);
+    for (int i = t; i < 2048 / 16; i += 128) reinterpret_cast<uint4*>(smem + L::sfp_off)[i] = make_uint4(0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu);
+    // rows of the query tile that no head writes below stay zero
+    reinterpret_cast<uint4*>(smem + L::q_off)[t] = make_uint4(0u, 0u, 0u, 0u);
     asm volatile("bar.sync 1, 128;" ::: "memory");                  // fills done before the query terms land in them
-    // query head h = warp as two MXFP8 terms: q = hi + lo (lib/golden block rule on q, then on the residual)
-    const int h = warp;
-    float x[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-    if (h < p.grp) {
-      const uint2 raw = *reinterpret_cast<const uint2*>(p.q + ((size_t)b * p.H + hkv * p.grp + h) * kD + lane * 4);
-      x[0] = __uint_as_float(raw.x << 16); x[1] = __uint_as_float(raw.x & 0xFFFF0000u);
-      x[2] = __uint_as_float(raw.y << 16); x[3] = __uint_as_float(raw.y & 0xFFFF0000u);
-    }
+    // query heads h = warp, warp + 4 as two MXFP8 terms each: q = hi + lo (lib/golden block rule on q, then on the residual)
 #pragma unroll
-    for (int term = 0; term < 2; ++term) {
-      float amax = fmaxf(fmaxf(fabsf(x[0]), fabsf(x[1])), fmaxf(fabsf(x[2]), fabsf(x[3])));
-      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));   // the 8 lanes of one 32-wide block of d
-      uint32_t code = 127u;
-      float p2 = 1.0f;
-      if (amax > 0.0f && amax < 3.0e38f) block_scale<0>(amax, code, p2);
-      const float back = e8m0_to_f32(code);
-      uint32_t word = 0;
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const uint32_t c = encode_rne<0>(x[e] * p2);
-        word |= c << (8 * e);
-        x[e] -= decode_elem<0>(c) * back;                          // residual, exact
+    for (int h = warp; h < HH; h += kWorkers) {
+      float x[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+      if (h < p.grp) {
+        const uint2 raw = *reinterpret_cast<const uint2*>(p.q + ((size_t)b * p.H + hkv * p.grp + h) * kD + lane * 4);
+        x[0] = __uint_as_float(raw.x << 16); x[1] = __uint_as_float(raw.x & 0xFFFF0000u);
+        x[2] = __uint_as_float(raw.y << 16); x[3] = __uint_as_float(raw.y & 0xFFFF0000u);
       }
-      const int n = term * 4 + h;
-      *reinterpret_cast<uint32_t*>(smem + q_off + sw128(n, lane * 4)) = word;
-      if ((lane & 7) == 0) smem[sfq_off + n * 16 + (lane >> 3)] = (uint8_t)code;
+#pragma unroll
+      for (int term = 0; term < 2; ++term) {
+        float amax = fmaxf(fmaxf(fabsf(x[0]), fabsf(x[1])), fmaxf(fabsf(x[2]), fabsf(x[3])));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));   // the 8 lanes of one 32-wide block of d
+        uint32_t code = 127u;
+        float p2 = 1.0f;
+        if (amax > 0.0f && amax < 3.0e38f) block_scale<0>(amax, code, p2);
+        const float back = e8m0_to_f32(code);
+        uint32_t word = 0;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const uint32_t c = encode_rne<0>(x[e] * p2);
+          word |= c << (8 * e);
+          x[e] -= decode_elem<0>(c) * back;                          // residual, exact
+        }
+        const int n = term * HH + h;
+        *reinterpret_cast<uint32_t*>(smem + L::q_off + sw128(n, lane * 4)) = word;
+        if ((lane & 7) == 0) smem[L::sfq_off + n * 16 + (lane >> 3)] = (uint8_t)code;
+      }
     }
     fence_proxy_async_smem();
   }
@@ -211,7 +222,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_consta
       for (int j = 0; j < n_tiles; ++j) {
         const int st = j % kStages;
         if (j >= kStages && !mbar_wait<20000>(&bars[bEmpty + st], ((j / kStages) - 1) & 1, abort_flag, p.status, 511)) break;
-        uint8_t* sb = smem + stage_off + st * kStageBytes;
+        uint8_t* sb = smem + L::stage_off + st * kStageBytes;
         const int key0 = (tile0 + j) * kTile;
         // scale rows past L are not read: the copy is clipped to the cache extent (L % 4 == 0 keeps it a 16-byte multiple)
         const uint32_t sbytes = (uint32_t)min(kTile, p.L - key0) * 4u;
@@ -224,18 +235,19 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_consta
     }
   } else if (warp == kWorkers + 1) {
     // ================= MMA issuer (all lanes re-tile the key scales, lane 0 issues) =================
-    const uint32_t q_addr = smem_u32(smem + q_off), p_addr = smem_u32(smem + p_off);
+    const uint32_t q_addr = smem_u32(smem + L::q_off), p_addr = smem_u32(smem + L::p_off);
     auto issue_pv = [&](int i) -> bool {                            // lane 0 only
       const int buf = i & 1, sti = i % kStages;
       if (!mbar_wait(&bars[bPF + buf], (i >> 1) & 1, abort_flag, p.status, 523)) return false;
       tc_fence_after();
-      tc_cp_32x128b_warpx4(tmem_base + cSfP + buf * 4, make_smem_desc(smem_u32(smem + sfp_off + buf * 512), 0, 128, kLayoutNone));
-      const uint32_t v_addr = smem_u32(smem + stage_off + sti * kStageBytes + kTileBytes);
+      tc_cp_32x128b_warpx4(tmem_base + cSfP + buf * 4, make_smem_desc(smem_u32(smem + L::sfp_off + buf * 512), 0, 128, kLayoutNone));
+      const uint32_t v_addr = smem_u32(smem + L::stage_off + sti * kStageBytes + kTileBytes);
+      const int pbuf = L::kPBufs == 2 ? buf : 0;
 #pragma unroll
       for (int kk = 0; kk < 4; ++kk) {
         // A = V tile [keys][d]: d is the contiguous (M) dimension, 32 keys per instruction
         const uint64_t adesc = make_smem_desc(v_addr + kk * 4096, kTileBytes, 1024, kLayoutSw128);
-        const uint64_t bdesc = make_smem_desc(p_addr + buf * 4096 + kk * 32, 16, 1024, kLayoutSw128);
+        const uint64_t bdesc = make_smem_desc(p_addr + pbuf * L::kPBytes + kk * 32, 16, 1024, kLayoutSw128);
         mma_mxf8f6f4_ss(tmem_base + cO, adesc, bdesc, idesc_with_sf(idesc_pv, kk, kk), tmem_base + cSfOne,
                         tmem_base + cSfP + buf * 4, (i > 0 || kk > 0) ? 1u : 0u);
       }
@@ -244,12 +256,12 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_consta
       return true;
     };
     if (lane == 0 && n_tiles > 0) {
-      tc_cp_32x128b_warpx4(tmem_base + cSfQ, make_smem_desc(smem_u32(smem + sfq_off), 0, 128, kLayoutNone));
-      tc_cp_32x128b_warpx4(tmem_base + cSfOne, make_smem_desc(smem_u32(smem + one_off), 0, 128, kLayoutNone));
+      tc_cp_32x128b_warpx4(tmem_base + cSfQ, make_smem_desc(smem_u32(smem + L::sfq_off), 0, 128, kLayoutNone));
+      tc_cp_32x128b_warpx4(tmem_base + cSfOne, make_smem_desc(smem_u32(smem + L::one_off), 0, 128, kLayoutNone));
     }
     for (int j = 0; j < n_tiles && ok; ++j) {
       const int st = j % kStages;
-      uint8_t* sb = smem + stage_off + st * kStageBytes;
+      uint8_t* sb = smem + L::stage_off + st * kStageBytes;
       ok = __all_sync(0xffffffffu, mbar_wait(&bars[bFull + st], (j / kStages) & 1, abort_flag, p.status, 521));
       if (!ok) break;
       // key scales [key][4] -> scale atom: word (key % 32) * 4 + key / 32
@@ -292,13 +304,13 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_consta
     // ================= workers: thread = key kt of the tile (S, P), thread = column d = kt (O) =================
     const int kt = warp * 32 + lane;
     const uint32_t lane_addr = ((uint32_t)(warp * 32)) << 16;
-    float m_ref[4], m_run[4], l_part[4];
+    float m_ref[HH], m_run[HH], l_part[HH];
 #pragma unroll
-    for (int h = 0; h < 4; ++h) { m_ref[h] = NEG_INF; m_run[h] = NEG_INF; l_part[h] = 0.0f; }
+    for (int h = 0; h < HH; ++h) { m_ref[h] = NEG_INF; m_run[h] = NEG_INF; l_part[h] = 0.0f; }
 
     for (int j = 0; j < n_tiles && ok; ++j) {
       const int buf = j & 1, st = j % kStages;
-      uint8_t* sb = smem + stage_off + st * kStageBytes;
+      uint8_t* sb = smem + L::stage_off + st * kStageBytes;
       ok = __all_sync(0xffffffffu, mbar_wait(&bars[bSF + buf], (j >> 1) & 1, abort_flag, p.status, 501));
       if (!ok) break;
       tc_fence_after();
@@ -312,63 +324,63 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_consta
       const int key = (tile0 + j) * kTile + kt;
       const bool valid = key < len;
       const bool tail = (tile0 + j + 1) * kTile > len;
-      float s[4];
-      uint32_t wmax[4];
+      float s[HH];
+      float* xw = xchg + (buf * kWorkers + warp) * HH;
 #pragma unroll
-      for (int h = 0; h < 4; ++h) {
-        s[h] = valid ? (__uint_as_float(c[h]) + __uint_as_float(c[4 + h])) * p.scale_log2 : NEG_INF;   // log2 domain
-        wmax[h] = redux_max_u32(f32_to_ordered(s[h]));
+      for (int h = 0; h < HH; ++h) {
+        s[h] = valid ? (__uint_as_float(c[h]) + __uint_as_float(c[HH + h])) * p.scale_log2 : NEG_INF;   // log2 domain
+        const uint32_t wmax = redux_max_u32(f32_to_ordered(s[h]));
+        if (lane == 0) xw[h] = ordered_to_f32(wmax);
       }
-      if (lane == 0) *reinterpret_cast<float4*>(xchg + (buf * 4 + warp) * 4) =
-          make_float4(ordered_to_f32(wmax[0]), ordered_to_f32(wmax[1]), ordered_to_f32(wmax[2]), ordered_to_f32(wmax[3]));
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars[bMX + buf]);
       ok = __all_sync(0xffffffffu, mbar_wait(&bars[bMX + buf], (j >> 1) & 1, abort_flag, p.status, 504));
       if (!ok) break;
-      float m_new[4];
-      {
-        const float4 a0 = *reinterpret_cast<const float4*>(xchg + (buf * 4 + 0) * 4);
-        const float4 a1 = *reinterpret_cast<const float4*>(xchg + (buf * 4 + 1) * 4);
-        const float4 a2 = *reinterpret_cast<const float4*>(xchg + (buf * 4 + 2) * 4);
-        const float4 a3 = *reinterpret_cast<const float4*>(xchg + (buf * 4 + 3) * 4);
-        m_new[0] = fmaxf(m_run[0], fmaxf(fmaxf(a0.x, a1.x), fmaxf(a2.x, a3.x)));
-        m_new[1] = fmaxf(m_run[1], fmaxf(fmaxf(a0.y, a1.y), fmaxf(a2.y, a3.y)));
-        m_new[2] = fmaxf(m_run[2], fmaxf(fmaxf(a0.z, a1.z), fmaxf(a2.z, a3.z)));
-        m_new[3] = fmaxf(m_run[3], fmaxf(fmaxf(a0.w, a1.w), fmaxf(a2.w, a3.w)));
-      }
-      // every thread of the CTA holds the same m_run / m_ref / m_new, so this decision is CTA-uniform
+      float m_new[HH];
+      // every thread of the CTA holds the same m_run / m_ref / m_new, so the decision below is CTA-uniform
       bool bump = (j == 0);
 #pragma unroll
-      for (int h = 0; h < 4; ++h) { bump = bump || (m_new[h] > m_ref[h] + kLazyLog2); m_run[h] = m_new[h]; }
+      for (int h = 0; h < HH; ++h) {
+        const float* xr = xchg + buf * kWorkers * HH + h;
+        m_new[h] = fmaxf(m_run[h], fmaxf(fmaxf(xr[0], xr[HH]), fmaxf(xr[2 * HH], xr[3 * HH])));
+        bump = bump || (m_new[h] > m_ref[h] + kLazyLog2);
+        m_run[h] = m_new[h];
+      }
       if (bump) {
         if (j > 0) {
-          // rescale O (this thread's row d = kt, all 32 columns) once the previous PV has landed
+          // rescale O (this thread's row d = kt, all columns) once the previous PV has landed
           ok = __all_sync(0xffffffffu, mbar_wait(&bars[bPV + ((j - 1) & 1)], ((j - 1) >> 1) & 1, abort_flag, p.status, 502));
           if (!ok) break;
           tc_fence_after();
-          float corr[4];
+          float corr[HH];
 #pragma unroll
-          for (int h = 0; h < 4; ++h) { corr[h] = ex2_approx(m_ref[h] - m_new[h]); l_part[h] *= corr[h]; }
-          uint32_t o[32];
-          tmem_ld32(tmem_base + lane_addr + cO, o);
-          tc_wait_ld();
+          for (int h = 0; h < HH; ++h) { corr[h] = ex2_approx(m_ref[h] - m_new[h]); l_part[h] *= corr[h]; }
 #pragma unroll
-          for (int n = 0; n < 32; ++n) o[n] = __float_as_uint(__uint_as_float(o[n]) * corr[(n & 15) >> 2]);
-          tmem_st32(tmem_base + lane_addr + cO, o);
+          for (int part = 0; part < L::kNp / 32; ++part) {
+            uint32_t o[32];
+            tmem_ld32(tmem_base + lane_addr + cO + part * 32, o);
+            tc_wait_ld();
+#pragma unroll
+            for (int n = 0; n < 32; ++n) o[n] = __float_as_uint(__uint_as_float(o[n]) * corr[((part * 32 + n) % (4 * HH)) >> 2]);
+            tmem_st32(tmem_base + lane_addr + cO + part * 32, o);
+          }
           tc_wait_st();
         }
 #pragma unroll
-        for (int h = 0; h < 4; ++h) m_ref[h] = m_new[h];
+        for (int h = 0; h < HH; ++h) m_ref[h] = m_new[h];
       }
 
       // ---- p, row sums, block exponents -------------------------------------------------------------------
-      float pr[4];
-      uint32_t eh[4];      // biased exponent of the largest p of this warp's 32 keys, per head
+      float ph[HH];
+      uint32_t eh[HH];     // biased exponent of the largest p of this warp's 32 keys, per head
+      uint32_t emin = 255u, emax = 0u;
 #pragma unroll
-      for (int h = 0; h < 4; ++h) {
-        pr[h] = ex2_approx(s[h] - m_ref[h]);            // <= 2^8; masked keys give 0
-        l_part[h] += pr[h];
-        eh[h] = redux_max_u32(__float_as_uint(pr[h])) >> 23;
+      for (int h = 0; h < HH; ++h) {
+        const float pr = ex2_approx(s[h] - m_ref[h]);            // <= 2^8; masked keys give 0
+        l_part[h] += pr;
+        eh[h] = redux_max_u32(__float_as_uint(pr)) >> 23;
+        ph[h] = pr * pow2i(134 - (int)eh[h]);
+        emin = min(emin, eh[h]); emax = max(emax, eh[h]);
       }
       const uint32_t svw = valid ? *reinterpret_cast<const uint32_t*>(sb + 2 * kTileBytes + 512 + kt * 4) : 0u;
       uint32_t svmax[4];
@@ -376,24 +388,22 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_consta
       for (int g = 0; g < 4; ++g) svmax[g] = redux_max_u32((svw >> (8 * g)) & 0xFFu);
       // element (h, g) = p * 2^(sv[g] - svmax[g]) * 2^(7 - (eh - 127)) <= 2^8 under the block scale code
       // svmax[g] + eh[h] - 134 (kept >= 4 so that the low term's code, 4 less, exists)
-      float fg[4], ph[4];
+      float fg[4];
 #pragma unroll
       for (int g = 0; g < 4; ++g) fg[g] = pow2i((int)((svw >> (8 * g)) & 0xFFu) - (int)svmax[g]);
-#pragma unroll
-      for (int h = 0; h < 4; ++h) ph[h] = pr[h] * pow2i(134 - (int)eh[h]);
-      uint32_t smin = min(min(svmax[0], svmax[1]), min(svmax[2], svmax[3]));
-      uint32_t smax = max(max(svmax[0], svmax[1]), max(svmax[2], svmax[3]));
-      uint32_t emin = min(min(eh[0], eh[1]), min(eh[2], eh[3]));
-      uint32_t emax = max(max(eh[0], eh[1]), max(eh[2], eh[3]));
+      const uint32_t smin = min(min(svmax[0], svmax[1]), min(svmax[2], svmax[3]));
+      const uint32_t smax = max(max(svmax[0], svmax[1]), max(svmax[2], svmax[3]));
       const bool plain = (smin + emin >= 138u) && (smax + emax <= 388u);      // every code in [4, 254]
 
-      if (j >= 2) {      // the P buffer is free once the PV of two tiles ago has read it
-        ok = __all_sync(0xffffffffu, mbar_wait(&bars[bPV + buf], ((j - 2) >> 1) & 1, abort_flag, p.status, 503));
+      // the P buffer is free once the PV that read it has completed: two tiles ago with two buffers, the last one with one
+      if (j >= L::kPBufs) {
+        const int i = j - L::kPBufs;
+        ok = __all_sync(0xffffffffu, mbar_wait(&bars[bPV + (i & 1)], (i >> 1) & 1, abort_flag, p.status, 503));
         if (!ok) break;
       }
-      uint8_t* pt = smem + p_off + buf * 4096;
+      uint8_t* pt = smem + L::p_off + (L::kPBufs == 2 ? buf : 0) * L::kPBytes;
 #pragma unroll
-      for (int h = 0; h < 4; ++h) {
+      for (int h = 0; h < HH; ++h) {
 #pragma unroll
         for (int g = 0; g < 4; g += 2) {
           float v0 = ph[h] * fg[g], v1 = ph[h] * fg[g + 1];
@@ -409,16 +419,20 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_consta
           const int n = h * 4 + g;
           pt[sw128(n, kt)] = (uint8_t)hi;
           pt[sw128(n + 1, kt)] = (uint8_t)(hi >> 8);
-          pt[sw128(16 + n, kt)] = (uint8_t)lo;
-          pt[sw128(16 + n + 1, kt)] = (uint8_t)(lo >> 8);
+          pt[sw128(4 * HH + n, kt)] = (uint8_t)lo;
+          pt[sw128(4 * HH + n + 1, kt)] = (uint8_t)(lo >> 8);
         }
       }
-      {   // block scale of column n = lane for this warp's 32 keys (k-block = warp)
-        const int term = lane >> 4, hh = (lane >> 2) & 3, gg = lane & 3;
+#pragma unroll
+      for (int part = 0; part < L::kNp / 32; ++part) {   // block scale of column n for this warp's 32 keys (k-block = warp)
+        const int n = part * 32 + lane;
+        const int term = n / (4 * HH), hh = (n >> 2) % HH, gg = n & 3;
         const uint32_t sv_s = gg == 0 ? svmax[0] : gg == 1 ? svmax[1] : gg == 2 ? svmax[2] : svmax[3];
-        const uint32_t eh_s = hh == 0 ? eh[0] : hh == 1 ? eh[1] : hh == 2 ? eh[2] : eh[3];
+        uint32_t eh_s = eh[0];
+#pragma unroll
+        for (int h = 1; h < HH; ++h) eh_s = (hh == h) ? eh[h] : eh_s;
         const int code = min(max((int)sv_s + (int)eh_s - 134, 4), 254) - 4 * term;
-        smem[sfp_off + buf * 512 + lane * 16 + warp] = (uint8_t)code;
+        smem[L::sfp_off + buf * 512 + (n & 31) * 16 + (n >> 5) * 4 + warp] = (uint8_t)code;
       }
       if (tail && !valid) {   // a key past kv_len: its V row may hold anything; 0 * NaN must not reach the accumulator
         uint4* vrow = reinterpret_cast<uint4*>(sb + kTileBytes + kt * 128);
@@ -432,39 +446,47 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_consta
     }
 
     // ---- epilogue: O^T row d = kt, the columns of group g = warp -------------------------------------------
-    float oh[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    float oh[HH];
+#pragma unroll
+    for (int h = 0; h < HH; ++h) oh[h] = 0.0f;
     if (ok && n_tiles > 0) {
       const int last = n_tiles - 1;
       ok = __all_sync(0xffffffffu, mbar_wait(&bars[bPV + (last & 1)], (last >> 1) & 1, abort_flag, p.status, 505));
       if (ok) {
         tc_fence_after();
-        uint32_t o[32];
-        tmem_ld32(tmem_base + lane_addr + cO, o);
-        tc_wait_ld();
 #pragma unroll
-        for (int h = 0; h < 4; ++h) {
-          float acc = 0.0f;
+        for (int part = 0; part < L::kNp / 32; ++part) {
+          uint32_t o[32];
+          tmem_ld32(tmem_base + lane_addr + cO + part * 32, o);
+          tc_wait_ld();
 #pragma unroll
-          for (int g = 0; g < 4; ++g)
-            if (g == warp) acc = __uint_as_float(o[h * 4 + g]) + __uint_as_float(o[16 + h * 4 + g]);
-          oh[h] = acc;
+          for (int n = 0; n < 32; ++n) {
+            const int col = part * 32 + n;                       // = term * 4 HH + h * 4 + g: both terms add up
+            if ((col & 3) == warp) oh[(col % (4 * HH)) >> 2] += __uint_as_float(o[n]);
+          }
         }
       }
     }
-    float* lsum = reinterpret_cast<float*>(smem + p_off);           // [4 heads][128 threads]: the P tiles are free now
+    float* lsum = reinterpret_cast<float*>(smem + L::p_off);        // [HH heads][128 threads]: the P tiles are free now
 #pragma unroll
-    for (int h = 0; h < 4; ++h) lsum[h * 128 + kt] = l_part[h];
+    for (int h = 0; h < HH; ++h) lsum[h * 128 + kt] = l_part[h];
     asm volatile("bar.sync 1, 128;" ::: "memory");                  // workers only; every worker reaches this point
     if (ok) {
-      for (int h = 0; h < p.grp; ++h) {
-        const size_t bh = (size_t)b * p.H + hkv * p.grp + h;
-        p.part_o[(bh * p.nsplit + split) * 128 + kt] = oh[h];
+#pragma unroll
+      for (int h = 0; h < HH; ++h) {
+        if (h < p.grp) {
+          const size_t bh = (size_t)b * p.H + hkv * p.grp + h;
+          p.part_o[(bh * p.nsplit + split) * 128 + kt] = oh[h];
+        }
       }
       if (kt < p.grp) {
         float l = 0.0f;
         for (int i = 0; i < 128; ++i) l += lsum[kt * 128 + i];
+        float mr = m_ref[0];
+#pragma unroll
+        for (int h = 1; h < HH; ++h) mr = (kt == h) ? m_ref[h] : mr;
         const size_t bh = (size_t)b * p.H + hkv * p.grp + kt;
-        p.part_ml[(bh * p.nsplit + split) * 2] = kt == 0 ? m_ref[0] : kt == 1 ? m_ref[1] : kt == 2 ? m_ref[2] : m_ref[3];
+        p.part_ml[(bh * p.nsplit + split) * 2] = mr;
         p.part_ml[(bh * p.nsplit + split) * 2 + 1] = l;
       }
     }

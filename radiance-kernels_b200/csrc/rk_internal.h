@@ -11,6 +11,7 @@ extern cudaEvent_t g_ev_before, g_ev_after;   // optional profiling events aroun
 int num_sms();                 // SM count of the current device (cached per device)
 int* device_status_word();     // per-device int in global memory, zeroed at creation; kernels CAS error codes into it
 
+int launch_quantize_rows_bf16(const void* x, int64_t rows, int64_t cols, int fmt, uint8_t* codes, uint8_t* scales, cudaStream_t st);
 int launch_quantize_rows(const float* x, int64_t rows, int64_t cols, int fmt, uint8_t* codes, uint8_t* scales, cudaStream_t st);
 int launch_quantize_keys(const float* x, int64_t batch, int64_t rows, int64_t cols, int fmt, uint8_t* codes, uint8_t* scales, cudaStream_t st);
 int launch_rebase_v(const uint8_t* codes, const uint8_t* scales, int64_t batch, int64_t S, int64_t d, int fmt,

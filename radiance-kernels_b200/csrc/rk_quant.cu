@@ -62,7 +62,8 @@ __global__ void verify_encoder_kernel(uint64_t first, uint64_t count, unsigned l
   if (bad) atomicAdd(mismatches, bad);
 }
 
-template <int FMT>
+// BF16IN: the input is bf16 (one 16-byte load per chunk, widened exactly to fp32) instead of fp32.
+template <int FMT, bool BF16IN = false>
 __global__ void __launch_bounds__(256) quantize_rows_kernel(const float4* __restrict__ x, int64_t nchunks,
                                                             uint2* __restrict__ codes, uint8_t* __restrict__ scales) {
   // chunk = 8 consecutive elements; 4 consecutive lanes = one 32-element block.
@@ -74,7 +75,16 @@ __global__ void __launch_bounds__(256) quantize_rows_kernel(const float4* __rest
   for (int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; c - lane < nchunks; c += stride) {
     const bool live = c < nchunks;
     float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
-    if (live) { a = __ldcs(x + 2 * c); b = __ldcs(x + 2 * c + 1); }
+    if (live) {
+      if (BF16IN) {
+        const float4 raw = __ldcs(x + c);                      // 8 bf16
+        const uint32_t w[4] = {__float_as_uint(raw.x), __float_as_uint(raw.y), __float_as_uint(raw.z), __float_as_uint(raw.w)};
+        a = make_float4(__uint_as_float(w[0] << 16), __uint_as_float(w[0] & 0xFFFF0000u), __uint_as_float(w[1] << 16), __uint_as_float(w[1] & 0xFFFF0000u));
+        b = make_float4(__uint_as_float(w[2] << 16), __uint_as_float(w[2] & 0xFFFF0000u), __uint_as_float(w[3] << 16), __uint_as_float(w[3] & 0xFFFF0000u));
+      } else {
+        a = __ldcs(x + 2 * c); b = __ldcs(x + 2 * c + 1);
+      }
+    }
     const float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
     float amax = 0.0f, nonfinite = 0.0f;
 #pragma unroll
@@ -631,6 +641,16 @@ static int grid_for(int64_t work_items, int threads, int per_sm) {
     case 3: { constexpr int F = 3; __VA_ARGS__; } break; \
     default: return RK_ERR_BAD_FORMAT;             \
   }
+
+int launch_quantize_rows_bf16(const void* x, int64_t rows, int64_t cols, int fmt, uint8_t* codes, uint8_t* scales,
+                              cudaStream_t st) {
+  const int64_t nchunks = rows * cols / 8;
+  if (nchunks == 0) return RK_OK;
+  const int grid = grid_for(nchunks, 256, 8);
+  RK_DISPATCH_FMT(fmt, (quantize_rows_kernel<F, true><<<grid, 256, 0, st>>>(reinterpret_cast<const float4*>(x), nchunks,
+                                                                            reinterpret_cast<uint2*>(codes), scales)));
+  return (int)cudaGetLastError();
+}
 
 int launch_quantize_rows(const float* x, int64_t rows, int64_t cols, int fmt, uint8_t* codes, uint8_t* scales,
                          cudaStream_t st) {

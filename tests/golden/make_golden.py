@@ -1,9 +1,10 @@
 #!/usr/bin/env python3
 """Regenerate the golden fixtures in this directory from the reference tree.
 
-Run in a container that has the reference checked out (default /root/reference):
+Run where the reference tree is checked out (its location: --ref, or the
+environment variable RK_REFERENCE_DIR):
 
-    python tests/golden/make_golden.py [--ref /root/reference]
+    python tests/golden/make_golden.py --ref <reference tree>
 
 It never copies reference code into the repo; it runs / imports the reference's
 own Python (lib/golden/golden.py, kernels/simt_quant/gen_quant.py) from a
@@ -23,6 +24,7 @@ reference tree is read-only) and stores only input/output vectors:
                           X, the half-width cos / sin caches and the rotated output.
 """
 import argparse
+import os
 import importlib.util
 import pathlib
 import re
@@ -115,7 +117,7 @@ def make_rope_vectors(ref):
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default="/root/reference")
+    ap.add_argument("--ref", default=os.environ.get("RK_REFERENCE_DIR", "/root/reference"))
     ref = pathlib.Path(ap.parse_args().ref)
     make_simt_quant_kat(ref)
     make_golden_py_vectors(ref)

@@ -199,3 +199,17 @@ def test_rope_quantize_positions_and_layouts():
     y = oracle.rope(x.reshape(-1, d), pos2, c, s)
     oc, os_ = oracle.quantize(y)
     assert np.array_equal(np_(codes).reshape(-1, d), oc) and np.array_equal(np_(scales).reshape(-1, d // 32), os_)
+
+
+@pytest.mark.parametrize("fmt", [0, 1, 2, 3])
+def test_bf16_input_quantizer_equals_fp32_path(fmt):
+    """A bf16 tensor quantizes to exactly what its fp32 widening does (and to what the oracle says)."""
+    g = torch.Generator(device="cuda").manual_seed(70 + fmt)
+    x = (torch.randn(333, 256, generator=g, device="cuda") * torch.exp2(torch.randint(-20, 20, (333, 1), generator=g, device="cuda").float())).bfloat16()
+    x[5] = 0
+    x[7, 3] = float("inf")
+    cb, sb = rk.mx_quantize(x, fmt)
+    cf, sf = rk.mx_quantize(x.float(), fmt)
+    assert torch.equal(cb, cf) and torch.equal(sb, sf)
+    oc, os_ = oracle.quantize(np_(x.float()), fmt=fmt)
+    assert np.array_equal(np_(cb), oc) and np.array_equal(np_(sb), os_)
