@@ -112,6 +112,23 @@ def ref_codec():
     return R
 
 
+def ref_requant():
+    """The reference attention kernel's own P-requantization helpers behind a C shim (oracle/_ref/libref_requant.so),
+    or None when oracle/_ref was never built."""
+    so = _HERE / "_ref" / "libref_requant.so"
+    if not so.exists():
+        return None
+    R = C.CDLL(str(so))
+    R.ref_bf16_to_e4m3_scaled.restype = C.c_uint8
+    R.ref_bf16_to_e4m3_scaled.argtypes = [C.c_uint16, C.c_int]
+    R.ref_bf16_floor_log2.restype = C.c_int
+    R.ref_bf16_floor_log2.argtypes = [C.c_uint16]
+    for n in ("ref_bf16_to_e4m3_trunc", "ref_bf16_to_e4m3_rne"):
+        getattr(R, n).restype = C.c_uint8
+        getattr(R, n).argtypes = [C.c_uint16]
+    return R
+
+
 def _p(a):
     return None if a is None else a.ctypes.data_as(C.c_void_p)
 

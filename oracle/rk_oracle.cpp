@@ -13,13 +13,22 @@
 //     lib/golden/golden.py and kernels/simt_quant/gen_quant.py.
 //   * RoPE (rko_rope_rows) and the tanh soft-cap: PINNED against vectors made by
 //     importing rope_caches / rope_apply / softcap from lib/golden/golden.py.
-//   * attention (prefill, decode): PARITY UNPINNED.  The reference commits no
-//     attention golden vectors and its Python attention model imports a module
-//     (fp8_matmul_model, from the un-vendored submodule lib/mxgemmini ->
-//     Rakanic/gemmini-rocc-tests, no pinned revision) that is absent.  The
-//     structure below follows the reference model line by line; the matmuls
-//     are fp32-accumulated over exactly decoded operands and the softmax state
-//     is fp32, as the build target asks.
+//   * the P requantization rule (p_block_scale_code, p_code): PINNED against the
+//     reference attention kernel's own helpers bf16_floor_log2 /
+//     bf16_to_e4m3_scaled (kernels/flash_attention_mx_gqa/flash_mx_impl.hpp:53-77)
+//     compiled from the reference tree, over every non-negative finite bf16 p.
+//   * the fp32 attention reference (rko_attn_fp32_ref: causal mask with a query
+//     offset, GQA head map, soft-cap before the mask, sliding window): PINNED
+//     against the reference's own attention_reference_causal_gqa /
+//     attention_reference_gemma (golden vectors made by importing its model files).
+//   * the MX attention composition (prefill, decode): PARITY UNPINNED.  The
+//     reference commits no MX attention golden vectors and the MX half of its
+//     Python model calls into a module (fp8_matmul_model, from the un-vendored
+//     submodule lib/mxgemmini -> Rakanic/gemmini-rocc-tests, no pinned revision)
+//     that is absent.  Every rule the composition uses is pinned above; the
+//     structure below follows the reference model line by line; the matmuls are
+//     fp32-accumulated over exactly decoded operands and the softmax state is
+//     fp32, as the build target asks.
 #include <algorithm>
 #include <atomic>
 #include <cmath>

@@ -19,6 +19,14 @@ reference tree is read-only) and stores only input/output vectors:
                           edge-case inputs chosen here: fp8_code_rshift (ties,
                           subnormals, saturation, signed zero, inf), block_exp /
                           pow2_neg_e, softcap (fp64 tanh reference).
+  attn_fp32_ref_vectors.npz  the reference's own pure-fp32 attention references
+                          (attention_reference_causal_gqa of kernels/flash_attention_mx_gqa/
+                          flash_attention_model.py, attention_reference_gemma with soft-cap and
+                          sliding window of kernels/flash_attention_mx_gemma/...), their mask
+                          helpers and blocks_used, on seeded GQA inputs.  The model files import
+                          fp8_matmul_model from a submodule that is absent; an empty stand-in
+                          module satisfies that import, and only functions that never touch it
+                          are called.
   rope_vectors.npz        lib/golden/golden.py rope_caches + rope_apply (HF Llama
                           rotate-half) on seeded inputs for head dims 64, 128, 256:
                           X, the half-width cos / sin caches and the rotated output.
@@ -115,6 +123,52 @@ def make_rope_vectors(ref):
     print("rope_vectors.npz:", {k: v.shape for k, v in out.items() if k.startswith("y")})
 
 
+def load_attention_model(path):
+    """Import a flash_attention_model.py of the reference; `fp8_matmul_model` (absent submodule) becomes a stand-in
+    that only carries the three constants the module reads at import time."""
+    import types
+    stub = types.ModuleType("fp8_matmul_model")
+    stub.GROUP, stub.INPUT_SPEC, stub.TILE = 32, "fp8:e4m3", 16
+    sys.modules["fp8_matmul_model"] = stub
+    try:
+        spec = importlib.util.spec_from_file_location("ref_attn_model_" + path.parent.name, path)
+        mod = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(mod)
+    finally:
+        del sys.modules["fp8_matmul_model"]
+    return mod
+
+
+def make_attn_fp32_ref_vectors(ref):
+    import torch
+    gqa = load_attention_model(ref / "kernels" / "flash_attention_mx_gqa" / "flash_attention_model.py")
+    gem = load_attention_model(ref / "kernels" / "flash_attention_mx_gemma" / "flash_attention_model.py")
+    out = {}
+    # causal GQA, query block offset into the keys (the reference's own generator and head layout)
+    n_q, n_kv, Sq, Sk, d, q_pos0 = 4, 2, 24, 64, 32, 36
+    Q, K, V = gqa.make_inputs_gqa(Sq, Sk, d, n_q, n_kv, seed=3)
+    scale = d ** -0.5
+    out["gqa_q"], out["gqa_k"], out["gqa_v"] = Q.numpy(), K.numpy(), V.numpy()
+    out["gqa_o"] = gqa.attention_reference_causal_gqa(Q, K, V, scale, q_pos0).numpy()
+    out["gqa_meta"] = np.array([q_pos0], np.int32)
+    out["gqa_mask"] = gqa.causal_bool_mask(Sq, Sk, q_pos0).numpy()
+    out["blocks_used"] = np.array([[sq, sk, qp, bn, gqa.blocks_used(sq, sk, qp, bn)]
+                                   for sq in (64, 128) for sk in (128, 512) for qp in (0, 64, 300) for bn in (64, 128)],
+                                  np.int32)
+    # Gemma: soft-cap (Q scaled up so that it bites, as the reference's generator does) and sliding window
+    n_q, n_kv, Sq, Sk, d, q_pos0, cap, window = 4, 2, 24, 64, 32, 40, 50.0, 20
+    Q, K, V = gem.make_inputs_gqa(Sq, Sk, d, n_q, n_kv, seed=5)
+    Q = Q * 20.0
+    out["gem_q"], out["gem_k"], out["gem_v"] = Q.numpy(), K.numpy(), V.numpy()
+    out["gem_o_cap_win"] = gem.attention_reference_gemma(Q, K, V, scale, q_pos0, attn_softcap=cap, window=window).numpy()
+    out["gem_o_cap"] = gem.attention_reference_gemma(Q, K, V, scale, q_pos0, attn_softcap=cap, window=None).numpy()
+    out["gem_meta"] = np.array([q_pos0, window], np.int32)
+    out["gem_cap"] = np.array([cap], np.float32)
+    out["gem_mask"] = gem.gemma_bool_mask(Sq, Sk, q_pos0, window).numpy()
+    np.savez_compressed(HERE / "attn_fp32_ref_vectors.npz", **out)
+    print("attn_fp32_ref_vectors.npz:", out["gqa_o"].shape, out["gem_o_cap_win"].shape, out["blocks_used"].shape)
+
+
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--ref", default=os.environ.get("RK_REFERENCE_DIR", "/root/reference"))
@@ -122,3 +176,4 @@ if __name__ == "__main__":
     make_simt_quant_kat(ref)
     make_golden_py_vectors(ref)
     make_rope_vectors(ref)
+    make_attn_fp32_ref_vectors(ref)

@@ -101,3 +101,73 @@ def test_rope_matches_reference_rope_apply():
         perm = np.random.default_rng(d).permutation(x.shape[0]).astype(np.int32)
         got = oracle.rope(x[perm], perm, c, s)
         assert np.array_equal(got.view(np.uint32), y[perm].view(np.uint32)), d
+
+
+def test_p_requant_rule_matches_the_reference_kernel_helpers():
+    """The oracle's P rule (block scale = floor(log2 pmax) clamped <= 0; element truncated to E4M3 under that scale,
+    flushed below 2^-6, saturated at 448) against the reference attention kernel's own helpers
+    bf16_floor_log2 / bf16_to_e4m3_scaled (kernels/flash_attention_mx_gqa/flash_mx_impl.hpp:53-77) compiled from the
+    reference tree: every non-negative finite bf16 value, every block exponent a softmax can produce."""
+    R = oracle.ref_requant()
+    if R is None:
+        pytest.skip("oracle/_ref not built (reference tree absent)")
+    L = oracle.lib()
+    bits = np.arange(0, 0x7F80, dtype=np.uint32)                 # +0 .. largest finite bf16
+    vals = (bits << 16).view(np.float32)
+    for b, v in zip(bits[::7], vals[::7]):                       # block scale on a 1-in-7 sample of all bf16 values
+        se = min(R.ref_bf16_floor_log2(int(b)), 0)
+        assert L.rko_p_block_scale_code(float(v)) == se + 127, hex(int(b))
+    bad = 0
+    for se in (0, -1, -2, -5, -6, -7, -13, -30, -100, -126):
+        for b, v in zip(bits[::3], vals[::3]):
+            if L.rko_p_code(float(v), se + 127) != R.ref_bf16_to_e4m3_scaled(int(b), se):
+                bad += 1
+    assert bad == 0
+
+
+def test_fp32_attention_reference_matches_the_reference_models():
+    """oracle.attn_fp32_ref (causal mask with a query offset, GQA head map, soft-cap before the mask, sliding window)
+    against the reference's own pure-fp32 attention references, attention_reference_causal_gqa and
+    attention_reference_gemma (tests/golden/attn_fp32_ref_vectors.npz, made by importing the reference's model
+    files).  fp32 tolerance: the two sum in different orders."""
+    z = np.load(os.path.join(G, "attn_fp32_ref_vectors.npz"))
+    d = z["gqa_q"].shape[-1]
+    o = oracle.attn_fp32_ref(z["gqa_q"][None], z["gqa_k"][None], z["gqa_v"][None], causal=True, softmax_scale=d ** -0.5,
+                             q_pos0=int(z["gqa_meta"][0]))
+    assert np.abs(o[0] - z["gqa_o"]).max() <= 2e-6 * max(1.0, np.abs(z["gqa_o"]).max())
+    q_pos0, window = int(z["gem_meta"][0]), int(z["gem_meta"][1])
+    cap = float(z["gem_cap"][0])
+    o = oracle.attn_fp32_ref(z["gem_q"][None], z["gem_k"][None], z["gem_v"][None], causal=True, softmax_scale=d ** -0.5,
+                             q_pos0=q_pos0, window=window, softcap=cap)
+    assert np.abs(o[0] - z["gem_o_cap_win"]).max() <= 5e-6 * max(1.0, np.abs(z["gem_o_cap_win"]).max())
+    o = oracle.attn_fp32_ref(z["gem_q"][None], z["gem_k"][None], z["gem_v"][None], causal=True, softmax_scale=d ** -0.5,
+                             q_pos0=q_pos0, softcap=cap)
+    assert np.abs(o[0] - z["gem_o_cap"]).max() <= 5e-6 * max(1.0, np.abs(z["gem_o_cap"]).max())
+    # the masks those references use, restated: masked iff key > q_pos0 + row, or (window) key <= q_pos0 + row - window
+    Sq, Sk = z["gem_mask"].shape
+    qpos = q_pos0 + np.arange(Sq)[:, None]
+    kpos = np.arange(Sk)[None, :]
+    assert np.array_equal(z["gem_mask"], (kpos > qpos) | (kpos <= qpos - window))
+    # blocks_used: leading key blocks not wholly above the diagonal = min(Nblk, max_qpos // block_n + 1)
+    for sq, sk, qp, bn, want in z["blocks_used"]:
+        assert min(sk // bn, (qp + sq - 1) // bn + 1) == want
+
+
+def test_mx_oracle_tracks_the_pinned_fp32_reference():
+    """The MX attention oracle on the same inputs (quantized with the pinned block quantizer) stays within MX
+    quantization error of the reference's fp32 output, with the query offset, GQA map, soft-cap and sliding window
+    in play: a mask or head-map disagreement between the two paths would show as an O(1) error."""
+    z = np.load(os.path.join(G, "attn_fp32_ref_vectors.npz"))
+    # the Gemma case scales Q by 20 so that the cap bites: its rows are peaked and quantization error moves weight
+    # between near-tied keys, hence the looser bound
+    for tag, want, tol, kw in (("gqa", z["gqa_o"], 0.08, dict(q_pos0=int(z["gqa_meta"][0]))),
+                               ("gem", z["gem_o_cap_win"], 0.25, dict(q_pos0=int(z["gem_meta"][0]), window=int(z["gem_meta"][1]),
+                                                                      softcap=float(z["gem_cap"][0])))):
+        Q, K, V = z[tag + "_q"], z[tag + "_k"], z[tag + "_v"]
+        d = Q.shape[-1]
+        quant = lambda t: [np.stack(x) for x in zip(*[oracle.quantize(m) for m in t])]
+        qc, qs = quant(Q); kc, ks = quant(K); vc, vs = quant(V)
+        r = oracle.attn_prefill(qc[None], kc[None], vc[None], qs[None], ks[None], vs[None], causal=True,
+                                softmax_scale=d ** -0.5, block_n=128, **kw)
+        rel = np.linalg.norm(r["o_f32"][0] - want) / np.linalg.norm(want)
+        assert rel < tol, (tag, rel)
