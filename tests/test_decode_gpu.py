@@ -52,6 +52,28 @@ def test_ragged_kv_len_and_splits():
     run(1, 4, 1, 132, lens=[129], num_splits=2, seed=5)
 
 
+def test_empty_and_tiny_sequences():
+    """kv_len 0 gives O = 0 and LSE = -inf (the l <= 0 guard); lengths below one key tile and one key short of it."""
+    g = torch.Generator(device="cuda").manual_seed(12)
+    q = torch.randn(4, 8, 128, generator=g, device="cuda").bfloat16()
+    K = torch.randn(4, 2, 256, 128, generator=g, device="cuda")
+    V = torch.randn(4, 2, 256, 128, generator=g, device="cuda")
+    kc, ks = rk.mx_quantize(K); vc, vs = rk.mx_quantize(V)
+    lens = [0, 5, 127, 129]
+    kl = torch.tensor(lens, dtype=torch.int32, device="cuda")
+    lse = torch.empty(4, 8, dtype=torch.float32, device="cuda")
+    o = rk.attn_decode(q, kc, vc, ks, vs, kv_len=kl, lse=lse)
+    torch.cuda.synchronize()
+    assert rk.last_device_status() == 0
+    ref = oracle.attn_decode(np_(q.view(torch.uint16)), np_(kc), np_(vc), np_(ks), np_(vs), softmax_scale=128 ** -0.5,
+                             kv_len=np.array(lens, np.int32), want_lse=True)
+    got = np_(o.float())
+    assert np.all(got[0] == 0.0) and np.all(np.isneginf(np_(lse)[0]))
+    ma, rl = errors(got, ref["o_f32"])
+    assert ma <= MAX_ABS and rl <= REL_L2, (ma, rl)
+    assert np.abs(np_(lse)[1:] - ref["lse"][1:]).max() < 2e-3
+
+
 def test_split_count_does_not_change_result_much():
     a, _ = run(1, 8, 2, 8192, num_splits=1, seed=6)
     b, _ = run(1, 8, 2, 8192, num_splits=8, seed=6)
