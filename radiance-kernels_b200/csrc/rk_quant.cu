@@ -62,6 +62,9 @@ __global__ void verify_encoder_kernel(uint64_t first, uint64_t count, unsigned l
   if (bad) atomicAdd(mismatches, bad);
 }
 
+#ifndef RK_QUANT_UNROLL
+#define RK_QUANT_UNROLL 1
+#endif
 // BF16IN: the input is bf16 (one 16-byte load per chunk, widened exactly to fp32) instead of fp32.
 template <int FMT, bool BF16IN = false>
 __global__ void __launch_bounds__(256) quantize_rows_kernel(const float4* __restrict__ x, int64_t nchunks,
@@ -72,41 +75,53 @@ __global__ void __launch_bounds__(256) quantize_rows_kernel(const float4* __rest
   // 4-lane group is either wholly live or wholly idle).
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   const int lane = threadIdx.x & 31;
-  for (int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; c - lane < nchunks; c += stride) {
-    const bool live = c < nchunks;
-    float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
-    if (live) {
-      if (BF16IN) {
-        const float4 raw = __ldcs(x + c);                      // 8 bf16
-        const uint32_t w[4] = {__float_as_uint(raw.x), __float_as_uint(raw.y), __float_as_uint(raw.z), __float_as_uint(raw.w)};
-        a = make_float4(__uint_as_float(w[0] << 16), __uint_as_float(w[0] & 0xFFFF0000u), __uint_as_float(w[1] << 16), __uint_as_float(w[1] & 0xFFFF0000u));
-        b = make_float4(__uint_as_float(w[2] << 16), __uint_as_float(w[2] & 0xFFFF0000u), __uint_as_float(w[3] << 16), __uint_as_float(w[3] & 0xFFFF0000u));
-      } else {
-        a = __ldcs(x + 2 * c); b = __ldcs(x + 2 * c + 1);
+  // RK_QUANT_UNROLL chunks per trip, their loads issued together (more bytes in flight per thread).
+  constexpr int U = RK_QUANT_UNROLL;
+  for (int64_t c0 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; c0 - lane < nchunks; c0 += U * stride) {
+    float4 a[U], b[U];
+#pragma unroll
+    for (int u = 0; u < U; u++) {
+      const int64_t c = c0 + u * stride;
+      a[u] = make_float4(0.f, 0.f, 0.f, 0.f); b[u] = a[u];
+      if (c < nchunks) {
+        if (BF16IN) {
+          const float4 raw = __ldcs(x + c);                      // 8 bf16
+          const uint32_t w[4] = {__float_as_uint(raw.x), __float_as_uint(raw.y), __float_as_uint(raw.z), __float_as_uint(raw.w)};
+          a[u] = make_float4(__uint_as_float(w[0] << 16), __uint_as_float(w[0] & 0xFFFF0000u), __uint_as_float(w[1] << 16), __uint_as_float(w[1] & 0xFFFF0000u));
+          b[u] = make_float4(__uint_as_float(w[2] << 16), __uint_as_float(w[2] & 0xFFFF0000u), __uint_as_float(w[3] << 16), __uint_as_float(w[3] & 0xFFFF0000u));
+        } else {
+          a[u] = __ldcs(x + 2 * c); b[u] = __ldcs(x + 2 * c + 1);
+        }
       }
     }
-    const float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
-    float amax = 0.0f, nonfinite = 0.0f;
 #pragma unroll
-    for (int j = 0; j < 8; j++) {
-      amax = fmaxf(amax, fabsf(v[j]));          // a NaN never wins, as in the reference's compare loop
-      nonfinite = fmaf(v[j], 0.0f, nonfinite);  // stays 0 unless an element is NaN or +-inf
+    for (int u = 0; u < U; u++) {
+      const int64_t c = c0 + u * stride;
+      if (c - lane >= nchunks) break;                            // warp-uniform: the shuffles below need whole warps
+      const bool live = c < nchunks;
+      const float v[8] = {a[u].x, a[u].y, a[u].z, a[u].w, b[u].x, b[u].y, b[u].z, b[u].w};
+      float amax = 0.0f, nonfinite = 0.0f;
+#pragma unroll
+      for (int j = 0; j < 8; j++) {
+        amax = fmaxf(amax, fabsf(v[j]));          // a NaN never wins, as in the reference's compare loop
+        nonfinite = fmaf(v[j], 0.0f, nonfinite);  // stays 0 unless an element is NaN or +-inf
+      }
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+      if (!live) continue;
+      uint32_t scode = 0; float p2 = 1.0f;
+      if (amax > 0.0f) block_scale<FMT>(amax, scode, p2);
+      uint32_t w0, w1;
+      if (nonfinite == 0.0f) {
+        w0 = hw_encode4<FMT>(v[0] * p2, v[1] * p2, v[2] * p2, v[3] * p2);
+        w1 = hw_encode4<FMT>(v[4] * p2, v[5] * p2, v[6] * p2, v[7] * p2);
+      } else {
+        w0 = ref_encode4<FMT>(v[0] * p2, v[1] * p2, v[2] * p2, v[3] * p2);
+        w1 = ref_encode4<FMT>(v[4] * p2, v[5] * p2, v[6] * p2, v[7] * p2);
+      }
+      __stcs(codes + c, make_uint2(w0, w1));
+      if ((c & 3) == 0) scales[c >> 2] = (uint8_t)scode;
     }
-    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-    if (!live) continue;
-    uint32_t scode = 0; float p2 = 1.0f;
-    if (amax > 0.0f) block_scale<FMT>(amax, scode, p2);
-    uint32_t w0, w1;
-    if (nonfinite == 0.0f) {
-      w0 = hw_encode4<FMT>(v[0] * p2, v[1] * p2, v[2] * p2, v[3] * p2);
-      w1 = hw_encode4<FMT>(v[4] * p2, v[5] * p2, v[6] * p2, v[7] * p2);
-    } else {
-      w0 = ref_encode4<FMT>(v[0] * p2, v[1] * p2, v[2] * p2, v[3] * p2);
-      w1 = ref_encode4<FMT>(v[4] * p2, v[5] * p2, v[6] * p2, v[7] * p2);
-    }
-    __stcs(codes + c, make_uint2(w0, w1));
-    if ((c & 3) == 0) scales[c >> 2] = (uint8_t)scode;
   }
 }
 
