@@ -317,7 +317,7 @@ int rk_rope_mx_quantize(const float* x, int64_t rows, int32_t d, const int32_t* 
   if (!x || !cos_half || !sin_half || !codes || !scales) return RK_ERR_NULL_POINTER;
   if (rows < 0 || d <= 0 || d % 64 != 0 || n_pos <= 0) return RK_ERR_BAD_SHAPE;      // both halves are whole blocks
   if (!pos && (seq_len <= 0 || pos0 < 0 || (int64_t)pos0 + seq_len > n_pos)) return RK_ERR_BAD_SHAPE;
-  if (fmt < 0 || fmt > 3) return RK_ERR_UNSUPPORTED;
+  if (fmt < 0 || fmt > 3) return RK_ERR_BAD_FORMAT;
   if (!aligned(x, 16) || !aligned(cos_half, 16) || !aligned(sin_half, 16) || !aligned(codes, 8)) return RK_ERR_MISALIGNED;
   return launch_rope_quantize_rows(x, rows, d, pos, seq_len, pos0, cos_half, sin_half, fmt, codes, scales, (cudaStream_t)stream);
 }
@@ -327,7 +327,7 @@ int rk_kv_cache_append(const float* k_new, const float* v_new, int32_t B, int32_
                        uint8_t* v_scales, void* stream) {
   if (!k_new || !v_new || !pos || !k_codes || !k_scales || !v_codes || !v_scales) return RK_ERR_NULL_POINTER;
   if (B < 0 || H_kv < 0 || L <= 0 || d <= 0 || d % 32 != 0) return RK_ERR_BAD_SHAPE;
-  if (fmt < 0 || fmt > 3) return RK_ERR_UNSUPPORTED;
+  if (fmt < 0 || fmt > 3) return RK_ERR_BAD_FORMAT;
   if (!aligned(k_new, 16) || !aligned(v_new, 16) || !aligned(k_codes, 8) || !aligned(v_codes, 8)) return RK_ERR_MISALIGNED;
   return launch_kv_append(k_new, v_new, B, H_kv, L, d, pos, fmt, k_codes, k_scales, v_codes, v_scales, (cudaStream_t)stream);
 }

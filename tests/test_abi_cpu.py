@@ -103,6 +103,29 @@ def test_quantizer_argument_errors():
     assert L.rk_mx_quantize(4100, 4, 64, 0, 4096, 4096, None) == -5
 
 
+def test_producer_and_cache_entry_points_reject_bad_arguments():
+    L = rk.lib()
+    ok = 4096                                              # an aligned, non-null stand-in pointer; nothing is launched
+    # bf16 quantizer: same rules as the fp32 one
+    assert L.rk_mx_quantize_bf16(None, 4, 32, 0, None, None, None) == -1
+    assert L.rk_mx_quantize_bf16(ok, 4, 48, 0, ok, ok, None) == -2
+    assert L.rk_mx_quantize_bf16(ok, 4, 64, 5, ok, ok, None) == -3
+    assert L.rk_mx_quantize_bf16(ok + 2, 4, 64, 0, ok, ok, None) == -5
+    # RoPE + quantizer: d must be a multiple of 64, positions inside the caches
+    assert L.rk_rope_mx_quantize(None, 4, 128, None, 4, 0, ok, ok, 16, 0, ok, ok, None) == -1
+    assert L.rk_rope_mx_quantize(ok, 4, 96, None, 4, 0, ok, ok, 16, 0, ok, ok, None) == -2
+    assert L.rk_rope_mx_quantize(ok, 4, 128, None, 0, 0, ok, ok, 16, 0, ok, ok, None) == -2      # no pos list and no seq_len
+    assert L.rk_rope_mx_quantize(ok, 4, 128, None, 12, 8, ok, ok, 16, 0, ok, ok, None) == -2     # pos0 + seq_len > n_pos
+    assert L.rk_rope_mx_quantize(ok, 4, 128, None, 4, 0, ok, ok, 16, 7, ok, ok, None) == -3
+    assert L.rk_rope_mx_quantize(ok + 4, 4, 128, None, 4, 0, ok, ok, 16, 0, ok, ok, None) == -5
+    # KV-cache append
+    assert L.rk_kv_cache_append(None, ok, 1, 1, 128, 128, ok, 0, ok, ok, ok, ok, None) == -1
+    assert L.rk_kv_cache_append(ok, ok, 1, 1, 128, 100, ok, 0, ok, ok, ok, ok, None) == -2
+    assert L.rk_kv_cache_append(ok, ok, 1, 1, 0, 128, ok, 0, ok, ok, ok, ok, None) == -2
+    assert L.rk_kv_cache_append(ok, ok, 1, 1, 128, 128, ok, 4, ok, ok, ok, ok, None) == -3
+    assert L.rk_kv_cache_append(ok + 4, ok, 1, 1, 128, 128, ok, 0, ok, ok, ok, ok, None) == -5
+
+
 def test_no_cpu_fallback():
     """The product path has no CPU route: calling it with CPU tensors raises instead of computing."""
     import torch
