@@ -62,9 +62,6 @@ __global__ void verify_encoder_kernel(uint64_t first, uint64_t count, unsigned l
   if (bad) atomicAdd(mismatches, bad);
 }
 
-#ifndef RK_QUANT_UNROLL
-#define RK_QUANT_UNROLL 1
-#endif
 // BF16IN: the input is bf16 (one 16-byte load per chunk, widened exactly to fp32) instead of fp32.
 template <int FMT, bool BF16IN = false>
 __global__ void __launch_bounds__(256) quantize_rows_kernel(const float4* __restrict__ x, int64_t nchunks,
@@ -75,8 +72,9 @@ __global__ void __launch_bounds__(256) quantize_rows_kernel(const float4* __rest
   // 4-lane group is either wholly live or wholly idle).
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   const int lane = threadIdx.x & 31;
-  // RK_QUANT_UNROLL chunks per trip, their loads issued together (more bytes in flight per thread).
-  constexpr int U = RK_QUANT_UNROLL;
+  // U chunks per trip, their loads issued together: the bf16 path loads half the bytes per chunk and gains 7 %
+  // from two chunks in flight (measured); the fp32 path does not.
+  constexpr int U = BF16IN ? 2 : 1;
   for (int64_t c0 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; c0 - lane < nchunks; c0 += U * stride) {
     float4 a[U], b[U];
 #pragma unroll
