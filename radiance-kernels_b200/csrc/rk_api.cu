@@ -250,8 +250,13 @@ int rk_attn_prefill_host(const rk_prefill_args* h, void* arena, size_t arena_byt
 
   // chunks: whole batches when there are many, ranges of KV heads inside a batch when there are few
   const int grp = h->H / h->H_kv;
-  const int batches_per_chunk = h->B >= 8 ? (h->B + 7) / 8 : 1;
-  const int chunks_per_batch = h->B >= 8 ? 1 : std::max(1, std::min(h->H_kv, 8 / h->B));
+#ifndef RK_HOST_CHUNKS
+#define RK_HOST_CHUNKS 8
+#endif
+  constexpr int kTarget = RK_HOST_CHUNKS;              // chunks aimed at (<= kHostMaxChunks): more chunks, shorter pipeline head and tail
+  static_assert(kTarget <= kHostMaxChunks, "event pool");
+  const int batches_per_chunk = h->B >= kTarget ? (h->B + kTarget - 1) / kTarget : 1;
+  const int chunks_per_batch = h->B >= kTarget ? 1 : std::max(1, std::min(h->H_kv, kTarget / h->B));
   const int kv_per_chunk = (h->H_kv + chunks_per_batch - 1) / chunks_per_batch;
 
   if ((e = cudaEventRecord(hp.start, st)) != cudaSuccess) return (int)e;
