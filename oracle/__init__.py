@@ -78,6 +78,8 @@ def lib():
         for n in ("rko_dequant_rows", "rko_dequant_cols"):
             getattr(L, n).restype = None
             getattr(L, n).argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int, C.c_void_p]
+        L.rko_quantize_rows_mxgolden.restype = None
+        L.rko_quantize_rows_mxgolden.argtypes = [C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p]
         L.rko_rope_rows.restype = None
         L.rko_rope_rows.argtypes = [C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
         L.rko_rebase_v.restype = None
@@ -135,6 +137,23 @@ def _p(a):
 
 def hardware_threads():
     return lib().rko_hardware_threads()
+
+
+def quantize_mxgolden(x):
+    """The reference's other rule (requant post-pass of lib/golden/mx_golden.cpp) on fp32 rows [rows, cols], cols a
+    multiple of 32: scale = floor(log2 amax) - 8, elements RNE with subnormals flushed.  Oracle mode only."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    rows, cols = x.shape
+    codes = np.empty((rows, cols), np.uint8)
+    scales = np.empty((rows, cols // 32), np.uint8)
+    lib().rko_quantize_rows_mxgolden(_p(x), rows, cols, _p(codes), _p(scales))
+    return codes, scales
+
+
+def ref_mx_golden_path():
+    """Path of the reference's mx_golden program built under oracle/_ref, or None."""
+    exe = _HERE / "_ref" / "mx_golden"
+    return str(exe) if exe.exists() else None
 
 
 def rope(x, pos, cos_half, sin_half):

@@ -171,3 +171,40 @@ def test_mx_oracle_tracks_the_pinned_fp32_reference():
                                 softmax_scale=d ** -0.5, block_n=128, **kw)
         rel = np.linalg.norm(r["o_f32"][0] - want) / np.linalg.norm(want)
         assert rel < tol, (tag, rel)
+
+
+def test_mx_golden_requant_rule_against_the_reference_program(tmp_path):
+    """oracle.quantize_mxgolden against the reference's own mx_golden program (built under oracle/_ref from
+    lib/golden/mx_golden.cpp): an identity-times-B matmul makes C = B's values, the program is run once for C in bf16
+    and once with its requant post-pass (MX_OUT_FMT=0); codes and scale codes must match bit for bit."""
+    import subprocess
+    exe = oracle.ref_mx_golden_path()
+    if exe is None:
+        pytest.skip("oracle/_ref not built (reference tree absent)")
+    rng = np.random.default_rng(9)
+    M = N = K = 32
+    A = np.zeros((M, K), np.uint8)
+    A[np.arange(M), np.arange(K)] = 0x38                      # 1.0
+    expo = rng.integers(1, 15, (K, N)).astype(np.uint8)       # normal codes only: no e4m3 subnormals in the mesh
+    Bc = ((rng.integers(0, 2, (K, N)) << 7) | (expo << 3) | rng.integers(0, 8, (K, N))).astype(np.uint8)
+    Bc[3, :] = 0                                              # a zero row of C
+    Bc[5, 4:] = 0x08                                          # a row with one dominant element and many tiny ones
+    Bc[5, 0] = 0x66                                          # 12.0: large against 2^-6, small enough for the mesh accumulator
+    sa = np.full((1, M), 127, np.uint8)
+    sb = rng.integers(121, 133, (1, N)).astype(np.uint8)
+    names = {}
+    for n, arr in (("A", A), ("B", Bc), ("SA", sa), ("SB", sb)):
+        names[n] = str(tmp_path / (n + ".bin"))
+        arr.tofile(names[n])
+    cbin, qbin, sbin = str(tmp_path / "C.bin"), str(tmp_path / "Q.bin"), str(tmp_path / "S.bin")
+    args = [exe, str(M), str(N), str(K), names["A"], names["B"], names["SA"], names["SB"]]
+    env = {k: v for k, v in os.environ.items() if not k.startswith("MX_")}
+    subprocess.run(args + [cbin], check=True, env=env)
+    subprocess.run(args + [qbin], check=True, env=dict(env, MX_OUT_FMT="0", MX_SCALES_OUT=sbin))
+    C = (np.fromfile(cbin, np.uint16).astype(np.uint32) << 16).view(np.float32).reshape(M, N)
+    want_codes = np.fromfile(qbin, np.uint8).reshape(M, N)
+    want_scales = np.fromfile(sbin, np.uint8).reshape(M, N // 32)
+    assert np.count_nonzero(C) > 900                          # the matmul really produced B's values
+    codes, scales = oracle.quantize_mxgolden(C)
+    assert np.array_equal(scales, want_scales)
+    assert np.array_equal(codes, want_codes)
