@@ -47,7 +47,7 @@ def prefill_algorithmic_bytes(c):
 # DRAM traffic of one launch from the ncu captures summarised under profiles/ (dram__bytes_read.sum +
 # dram__bytes_write.sum), per unit of work; both kernels' traffic is proportional to the unit count.
 NCU_PREFILL_DRAM_BYTES_PER_HEAD = (103.966976e6 + 34.787584e6) / 64        # S=4096, d=128, causal
-NCU_DECODE_DRAM_BYTES_PER_SEQUENCE = (553.774080e6 + 7.930112e6) / 8        # H_kv=8, L=32768, d=128
+NCU_DECODE_DRAM_BYTES_PER_SEQUENCE = (553.775104e6 + 6.571264e6) / 8        # H_kv=8, L=32768, d=128
 
 
 def decode_bytes(c):
@@ -338,7 +338,7 @@ def main():
                   "roofline": {"bound": "hbm", "achieved": by / (dk * 1e-3) / 1e9, "peak": peaks["hbm"], "unit": "GB/s",
                                "frac": by / (dk * 1e-3) / 1e9 / peaks["hbm"],
                                "traffic": NCU_DECODE_DRAM_BYTES_PER_SEQUENCE * Bd if (Hkd, Ld, dd) == (8, 32768, 128) else None,
-                               "traffic_note": "ncu dram read+write of one launch at B=8 (561.70 MB), scaled by B",
+                               "traffic_note": "ncu dram read+write of one launch at B=8 (560.35 MB), scaled by B",
                                "kernel": "decode_tc_kernel",
                                "kernel_ms": dk, "peak_note": f"{peaks['source']} HBM copy bandwidth; nominal 8000 GB/s"}}
         if rk.last_device_status() != 0:
