@@ -22,6 +22,7 @@
 // Roofline: tensor-core bound by FLOP count (4*S_q*S_kv*d per head, half of it
 // when causal); in practice the softmax/requant ALU work per S element bounds it.
 #include <cuda.h>
+#include <algorithm>
 #include <cuda_bf16.h>
 
 #include "rk_common.cuh"
@@ -124,7 +125,7 @@ __device__ __forceinline__ void softmax_rows(const PrefillParams& p, uint8_t* sm
     if (lane == 0) mbar_arrive(s_empty);        // one arrival per warp: S may be overwritten once all 16 have read
     if (lane == 0 && sslot < 2) RK_STAMP(sslot, j, 2);
 
-    if (p.dbg && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && j == 0) {
+    if (p.dbg && qt == p.n_q_tiles - 1 && bh == 0 && j == 0) {
 #pragma unroll
       for (int c = 0; c < 32; ++c) p.dbg[row * 128 + part * 32 + c] = s[c];
     }
@@ -227,7 +228,7 @@ __device__ __forceinline__ void softmax_rows(const PrefillParams& p, uint8_t* sm
     l_run = l_run * corr + ((ls0 + ls1) + (ls2 + ls3));
     smem[L::sfp_off + pb * kSfAtomBytes + (row & 31) * 16 + (row >> 5) * 4 + part] = (uint8_t)sc;
 
-    if (p.dbg && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && j == 0) {
+    if (p.dbg && qt == p.n_q_tiles - 1 && bh == 0 && j == 0) {
       // P codes as written (un-swizzled view) and the scale bytes, after the 128x128 S dump
       uint32_t* d32 = reinterpret_cast<uint32_t*>(p.dbg + 128 * 128);
 #pragma unroll
@@ -291,7 +292,7 @@ __device__ __forceinline__ void softmax_rows(const PrefillParams& p, uint8_t* sm
     const bool live = q_row < p.S_q;
     __nv_bfloat16* orow = p.o + ((size_t)bh * p.S_q + q_row) * p.d;
     const int ncols = p.d / kParts;                 // 16, 32 or 64 output columns per thread
-    if (p.dbg && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && part == 0) {
+    if (p.dbg && qt == p.n_q_tiles - 1 && bh == 0 && part == 0) {
       p.dbg[128 * 128 + 128 * 32 + 128 + row * 2 + 0] = m_run;
       p.dbg[128 * 128 + 128 * 32 + 128 + row * 2 + 1] = l_tot;
     }
@@ -348,8 +349,14 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
   // an earlier launch on this device gave up on a wait: do nothing until the host has read the status
   if (*reinterpret_cast<volatile int*>(p.status) != 0) return;
   // heavy (late) query tiles first within a head; heads adjacent so a KV head's tiles share L2
-  const int qt = p.n_q_tiles - 1 - (int)blockIdx.x;
-  const int h = blockIdx.y, b = blockIdx.z;
+  // work order: see PrefillParams::head_group (heaviest query tiles of a whole group of heads first)
+  const int n_bh = p.B * p.H;
+  const int per_group = p.n_q_tiles * p.head_group;
+  const int grp_i = (int)blockIdx.x / per_group, r = (int)blockIdx.x % per_group;
+  const int heads_here = min(p.head_group, n_bh - grp_i * p.head_group);
+  const int qt = p.n_q_tiles - 1 - r / heads_here;
+  const int bh_lin = grp_i * p.head_group + r % heads_here;
+  const int h = bh_lin % p.H, b = bh_lin / p.H;
   const int bh = b * p.H + h;
   const int bhkv = b * p.H_kv + h / (p.H / p.H_kv);
 
@@ -594,7 +601,15 @@ int launch_prefill(const rk_prefill_args& a, const uint8_t* q_codes, const uint8
   p.lse = a.lse;
   p.status = device_status_word();
   p.dbg = g_prefill_dbg;
-  p.H = a.H; p.H_kv = a.H_kv; p.S_q = a.S_q; p.S_kv = a.S_kv; p.d = a.d;
+  p.B = a.B; p.H = a.H; p.H_kv = a.H_kv; p.S_q = a.S_q; p.S_kv = a.S_kv; p.d = a.d;
+  {
+    // heads whose K and V (shared by the query heads of a KV head) fit in about 100 MB of L2, in equal groups
+    const double per_head = 2.0 * a.S_kv * a.d * ((double)a.H_kv / a.H);
+    const int n_bh = a.B * a.H;
+    const int fit = (int)std::max(8.0, 100.0e6 / std::max(per_head, 1.0));
+    const int ngroups = (n_bh + fit - 1) / fit;
+    p.head_group = (n_bh + ngroups - 1) / ngroups;
+  }
   p.n_q_tiles = (a.S_q + kBlockM - 1) / kBlockM;
   p.n_kv_tiles = (a.S_kv + kBlockN - 1) / kBlockN;
   p.q_pos0 = a.q_pos0; p.causal = a.causal; p.window = a.window;
@@ -608,7 +623,7 @@ int launch_prefill(const rk_prefill_args& a, const uint8_t* q_codes, const uint8
 
   const uint32_t idesc_qk = make_idesc(a.q_fmt, a.kv_fmt, false, false, 128, 128);
   const uint32_t idesc_pv = make_idesc(RK_FMT_E4M3, a.kv_fmt, false, /*B MN-major*/ !kv6, 128, 128);
-  dim3 grid(p.n_q_tiles, a.H, a.B);
+  dim3 grid(p.n_q_tiles * a.H * a.B, 1, 1);
   const bool cap = a.softcap > 0.0f;
   if (a.d <= 128) return launch_prefill2q(tq, tk, tv, p, idesc_qk, idesc_pv, cap, a.B, st);   // two query tiles per CTA
   return cap ? launch_cfg<2, 2, true>(tq, tk, tv, p, idesc_qk, idesc_pv, grid, st)

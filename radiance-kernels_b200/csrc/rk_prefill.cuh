@@ -33,8 +33,9 @@ struct PrefillParams {
   float* lse;
   int* status;
   float* dbg;          // optional stage dump of CTA (0,0,0), first key tile
-  int H, H_kv, S_q, S_kv, d;
+  int B, H, H_kv, S_q, S_kv, d;
   int n_q_tiles, n_kv_tiles;
+  int head_group;      // (batch, head) pairs per work-order group: the heaviest query tiles of a whole group run first
   int q_pos0, causal, window;
   int q_tile_tx, kv_tile_tx;   // bytes one Q / K / V tile load adds to its mbarrier: 16384, or 12288 for 6-bit tensors
                                // (the transaction counts the packed source bytes, not the padded shared-memory image)
