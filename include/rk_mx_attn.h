@@ -60,6 +60,19 @@ enum { RK_FMT_E4M3 = 0, RK_FMT_E5M2 = 1, RK_FMT_E2M3 = 2, RK_FMT_E3M2 = 3 };
  *       V is re-blocked along the keys into the workspace before the kernel runs. */
 enum { RK_V_SCALES_ALONG_KEYS = 0, RK_V_SCALES_ALONG_D = 1 };
 
+/* Where the block scales of a [S][d] matrix (blocks of 32 along d) sit in memory.
+ * ROWMAJOR  : [batch][S][d/32].
+ * GROUPMAJOR: [batch][d/32][S], the reference's own order for Q (QK_A_scales_row[FA_GK][FA_SQ] per head,
+ *             kernels/flash_attention_mx/gen_data.py:82-83; kernels/flash_attention_mx_gqa/fa_gen_data.py:101-104).
+ * SF_ATOMS  : [batch][ceil(S/128)][ceil(d/128)][512]: the scale-factor atoms the tensor core reads.  The atom of
+ *             row tile t and 128-column chunk c holds, at byte (r%32)*16 + (r/32)*4 + kb, the scale of row
+ *             128t + r, columns 128c + 32kb .. +31.  rk_mx_quantize_ex writes it; passing it to rk_attn_prefill
+ *             saves the two re-tiling launches of every call.  For V scaled along the keys the atom of key tile t
+ *             and chunk c holds, at byte (n%32)*16 + (n/32)*4 + kb, the scale of column 128c + n, keys
+ *             128t + 32kb .. +31 (rk_mx_quantize_keys_ex writes it).  Bytes that belong to rows or columns past
+ *             the matrix edge must hold a finite scale code (the quantizers write 0x7F there). */
+enum { RK_SCALES_ROWMAJOR = 0, RK_SCALES_GROUPMAJOR = 1, RK_SCALES_SF_ATOMS = 2 };
+
 RK_API const char* rk_error_string(int code);
 RK_API int rk_version(void);
 
@@ -83,6 +96,26 @@ RK_API int rk_mx_quantize_bf16(const void* x_bf16, int64_t rows, int64_t cols, i
                                uint8_t* codes, uint8_t* scales, void* stream);
 RK_API int rk_mx_quantize_keys(const float* x, int64_t batch, int64_t rows, int64_t cols, int fmt,
                         uint8_t* codes, uint8_t* scales, void* stream);
+/* The same two quantizers with a choice of scale layout (RK_SCALES_*), per matrix of a batch:
+ *   rk_mx_quantize_ex      x fp32 (x_is_bf16 = 0) or bf16 (1) [batch][S][d], blocks along d; codes [batch][S][d];
+ *                          scales in `scale_layout` (all three).  d a multiple of 32.
+ *   rk_mx_quantize_keys_ex x fp32 [batch][rows][cols], blocks down the rows; scales ROWMAJOR
+ *                          ([batch][ceil(rows/32)][cols]) or SF_ATOMS.
+ * SF_ATOMS output is 16-byte aligned atoms of 512 bytes; the call first fills bytes of ragged edges with 0x7F. */
+RK_API int rk_mx_quantize_ex(const void* x, int x_is_bf16, int64_t batch, int64_t S, int64_t d, int fmt,
+                             uint8_t* codes, uint8_t* scales, int scale_layout, void* stream);
+RK_API int rk_mx_quantize_keys_ex(const float* x, int64_t batch, int64_t rows, int64_t cols, int fmt,
+                                  uint8_t* codes, uint8_t* scales, int scale_layout, void* stream);
+
+/* Import of the reference's streaming K operand.  Its generator emits K per KV head and key block j as a
+ * transposed tile K^T [d][Bk] (QK_B_blocks[(kv*NBU + j)*FA_D][FA_BK]) with group-major scales
+ * (QK_B_scales_blocks[(kv*NBU + j)*FA_GK][FA_BK]) -- kernels/flash_attention_mx_gqa/fa_gen_data.py:110-117 -- a
+ * layout made for the Gemmini DMA.  This call turns `heads` x `n_blocks` such tiles into the natural layout
+ * rk_attn_prefill takes: k codes [heads][n_blocks*Bk][d], k scales [heads][n_blocks*Bk][d/32] (row-major).
+ * Bk and d multiples of 32. */
+RK_API int rk_import_kt_blocks(const uint8_t* kt_blocks, const uint8_t* kt_scale_blocks, int64_t heads,
+                               int32_t n_blocks, int32_t Bk, int32_t d, uint8_t* k_codes, uint8_t* k_scales,
+                               void* stream);
 
 /* Re-block V from scales along d to scales along the keys (decode exactly, then
  * the same block rule down each column).  No reference counterpart: the
@@ -107,9 +140,9 @@ typedef struct rk_prefill_args {
   const uint8_t* q;        /* codes [B][H][S_q][d]      (QK_A_in) */
   const uint8_t* k;        /* codes [B][H_kv][S_kv][d]  (QK_B_blocks, natural [key][d] order) */
   const uint8_t* v;        /* codes [B][H_kv][S_kv][d]  (V_in) */
-  const uint8_t* q_scale;  /* E8M0 [B][H][S_q][d/32]    (QK_A_scales_row, row-major) */
-  const uint8_t* k_scale;  /* E8M0 [B][H_kv][S_kv][d/32] */
-  const uint8_t* v_scale;  /* E8M0, layout chosen by v_scale_axis */
+  const uint8_t* q_scale;  /* E8M0, [B*H] matrices [S_q][d] in q_scale_layout (QK_A_scales_row as it lies = GROUPMAJOR) */
+  const uint8_t* k_scale;  /* E8M0, [B*H_kv] matrices [S_kv][d] in k_scale_layout */
+  const uint8_t* v_scale;  /* E8M0, axis chosen by v_scale_axis, layout by v_scale_layout */
   void* o;                 /* bf16 [B][H][S_q][d]  (O_GMEM, kernels/flash_attention_mx_gqa/kernel.cpp:50,115) */
   float* lse;              /* optional fp32 [B][H][S_q]: running max + log(l), natural log */
   int32_t B, H, H_kv, S_q, S_kv, d;   /* d in {64,128,256}; H % H_kv == 0 */
@@ -123,6 +156,9 @@ typedef struct rk_prefill_args {
   int32_t v_scale_axis;    /* RK_V_SCALES_ALONG_KEYS | RK_V_SCALES_ALONG_D */
   int32_t block_n;         /* keys per online-softmax step; 0 = default.  On return from
                               rk_attn_prefill_block_n() the value the kernel uses (128). */
+  int32_t q_scale_layout;  /* RK_SCALES_ROWMAJOR (0) | RK_SCALES_GROUPMAJOR | RK_SCALES_SF_ATOMS */
+  int32_t k_scale_layout;  /* same three */
+  int32_t v_scale_layout;  /* RK_SCALES_ROWMAJOR (0), or RK_SCALES_SF_ATOMS with v_scale_axis = RK_V_SCALES_ALONG_KEYS */
   void* workspace;         /* >= rk_attn_prefill_workspace_bytes(), 256-byte aligned */
   size_t workspace_bytes;
 } rk_prefill_args;
@@ -213,15 +249,19 @@ RK_API int rk_kv_cache_append(const float* k_new, const float* v_new, int32_t B,
  *     overwrite each other's partials: serialise them.
  *   - A bounded wait that gives up is recorded in a status word of its own inside the library image
  *     (rk_last_device_status() does not see it); it is sticky: later no-allocation launches on that
- *     device return without computing. */
+ *     device return without computing until rk_attn_decode_noalloc_status() has read and cleared it. */
 #define RK_DECODE_NOALLOC_SCRATCH_BYTES (5u << 20)
 RK_API int rk_attn_decode_noalloc(const rk_decode_args* a, void* stream);
+/* Status word of the no-allocation decode path on the current device: 0 = clean, otherwise the code of the
+ * wait that gave up (the output of that call and of every later one is not valid).  Synchronises the device,
+ * clears the word, allocates nothing.  No counterpart in the reference. */
+RK_API int rk_attn_decode_noalloc_status(void);
 
 /* Profiling aid (no reference counterpart): when both are non-NULL, the next rk_attn_prefill /
  * rk_attn_decode calls record cudaEvent_t `before` right before their main kernel (the tiled
  * attention kernel / the split-KV kernel) and `after` right after it, on the call's stream, so a
  * caller can time that kernel apart from the preparation passes.  Pass NULLs to switch it off. */
-RK_API void rk_profile_set_events(void* before, void* after);
+RK_API void rk_profile_set_events(void* before, void* after);   /* process-wide: set it while no other thread is in a call */
 
 /* Status word of the last kernel that ran on the current device: 0 = clean;
  * non-zero = a bounded wait inside a kernel gave up (the code says which) and

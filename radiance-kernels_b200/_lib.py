@@ -22,6 +22,7 @@ class PrefillArgs(C.Structure):
         ("q_pos0", C.c_int32), ("causal", C.c_int32), ("window", C.c_int32),
         ("softcap", C.c_float), ("softmax_scale", C.c_float),
         ("q_fmt", C.c_int32), ("kv_fmt", C.c_int32), ("v_scale_axis", C.c_int32), ("block_n", C.c_int32),
+        ("q_scale_layout", C.c_int32), ("k_scale_layout", C.c_int32), ("v_scale_layout", C.c_int32),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
     ]
 
@@ -43,6 +44,9 @@ SYMBOLS = {
     "rk_mx_quantize": (C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]),
     "rk_mx_quantize_bf16": (C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]),
     "rk_mx_quantize_keys": (C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "rk_mx_quantize_ex": (C.c_int, [C.c_void_p, C.c_int, C.c_int64, C.c_int64, C.c_int64, C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
+    "rk_mx_quantize_keys_ex": (C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
+    "rk_import_kt_blocks": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p]),
     "rk_mx_rebase_v": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]),
     "rk_attn_prefill_block_n": (C.c_int, [C.POINTER(PrefillArgs)]),
     "rk_attn_prefill_workspace_bytes": (C.c_size_t, [C.POINTER(PrefillArgs)]),
@@ -53,6 +57,7 @@ SYMBOLS = {
     "rk_attn_decode_workspace_bytes": (C.c_size_t, [C.POINTER(DecodeArgs)]),
     "rk_attn_decode": (C.c_int, [C.POINTER(DecodeArgs), C.c_void_p]),
     "rk_attn_decode_noalloc": (C.c_int, [C.POINTER(DecodeArgs), C.c_void_p]),
+    "rk_attn_decode_noalloc_status": (C.c_int, []),
     "rk_rope_mx_quantize": (C.c_int, [C.c_void_p, C.c_int64, C.c_int32, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p,
                                       C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p]),
     "rk_kv_cache_append": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_int32,
@@ -88,6 +93,13 @@ def lib():
         L.rk_debug_set_prefill_dump.argtypes = [C.c_void_p]
         L.rk_debug_set_decode_path.restype = None
         L.rk_debug_set_decode_path.argtypes = [C.c_int]
+        L.rk_debug_mxfp8_mma_loop.restype = C.c_int
+        L.rk_debug_mxfp8_mma_loop.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]
+        L.rk_debug_wait_runs_out.restype = C.c_int
+        L.rk_debug_wait_runs_out.argtypes = [C.c_int, C.c_int, C.c_void_p]
+        for name in ("rk_debug_set_prefill_path", "rk_debug_set_prefill_perturb"):
+            getattr(L, name).restype = None
+            getattr(L, name).argtypes = [C.c_int]
         _LIB = L
     return _LIB
 

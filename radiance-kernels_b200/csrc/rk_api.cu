@@ -9,21 +9,29 @@
 #include "rk_internal.h"
 
 namespace rk {
+extern int g_prefill_path, g_prefill_perturb;
+
+// The status word kernels record a given-up wait in: part of the library image (zero at load) on every device,
+// so it can never fail to allocate; its device address is looked up once per device.
+static __device__ int g_status_word;
 
 namespace {
 struct DeviceState { int sms = 0; int* status = nullptr; };
 std::mutex g_mu;
 DeviceState g_dev[64];
 
-DeviceState& dev_state() {
+DeviceState dev_state() {
   int dev = 0;
-  cudaGetDevice(&dev);
+  if (cudaGetDevice(&dev) != cudaSuccess) return DeviceState();
   std::lock_guard<std::mutex> lk(g_mu);
   DeviceState& s = g_dev[dev & 63];
-  if (s.sms == 0) {
-    cudaDeviceGetAttribute(&s.sms, cudaDevAttrMultiProcessorCount, dev);
-    if (s.sms <= 0) s.sms = 1;
-    if (cudaMalloc(&s.status, sizeof(int)) == cudaSuccess) cudaMemset(s.status, 0, sizeof(int));
+  if (s.sms == 0 || !s.status) {                 // a failed lookup is not cached: the next call tries again
+    int sms = 0;
+    void* ptr = nullptr;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) return DeviceState();
+    if (cudaGetSymbolAddress(&ptr, g_status_word) != cudaSuccess || !ptr) { cudaGetLastError(); return DeviceState(); }
+    s.sms = sms;
+    s.status = static_cast<int*>(ptr);
   }
   return s;
 }
@@ -31,7 +39,7 @@ size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
 }  // namespace
 
-int num_sms() { return dev_state().sms; }
+int num_sms() { const int n = dev_state().sms; return n > 0 ? n : 1; }
 int* device_status_word() { return dev_state().status; }
 
 extern float* g_prefill_dbg;
@@ -69,6 +77,12 @@ static int check_prefill_shape(const rk_prefill_args* a) {
   if (a->v_scale_axis != RK_V_SCALES_ALONG_KEYS && a->v_scale_axis != RK_V_SCALES_ALONG_D) return RK_ERR_BAD_FORMAT;
   if (a->q_fmt < 0 || a->q_fmt > 3 || a->kv_fmt < 0 || a->kv_fmt > 3) return RK_ERR_BAD_FORMAT;
   if (a->block_n != 0 && a->block_n != 128) return RK_ERR_UNSUPPORTED;
+  if (a->q_scale_layout < 0 || a->q_scale_layout > RK_SCALES_SF_ATOMS || a->k_scale_layout < 0 ||
+      a->k_scale_layout > RK_SCALES_SF_ATOMS)
+    return RK_ERR_BAD_FORMAT;
+  if (a->v_scale_layout != RK_SCALES_ROWMAJOR &&
+      !(a->v_scale_layout == RK_SCALES_SF_ATOMS && a->v_scale_axis == RK_V_SCALES_ALONG_KEYS))
+    return RK_ERR_BAD_FORMAT;
   return RK_OK;
 }
 
@@ -94,7 +108,7 @@ const char* rk_error_string(int code) {
   }
 }
 
-int rk_version(void) { return 100; }
+int rk_version(void) { return 200; }
 
 int rk_mx_quantize(const float* x, int64_t rows, int64_t cols, int fmt, uint8_t* codes, uint8_t* scales, void* stream) {
   if (!x || !codes || !scales) return RK_ERR_NULL_POINTER;
@@ -119,6 +133,49 @@ int rk_mx_quantize_keys(const float* x, int64_t batch, int64_t rows, int64_t col
   if (fmt < 0 || fmt > 3) return RK_ERR_BAD_FORMAT;
   if (!aligned(x, 16) || !aligned(codes, 4) || !aligned(scales, 4)) return RK_ERR_MISALIGNED;
   return launch_quantize_keys(x, batch, rows, cols, fmt, codes, scales, (cudaStream_t)stream);
+}
+
+int rk_mx_quantize_ex(const void* x, int x_is_bf16, int64_t batch, int64_t S, int64_t d, int fmt, uint8_t* codes,
+                      uint8_t* scales, int scale_layout, void* stream) {
+  if (!x || !codes || !scales) return RK_ERR_NULL_POINTER;
+  if (batch < 0 || S < 0 || d < 0 || d % 32 != 0) return RK_ERR_BAD_SHAPE;
+  if (fmt < 0 || fmt > 3) return RK_ERR_BAD_FORMAT;
+  if (scale_layout < 0 || scale_layout > RK_SCALES_SF_ATOMS) return RK_ERR_BAD_FORMAT;
+  if (!aligned(x, 16) || !aligned(codes, 8)) return RK_ERR_MISALIGNED;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (scale_layout == RK_SCALES_SF_ATOMS) {
+    if (!aligned(scales, 16)) return RK_ERR_MISALIGNED;
+    if (S % 128 != 0 || d % 128 != 0) {   // bytes of rows / blocks past the edge are never written by the kernel
+      const size_t bytes = (size_t)batch * ((S + 127) / 128) * ((d + 127) / 128) * 512;
+      cudaError_t e = cudaMemsetAsync(scales, 0x7F, bytes, st);
+      if (e != cudaSuccess) return (int)e;
+    }
+  }
+  return launch_quantize_rows_ex(x, x_is_bf16 != 0, batch, S, d, fmt, codes, scales, scale_layout, st);
+}
+
+int rk_mx_quantize_keys_ex(const float* x, int64_t batch, int64_t rows, int64_t cols, int fmt, uint8_t* codes,
+                           uint8_t* scales, int scale_layout, void* stream) {
+  if (scale_layout == RK_SCALES_ROWMAJOR) return rk_mx_quantize_keys(x, batch, rows, cols, fmt, codes, scales, stream);
+  if (scale_layout != RK_SCALES_SF_ATOMS) return RK_ERR_BAD_FORMAT;
+  if (!x || !codes || !scales) return RK_ERR_NULL_POINTER;
+  if (batch < 0 || rows < 0 || cols < 0 || cols % 4 != 0) return RK_ERR_BAD_SHAPE;
+  if (fmt < 0 || fmt > 3) return RK_ERR_BAD_FORMAT;
+  if (!aligned(x, 16) || !aligned(codes, 4) || !aligned(scales, 16)) return RK_ERR_MISALIGNED;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (rows % 128 != 0 || cols % 128 != 0) {
+    const size_t bytes = (size_t)batch * ((rows + 127) / 128) * ((cols + 127) / 128) * 512;
+    cudaError_t e = cudaMemsetAsync(scales, 0x7F, bytes, st);
+    if (e != cudaSuccess) return (int)e;
+  }
+  return launch_quantize_keys_atoms(x, batch, rows, cols, fmt, codes, scales, st);
+}
+
+int rk_import_kt_blocks(const uint8_t* kt_blocks, const uint8_t* kt_scale_blocks, int64_t heads, int32_t n_blocks,
+                        int32_t Bk, int32_t d, uint8_t* k_codes, uint8_t* k_scales, void* stream) {
+  if (!kt_blocks || !kt_scale_blocks || !k_codes || !k_scales) return RK_ERR_NULL_POINTER;
+  if (heads < 0 || n_blocks < 0 || Bk <= 0 || d <= 0 || Bk % 32 != 0 || d % 32 != 0) return RK_ERR_BAD_SHAPE;
+  return launch_import_kt_blocks(kt_blocks, kt_scale_blocks, heads, n_blocks, Bk, d, k_codes, k_scales, (cudaStream_t)stream);
 }
 
 int rk_mx_rebase_v(const uint8_t* codes, const uint8_t* scales, int64_t batch, int64_t S, int64_t d, int fmt,
@@ -148,8 +205,24 @@ int rk_attn_prefill(const rk_prefill_args* a, void* stream) {
   uint8_t* ws = reinterpret_cast<uint8_t*>(a->workspace);
   const int64_t bhq = (int64_t)a->B * a->H, bhkv = (int64_t)a->B * a->H_kv;
 
-  if ((rc = launch_retile_rowscales(a->q_scale, bhq, a->S_q, a->d, ws + w.q_sf, st)) != RK_OK) return rc;
-  if ((rc = launch_retile_rowscales(a->k_scale, bhkv, a->S_kv, a->d, ws + w.k_sf, st)) != RK_OK) return rc;
+  // Q / K scales -> scale-factor atoms (or the caller's atoms as they lie)
+  const uint8_t* q_sf = ws + w.q_sf;
+  const uint8_t* k_sf = ws + w.k_sf;
+  const uint8_t* v_sf = ws + w.v_sf;
+  if (a->q_scale_layout == RK_SCALES_SF_ATOMS) {
+    if (!aligned(a->q_scale, 16)) return RK_ERR_MISALIGNED;
+    q_sf = a->q_scale;
+  } else if ((rc = (a->q_scale_layout == RK_SCALES_GROUPMAJOR ? launch_retile_groupscales : launch_retile_rowscales)(
+                  a->q_scale, bhq, a->S_q, a->d, ws + w.q_sf, st)) != RK_OK) {
+    return rc;
+  }
+  if (a->k_scale_layout == RK_SCALES_SF_ATOMS) {
+    if (!aligned(a->k_scale, 16)) return RK_ERR_MISALIGNED;
+    k_sf = a->k_scale;
+  } else if ((rc = (a->k_scale_layout == RK_SCALES_GROUPMAJOR ? launch_retile_groupscales : launch_retile_rowscales)(
+                  a->k_scale, bhkv, a->S_kv, a->d, ws + w.k_sf, st)) != RK_OK) {
+    return rc;
+  }
   const uint8_t* v_codes = a->v;
   if (a->v_scale_axis == RK_V_SCALES_ALONG_D) {
     if (a->S_kv % 128 != 0 || a->d % 128 != 0) {
@@ -160,6 +233,9 @@ int rk_attn_prefill(const rk_prefill_args* a, void* stream) {
     if ((rc = launch_rebase_v(a->v, a->v_scale, bhkv, a->S_kv, a->d, a->kv_fmt, ws + w.v_codes, ws + w.v_sf, true, st)) != RK_OK)
       return rc;
     v_codes = ws + w.v_codes;
+  } else if (a->v_scale_layout == RK_SCALES_SF_ATOMS) {
+    if (!aligned(a->v_scale, 16)) return RK_ERR_MISALIGNED;
+    v_sf = a->v_scale;
   } else {
     if ((rc = launch_retile_keyscales(a->v_scale, bhkv, a->S_kv, a->d, ws + w.v_sf, st)) != RK_OK) return rc;
   }
@@ -175,7 +251,7 @@ int rk_attn_prefill(const rk_prefill_args* a, void* stream) {
     if ((rc = launch_pack6_transpose(v_codes, bhkv, a->S_kv, a->d, ws + w.v6t, st)) != RK_OK) return rc;
     v_codes = ws + w.v6t;
   }
-  return launch_prefill(*a, q_codes, k_codes, v_codes, ws + w.q_sf, ws + w.k_sf, ws + w.v_sf, st);
+  return launch_prefill(*a, q_codes, k_codes, v_codes, q_sf, k_sf, v_sf, st);
 }
 
 size_t rk_attn_prefill_host_arena_bytes(const rk_prefill_args* a) {
@@ -224,6 +300,9 @@ int rk_attn_prefill_host(const rk_prefill_args* h, void* arena, size_t arena_byt
   int rc = check_prefill_shape(h);
   if (rc != RK_OK) return rc;
   if (!h->q || !h->k || !h->v || !h->q_scale || !h->k_scale || !h->v_scale || !h->o || !arena) return RK_ERR_NULL_POINTER;
+  // the chunk offsets below are those of row-major scales
+  if (h->q_scale_layout != RK_SCALES_ROWMAJOR || h->k_scale_layout != RK_SCALES_ROWMAJOR || h->v_scale_layout != RK_SCALES_ROWMAJOR)
+    return RK_ERR_UNSUPPORTED;
   if (arena_bytes < rk_attn_prefill_host_arena_bytes(h) || !aligned(arena, 256)) return RK_ERR_WORKSPACE;
   cudaStream_t st = (cudaStream_t)stream;
   const size_t nbd = h->d / 32;
@@ -259,9 +338,15 @@ int rk_attn_prefill_host(const rk_prefill_args* h, void* arena, size_t arena_byt
   const int chunks_per_batch = h->B >= kTarget ? 1 : std::max(1, std::min(h->H_kv, kTarget / h->B));
   const int kv_per_chunk = (h->H_kv + chunks_per_batch - 1) / chunks_per_batch;
 
-  if ((e = cudaEventRecord(hp.start, st)) != cudaSuccess) return (int)e;
-  if ((e = cudaStreamWaitEvent(hp.h2d, hp.start, 0)) != cudaSuccess) return (int)e;
-  if ((e = cudaStreamWaitEvent(hp.d2h, hp.start, 0)) != cudaSuccess) return (int)e;
+  // an error in the middle leaves copies and kernels queued on three streams: wait for them before handing the
+  // buffers back to the caller
+  auto drain = [&](int code) {
+    cudaStreamSynchronize(hp.h2d); cudaStreamSynchronize(st); cudaStreamSynchronize(hp.d2h);
+    return code;
+  };
+  if ((e = cudaEventRecord(hp.start, st)) != cudaSuccess) return drain((int)e);
+  if ((e = cudaStreamWaitEvent(hp.h2d, hp.start, 0)) != cudaSuccess) return drain((int)e);
+  if ((e = cudaStreamWaitEvent(hp.d2h, hp.start, 0)) != cudaSuccess) return drain((int)e);
   int c = 0;
   for (int b0 = 0; b0 < h->B; b0 += batches_per_chunk) {
     const int nb = std::min(batches_per_chunk, h->B - b0);
@@ -271,7 +356,7 @@ int rk_attn_prefill_host(const rk_prefill_args* h, void* arena, size_t arena_byt
       const size_t qh = (size_t)b0 * h->H + (size_t)kv0 * grp, kh = (size_t)b0 * h->H_kv + kv0;
       const size_t nqh = (size_t)nb * nkv * grp, nkh = (size_t)nb * nkv;
       const size_t q_row = (size_t)h->S_q * h->d, k_row = (size_t)h->S_kv * h->d;
-#define RK_CP(dst, src, o, n) if ((e = cudaMemcpyAsync((dst) + (o), reinterpret_cast<const uint8_t*>(src) + (o), n, cudaMemcpyHostToDevice, hp.h2d)) != cudaSuccess) return (int)e
+#define RK_CP(dst, src, o, n) if ((e = cudaMemcpyAsync((dst) + (o), reinterpret_cast<const uint8_t*>(src) + (o), n, cudaMemcpyHostToDevice, hp.h2d)) != cudaSuccess) return drain((int)e)
       RK_CP(dq, h->q, qh * q_row, nqh * q_row);
       RK_CP(dk, h->k, kh * k_row, nkh * k_row);
       RK_CP(dv, h->v, kh * k_row, nkh * k_row);
@@ -279,8 +364,8 @@ int rk_attn_prefill_host(const rk_prefill_args* h, void* arena, size_t arena_byt
       RK_CP(dks, h->k_scale, kh * k_row / 32, nkh * k_row / 32);
       RK_CP(dvs, h->v_scale, kh * vs_head, nkh * vs_head);
 #undef RK_CP
-      if ((e = cudaEventRecord(hp.in[c], hp.h2d)) != cudaSuccess) return (int)e;
-      if ((e = cudaStreamWaitEvent(st, hp.in[c], 0)) != cudaSuccess) return (int)e;
+      if ((e = cudaEventRecord(hp.in[c], hp.h2d)) != cudaSuccess) return drain((int)e);
+      if ((e = cudaStreamWaitEvent(st, hp.in[c], 0)) != cudaSuccess) return drain((int)e);
       rk_prefill_args d = *h;
       d.B = nb; d.H = nkv * grp; d.H_kv = nkv;
       d.q = dq + qh * q_row; d.k = dk + kh * k_row; d.v = dv + kh * k_row;
@@ -288,17 +373,17 @@ int rk_attn_prefill_host(const rk_prefill_args* h, void* arena, size_t arena_byt
       d.o = dout + qh * q_row * 2;
       d.lse = h->lse ? reinterpret_cast<float*>(dlse) + qh * h->S_q : nullptr;
       d.workspace = ws; d.workspace_bytes = ws_bytes;       // chunks run one after the other on `st`: one workspace serves all
-      if ((rc = rk_attn_prefill(&d, stream)) != RK_OK) return rc;
-      if ((e = cudaEventRecord(hp.out[c], st)) != cudaSuccess) return (int)e;
-      if ((e = cudaStreamWaitEvent(hp.d2h, hp.out[c], 0)) != cudaSuccess) return (int)e;
+      if ((rc = rk_attn_prefill(&d, stream)) != RK_OK) return drain(rc);
+      if ((e = cudaEventRecord(hp.out[c], st)) != cudaSuccess) return drain((int)e);
+      if ((e = cudaStreamWaitEvent(hp.d2h, hp.out[c], 0)) != cudaSuccess) return drain((int)e);
       if ((e = cudaMemcpyAsync(reinterpret_cast<uint8_t*>(h->o) + qh * q_row * 2, dout + qh * q_row * 2, nqh * q_row * 2,
-                               cudaMemcpyDeviceToHost, hp.d2h)) != cudaSuccess) return (int)e;
+                               cudaMemcpyDeviceToHost, hp.d2h)) != cudaSuccess) return drain((int)e);
       if (h->lse && (e = cudaMemcpyAsync(h->lse + qh * h->S_q, reinterpret_cast<float*>(dlse) + qh * h->S_q,
-                                         nqh * h->S_q * 4, cudaMemcpyDeviceToHost, hp.d2h)) != cudaSuccess) return (int)e;
+                                         nqh * h->S_q * 4, cudaMemcpyDeviceToHost, hp.d2h)) != cudaSuccess) return drain((int)e);
     }
   }
-  if ((e = cudaEventRecord(hp.end, hp.d2h)) != cudaSuccess) return (int)e;
-  if ((e = cudaStreamWaitEvent(st, hp.end, 0)) != cudaSuccess) return (int)e;
+  if ((e = cudaEventRecord(hp.end, hp.d2h)) != cudaSuccess) return drain((int)e);
+  if ((e = cudaStreamWaitEvent(st, hp.end, 0)) != cudaSuccess) return drain((int)e);
   return (int)cudaStreamSynchronize(st);
 }
 
@@ -393,6 +478,8 @@ int rk_last_device_status(void) {
   return v;
 }
 
+int rk_attn_decode_noalloc_status(void) { return noalloc_status_read_clear(); }
+
 void rk_profile_set_events(void* before, void* after) { g_ev_before = (cudaEvent_t)before; g_ev_after = (cudaEvent_t)after; }
 
 /* Test hook (not in the public header): sweeps all 2^32 fp32 bit patterns and counts the inputs on which the
@@ -409,5 +496,30 @@ RK_API void rk_debug_set_prefill_dump(float* buf) { g_prefill_dbg = buf; }
 
 /* Test hook (not in the public header): 0 = choose the decode kernel by shape, 1 = always the mma.sync kernel. */
 RK_API void rk_debug_set_decode_path(int path) { g_decode_path = path; }
+
+/* Test hook (not in the public header): a one-CTA kernel that waits, with the library's bounded wait and a
+ * limit of `limit_us` microseconds, on an mbarrier nobody ever arrives at.  The wait must run out, record
+ * code 901 in the status word of the current device and let the kernel return normally.  `noalloc` != 0 uses
+ * the status word of the no-allocation decode entry point instead. */
+RK_API int rk_debug_wait_runs_out(int limit_us, int noalloc, void* stream) {
+  return launch_wait_runs_out(limit_us, noalloc != 0, (cudaStream_t)stream);
+}
+
+/* Measurement hook (not in the public header): on every SM, `iters` back-to-back 128 x 128 x 128 block-scaled
+ * MXFP8 products (four tcgen05.mma kind::mxf8f6f4 M=128 N=128 K=32 each) on one resident A tile and one resident
+ * B tile of 16 KiB each (device pointers, 16-byte aligned, any valid E4M3 codes): the tensor-pipe ceiling for the
+ * instruction shape the attention kernels use.  FLOP = SMs * iters * 2 * 128^3. */
+RK_API int rk_debug_mxfp8_mma_loop(const uint8_t* a_tile, const uint8_t* b_tile, int iters, void* stream) {
+  if (!a_tile || !b_tile) return RK_ERR_NULL_POINTER;
+  if (iters <= 0 || iters > (1 << 22)) return RK_ERR_BAD_SHAPE;
+  if (!aligned(a_tile, 16) || !aligned(b_tile, 16)) return RK_ERR_MISALIGNED;
+  return launch_mxfp8_mma_loop(a_tile, b_tile, iters, (cudaStream_t)stream);
+}
+
+/* Test hooks (not in the public header): which prefill kernel serves d <= 128 (0 = default, 1 = the
+ * two-threads-per-row kernel), and which warp role of the default kernel sleeps a little at every key tile
+ * (0 = none; 1, 2 = softmax of query tile A, B; 3 = correction; 4 = TMA producer; 5 = MMA issuer). */
+RK_API void rk_debug_set_prefill_path(int path) { g_prefill_path = path; }
+RK_API void rk_debug_set_prefill_perturb(int role) { g_prefill_perturb = role; }
 
 }  // extern "C"

@@ -18,8 +18,11 @@
 // tensor pipe only has to keep up with HBM):
 //   S[head][key]  = sum over the 4 scale blocks of d: 2^(sk-127) * (Q . K_codes)   m16n8k16 f16
 //                   (E4M3 -> f16 is exact; Q is pre-scaled per head by a power of two into f16 range)
-//   O[head][d]   += (P * 2^(sv-127)) . V_codes                                     m16n8k16 bf16
-//                   (E4M3 -> bf16 by bit placement, exact up to a 2^120 factor folded into P)
+//   O[head][d]   += (P * 2^(sv-vref)) . V_codes                                    m16n8k16 bf16
+//                   (E4M3 -> bf16 by bit placement, exact up to a 2^120 factor folded into P; vref is the warp's
+//                   running reference V scale code, at least 127 and at least every code seen so far: when a larger
+//                   code turns up the accumulator is rescaled by the exact power of two, like the running maximum,
+//                   so no V scale code can overflow the folded factor)
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -152,6 +155,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant_
 
   const float NEG_INF = __int_as_float(0xff800000);
   float m_run = NEG_INF, l_part = 0.0f;
+  int vref = 127;          // reference V scale code of this warp's accumulator: oacc = sum(p v) * 2^(127 - vref)
   float oacc[4][4][4];   // [32-col group][e][c-frag]; c0,c1 = head g, cols 32grp+8t+e, +4; c2,c3 = unused rows
 #pragma unroll
   for (int a = 0; a < 4; ++a)
@@ -264,6 +268,40 @@ decode_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant_
   #pragma unroll
             for (int e = 0; e < 4; ++e) { oacc[a][e][0] *= corr; oacc[a][e][1] *= corr; }
         }
+        // ---------------- V scale words of this lane's 8 keys; the warp's reference scale code ----------------
+        uint32_t vsw[2][4];
+  #pragma unroll
+        for (int ks = 0; ks < 2; ++ks) {
+          const int r0 = wkey0 + ks * 16 + 2 * t;               // V rows 2t, 2t+1, 2t+8, 2t+9 of this k-step
+          vsw[ks][0] = *reinterpret_cast<const uint32_t*>(svs + (r0) * 4);
+          vsw[ks][1] = *reinterpret_cast<const uint32_t*>(svs + (r0 + 1) * 4);
+          vsw[ks][2] = *reinterpret_cast<const uint32_t*>(svs + (r0 + 8) * 4);
+          vsw[ks][3] = *reinterpret_cast<const uint32_t*>(svs + (r0 + 9) * 4);
+          if (tail) {                                            // scales of keys past the end are not data
+            const int kk = gkey0 + ks * 16 + 2 * t;
+            if (kk >= len) vsw[ks][0] = 0u;
+            if (kk + 1 >= len) vsw[ks][1] = 0u;
+            if (kk + 8 >= len) vsw[ks][2] = 0u;
+            if (kk + 9 >= len) vsw[ks][3] = 0u;
+          }
+        }
+        {
+          uint32_t mw = __vmaxu4(__vmaxu4(__vmaxu4(vsw[0][0], vsw[0][1]), __vmaxu4(vsw[0][2], vsw[0][3])),
+                                 __vmaxu4(__vmaxu4(vsw[1][0], vsw[1][1]), __vmaxu4(vsw[1][2], vsw[1][3])));
+          mw = __vmaxu4(mw, mw >> 16);
+          const int vloc = (int)__reduce_max_sync(0xffffffffu, max(mw & 0xFFu, (mw >> 8) & 0xFFu));
+          if (vloc > vref) {                                     // warp-uniform
+            const int dn = vloc - vref;                          // accumulator *= 2^-dn, exact (or 0 below fp32 range)
+            const float f = dn < 127 ? __uint_as_float((uint32_t)(127 - dn) << 23) : 0.0f;
+  #pragma unroll
+            for (int a = 0; a < 4; ++a)
+  #pragma unroll
+              for (int e = 0; e < 4; ++e) { oacc[a][e][0] *= f; oacc[a][e][1] *= f; }
+            vref = vloc;
+          }
+        }
+        // bf16x2 of 2^(120 + 127 - vref): undoes the bit placement of V and moves P * 2^(sv-127) to the reference scale
+        const uint32_t two120 = ((uint32_t)(374 - vref) << 7) * 0x00010001u;
         // ---------------- O += P V, two k-steps of 16 keys ----------------
   #pragma unroll
         for (int ks = 0; ks < 2; ++ks) {
@@ -271,14 +309,10 @@ decode_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant_
           const uint32_t p01 = pack_bf16x2(pr[2 * ks][0], pr[2 * ks][1]);
           const uint32_t p89 = pack_bf16x2(pr[2 * ks + 1][0], pr[2 * ks + 1][1]);
           const int r0 = wkey0 + ks * 16 + 2 * t;               // V rows 2t, 2t+1, 2t+8, 2t+9 of this k-step
-          const uint32_t vs0 = *reinterpret_cast<const uint32_t*>(svs + (r0) * 4);
-          const uint32_t vs1 = *reinterpret_cast<const uint32_t*>(svs + (r0 + 1) * 4);
-          const uint32_t vs8 = *reinterpret_cast<const uint32_t*>(svs + (r0 + 8) * 4);
-          const uint32_t vs9 = *reinterpret_cast<const uint32_t*>(svs + (r0 + 9) * 4);
-          const uint32_t two120 = 0x7B807B80u;                   // bf16x2 of 2^120
+          const uint32_t vs0 = vsw[ks][0], vs1 = vsw[ks][1], vs8 = vsw[ks][2], vs9 = vsw[ks][3];
   #pragma unroll
           for (int grp = 0; grp < 4; ++grp) {
-            // P * 2^(sv-127) * 2^120 per (key, 32-col group); the 2^120 undoes the bf16 bit placement of V
+            // P * 2^(sv-127) * 2^(247-vref) per (key, 32-col group)
             uint32_t a0 = bf16x2_mul(bf16x2_mul(p01, ue8m0x2_to_bf16x2(prmt(vs0, vs1, 0x0040u + 0x11u * grp))), two120);
             uint32_t a2 = bf16x2_mul(bf16x2_mul(p89, ue8m0x2_to_bf16x2(prmt(vs8, vs9, 0x0040u + 0x11u * grp))), two120);
             if (tail) {
@@ -319,12 +353,13 @@ decode_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant_
     l_row += __shfl_xor_sync(0xffffffffu, l_row, 1);
     l_row += __shfl_xor_sync(0xffffffffu, l_row, 2);
     float* mine = red + (warp * 8 + g) * 132;
+    const float vback = __uint_as_float((uint32_t)vref << 23);   // 2^(vref-127): back to the true scale
 #pragma unroll
     for (int a = 0; a < 4; ++a)
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        mine[32 * a + 8 * t + e] = oacc[a][e][0];
-        mine[32 * a + 8 * t + 4 + e] = oacc[a][e][1];
+        mine[32 * a + 8 * t + e] = oacc[a][e][0] * vback;
+        mine[32 * a + 8 * t + 4 + e] = oacc[a][e][1] * vback;
       }
     if (t == 0) { mine[128] = m_run; mine[129] = l_row; }
   }
@@ -405,6 +440,7 @@ int launch_decode(const rk_decode_args& a, int nsplit, cudaStream_t st) {
   p.part_o = reinterpret_cast<float*>(a.workspace);
   p.part_ml = p.part_o + BH * nsplit * 128;
   p.status = device_status_word();
+  if (!p.status) return RK_ERR_NO_DEVICE;
   p.B = a.B; p.H = a.H; p.H_kv = a.H_kv; p.L = a.L; p.grp = a.H / a.H_kv; p.nsplit = nsplit;
   const float scale = a.softmax_scale > 0.0f ? a.softmax_scale : 1.0f / sqrtf((float)a.d);
   p.scale_log2 = scale * 1.4426950408889634f;
@@ -453,27 +489,77 @@ NoAllocDev g_noalloc_dev[64];
 std::mutex g_noalloc_mu;
 }  // namespace
 
-int launch_decode_noalloc(const rk_decode_args& a, cudaStream_t st) {
+// Set-up of the no-allocation path for the current device (once per device): in host code the array's name is
+// only a stand-in, the device address comes from the runtime, with that device current.
+static int noalloc_dev(NoAllocDev& out) {
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return (int)e;
+  std::lock_guard<std::mutex> lk(g_noalloc_mu);
+  NoAllocDev& slot = g_noalloc_dev[dev & 63];
+  if (!slot.ready) {
+    void* ptr = nullptr;
+    if ((e = cudaGetSymbolAddress(&ptr, g_noalloc_scratch)) != cudaSuccess) return (int)e;
+    slot.scratch = static_cast<float*>(ptr);
+    if ((e = cudaGetSymbolAddress(&ptr, g_noalloc_status)) != cudaSuccess) return (int)e;
+    slot.status = static_cast<int*>(ptr);
+    if ((e = cudaDeviceGetAttribute(&slot.sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return (int)e;
+    slot.ready = true;
+  }
+  out = slot;
+  return RK_OK;
+}
+
+// Status word of the no-allocation path on the current device: synchronises the device, returns the recorded code
+// (0 = clean) and clears it.  Plain copies to and from an address inside the library image: nothing is allocated.
+int noalloc_status_read_clear() {
+  NoAllocDev nd;
+  int rc = noalloc_dev(nd);
+  if (rc != RK_OK) return rc;
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) return (int)e;
+  int v = 0;
+  if ((e = cudaMemcpy(&v, nd.status, sizeof(int), cudaMemcpyDeviceToHost)) != cudaSuccess) return (int)e;
+  if (v != 0) {
+    const int zero = 0;
+    if ((e = cudaMemcpy(nd.status, &zero, sizeof(int), cudaMemcpyHostToDevice)) != cudaSuccess) return (int)e;
+  }
+  return v;
+}
+
+// Test hook: one CTA waits on an mbarrier nobody arrives at, with the bounded wait every kernel here uses.
+__global__ void wait_runs_out_kernel(int* status, unsigned long long limit_ns) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) { mbar_init(&bar, 1); abort_flag = 0; fence_barrier_init(); }
+  __syncthreads();
+  if (threadIdx.x == 0) mbar_wait(&bar, 0, &abort_flag, status, 901, limit_ns);
+  __syncthreads();
+}
+
+int launch_wait_runs_out(int limit_us, bool noalloc, cudaStream_t st) {
+  if (limit_us <= 0 || limit_us > 1000000) return RK_ERR_BAD_SHAPE;     // at most one second
+  int* status = nullptr;
+  if (noalloc) {
+    NoAllocDev nd;
+    int rc = noalloc_dev(nd);
+    if (rc != RK_OK) return rc;
+    status = nd.status;
+  } else {
+    status = device_status_word();
+    if (!status) return RK_ERR_NO_DEVICE;
+  }
+  wait_runs_out_kernel<<<1, 32, 0, st>>>(status, (unsigned long long)limit_us * 1000ull);
+  return (int)cudaGetLastError();
+}
+
+int launch_decode_noalloc(const rk_decode_args& a, cudaStream_t st) {
   NoAllocDev nd;
   {
-    std::lock_guard<std::mutex> lk(g_noalloc_mu);
-    NoAllocDev& slot = g_noalloc_dev[dev & 63];
-    if (!slot.ready) {
-      // In host code the array's name is only a stand-in; the device address comes from the runtime,
-      // once per device, with that device current.
-      void* ptr = nullptr;
-      if ((e = cudaGetSymbolAddress(&ptr, g_noalloc_scratch)) != cudaSuccess) return (int)e;
-      slot.scratch = static_cast<float*>(ptr);
-      if ((e = cudaGetSymbolAddress(&ptr, g_noalloc_status)) != cudaSuccess) return (int)e;
-      slot.status = static_cast<int*>(ptr);
-      if ((e = cudaDeviceGetAttribute(&slot.sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return (int)e;
-      slot.ready = true;
-    }
-    nd = slot;
+    int rc0 = noalloc_dev(nd);
+    if (rc0 != RK_OK) return rc0;
   }
+  cudaError_t e;
   // split count: the caller's, or the one that fills whole waves of 2 CTAs per SM best, shrunk to fit the array
   const int tiles = (a.L + kDecTileKeys - 1) / kDecTileKeys;
   const size_t BH = (size_t)a.B * a.H;

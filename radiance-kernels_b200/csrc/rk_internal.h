@@ -9,7 +9,8 @@ namespace rk {
 
 extern cudaEvent_t g_ev_before, g_ev_after;   // optional profiling events around the main kernels
 int num_sms();                 // SM count of the current device (cached per device)
-int* device_status_word();     // per-device int in global memory, zeroed at creation; kernels CAS error codes into it
+int* device_status_word();     // per-device int inside the library image, zero at load; kernels CAS error codes into it.
+                               // NULL when the device could not be queried: callers return RK_ERR_NO_DEVICE
 
 int launch_quantize_rows_bf16(const void* x, int64_t rows, int64_t cols, int fmt, uint8_t* codes, uint8_t* scales, cudaStream_t st);
 int launch_quantize_rows(const float* x, int64_t rows, int64_t cols, int fmt, uint8_t* codes, uint8_t* scales, cudaStream_t st);
@@ -20,6 +21,13 @@ int launch_retile_rowscales(const uint8_t* in, int64_t batch, int64_t S, int64_t
 int launch_pack6_rows(const uint8_t* in, int64_t rows, int64_t d, uint8_t* out, cudaStream_t st);
 int launch_pack6_transpose(const uint8_t* in, int64_t batch, int64_t S, int64_t d, uint8_t* out, cudaStream_t st);
 int launch_verify_encoder(int fmt, unsigned long long* mismatches, uint32_t* first_bad, cudaStream_t st);
+int launch_quantize_rows_ex(const void* x, bool bf16, int64_t batch, int64_t S, int64_t d, int fmt, uint8_t* codes,
+                            uint8_t* scales, int layout, cudaStream_t st);
+int launch_quantize_keys_atoms(const float* x, int64_t batch, int64_t rows, int64_t cols, int fmt, uint8_t* codes,
+                               uint8_t* scales, cudaStream_t st);
+int launch_retile_groupscales(const uint8_t* in, int64_t batch, int64_t S, int64_t d, uint8_t* out, cudaStream_t st);
+int launch_import_kt_blocks(const uint8_t* kt, const uint8_t* kts, int64_t heads, int nblk, int Bk, int d, uint8_t* k,
+                            uint8_t* ks, cudaStream_t st);
 int launch_retile_keyscales(const uint8_t* in, int64_t batch, int64_t S, int64_t d, uint8_t* out, cudaStream_t st);
 
 // q/k/v_codes: byte codes as the caller gave them, or -- for 6-bit formats -- the packed copies made by
@@ -33,6 +41,9 @@ int launch_kv_append(const float* k_new, const float* v_new, int B, int H_kv, in
                      uint8_t* k_codes, uint8_t* k_scales, uint8_t* v_codes, uint8_t* v_scales, cudaStream_t st);
 int launch_decode(const rk_decode_args& a, int num_splits, cudaStream_t st);
 int launch_decode_noalloc(const rk_decode_args& a, cudaStream_t st);
+int noalloc_status_read_clear();                            // status word of the no-allocation decode path: read, then clear
+int launch_mxfp8_mma_loop(const uint8_t* a_tile, const uint8_t* b_tile, int iters, cudaStream_t st);   // tensor-pipe ceiling probe
+int launch_wait_runs_out(int limit_us, bool noalloc, cudaStream_t st);   // test hook: a bounded wait that must give up
 extern int g_decode_path;                                   // test hook: 0 = by shape, 1 = mma.sync kernel only
 bool decode_uses_tc(const rk_decode_args& a);                // true when the tcgen05 decode kernel serves this call
 int decode_ctas_per_sm(const rk_decode_args& a);             // resident CTAs per SM of the kernel that serves it

@@ -581,6 +581,8 @@ static int launch_cfg(const CUtensorMap& tq, const CUtensorMap& tk, const CUtens
 }
 
 float* g_prefill_dbg = nullptr;   // set by rk_debug_set_prefill_dump (tests only)
+int g_prefill_path = 0;
+int g_prefill_perturb = 0;
 
 int launch_prefill(const rk_prefill_args& a, const uint8_t* q_codes, const uint8_t* k_codes, const uint8_t* v_codes,
                    const uint8_t* q_sf, const uint8_t* k_sf, const uint8_t* v_sf, cudaStream_t st) {
@@ -600,6 +602,7 @@ int launch_prefill(const rk_prefill_args& a, const uint8_t* q_codes, const uint8
   p.o = reinterpret_cast<__nv_bfloat16*>(a.o);
   p.lse = a.lse;
   p.status = device_status_word();
+  if (!p.status) return RK_ERR_NO_DEVICE;
   p.dbg = g_prefill_dbg;
   p.B = a.B; p.H = a.H; p.H_kv = a.H_kv; p.S_q = a.S_q; p.S_kv = a.S_kv; p.d = a.d;
   {
@@ -614,6 +617,7 @@ int launch_prefill(const rk_prefill_args& a, const uint8_t* q_codes, const uint8
   p.n_kv_tiles = (a.S_kv + kBlockN - 1) / kBlockN;
   p.q_pos0 = a.q_pos0; p.causal = a.causal; p.window = a.window;
   p.v_transposed = kv6 ? 1 : 0;
+  p.perturb = g_prefill_perturb;
   p.q_tile_tx = q6 ? kTileBytes * 3 / 4 : kTileBytes;
   p.kv_tile_tx = kv6 ? kTileBytes * 3 / 4 : kTileBytes;
   const float scale = a.softmax_scale > 0.0f ? a.softmax_scale : 1.0f / sqrtf((float)a.d);
@@ -625,7 +629,10 @@ int launch_prefill(const rk_prefill_args& a, const uint8_t* q_codes, const uint8
   const uint32_t idesc_pv = make_idesc(RK_FMT_E4M3, a.kv_fmt, false, /*B MN-major*/ !kv6, 128, 128);
   dim3 grid(p.n_q_tiles * a.H * a.B, 1, 1);
   const bool cap = a.softcap > 0.0f;
-  if (a.d <= 128) return launch_prefill2q(tq, tk, tv, p, idesc_qk, idesc_pv, cap, a.B, st);   // two query tiles per CTA
+  if (a.d <= 128) {                                     // two query tiles per CTA
+    return g_prefill_path == 1 ? launch_prefill2q(tq, tk, tv, p, idesc_qk, idesc_pv, cap, a.B, st)
+                               : launch_prefill2c(tq, tk, tv, p, idesc_qk, idesc_pv, cap, a.B, st);
+  }
   return cap ? launch_cfg<2, 2, true>(tq, tk, tv, p, idesc_qk, idesc_pv, grid, st)
              : launch_cfg<2, 2, false>(tq, tk, tv, p, idesc_qk, idesc_pv, grid, st);
 }

@@ -40,6 +40,7 @@ struct PrefillParams {
   int q_tile_tx, kv_tile_tx;   // bytes one Q / K / V tile load adds to its mbarrier: 16384, or 12288 for 6-bit tensors
                                // (the transaction counts the packed source bytes, not the padded shared-memory image)
   int v_transposed;    // V tiles are [d][keys] (K-major B operand; 6-bit V) instead of [keys][d]
+  int perturb;         // test hook: warp role that sleeps a little at every key tile (0 = none)
   float scale_log2;    // softmax_scale * log2(e)
   float cap_log2;      // softcap * log2(e)
   float inv_cap_scale; // softmax_scale / softcap
@@ -83,5 +84,10 @@ extern float* g_prefill_dbg;
 // Two 128-row query tiles per CTA (d <= 128); defined in rk_prefill2q.cu.
 int launch_prefill2q(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const PrefillParams& p,
                      uint32_t idesc_qk, uint32_t idesc_pv, bool softcap, int B, cudaStream_t st);
+// Two query tiles per CTA, one thread per row, correction warps (d <= 128); defined in rk_prefill2c.cu.
+int launch_prefill2c(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const PrefillParams& p,
+                     uint32_t idesc_qk, uint32_t idesc_pv, bool softcap, int B, cudaStream_t st);
+extern int g_prefill_path;      // test hook: 0 = default kernel by shape, 1 = the two-threads-per-row kernel for d <= 128
+extern int g_prefill_perturb;   // test hook: PrefillParams::perturb of the next launches
 
 }  // namespace rk

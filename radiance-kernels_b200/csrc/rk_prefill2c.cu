@@ -1,0 +1,527 @@
+// MX flash-attention prefill, two 128-row query tiles per CTA (head dim <= 128), one thread per query row and
+// separate correction warps.
+//
+// Stages as in fa_entry, kernels/flash_attention_mx_gqa/kernel.cpp:91-184 (QK_j -> fused softmax + requant ->
+// scale pack -> PV_j -> rescale/accumulate -> finalize); what this file decides is who does what:
+//
+//   warps 0-3    softmax of query tile A: thread = row (the one-lane-per-row form of fused_softmax_requant_tpr,
+//   warps 4-7    softmax of query tile B   kernels/flash_attention_mx_gqa/flash_mx_impl.hpp:314-394): a row's 128
+//                scores of a key tile sit in the thread's registers, so row max and row sum need no exchange
+//   warps 8-11   correction: rescale_accumulate (flash_mx_impl.hpp:508-532) on the O accumulators in TMEM, off the
+//                softmax warps' critical path; warp 8+q serves TMEM lane quadrant q of both tiles
+//   warp  12     TMA producer (one elected lane)
+//   warp  13     MMA issuer (one elected lane) + TMEM allocation
+//   warps 14-15  fill the fourth warpgroup (register reallocation works on whole warpgroups)
+//
+// Registers are moved between the warpgroups with setmaxnreg: the softmax threads hold a whole 128-score row
+// (kRegSoftmax), correction, TMA and MMA threads need few.  The S accumulator (128 TMEM columns) is shared by the
+// two tiles: a softmax group copies its rows to registers at once and hands the columns back, the MMA warp
+// alternates QK_A, QK_B.  Every K/V tile brought in by TMA serves both query tiles.
+#include "rk_prefill.cuh"
+
+namespace rk {
+
+namespace c2 {
+constexpr int kStages = 3;
+constexpr int kThreads = 512;
+constexpr int kWarpCorr = 8, kWarpTma = 12, kWarpMma = 13;
+constexpr uint32_t kRegSoftmax = 184, kRegCorr = 88, kRegIssue = 56;   // 128 * (2*184 + 88 + 56) = 65536 registers
+// TMEM columns
+constexpr uint32_t cS = 0, cO = 128 /* + g*128 */, cSfQ = 384 /* + g*4 */, cSfK = 392 /* + st*4 */,
+                   cSfP = 404 /* + (g*2+pb)*4 */, cSfV = 420 /* + st*4 */;
+// shared memory
+constexpr int q_off = 0;                                   // [2][16 KB]
+constexpr int k_off = q_off + 2 * kTileBytes;              // [3]
+constexpr int v_off = k_off + kStages * kTileBytes;        // [3]
+constexpr int p_off = v_off + kStages * kTileBytes;        // [2 groups][2]
+constexpr int sfq_off = p_off + 4 * kTileBytes;            // [2]
+constexpr int sfk_off = sfq_off + 2 * kSfAtomBytes;        // [3]
+constexpr int sfv_off = sfk_off + kStages * kSfAtomBytes;  // [3]
+constexpr int sfp_off = sfv_off + kStages * kSfAtomBytes;  // [2][2]
+constexpr int bar_off = sfp_off + 4 * kSfAtomBytes;
+// barrier indices
+constexpr int bQ = 0, bKF = 1, bKE = 4, bVF = 7, bVE = 10, bSF = 13 /* +g */, bSE = 15 /* +g */,
+              bPF = 17 /* + g*2+pb */, bPV = 21 /* + g*2+pb */, bCF = 25 /* + (g*2+pb)*4+quad */, bOR = 41 /* +g */,
+              bDRAIN = 43, nBars = 44;
+constexpr int misc_off = bar_off + nBars * 8;
+constexpr int corr_off = misc_off + 16;                    // [2 groups][2][128] floats: the O rescale factors of a tile
+constexpr int total = corr_off + 2 * 2 * 128 * 4;
+// test hook: which role sleeps a little at every key tile (schedule perturbation)
+constexpr int kPerturbSoftmaxA = 1, kPerturbSoftmaxB = 2, kPerturbCorr = 3, kPerturbTma = 4, kPerturbMma = 5;
+}  // namespace c2
+
+template <uint32_t N> RK_DEVINL void reg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
+template <uint32_t N> RK_DEVINL void reg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
+
+RK_DEVINL void perturb(const PrefillParams& p, int role, int j) {
+  if (p.perturb == role) __nanosleep(400 + 97 * (j & 7));
+}
+
+// ---- softmax warps: thread = query row -----------------------------------------------------------------------
+template <bool SOFTCAP>
+__device__ __forceinline__ void softmax_row_group(const PrefillParams& p, uint8_t* smem, uint64_t* bars, uint32_t tmem_base,
+                                                  volatile int* abort_flag, int grp, int qt, int bh, int n_tiles, int j0) {
+  using namespace c2;
+  uint64_t* s_full = bars + bSF + grp;
+  uint64_t* s_empty = bars + bSE + grp;
+  uint64_t* p_full = bars + bPF + grp * 2;
+  uint64_t* pv_done = bars + bPV + grp * 2;
+  uint64_t* corr_full = bars + bCF + grp * 8;
+  float* corr_sm = reinterpret_cast<float*>(smem + corr_off) + grp * 256;
+
+  const int lane = threadIdx.x & 31;
+  const int quad = (threadIdx.x >> 5) & 3;
+  const int row = quad * 32 + lane;
+  const uint32_t lane_addr = ((uint32_t)(quad * 32)) << 16;
+  const int q_row = qt * kBlockM + row;
+  const int q_pos = p.q_pos0 + q_row;
+  const float NEG_INF = __int_as_float(0xff800000);
+  const bool dump = p.dbg && qt == p.n_q_tiles - 1 && bh == 0;
+  const float sc_mul = SOFTCAP ? 1.0f : p.scale_log2;
+
+  float m_run = NEG_INF, l_run = 0.0f;
+  bool ok = true;
+
+  for (int j = 0; j < n_tiles && ok; ++j) {
+    const int pb = j & 1;
+    perturb(p, kPerturbSoftmaxA + grp, j);
+    ok = __all_sync(0xffffffffu, mbar_wait(s_full, j & 1, abort_flag, p.status, 101));
+    if (!ok) break;
+    tc_fence_after();
+
+    float s[128];
+#pragma unroll
+    for (int c = 0; c < 4; ++c) tmem_ld32(tmem_base + lane_addr + cS + c * 32, reinterpret_cast<uint32_t*>(s) + c * 32);
+    tc_wait_ld();
+    tc_fence_before();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(s_empty);       // hand the S columns back: the other query tile's QK^T may use them
+
+    if (dump && j == 0) {
+#pragma unroll
+      for (int c = 0; c < 128; ++c) p.dbg[row * 128 + c] = s[c];
+    }
+
+    // ---- (soft-cap,) mask, block maxima ----------------------------------------------------------------
+    const int key0 = (j + j0) * kBlockN;                      // first key of this tile (j counts from the first tile inside the window)
+    const bool tail = (key0 + kBlockN > p.S_kv);
+    const bool diag = p.causal && (key0 + kBlockN - 1 > p.q_pos0 + qt * kBlockM);
+    const bool need_mask = tail || diag || (p.window > 0);
+    if (SOFTCAP) {
+#pragma unroll
+      for (int c = 0; c < 128; ++c) {
+        const float e = ex2_approx(s[c] * (2.0f * 1.4426950408889634f * p.inv_cap_scale));
+        s[c] = p.cap_log2 * fmaf(-2.0f, rcp_approx(1.0f + e), 1.0f);
+      }
+    }
+    if (need_mask) {
+      int hi = p.S_kv - 1 - key0;                             // masked iff c > hi || c <= lo
+      if (p.causal) hi = min(hi, q_pos - key0);
+      const int lo = (p.window > 0) ? (q_pos - p.window - key0) : -1;
+#pragma unroll
+      for (int c = 0; c < 128; ++c) s[c] = (c > hi || c <= lo) ? NEG_INF : s[c];
+    }
+    float bmax[4];
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      float a0 = fmax3(s[g * 32 + 0], s[g * 32 + 1], s[g * 32 + 2]);
+      float a1 = fmax3(s[g * 32 + 3], s[g * 32 + 4], s[g * 32 + 5]);
+#pragma unroll
+      for (int c = 6; c < 30; c += 4) { a0 = fmax3(a0, s[g * 32 + c], s[g * 32 + c + 1]); a1 = fmax3(a1, s[g * 32 + c + 2], s[g * 32 + c + 3]); }
+      bmax[g] = fmax3(a0, a1, fmaxf(s[g * 32 + 30], s[g * 32 + 31]));
+    }
+    const float mx = fmaxf(fmax3(bmax[0], bmax[1], bmax[2]), bmax[3]);
+    const float m_new = fmaxf(m_run, mx * sc_mul);
+    // exponent = fma(s, scale, -m): lowering m by 2^-21 |m| keeps the row-max p in [1, 1 + 1e-5) in spite of
+    // the rounding residue of s*scale; the common factor cancels in O = sum(p v) / sum(p).
+    const float m_use = (m_new == NEG_INF) ? 0.0f : (SOFTCAP ? m_new : fmaf(-fabsf(m_new), 4.76837158203125e-7f, m_new));
+    const float corr = (m_run == NEG_INF) ? 1.0f : ex2_approx(m_run - m_new);
+    m_run = m_new;
+    // the correction warp of this lane quadrant can start on O while the exponentials run here
+    corr_sm[pb * 128 + row] = corr;
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&corr_full[pb * 4 + quad]);
+
+    // the P buffer and its scale atom are free once the P.V that read them two tiles ago has finished
+    if (j >= 2) {
+      ok = __all_sync(0xffffffffu, mbar_wait(&pv_done[pb], ((j - 2) >> 1) & 1, abort_flag, p.status, 102));
+      if (!ok) break;
+    }
+
+    // ---- p = 2^(x - m), row sum from the unquantised p, requant per 32-key block ---------------------
+    uint8_t* p_tile = smem + p_off + (grp * 2 + pb) * kTileBytes + row * 128;
+    float ls0 = 0.0f, ls1 = 0.0f, ls2 = 0.0f, ls3 = 0.0f;
+    uint32_t scale_word = 0;
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+#pragma unroll
+      for (int c = 0; c < 32; c += 4) {
+        float x0, x1, x2, x3;
+        fma2(s[g * 32 + c + 0], s[g * 32 + c + 1], sc_mul, -m_use, x0, x1);
+        fma2(s[g * 32 + c + 2], s[g * 32 + c + 3], sc_mul, -m_use, x2, x3);
+        const float p0 = ex2_approx(x0), p1 = ex2_approx(x1), p2 = ex2_approx(x2), p3 = ex2_approx(x3);
+        s[g * 32 + c + 0] = p0; s[g * 32 + c + 1] = p1; s[g * 32 + c + 2] = p2; s[g * 32 + c + 3] = p3;
+        add2(ls0, ls1, p0, p1);
+        add2(ls2, ls3, p2, p3);
+      }
+      const float pmax = ex2_approx(fmaf(bmax[g], sc_mul, -m_use));   // p of the block's arg-max element
+      int sc = (int)(__float_as_uint(pmax) >> 23);                    // E8M0 code: se = floor(log2 pmax) <= 0
+      sc = min(sc, 127);
+      scale_word |= (uint32_t)sc << (8 * g);
+      uint32_t w[8];
+      if (sc >= 7) {
+        // y = p * 2^(7-sc): exponent field = E4M3 exponent field, mantissa kept, so the truncated code is
+        // y's bits [20,27); .ftz zeroes everything below 2^-6 of the block scale.
+        const float f = __uint_as_float((uint32_t)(134 - sc) << 23);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          float y0, y1, y2, y3;
+          mul2_ftz(s[g * 32 + q * 4 + 0], s[g * 32 + q * 4 + 1], f, y0, y1);
+          mul2_ftz(s[g * 32 + q * 4 + 2], s[g * 32 + q * 4 + 3], f, y2, y3);
+          w[q] = pack_u8x2(__float_as_uint(y1) >> 20, __float_as_uint(y0) >> 20,
+                           pack_u8x2(__float_as_uint(y3) >> 20, __float_as_uint(y2) >> 20, 0u));
+        }
+      } else {
+        const int sub = (sc - 7) * 8;                                 // block max below 2^-120: exact integer form
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          uint32_t word = 0;
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const uint32_t bits = __float_as_uint(s[g * 32 + q * 4 + e]);
+            int t = (int)(bits >> 20) - sub;
+            t = (t >= 8 && bits >= 0x00800000u) ? t : 0;
+            word |= (uint32_t)t << (8 * e);
+          }
+          w[q] = word;
+        }
+      }
+      const int c0 = (2 * g) ^ (row & 7), c1 = (2 * g + 1) ^ (row & 7);     // 128-byte swizzle
+      *reinterpret_cast<uint4*>(p_tile + c0 * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+      *reinterpret_cast<uint4*>(p_tile + c1 * 16) = make_uint4(w[4], w[5], w[6], w[7]);
+    }
+    l_run = l_run * corr + ((ls0 + ls1) + (ls2 + ls3));
+    // the row's four block scales: bytes (row%32)*16 + (row/32)*4 + 0..3 of the 512-byte scale atom
+    *reinterpret_cast<uint32_t*>(smem + sfp_off + (grp * 2 + pb) * kSfAtomBytes + (row & 31) * 16 + (row >> 5) * 4) = scale_word;
+
+    if (dump && j == 0) {
+      uint32_t* d32 = reinterpret_cast<uint32_t*>(p.dbg + 128 * 128);
+#pragma unroll
+      for (int lc = 0; lc < 8; ++lc) {
+        const uint4 v4 = *reinterpret_cast<const uint4*>(p_tile + ((lc ^ (row & 7)) * 16));
+        d32[row * 32 + lc * 4 + 0] = v4.x; d32[row * 32 + lc * 4 + 1] = v4.y;
+        d32[row * 32 + lc * 4 + 2] = v4.z; d32[row * 32 + lc * 4 + 3] = v4.w;
+      }
+      d32[128 * 32 + row] = scale_word;
+    }
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&p_full[pb]);
+  }
+
+  // ---- epilogue: O / l -> bf16 (finalize_O, flash_mx_impl.hpp:535-553) ----------------------------------------
+  if (ok) {
+    const int last = n_tiles - 1;
+    ok = __all_sync(0xffffffffu, mbar_wait(&pv_done[last & 1], (last >> 1) & 1, abort_flag, p.status, 103));
+  }
+  if (ok) {
+    tc_fence_after();
+    const float inv_l = (l_run > 0.0f) ? 1.0f / l_run : 1.0f;
+    const bool live = q_row < p.S_q;
+    __nv_bfloat16* orow = p.o + ((size_t)bh * p.S_q + q_row) * p.d;
+    if (dump) {
+      p.dbg[128 * 128 + 128 * 32 + 128 + row * 2 + 0] = m_run;
+      p.dbg[128 * 128 + 128 * 32 + 128 + row * 2 + 1] = l_run;
+    }
+#pragma unroll 1
+    for (int c32 = 0; c32 < p.d / 32; ++c32) {
+      uint32_t r[32];
+      tmem_ld32(tmem_base + lane_addr + cO + grp * 128 + c32 * 32, r);
+      tc_wait_ld();
+      if (live) {
+        uint32_t packed[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(r[2 * i]) * inv_l, __uint_as_float(r[2 * i + 1]) * inv_l);
+          packed[i] = *reinterpret_cast<const uint32_t*>(&b2);
+        }
+        uint4* dst = reinterpret_cast<uint4*>(orow + c32 * 32);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) dst[i] = make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
+      }
+    }
+    if (p.lse && live)
+      p.lse[(size_t)bh * p.S_q + q_row] = (l_run > 0.0f) ? m_run * 0.6931471805599453f + logf(l_run) : NEG_INF;
+  }
+  tc_fence_before();
+}
+
+// ---- correction warps: O <- O * corr before the tile's P.V is added ---------------------------------------------
+__device__ __forceinline__ void correction_quadrant(const PrefillParams& p, uint8_t* smem, uint64_t* bars, uint32_t tmem_base,
+                                                    volatile int* abort_flag, const int nt[2], int n_all) {
+  using namespace c2;
+  const int lane = threadIdx.x & 31;
+  const int quad = (threadIdx.x >> 5) & 3;
+  const int row = quad * 32 + lane;
+  const uint32_t lane_addr = ((uint32_t)(quad * 32)) << 16;
+  const float* corr_sm = reinterpret_cast<const float*>(smem + corr_off);
+  const int o_chunks = p.d / 32;
+  bool ok = true;
+  for (int j = 0; j < n_all && ok; ++j) {
+    const int pb = j & 1;
+    perturb(p, kPerturbCorr, j);
+#pragma unroll 1
+    for (int g = 0; g < 2 && ok; ++g) {
+      if (j >= nt[g]) continue;
+      ok = __all_sync(0xffffffffu, mbar_wait<64>(&bars[bCF + (g * 2 + pb) * 4 + quad], (j >> 1) & 1, abort_flag, p.status, 401));
+      if (!ok) break;
+      const float corr = corr_sm[(g * 2 + pb) * 128 + row];
+      if (j > 0 && __any_sync(0xffffffffu, corr != 1.0f)) {
+        ok = __all_sync(0xffffffffu, mbar_wait(&bars[bPV + g * 2 + ((j - 1) & 1)], ((j - 1) >> 1) & 1, abort_flag, p.status, 402));
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll 1
+        for (int ch = 0; ch < o_chunks; ++ch) {
+          uint32_t r[32];
+          tmem_ld32(tmem_base + lane_addr + cO + g * 128 + ch * 32, r);
+          tc_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) mul2_ftz_inplace(r[i], r[i + 1], corr);
+          tmem_st32(tmem_base + lane_addr + cO + g * 128 + ch * 32, r);
+        }
+        tc_wait_st();
+        tc_fence_before();
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars[bOR + g]);   // the tile's P.V may accumulate into O now
+    }
+  }
+}
+
+template <bool SOFTCAP>
+__global__ void __launch_bounds__(c2::kThreads, 1)
+prefill2c_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                 const __grid_constant__ CUtensorMap tmap_v, const PrefillParams p, const uint32_t idesc_qk,
+                 const uint32_t idesc_pv) {
+  using namespace c2;
+  extern __shared__ __align__(1024) uint8_t smem_raw2c[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw2c) + 1023) & ~(uintptr_t)1023);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + bar_off);
+  uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(smem + misc_off);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + misc_off + 4);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (*reinterpret_cast<volatile int*>(p.status) != 0) return;   // an earlier launch gave up on a wait
+  const int n_pairs = (p.n_q_tiles + 1) / 2;
+  // Work order over the 1-D grid: (batch, head) pairs are taken in groups of p.head_group; inside a group the
+  // heaviest (latest) query-tile pairs of all its heads come first and the lightest last, so the grid ends on
+  // short CTAs, while a group's K/V still fits in L2.
+  const int n_bh = p.B * p.H;
+  const int per_group = n_pairs * p.head_group;
+  const int grp_i = (int)blockIdx.x / per_group, r = (int)blockIdx.x % per_group;
+  const int heads_here = min(p.head_group, n_bh - grp_i * p.head_group);
+  const int qp = n_pairs - 1 - r / heads_here;
+  const int bh_lin = grp_i * p.head_group + r % heads_here;
+  const int h = bh_lin % p.H, b = bh_lin / p.H;
+  const int bh = b * p.H + h;
+  const int bhkv = b * p.H_kv + h / (p.H / p.H_kv);
+
+  // key tiles each query tile needs (causal tiles wholly above the diagonal are never touched,
+  // kernels/flash_attention_mx_gqa/flash_attention_model.py:182-186); a tile past S_q needs none
+  int nt[2];
+#pragma unroll
+  for (int g = 0; g < 2; ++g) {
+    const int qt = 2 * qp + g;
+    int n = (qt < p.n_q_tiles) ? p.n_kv_tiles : 0;
+    if (n > 0 && p.causal) {
+      const int max_qpos = p.q_pos0 + min(qt * kBlockM + kBlockM, p.S_q) - 1;
+      n = max_qpos < 0 ? 0 : min(n, max_qpos / kBlockN + 1);
+    }
+    nt[g] = n;
+  }
+  // sliding window: key tiles wholly below the window of the pair's first row are masked for every row of both tiles
+  int j0 = 0;
+  if (p.window > 0) {
+    const int first_key = p.q_pos0 + 2 * qp * kBlockM - p.window + 1;  // lowest key the first row may see
+    j0 = min(max(first_key, 0) / kBlockN, max(min(nt[0], nt[1] > 0 ? nt[1] : nt[0]) - 1, 0));
+    nt[0] = max(nt[0] - j0, 0);                                         // tiles j0 .. j0 + nt - 1 are visited
+    nt[1] = max(nt[1] - j0, 0);
+  }
+  const int n_all = max(nt[0], nt[1]);
+
+  if (threadIdx.x == 0) {
+    mbar_init(&bars[bQ], 1);
+    for (int i = 0; i < kStages; ++i) { mbar_init(&bars[bKF + i], 1); mbar_init(&bars[bKE + i], 1); mbar_init(&bars[bVF + i], 1); mbar_init(&bars[bVE + i], 1); }
+    for (int g = 0; g < 2; ++g) {
+      mbar_init(&bars[bSF + g], 1); mbar_init(&bars[bSE + g], 4);
+      for (int i = 0; i < 2; ++i) { mbar_init(&bars[bPF + g * 2 + i], 4); mbar_init(&bars[bPV + g * 2 + i], 1); }
+      for (int i = 0; i < 8; ++i) mbar_init(&bars[bCF + g * 8 + i], 1);
+      mbar_init(&bars[bOR + g], 4);
+    }
+    mbar_init(&bars[bDRAIN], 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == kWarpMma) { tmem_alloc(tmem_ptr, kTmemCols); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_ptr;
+
+  if (warp < kWarpCorr) {
+    reg_inc<kRegSoftmax>();
+    const int grp = warp >> 2;
+    const int qt = 2 * qp + grp;
+    if (nt[grp] > 0) {
+      softmax_row_group<SOFTCAP>(p, smem, bars, tmem_base, abort_flag, grp, qt, bh, nt[grp], j0);
+    } else if (qt < p.n_q_tiles) {
+      // no visible key: O = 0 (the l <= 0 guard of finalize_O, kernels/flash_attention_mx_gemma/flash_mx_impl.hpp:554-560)
+      const int q_row = qt * kBlockM + (int)(threadIdx.x & 127);
+      if (q_row < p.S_q) {
+        __nv_bfloat16* orow = p.o + ((size_t)bh * p.S_q + q_row) * p.d;
+        for (int c = 0; c < p.d; c += 8) *reinterpret_cast<uint4*>(orow + c) = make_uint4(0, 0, 0, 0);
+        if (p.lse) p.lse[(size_t)bh * p.S_q + q_row] = __int_as_float(0xff800000);
+      }
+    }
+  } else if (warp < kWarpTma) {
+    reg_dec<kRegCorr>();
+    correction_quadrant(p, smem, bars, tmem_base, abort_flag, nt, n_all);
+  } else {
+    reg_dec<kRegIssue>();
+    if (warp == kWarpTma) {
+      // ================= TMA producer =================
+      if (lane == 0 && n_all > 0) {
+        prefetch_tmap(&tmap_q); prefetch_tmap(&tmap_k); prefetch_tmap(&tmap_v);
+        const int nq = (2 * qp + 1 < p.n_q_tiles) ? 2 : 1;
+        mbar_arrive_expect_tx(&bars[bQ], nq * (p.q_tile_tx + kSfAtomBytes));
+        for (int g = 0; g < nq; ++g) {
+          tma_load_3d(smem + q_off + g * kTileBytes, &tmap_q, &bars[bQ], 0, (2 * qp + g) * kBlockM, bh);
+          bulk_load_1d(smem + sfq_off + g * kSfAtomBytes, p.q_sf + ((size_t)bh * p.n_q_tiles + 2 * qp + g) * kSfAtomBytes,
+                       kSfAtomBytes, &bars[bQ]);
+        }
+        bool ok = true;
+        for (int j = 0; j < n_all && ok; ++j) {
+          const int st = j % kStages, use = j / kStages;
+          perturb(p, kPerturbTma, j);
+          if (use > 0) ok = mbar_wait<128>(&bars[bKE + st], (use - 1) & 1, abort_flag, p.status, 201);
+          if (!ok) break;
+          mbar_arrive_expect_tx(&bars[bKF + st], p.kv_tile_tx + kSfAtomBytes);
+          tma_load_3d(smem + k_off + st * kTileBytes, &tmap_k, &bars[bKF + st], 0, (j + j0) * kBlockN, bhkv);
+          bulk_load_1d(smem + sfk_off + st * kSfAtomBytes, p.k_sf + ((size_t)bhkv * p.n_kv_tiles + j + j0) * kSfAtomBytes,
+                       kSfAtomBytes, &bars[bKF + st]);
+          if (use > 0) ok = mbar_wait<128>(&bars[bVE + st], (use - 1) & 1, abort_flag, p.status, 202);
+          if (!ok) break;
+          mbar_arrive_expect_tx(&bars[bVF + st], p.kv_tile_tx + kSfAtomBytes);
+          if (p.v_transposed) tma_load_3d(smem + v_off + st * kTileBytes, &tmap_v, &bars[bVF + st], (j + j0) * kBlockN, 0, bhkv);
+          else tma_load_3d(smem + v_off + st * kTileBytes, &tmap_v, &bars[bVF + st], 0, (j + j0) * kBlockN, bhkv);
+          bulk_load_1d(smem + sfv_off + st * kSfAtomBytes, p.v_sf + ((size_t)bhkv * p.n_kv_tiles + j + j0) * kSfAtomBytes,
+                       kSfAtomBytes, &bars[bVF + st]);
+        }
+      }
+    } else if (warp == kWarpMma) {
+      // ================= MMA issuer =================
+      if (lane == 0 && n_all > 0) {
+        const uint32_t q_addr = smem_u32(smem + q_off), k_addr = smem_u32(smem + k_off);
+        const uint32_t v_addr = smem_u32(smem + v_off), pt_addr = smem_u32(smem + p_off);
+        bool ok = mbar_wait(&bars[bQ], 0, abort_flag, p.status, 301);
+        if (ok) {
+          for (int g = 0; g < 2; ++g)
+            tc_cp_32x128b_warpx4(tmem_base + cSfQ + g * 4, make_smem_desc(smem_u32(smem + sfq_off + g * kSfAtomBytes), 0, 128, kLayoutNone));
+        }
+        int s_user_g = -1, s_user_j = 0;       // who read the shared S columns last
+        auto issue_qk = [&](int g, int j, int st) -> bool {
+          if (s_user_g >= 0 && !mbar_wait(&bars[bSE + s_user_g], s_user_j & 1, abort_flag, p.status, 305)) return false;
+          tc_fence_after();
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) {
+            const uint64_t adesc = make_smem_desc(q_addr + g * kTileBytes + kk * 32, 16, 1024, kLayoutSw128);
+            const uint64_t bdesc = make_smem_desc(k_addr + st * kTileBytes + kk * 32, 16, 1024, kLayoutSw128);
+            mma_mxf8f6f4_ss(tmem_base + cS, adesc, bdesc, idesc_with_sf(idesc_qk, kk, kk), tmem_base + cSfQ + g * 4,
+                            tmem_base + cSfK + st * 4, kk > 0 ? 1u : 0u);
+          }
+          tc_commit(&bars[bSF + g]);
+          s_user_g = g; s_user_j = j;
+          return true;
+        };
+        auto issue_pv = [&](int g, int i, bool first_of_tile, bool last_of_tile) -> bool {
+          const int pb = i & 1, st = i % kStages, use = i / kStages;
+          if (first_of_tile) {
+            if (!mbar_wait(&bars[bVF + st], use & 1, abort_flag, p.status, 303)) return false;
+            tc_cp_32x128b_warpx4(tmem_base + cSfV + st * 4, make_smem_desc(smem_u32(smem + sfv_off + st * kSfAtomBytes), 0, 128, kLayoutNone));
+          }
+          if (!mbar_wait(&bars[bPF + g * 2 + pb], (i >> 1) & 1, abort_flag, p.status, 304)) return false;
+          if (!mbar_wait(&bars[bOR + g], i & 1, abort_flag, p.status, 307)) return false;     // O rescaled for this tile
+          tc_fence_after();
+          tc_cp_32x128b_warpx4(tmem_base + cSfP + (g * 2 + pb) * 4,
+                               make_smem_desc(smem_u32(smem + sfp_off + (g * 2 + pb) * kSfAtomBytes), 0, 128, kLayoutNone));
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) {
+            const uint64_t adesc = make_smem_desc(pt_addr + (g * 2 + pb) * kTileBytes + kk * 32, 16, 1024, kLayoutSw128);
+            // V tile [keys][d] is the MN-major B operand; a 6-bit V is stored transposed and is K-major like K
+            const uint64_t bdesc = p.v_transposed ? make_smem_desc(v_addr + st * kTileBytes + kk * 32, 16, 1024, kLayoutSw128)
+                                                  : make_smem_desc(v_addr + st * kTileBytes + kk * 4096, kTileBytes, 1024, kLayoutSw128);
+            mma_mxf8f6f4_ss(tmem_base + cO + g * 128, adesc, bdesc, idesc_with_sf(idesc_pv, kk, kk),
+                            tmem_base + cSfP + (g * 2 + pb) * 4, tmem_base + cSfV + st * 4, (i > 0 || kk > 0) ? 1u : 0u);
+          }
+          tc_commit(&bars[bPV + g * 2 + pb]);
+          if (last_of_tile) tc_commit(&bars[bVE + st]);
+          return true;
+        };
+        // PVs of tile i: group 0 first, then group 1; flags tell which one opens / closes the V stage
+        auto pv_flags = [&](int g, int i, bool& first, bool& last) {
+          const bool a = i < nt[0], bb = i < nt[1];
+          first = (g == 0) ? true : !a;
+          last = (g == 1) ? true : !bb;
+        };
+        for (int j = 0; j < n_all && ok; ++j) {
+          const int st = j % kStages, use = j / kStages;
+          perturb(p, kPerturbMma, j);
+          ok = mbar_wait(&bars[bKF + st], use & 1, abort_flag, p.status, 302);
+          if (!ok) break;
+          tc_cp_32x128b_warpx4(tmem_base + cSfK + st * 4, make_smem_desc(smem_u32(smem + sfk_off + st * kSfAtomBytes), 0, 128, kLayoutNone));
+          bool f, l;
+          if (j < nt[0]) ok = issue_qk(0, j, st);
+          if (ok && j > 0 && j - 1 < nt[0]) { pv_flags(0, j - 1, f, l); ok = issue_pv(0, j - 1, f, l); }
+          if (ok && j < nt[1]) ok = issue_qk(1, j, st);
+          if (ok) tc_commit(&bars[bKE + st]);
+          if (ok && j > 0 && j - 1 < nt[1]) { pv_flags(1, j - 1, f, l); ok = issue_pv(1, j - 1, f, l); }
+        }
+        if (ok) {
+          bool f, l;
+          const int i = n_all - 1;
+          if (i < nt[0]) { pv_flags(0, i, f, l); ok = issue_pv(0, i, f, l); }
+          if (ok && i < nt[1]) { pv_flags(1, i, f, l); ok = issue_pv(1, i, f, l); }
+        }
+        tc_commit(&bars[bDRAIN]);
+        mbar_wait(&bars[bDRAIN], 0, abort_flag, p.status, 306);
+      }
+      __syncwarp();
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == kWarpMma) { tc_fence_after(); tmem_dealloc(tmem_base, kTmemCols); }
+}
+
+template <bool SOFTCAP>
+static int launch2c_cfg(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const PrefillParams& p,
+                        uint32_t idesc_qk, uint32_t idesc_pv, dim3 grid, cudaStream_t st) {
+  const int smem_bytes = c2::total + 1024;
+  auto kern = prefill2c_kernel<SOFTCAP>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+  if (e != cudaSuccess) return (int)e;
+  if (g_ev_before && g_ev_after) cudaEventRecord(g_ev_before, st);
+  kern<<<grid, c2::kThreads, smem_bytes, st>>>(tq, tk, tv, p, idesc_qk, idesc_pv);
+  if (g_ev_before && g_ev_after) cudaEventRecord(g_ev_after, st);
+  return (int)cudaGetLastError();
+}
+
+int launch_prefill2c(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const PrefillParams& p,
+                     uint32_t idesc_qk, uint32_t idesc_pv, bool softcap, int B, cudaStream_t st) {
+  dim3 grid(((p.n_q_tiles + 1) / 2) * p.H * B, 1, 1);
+  return softcap ? launch2c_cfg<true>(tq, tk, tv, p, idesc_qk, idesc_pv, grid, st)
+                 : launch2c_cfg<false>(tq, tk, tv, p, idesc_qk, idesc_pv, grid, st);
+}
+
+}  // namespace rk

@@ -63,9 +63,19 @@ __global__ void verify_encoder_kernel(uint64_t first, uint64_t count, unsigned l
 }
 
 // BF16IN: the input is bf16 (one 16-byte load per chunk, widened exactly to fp32) instead of fp32.
-template <int FMT, bool BF16IN = false>
+// Offset of (row r of a 128-row tile, 32-element block kb of a 128-element
+// chunk) inside a 512-byte scale-factor atom: 32 rows x 16 bytes, row r%32,
+// byte (r/32)*4 + kb.  One tcgen05.cp 32x128b.warpx4 moves an atom to 4 TMEM
+// columns (lane = r%32, column = r/32, byte = kb).
+__host__ __device__ inline int sf_atom_offset(int r, int kb) { return (r & 31) * 16 + (r >> 5) * 4 + kb; }
+
+// LAYOUT: where a block's scale byte goes -- 0 row-major [rows][d/32]; 1 group-major [batch][d/32][S]; 2 the
+// 512-byte scale-factor atoms [batch][ceil(S/128)][ceil(d/128)][512] the attention kernel copies into TMEM
+// (S = rows per matrix of the batch, nbd = d/32; both unused for layout 0).
+template <int FMT, bool BF16IN = false, int LAYOUT = 0>
 __global__ void __launch_bounds__(256) quantize_rows_kernel(const float4* __restrict__ x, int64_t nchunks,
-                                                            uint2* __restrict__ codes, uint8_t* __restrict__ scales) {
+                                                            uint2* __restrict__ codes, uint8_t* __restrict__ scales,
+                                                            int64_t S = 0, int nbd = 0) {
   // chunk = 8 consecutive elements; 4 consecutive lanes = one 32-element block.
   // Warp-uniform loop bound: all 32 lanes run the shuffles even when the last
   // chunks of the array end inside this warp (nchunks is a multiple of 4, so a
@@ -118,7 +128,20 @@ __global__ void __launch_bounds__(256) quantize_rows_kernel(const float4* __rest
         w1 = ref_encode4<FMT>(v[4] * p2, v[5] * p2, v[6] * p2, v[7] * p2);
       }
       __stcs(codes + c, make_uint2(w0, w1));
-      if ((c & 3) == 0) scales[c >> 2] = (uint8_t)scode;
+      if ((c & 3) == 0) {
+        if (LAYOUT == 0) {
+          scales[c >> 2] = (uint8_t)scode;
+        } else {
+          const int64_t bi = c >> 2, row = bi / nbd, mat = row / S;
+          const int blk = (int)(bi % nbd), r = (int)(row % S);
+          if (LAYOUT == 1) {
+            scales[(mat * nbd + blk) * S + r] = (uint8_t)scode;
+          } else {
+            const int64_t ntile = (S + 127) / 128, dch = (nbd + 3) / 4;
+            scales[((mat * ntile + r / 128) * dch + blk / 4) * 512 + sf_atom_offset(r & 127, blk & 3)] = (uint8_t)scode;
+          }
+        }
+      }
     }
   }
 }
@@ -241,7 +264,9 @@ __global__ void __launch_bounds__(128) kv_append_kernel(const float* __restrict_
 }
 
 // One thread = 4 adjacent columns x one 32-row block.
-template <int FMT>
+// ATOMS: scales go to the scale-factor atoms [batch][ceil(rows/128)][ceil(cols/128)][512] (byte = column n of the
+// chunk, 32-key block kbi of the tile) instead of row-major [batch][ceil(rows/32)][cols].
+template <int FMT, bool ATOMS = false>
 __global__ void __launch_bounds__(128) quantize_keys_kernel(const float* __restrict__ x, int64_t batch, int64_t rows,
                                                             int64_t cols, uint8_t* __restrict__ codes,
                                                             uint8_t* __restrict__ scales) {
@@ -270,15 +295,16 @@ __global__ void __launch_bounds__(128) quantize_keys_kernel(const float* __restr
                                              : ref_encode4<FMT>(v.x * p2[0], v.y * p2[1], v.z * p2[2], v.w * p2[3]);
       *reinterpret_cast<uint32_t*>(cb + (int64_t)j * cols) = w;
     }
-    *reinterpret_cast<uint32_t*>(scales + (bt * nkb + kb) * cols + c4 * 4) = sc[0] | (sc[1] << 8) | (sc[2] << 16) | (sc[3] << 24);
+    if (!ATOMS) {
+      *reinterpret_cast<uint32_t*>(scales + (bt * nkb + kb) * cols + c4 * 4) = sc[0] | (sc[1] << 8) | (sc[2] << 16) | (sc[3] << 24);
+    } else {
+      const int64_t ntile = (rows + 127) / 128, dch = (cols + 127) / 128;
+      uint8_t* atom = scales + ((bt * ntile + kb / 4) * dch + (c4 * 4) / 128) * 512;
+#pragma unroll
+      for (int q = 0; q < 4; q++) atom[((int)((c4 * 4 + q) & 31)) * 16 + ((int)(((c4 * 4 + q) & 127) >> 5)) * 4 + (int)(kb & 3)] = (uint8_t)sc[q];
+    }
   }
 }
-
-// Offset of (row r of a 128-row tile, 32-element block kb of a 128-element
-// chunk) inside a 512-byte scale-factor atom: 32 rows x 16 bytes, row r%32,
-// byte (r/32)*4 + kb.  One tcgen05.cp 32x128b.warpx4 moves an atom to 4 TMEM
-// columns (lane = r%32, column = r/32, byte = kb).
-__host__ __device__ inline int sf_atom_offset(int r, int kb) { return (r & 31) * 16 + (r >> 5) * 4 + kb; }
 
 // Exact value of element code `c` times 2^(s-127) as an fp32.  Normal codes under ordinary scales are
 // placed by integer arithmetic (E4M3: bits = (mag + 8 s - 56) << 20); everything else (subnormal codes,
@@ -569,6 +595,57 @@ __global__ void retile_rowscales_kernel(const uint8_t* __restrict__ in, int64_t 
   }
 }
 
+// scales along d, group-major [batch][d/32][S] (the reference's QK_A_scales_row[FA_GK][FA_SQ] per head,
+// kernels/flash_attention_mx/gen_data.py:82-83)  ->  atoms [batch][ntile][dch][512]
+__global__ void retile_groupscales_kernel(const uint8_t* __restrict__ in, int64_t batch, int64_t S, int64_t d,
+                                          uint8_t* __restrict__ out) {
+  const int64_t nbd = d / 32, ntile = (S + 127) / 128, dch = (d + 127) / 128;
+  const int64_t total = batch * ntile * dch * 128;   // one thread per (atom, row): writes 4 bytes; a warp reads 32 adjacent rows
+  for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (int64_t)gridDim.x * blockDim.x) {
+    const int r = (int)(t % 128);
+    const int64_t atom = t / 128, ch = atom % dch, tile = (atom / dch) % ntile, bt = atom / (dch * ntile);
+    const int64_t row = tile * 128 + r;
+    uint32_t w = 0;
+#pragma unroll
+    for (int kb = 0; kb < 4; kb++) {
+      const int64_t blk = ch * 4 + kb;
+      const uint32_t sc = (row < S && blk < nbd) ? in[(bt * nbd + blk) * S + row] : 0x7Fu;
+      w |= sc << (8 * kb);
+    }
+    *reinterpret_cast<uint32_t*>(out + atom * 512 + sf_atom_offset(r, 0)) = w;
+  }
+}
+
+// The reference's streaming K operand (kernels/flash_attention_mx_gqa/fa_gen_data.py:110-117): per KV head and key
+// block j a transposed tile K^T [d][Bk] (QK_B_blocks) with group-major scales [d/32][Bk] (QK_B_scales_blocks)
+// -> natural K codes [heads][nblk*Bk][d] and row-major scales [heads][nblk*Bk][d/32].
+// One CTA transposes a 32 x 32 byte tile through shared memory; scales by one thread per output byte.
+__global__ void __launch_bounds__(256) import_kt_blocks_kernel(const uint8_t* __restrict__ kt, const uint8_t* __restrict__ kts,
+                                                               int64_t heads, int nblk, int Bk, int d,
+                                                               uint8_t* __restrict__ k, uint8_t* __restrict__ ks) {
+  __shared__ uint8_t tile[32][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;           // 32 x 8
+  const int64_t tiles_k = Bk / 32, tiles_d = d / 32;
+  const int64_t ntiles = heads * nblk * tiles_d * tiles_k;
+  for (int64_t t = blockIdx.x; t < ntiles; t += gridDim.x) {
+    const int64_t tk = t % tiles_k, td = (t / tiles_k) % tiles_d, blk = t / (tiles_k * tiles_d);   // blk = head * nblk + j
+    const uint8_t* src = kt + (blk * d + td * 32) * Bk + tk * 32;    // rows = d index, cols = key inside the block
+#pragma unroll
+    for (int i = 0; i < 4; ++i) tile[ty + 8 * i][tx] = src[(int64_t)(ty + 8 * i) * Bk + tx];
+    __syncthreads();
+    uint8_t* dst = k + (blk * Bk + tk * 32) * d + td * 32;            // rows = key, cols = d index
+#pragma unroll
+    for (int i = 0; i < 4; ++i) dst[(int64_t)(ty + 8 * i) * d + tx] = tile[tx][ty + 8 * i];
+    __syncthreads();
+  }
+  const int nbd = d / 32;
+  const int64_t nsc = heads * nblk * (int64_t)Bk * nbd;
+  for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < nsc; t += (int64_t)gridDim.x * blockDim.x) {
+    const int g = (int)(t % nbd);
+    const int64_t key = (t / nbd) % Bk, blk = t / ((int64_t)nbd * Bk);
+    ks[t] = kts[(blk * nbd + g) * Bk + key];
+  }
+}
 
 // ---- 6-bit operands ---------------------------------------------------------------------------------
 // The tensor core reads 6-bit elements from shared memory as 16 codes in 12 bytes + 4 bytes of padding;
@@ -662,6 +739,48 @@ int launch_quantize_rows_bf16(const void* x, int64_t rows, int64_t cols, int fmt
   const int grid = grid_for(nchunks, 256, 8);
   RK_DISPATCH_FMT(fmt, (quantize_rows_kernel<F, true><<<grid, 256, 0, st>>>(reinterpret_cast<const float4*>(x), nchunks,
                                                                             reinterpret_cast<uint2*>(codes), scales)));
+  return (int)cudaGetLastError();
+}
+
+// Blocks along d with a chosen scale layout (see quantize_rows_kernel); x is fp32 or bf16 [batch][S][d].
+int launch_quantize_rows_ex(const void* x, bool bf16, int64_t batch, int64_t S, int64_t d, int fmt, uint8_t* codes,
+                            uint8_t* scales, int layout, cudaStream_t st) {
+  const int64_t nchunks = batch * S * d / 8;
+  if (nchunks == 0) return RK_OK;
+  const int grid = grid_for(nchunks, 256, 8);
+  const float4* xp = reinterpret_cast<const float4*>(x);
+  uint2* cp = reinterpret_cast<uint2*>(codes);
+  const int nbd = (int)(d / 32);
+#define RK_QX(BF, LAY) RK_DISPATCH_FMT(fmt, (quantize_rows_kernel<F, BF, LAY><<<grid, 256, 0, st>>>(xp, nchunks, cp, scales, S, nbd)))
+  if (layout == RK_SCALES_ROWMAJOR) { if (bf16) { RK_QX(true, 0); } else { RK_QX(false, 0); } }
+  else if (layout == RK_SCALES_GROUPMAJOR) { if (bf16) { RK_QX(true, 1); } else { RK_QX(false, 1); } }
+  else if (layout == RK_SCALES_SF_ATOMS) { if (bf16) { RK_QX(true, 2); } else { RK_QX(false, 2); } }
+  else return RK_ERR_BAD_FORMAT;
+#undef RK_QX
+  return (int)cudaGetLastError();
+}
+
+int launch_quantize_keys_atoms(const float* x, int64_t batch, int64_t rows, int64_t cols, int fmt, uint8_t* codes,
+                               uint8_t* scales, cudaStream_t st) {
+  const int64_t total = batch * ((rows + 31) / 32) * (cols / 4);
+  if (total == 0) return RK_OK;
+  const int grid = grid_for(total, 128, 16);
+  RK_DISPATCH_FMT(fmt, (quantize_keys_kernel<F, true><<<grid, 128, 0, st>>>(x, batch, rows, cols, codes, scales)));
+  return (int)cudaGetLastError();
+}
+
+int launch_retile_groupscales(const uint8_t* in, int64_t batch, int64_t S, int64_t d, uint8_t* out, cudaStream_t st) {
+  const int64_t total = batch * ((S + 127) / 128) * ((d + 127) / 128) * 128;
+  if (total == 0) return RK_OK;
+  retile_groupscales_kernel<<<grid_for(total, 256, 8), 256, 0, st>>>(in, batch, S, d, out);
+  return (int)cudaGetLastError();
+}
+
+int launch_import_kt_blocks(const uint8_t* kt, const uint8_t* kts, int64_t heads, int nblk, int Bk, int d, uint8_t* k,
+                            uint8_t* ks, cudaStream_t st) {
+  const int64_t ntiles = heads * nblk * (d / 32) * (Bk / 32);
+  if (ntiles == 0) return RK_OK;
+  import_kt_blocks_kernel<<<(int)min(ntiles, (int64_t)num_sms() * 16), 256, 0, st>>>(kt, kts, heads, nblk, Bk, d, k, ks);
   return (int)cudaGetLastError();
 }
 

@@ -142,3 +142,34 @@ def test_shard_range_covers_units_once():
                 lo, hi = rk.shard_range(n, r, world)
                 got += list(range(lo, hi))
             assert got == list(range(n))
+
+
+def test_front_end_rejects_wrong_dtypes_and_shapes():
+    """The Python front end checks dtype and exact shape of every tensor against B/H/H_kv/S/d before a pointer
+    reaches the library (the checks run on CPU tensors here; nothing is launched)."""
+    import torch
+    from radiance_kernels_b200 import api
+    B, H, Hkv, S, d = 1, 4, 2, 64, 128
+    u8 = lambda *sh: torch.zeros(sh, dtype=torch.uint8)
+    good = dict(q=u8(B, H, S, d), k=u8(B, Hkv, S, d), v=u8(B, Hkv, S, d), q_scale=u8(B, H, S, 4), k_scale=u8(B, Hkv, S, 4),
+                v_scale=u8(B, Hkv, S, 4), o=torch.zeros(B, H, S, d, dtype=torch.bfloat16), lse=torch.zeros(B, H, S))
+    api._check_prefill_tensors(**good, v_scale_axis=rk.V_SCALES_ALONG_D)
+    bad_cases = [("k", u8(B, Hkv, S, 64)), ("q_scale", u8(B, H, S, 3)), ("v_scale", u8(B, Hkv, 2, d)),
+                 ("q", torch.zeros(B, H, S, d, dtype=torch.int8)), ("o", torch.zeros(B, H, S, d)),
+                 ("lse", torch.zeros(B, H, S + 1)), ("v", u8(B, H, S, d))]
+    for name, t in bad_cases:
+        with pytest.raises(ValueError):
+            api._check_prefill_tensors(**{**good, name: t}, v_scale_axis=rk.V_SCALES_ALONG_D)
+    with pytest.raises(ValueError):
+        api._check_prefill_tensors(**good, v_scale_axis=rk.V_SCALES_ALONG_KEYS)     # v_scale has the other layout
+    with pytest.raises(ValueError):
+        api._check_prefill_tensors(**good, v_scale_axis=5)
+    L = 256
+    dq = torch.zeros(B, H, d, dtype=torch.bfloat16)
+    dgood = dict(q=dq, k=u8(B, Hkv, L, d), v=u8(B, Hkv, L, d), k_scale=u8(B, Hkv, L, 4), v_scale=u8(B, Hkv, L, 4),
+                 kv_len=torch.zeros(B, dtype=torch.int32), out=torch.zeros(B, H, d, dtype=torch.bfloat16), lse=torch.zeros(B, H))
+    api._check_decode_tensors(**dgood)
+    for name, t in [("v", u8(B, Hkv, L, 64)), ("k_scale", u8(B, Hkv, L, 8)), ("kv_len", torch.zeros(B, dtype=torch.int64)),
+                    ("out", torch.zeros(B, H, d)), ("lse", torch.zeros(B, H, 2))]:
+        with pytest.raises(ValueError):
+            api._check_decode_tensors(**{**dgood, name: t})

@@ -80,9 +80,24 @@ def test_split_count_does_not_change_result_much():
     assert np.abs(a - b).max() < 4e-3
 
 
-def test_lse_and_large_v_scale():
+def test_lse_output():
     run(1, 8, 2, 1024, want_lse=True, seed=7)
-    run(1, 8, 2, 1024, vmul=300.0, seed=8) if False else None
+
+
+@pytest.mark.parametrize("top_code", [134, 135, 200, 60])
+def test_v_scale_codes_at_and_beyond_the_bf16_folding_edge(top_code):
+    """V block scales whose largest code is 134 (the last one a fixed 2^120 folding constant can take in bf16), 135,
+    200 and a very small 60, mixed with codes up to 24 below it inside every block of 32 keys: both decode kernels
+    must re-centre the factor they fold into P and match the oracle.  Output magnitudes follow the scale, so the
+    absolute bound is relative to the reference's largest value."""
+    g = torch.Generator(device="cuda").manual_seed(40 + top_code)
+    q = torch.randn(2, 8, 128, generator=g, device="cuda").bfloat16()
+    kc, ks, vc, vs = _quantized_cache(2, 2, 1024, seed=41 + top_code)
+    vs = torch.randint(top_code - 24, top_code + 1, vs.shape, generator=g, dtype=torch.uint8, device="cuda")
+    vs[:, :, 5::97] = top_code                      # the top code is present in every sequence
+    (legacy, tc), ref = _check(q, kc, ks, vc, vs)
+    big = float(np.abs(ref["o_f32"]).max())
+    assert np.abs(legacy - tc).max() <= 4e-3 * max(1.0, big)
 
 
 def test_full_length_one_sequence():

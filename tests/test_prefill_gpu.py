@@ -202,3 +202,8 @@ def test_stage_parity_s_and_requantized_p(d, qmul):
     diff = pcodes.astype(np.int32) - r["p_codes"][rows, :128].astype(np.int32)
     bad = np.count_nonzero(diff)
     assert np.abs(diff).max() <= 1 and bad <= 0.0005 * diff.size, (bad, int(np.abs(diff).max()))
+    # running max and row sum after the tile's last key tile: m is kept in the log2 domain on the GPU
+    ml = dd[128 * 128 + 128 * 32 + 128: 128 * 128 + 128 * 32 + 128 + 256].reshape(128, 2)
+    m_gpu, l_gpu = ml[:, 0] * np.log(2.0), ml[:, 1]
+    assert np.abs(m_gpu - r["m"][rows]).max() <= 4e-6 * np.abs(r["m"][rows]).max() + 1e-6
+    assert np.abs(l_gpu / r["l"][rows] - 1.0).max() <= 1e-4

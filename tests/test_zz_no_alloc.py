@@ -10,6 +10,7 @@ import numpy as np
 import pytest
 import torch
 
+import oracle
 import radiance_kernels_b200 as rk
 from radiance_kernels_b200._lib import DecodeArgs
 from helpers import MAX_ABS, REL_L2, errors, np_
@@ -45,12 +46,17 @@ def test_noalloc_decode_matches_workspace_decode_twice_in_a_row():
     for args in (dict(B=2, H=8, Hkv=2, L=2048, seed=21), dict(B=3, H=16, Hkv=4, L=1000, seed=22, lens=[1000, 3, 517])):
         q, kc, vc, ks, vs, kl = _case(**args)
         want = rk.attn_decode(q, kc, vc, ks, vs, kv_len=kl)
+        ref = oracle.attn_decode(np_(q.view(torch.uint16)), np_(kc), np_(vc), np_(ks), np_(vs), softmax_scale=128 ** -0.5,
+                                 kv_len=None if kl is None else np_(kl))
         for _ in range(2):
             rc, got = _noalloc(q, kc, vc, ks, vs, kl)
             assert rc == 0
             torch.cuda.synchronize()
             ma, rl = errors(np_(got.float()), np_(want.float()))
             assert ma <= MAX_ABS and rl <= REL_L2, (ma, rl)
+            ma, rl = errors(np_(got.float()), ref["o_f32"])          # and against the CPU oracle itself
+            assert ma <= MAX_ABS and rl <= REL_L2, (ma, rl)
+            assert rk.lib().rk_attn_decode_noalloc_status() == 0     # this path's own status word
     assert rk.last_device_status() == 0
 
 
