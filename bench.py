@@ -7,8 +7,12 @@ Workload (named in the JSON line): MXFP8 causal MHA prefill B=8 H=16 S=4096 d=12
 N(0,1) Q/K/V quantized to E4M3 + E8M0 block-32 along d, bf16 output.  A "step" is one pass of the whole
 prefill path over that batch through the C ABI: scale re-tiling, V re-blocking along the keys and the tiled
 attention kernel.  With N > 1 every rank runs its own batch of independent (batch, head) units (weak
-scaling, no data-path collective); time is the max over ranks, value the FLOP of all ranks over it.
-The same line also carries the decode leg (batch 64, 32 query heads / 8 KV heads, d=128, KV length 32768).
+scaling, no data-path collective); time is the max over ranks, value the FLOP of all ranks over it; the
+same run also shards ONE global batch over the ranks by (batch, KV head) units (`strong_scaling`), with the
+optional NCCL gather of O timed apart.
+The line also carries the decode leg (batch 64, 32 query heads / 8 KV heads, d=128, KV length 32768), the
+other benchmark configurations and the preparation kernels, each with its own roofline (`extras`), and the
+tensor-pipe ceiling measured on this device by a GEMM-only loop of the same block-scaled MMAs.
 
 `--impl reference` times the CPU restatement of the reference path (oracle/) on the host cores on a bounded
 sample of the same workload: the reference's own attention cannot run here (its Python model imports an
@@ -16,6 +20,7 @@ un-vendored module, its kernels need the Muon toolchain and an RTL simulator).
 """
 import argparse
 import ctypes as C
+import datetime
 import json
 import os
 import subprocess
@@ -32,6 +37,8 @@ PREFILL = dict(B=8, H=16, H_kv=16, S=4096, d=128)
 DECODE = dict(B=64, H=32, H_kv=8, L=32768, d=128)
 WORKLOAD = "MXFP8 causal MHA prefill B=8 H=16 S=4096 d=128 (E4M3 + E8M0 block-32 along d, P requantized, bf16 out)"
 METRIC = "MX attention prefill TFLOP/s (all GPUs) [decode HBM GB/s in `decode`]"
+NOMINAL_FP8_TFLOPS = 4500.0
+NOMINAL_HBM_GBS = 8000.0
 
 
 def prefill_flops(c):
@@ -46,7 +53,7 @@ def prefill_algorithmic_bytes(c):
 
 # DRAM traffic of one launch from the ncu captures summarised under profiles/ (dram__bytes_read.sum +
 # dram__bytes_write.sum), per unit of work; both kernels' traffic is proportional to the unit count.
-NCU_PREFILL_DRAM_BYTES_PER_HEAD = (103.966976e6 + 34.787584e6) / 64        # S=4096, d=128, causal
+NCU_PREFILL_DRAM_BYTES_PER_HEAD = (157.811456e6 + 34.141440e6) / 64         # S=4096, d=128, causal
 NCU_DECODE_DRAM_BYTES_PER_SEQUENCE = (553.775104e6 + 6.571264e6) / 8        # H_kv=8, L=32768, d=128
 
 
@@ -65,55 +72,74 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """nvidia-smi clocks / throttle reasons sampled while the timed region runs."""
-    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+    """nvidia-smi clocks / throttle reasons, time-stamped, sampled while the benchmark runs; `window(t0, t1)`
+    summarises the samples whose time stamps fall inside one timed region (host clock, seconds)."""
+    Q = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
          "clocks_event_reasons.sw_power_cap")
+    NAMES = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
 
-    def __init__(self, gpu_index):
-        self.gpu = gpu_index
-        self.proc = None
-        self.path = None
+    def __init__(self, gpu_index, period_ms=50):
+        self.gpu, self.period_ms = gpu_index, period_ms
+        self.proc = self.path = self.fh = None
+        self.samples = []
 
-    def start(self):
+    def __enter__(self):
         try:
             fd, self.path = tempfile.mkstemp(suffix=".csv")
-            os.close(fd)
+            self.fh = os.fdopen(fd, "w")
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.gpu), "--query-gpu=" + self.Q,
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
-                                         stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+                                          "--format=csv,noheader,nounits", "-lms", str(self.period_ms)],
+                                         stdout=self.fh, stderr=subprocess.DEVNULL)
         except Exception:
             self.proc = None
+        return self
 
-    def stop(self):
-        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
-        if self.proc is None:
-            return out
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except Exception:
-            self.proc.kill()
-        sm, mx, reasons = [], [], set()
-        try:
-            for line in open(self.path):
-                f = [x.strip() for x in line.split(",")]
-                if len(f) < 8:
-                    continue
-                try:
-                    sm.append(float(f[1])); mx.append(float(f[2]))
-                except ValueError:
-                    continue
-                for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[4:8]):
-                    if v.lower().startswith("active"):
-                        reasons.add(name)
-            os.unlink(self.path)
-        except Exception:
-            pass
-        if sm:
-            top = sorted(sm)[len(sm) // 2:]             # the loaded half of the samples
-            out.update(sm_mhz=float(np.median(top)), sm_max_mhz=float(max(mx)), reasons=sorted(reasons), samples=len(sm))
-        return out
+    def __exit__(self, *exc):
+        self._stop()
+        return False
+
+    def _stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except Exception:
+                self.proc.kill()
+            self.proc = None
+        if self.fh is not None:
+            self.fh.close()
+            self.fh = None
+        if self.path is not None:
+            try:
+                for line in open(self.path):
+                    f = [x.strip() for x in line.split(",")]
+                    if len(f) < 8:
+                        continue
+                    try:
+                        ts = datetime.datetime.strptime(f[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                        self.samples.append((ts, float(f[1]), float(f[2]), float(f[3]),
+                                             [n for n, v in zip(self.NAMES, f[4:8]) if v.lower().startswith("active")]))
+                    except ValueError:
+                        continue
+                os.unlink(self.path)
+            except Exception:
+                pass
+            self.path = None
+
+    def window(self, t0, t1):
+        """Median SM clock and the throttle reasons seen between host times t0 and t1.  A region shorter than the
+        sampling period may hold no sample: the nearest one on either side is used and `samples` says 0."""
+        self._stop()
+        inside = [s for s in self.samples if t0 <= s[0] <= t1]
+        n = len(inside)
+        if not inside and self.samples:
+            inside = sorted(self.samples, key=lambda s: min(abs(s[0] - t0), abs(s[0] - t1)))[:2]
+        if not inside:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": float(np.median([s[1] for s in inside])), "sm_max_mhz": float(max(s[2] for s in inside)),
+                "power_w_max": float(max(s[3] for s in inside)),
+                "reasons": sorted({r for s in inside for r in s[4]}), "samples": n}
 
 
 def cpu_sample(kind, nthreads, seconds_target=10.0):
@@ -178,6 +204,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-decode", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-extras", action="store_true", help="skip the other configurations, the preparation kernels, "
+                    "the tensor-pipe ceiling and the long (2 s) loop")
     ap.add_argument("--case", default="full", choices=["full", "small"],
                     help="small: a reduced batch of the same shapes, for profiler captures only (not a bench number)")
     args = ap.parse_args()
@@ -191,11 +219,23 @@ def main():
         return
 
     import torch
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product path has no CPU fallback")
+    if args.case == "small":
+        PREFILL.update(B=4)
+        DECODE.update(B=8)
+        args.no_extras = True
+    with ClockSampler(local) as sampler:               # the poller is stopped whatever happens below
+        line = run_ours(args, rank, world, local, sampler)
+    if line is not None:
+        print(json.dumps(line), flush=True)
+
+
+def run_ours(args, rank, world, local, sampler):
+    import torch
     import torch.distributed as dist
     import radiance_kernels_b200 as rk
 
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device: the product path has no CPU fallback")
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
@@ -214,11 +254,35 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
+    def timed(fn, steps, warm=3):
+        """ms per call: CUDA events on the current stream around `steps` back-to-back calls, after `warm` calls."""
+        for _ in range(warm):
+            fn()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        a.record()
+        for _ in range(steps):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / steps
+
+    def kernel_ms(fn, steps):
+        """ms of the main kernel inside `fn` (the library records events around it), averaged over `steps` calls."""
+        e0 = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+        e1 = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+        for ev in e0 + e1:
+            ev.record()                                # materialise the cudaEvent_t handles
+        torch.cuda.synchronize()
+        for i in range(steps):
+            L.rk_profile_set_events(C.c_void_p(e0[i].cuda_event), C.c_void_p(e1[i].cuda_event))
+            fn()
+        L.rk_profile_set_events(None, None)
+        torch.cuda.synchronize()
+        return float(np.mean([a.elapsed_time(b) for a, b in zip(e0, e1)]))
+
     L = rk.lib()
     peaks = measured_peaks()
-    if args.case == "small":
-        PREFILL.update(B=4)
-        DECODE.update(B=8)
     c = PREFILL
     B, H, Hkv, S, d = c["B"], c["H"], c["H_kv"], c["S"], c["d"]
     g = torch.Generator(device=dev).manual_seed(1000 + rank)
@@ -233,17 +297,16 @@ def main():
     def step():
         rk.attn_prefill(qc, kc, vc, qs, ks, vs, causal=True, v_scale_axis=rk.V_SCALES_ALONG_D, out=o, workspace=ws)
 
-    # ---- device-resident timing ----------------------------------------------------------------------
-    sampler = ClockSampler(local)
-    sampler.start()                                    # runs through warm-up and every timed region below
+    # ---- device-resident timing: exactly `steps` steps, max over ranks --------------------------------------
     for _ in range(args.warmup):
         step()
     kev0 = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
     kev1 = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     for ev in kev0 + kev1:
-        ev.record()                                    # materialise the cudaEvent_t handles
+        ev.record()
     barrier()
+    t_region0 = time.time()
     e0.record()
     for i in range(args.steps):
         L.rk_profile_set_events(C.c_void_p(kev0[i].cuda_event), C.c_void_p(kev1[i].cuda_event))
@@ -251,6 +314,7 @@ def main():
     L.rk_profile_set_events(None, None)
     e1.record()
     barrier()
+    t_region1 = time.time()
     ms_total = max_over_ranks(e0.elapsed_time(e1))
     ms_step = ms_total / args.steps
     kern_ms = float(np.mean([a.elapsed_time(b) for a, b in zip(kev0, kev1)]))
@@ -259,15 +323,60 @@ def main():
         raise SystemExit(f"device status {status}: a kernel gave up on a bounded wait; no number reported")
     flops = prefill_flops(c)
     value = flops * world / (ms_step * 1e-3) / 1e12
-    fp8_peak = 2.0 * peaks["bf16_sustained"]
-    roofline = {"bound": "tensor", "achieved": flops / (kern_ms * 1e-3) / 1e12, "peak": fp8_peak, "unit": "TFLOP/s",
-                "frac": flops / (kern_ms * 1e-3) / 1e12 / fp8_peak,
+    achieved = flops / (kern_ms * 1e-3) / 1e12
+
+    # ---- the tensor-pipe ceiling on this device, and the same kernel in a loop of at least 2 s ---------------
+    mma_peak = None
+    sustained = None
+    t_long = None
+    if not args.no_extras:
+        tiles = torch.randint(0, 0x7E, (2, 128 * 128), dtype=torch.uint8, device=dev)      # valid E4M3 codes
+        iters = 8192
+        sms = torch.cuda.get_device_properties(dev).multi_processor_count
+
+        def mma_loop():
+            rc = L.rk_debug_mxfp8_mma_loop(C.c_void_p(tiles[0].data_ptr()), C.c_void_p(tiles[1].data_ptr()), iters,
+                                           C.c_void_p(torch.cuda.current_stream().cuda_stream))
+            if rc != 0:
+                raise SystemExit(f"rk_debug_mxfp8_mma_loop failed: {rc}")
+
+        mma_flops = sms * iters * 2.0 * 128 ** 3
+        torch.cuda.synchronize(); time.sleep(0.5)                    # start the burst figure from an idle, cool part
+        burst_ms = min(timed(mma_loop, 1, warm=1) for _ in range(3))
+        n_sus = max(1, int(2500.0 / burst_ms))
+        t0 = time.time()
+        sus_ms = timed(mma_loop, n_sus, warm=0)
+        t1 = time.time()
+        mma_peak = {"burst_tflops": mma_flops / (burst_ms * 1e-3) / 1e12, "sustained_tflops": mma_flops / (sus_ms * 1e-3) / 1e12,
+                    "sustained_seconds": sus_ms * n_sus * 1e-3, "sustained_clocks": sampler_window(sampler, t0, t1, rank),
+                    "what": "tcgen05.mma kind::mxf8f6f4.block_scale M=128 N=128 K=32, operands and scales resident in shared "
+                            "memory / TMEM, one CTA per SM, no TMA and no softmax in the loop"}
+        # the attention kernel for at least 2 s: its sustained speed and the clock it ran at
+        n_long = max(args.steps, int(2200.0 / ms_step))
+        t0 = time.time()
+        long_ms = timed(step, n_long, warm=0)
+        t1 = time.time()
+        t_long = (t0, t1)
+        long_kern = kernel_ms(step, 10)
+        sustained = {"steps": n_long, "ms_per_step": long_ms, "kernel_ms_after_loop": long_kern,
+                     "tflops": flops / (long_ms * 1e-3) / 1e12}
+        del tiles
+
+    peak_burst = mma_peak["burst_tflops"] if mma_peak else 2.0 * peaks["bf16_burst"]
+    roofline = {"bound": "tensor", "achieved": achieved, "peak": peak_burst, "unit": "TFLOP/s",
+                "frac": achieved / peak_burst,
                 "traffic": NCU_PREFILL_DRAM_BYTES_PER_HEAD * c["B"] * c["H"] if (c["S"], c["d"]) == (4096, 128) else None,
-                "traffic_note": "ncu dram read+write of one launch at B=4 (138.75 MB for 64 (batch, head) units), scaled by "
+                "traffic_note": "ncu dram read+write of one launch at B=4 (191.95 MB for 64 (batch, head) units), scaled by "
                                 "the unit count; algorithmic bytes per launch: %d" % prefill_algorithmic_bytes(c),
-                "kernel": "prefill2q_kernel<false>", "kernel_ms": kern_ms,
-                "peak_note": f"2 x {peaks['source']} sustained cuBLAS bf16 ({peaks['bf16_sustained']} TF/s) as the dense "
-                             f"MXFP8 proxy; nominal dense FP8 is 4500 TF/s (frac of nominal {flops / (kern_ms * 1e-3) / 1e12 / 4500.0:.4f})"}
+                "kernel": "prefill2c_kernel<false>", "kernel_ms": kern_ms,
+                "peak_measured_mxfp8": mma_peak,
+                "frac_of_2x_bf16_burst": achieved / (2.0 * peaks["bf16_burst"]),
+                "frac_of_nominal": achieved / NOMINAL_FP8_TFLOPS,
+                "peak_note": ("peak = the tensor-pipe ceiling measured in this run by a GEMM-only loop of the same block-scaled "
+                              "MMAs (burst: the timed region is a few ms at full clock)" if mma_peak else
+                              f"peak = 2 x {peaks['source']} burst cuBLAS bf16 ({peaks['bf16_burst']} TF/s) as the dense MXFP8 proxy") +
+                             f"; 2 x {peaks['source']} cuBLAS bf16 burst = {2 * peaks['bf16_burst']:.1f}, sustained = "
+                             f"{2 * peaks['bf16_sustained']:.1f}; nominal dense FP8 {NOMINAL_FP8_TFLOPS:.0f} TF/s"}
 
     # ---- end to end through the host-buffer entry point ----------------------------------------------------
     e2e = None
@@ -277,7 +386,6 @@ def main():
         runner.run()
         n_e2e = max(3, min(args.steps, 10))
         barrier()
-        t0 = time.perf_counter()
         f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         f0.record()
         for _ in range(n_e2e):
@@ -287,8 +395,39 @@ def main():
         ms_e2e = max_over_ranks(f0.elapsed_time(f1)) / n_e2e
         e2e = {"value": flops * world / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms_e2e,
                "h2d_bytes_per_step": runner.h2d_bytes, "d2h_bytes_per_step": runner.d2h_bytes, "steps": n_e2e}
-        del runner, host
+        # what the bus alone allows: the same bytes, host -> device and device -> host on two streams at once,
+        # every rank at the same time (the ranks of one box share the host's memory and root complexes)
+        s_in, s_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+        dsts = [torch.empty_like(t, device=dev) for t in host]
+        barrier()
+        c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        c0.record()
+        s_in.wait_event(c0); s_out.wait_event(c0)
+        for _ in range(n_e2e):
+            with torch.cuda.stream(s_in):
+                for hsrc, ddst in zip(host, dsts):
+                    ddst.copy_(hsrc, non_blocking=True)
+            with torch.cuda.stream(s_out):
+                runner.o.copy_(o, non_blocking=True)
+        torch.cuda.current_stream().wait_stream(s_in); torch.cuda.current_stream().wait_stream(s_out)
+        c1.record()
+        barrier()
+        ms_copy = max_over_ranks(c0.elapsed_time(c1)) / n_e2e
+        e2e.update(copy_ceiling_ms=ms_copy, frac_of_copy_ceiling=ms_copy / ms_e2e,
+                   copy_ceiling_note="pinned cudaMemcpyAsync of the step's input bytes in and output bytes out on two streams, "
+                                     "all ranks at once, no compute")
+        del runner, host, dsts
     launches = args.steps * 4          # 2 scale re-tilings, V re-blocking, attention kernel per step
+
+    # ---- one global batch sharded over the ranks by (batch, KV head) units (N > 1) ------------------------------
+    strong = None
+    if world > 1:
+        strong = strong_scaling_leg(args, rk, dist, dev, rank, world, barrier, max_over_ranks)
+
+    # ---- the other configurations and the preparation kernels ------------------------------------------------
+    extras = None
+    if not args.no_extras and rank == 0:
+        extras = run_extras(rk, L, dev, peaks, peak_burst, timed, kernel_ms, qc, qs, vc, vs)
     del qc, kc, vc, qs, ks, vs, o, ws
     torch.cuda.empty_cache()
 
@@ -318,19 +457,14 @@ def main():
         for _ in range(args.warmup):
             dstep()
         d0, d1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        k0.record(); k1.record()
         barrier()
         d0.record()
         for i in range(args.steps):
-            if i == args.steps - 1:
-                L.rk_profile_set_events(C.c_void_p(k0.cuda_event), C.c_void_p(k1.cuda_event))
             dstep()
-        L.rk_profile_set_events(None, None)
         d1.record()
         barrier()
         dms = max_over_ranks(d0.elapsed_time(d1)) / args.steps
-        dk = k0.elapsed_time(k1)
+        dk = kernel_ms(dstep, min(args.steps, 10))
         by = decode_bytes(dc)
         decode = {"metric": "decode attention HBM GB/s (all GPUs)", "value": by * world / (dms * 1e-3) / 1e9, "unit": "GB/s",
                   "ms_per_step": dms, "workload": "batch 64, 32 query heads / 8 KV heads, d=128, KV length 32768, MXFP8 cache",
@@ -339,14 +473,21 @@ def main():
                                "frac": by / (dk * 1e-3) / 1e9 / peaks["hbm"],
                                "traffic": NCU_DECODE_DRAM_BYTES_PER_SEQUENCE * Bd if (Hkd, Ld, dd) == (8, 32768, 128) else None,
                                "traffic_note": "ncu dram read+write of one launch at B=8 (560.35 MB), scaled by B",
-                               "kernel": "decode_tc_kernel",
-                               "kernel_ms": dk, "peak_note": f"{peaks['source']} HBM copy bandwidth; nominal 8000 GB/s"}}
+                               "kernel": "decode_tc_kernel", "kernel_ms": dk, "frac_of_nominal": by / (dk * 1e-3) / 1e9 / NOMINAL_HBM_GBS,
+                               "peak_note": f"{peaks['source']} HBM copy bandwidth; nominal {NOMINAL_HBM_GBS:.0f} GB/s"}}
         if rk.last_device_status() != 0:
             raise SystemExit("device status non-zero after the decode leg")
         launches += args.steps * 2
         del kcd, vcd, ksd, vsd
 
-    clocks = sampler.stop()
+    clocks = sampler_window(sampler, t_region0, t_region1, rank)
+    if sustained is not None and t_long is not None:
+        sustained["clocks"] = sampler_window(sampler, t_long[0], t_long[1], rank)
+        mhz = sustained["clocks"].get("sm_mhz")
+        sustained["ms_x_mhz"] = sustained["ms_per_step"] * mhz if mhz else None
+        if mma_peak:
+            sustained["frac_of_sustained_peak"] = sustained["tflops"] / mma_peak["sustained_tflops"]
+        roofline["sustained"] = sustained
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         import oracle
@@ -356,7 +497,7 @@ def main():
         dist.barrier()
         dist.destroy_process_group()
     if rank != 0:
-        return
+        return None
     line = {"metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "mxfp8_e4m3 (e8m0 block scales, fp32 accumulate, bf16 out)", "data": "synthetic",
@@ -364,9 +505,150 @@ def main():
                        "parallelism": f"units sharded over {world} GPU(s), no collective on the data path",
                        "l2": "inputs + output (335 MB) exceed the 126 MB L2; no flush between steps"},
             "roofline": roofline, "e2e": e2e, "gpu_launches": launches, "clocks": clocks, "decode": decode}
+    if strong is not None:
+        line["strong_scaling"] = strong
+    if extras is not None:
+        line["extras"] = extras
     if cpu is not None:
         line["cpu_baseline"] = cpu
-    print(json.dumps(line), flush=True)
+    return line
+
+
+def sampler_window(sampler, t0, t1, rank):
+    return sampler.window(t0, t1)
+
+
+def strong_scaling_leg(args, rk, dist, dev, rank, world, barrier, max_over_ranks):
+    """ONE global B=8 H=16 S=4096 d=128 batch, its 128 (batch, KV head) units cut into contiguous blocks (shard_range),
+    every rank computing its block with rk_attn_prefill; then the optional gather of O with NCCL, timed apart."""
+    import torch
+    c = dict(B=8, H=16, H_kv=16, S=4096, d=128)
+    grp = c["H"] // c["H_kv"]
+    n_units = c["B"] * c["H_kv"]
+    lo, hi = rk.shard_range(n_units, rank, world)
+    nloc = hi - lo
+    S, d = c["S"], c["d"]
+    # a unit = one KV head with its `grp` query heads: the slice is a batch of nloc such units
+    g = torch.Generator(device=dev).manual_seed(4242)                   # same seed everywhere: one global problem
+    out = {"workload": "one global B=8 H=16 S=4096 d=128 causal batch, 128 (batch, KV head) units in contiguous blocks per rank",
+           "units_per_rank": [rk.shard_range(n_units, r, world)[1] - rk.shard_range(n_units, r, world)[0] for r in range(world)]}
+    if nloc == 0:
+        ms = 0.0
+        o = torch.empty(0, grp, S, d, dtype=torch.bfloat16, device=dev)
+    else:
+        # every rank draws the whole problem's random stream unit by unit and keeps its own block
+        qc = torch.empty(nloc, grp, S, d, dtype=torch.uint8, device=dev); qs = torch.empty(nloc, grp, S, d // 32, dtype=torch.uint8, device=dev)
+        kc = torch.empty(nloc, 1, S, d, dtype=torch.uint8, device=dev); ks = torch.empty(nloc, 1, S, d // 32, dtype=torch.uint8, device=dev)
+        vc = torch.empty_like(kc); vs = torch.empty_like(ks)
+        for u in range(n_units):
+            x = torch.randn(grp + 2, S, d, generator=g, device=dev)
+            if lo <= u < hi:
+                qc[u - lo], qs[u - lo] = rk.mx_quantize(x[:grp].contiguous())
+                kc[u - lo, 0], ks[u - lo, 0] = rk.mx_quantize(x[grp].contiguous())
+                vc[u - lo, 0], vs[u - lo, 0] = rk.mx_quantize(x[grp + 1].contiguous())
+        o = torch.empty(nloc, grp, S, d, dtype=torch.bfloat16, device=dev)
+        ws = torch.empty(rk.attn_prefill_workspace_bytes(nloc, grp, 1, S, S, d, rk.V_SCALES_ALONG_D) + 256, dtype=torch.uint8, device=dev)
+
+        def step():
+            rk.attn_prefill(qc, kc, vc, qs, ks, vs, causal=True, v_scale_axis=rk.V_SCALES_ALONG_D, out=o, workspace=ws)
+
+        for _ in range(args.warmup):
+            step()
+    barrier()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    if nloc:
+        for _ in range(args.steps):
+            step()
+    b.record()
+    barrier()
+    ms = max_over_ranks(a.elapsed_time(b)) / args.steps
+    flops = prefill_flops(c)
+    out.update(ms_per_step=ms, value=flops / (ms * 1e-3) / 1e12, unit="TFLOP/s")
+    # optional gather of O on every rank (equal blocks only: all_gather_into_tensor wants equal shapes)
+    if n_units % world == 0:
+        full = torch.empty(n_units, grp, S, d, dtype=torch.bfloat16, device=dev)
+        for _ in range(2):
+            dist.all_gather_into_tensor(full, o)
+        barrier()
+        a.record()
+        for _ in range(5):
+            dist.all_gather_into_tensor(full, o)
+        b.record()
+        barrier()
+        gms = max_over_ranks(a.elapsed_time(b)) / 5
+        out.update(gather_ms=gms, gather_bytes_per_rank=int(o.numel() * 2),
+                   gather_note="ncclAllGather of the bf16 O blocks (optional: only for callers that need O on one device)")
+    return out
+
+
+def run_extras(rk, L, dev, peaks, peak_burst, timed, kernel_ms, qc, qs, vc, vs):
+    """The other benchmark configurations (whole C-ABI call and attention kernel alone) and the preparation kernels,
+    each against its own roofline."""
+    import torch
+    out = {}
+
+    def prefill_case(name, B, H, Hkv, S, d, mul=1.0, softcap=0.0, q_fmt=0, kv_fmt=0, steps=5):
+        g = torch.Generator(device=dev).manual_seed(77)
+        Q = torch.randn(B, H, S, d, generator=g, device=dev) * mul
+        K = torch.randn(B, Hkv, S, d, generator=g, device=dev) * mul
+        V = torch.randn(B, Hkv, S, d, generator=g, device=dev) * mul
+        q_c, q_s = rk.mx_quantize(Q, q_fmt); k_c, k_s = rk.mx_quantize(K, kv_fmt); v_c, v_s = rk.mx_quantize(V, kv_fmt)
+        del Q, K, V
+        o = torch.empty(B, H, S, d, dtype=torch.bfloat16, device=dev)
+        ws = torch.empty(rk.attn_prefill_workspace_bytes(B, H, Hkv, S, S, d, rk.V_SCALES_ALONG_D, q_fmt, kv_fmt) + 256,
+                         dtype=torch.uint8, device=dev)
+
+        def fn():
+            rk.attn_prefill(q_c, k_c, v_c, q_s, k_s, v_s, causal=True, softcap=softcap, q_fmt=q_fmt, kv_fmt=kv_fmt,
+                            v_scale_axis=rk.V_SCALES_ALONG_D, out=o, workspace=ws)
+
+        ms = timed(fn, steps)
+        km = kernel_ms(fn, steps)
+        fl = 4.0 * B * H * S * S * d * 0.5
+        out[name] = {"ms_per_call": ms, "tflops": fl / (ms * 1e-3) / 1e12,
+                     "roofline": {"bound": "tensor", "achieved": fl / (km * 1e-3) / 1e12, "peak": peak_burst, "unit": "TFLOP/s",
+                                  "frac": fl / (km * 1e-3) / 1e12 / peak_burst, "kernel_ms": km,
+                                  "frac_of_nominal": fl / (km * 1e-3) / 1e12 / NOMINAL_FP8_TFLOPS, "traffic": None}}
+
+    prefill_case("prefill_gqa_B4_H32_kv8_S8192_d128", 4, 32, 8, 8192, 128)
+    prefill_case("prefill_gemma_B2_H16_kv8_S8192_d256_cap50", 2, 16, 8, 8192, 256, mul=0.5, softcap=50.0)
+    prefill_case("prefill_gemma_mxfp6_e2m3q_e3m2kv", 2, 16, 8, 8192, 256, mul=0.5, softcap=50.0, q_fmt=rk.E2M3, kv_fmt=rk.E3M2)
+
+    # quantizer: fp32 and bf16 input, 67 M elements (one tensor of the headline workload)
+    x = torch.randn(8 * 16 * 4096, 128, device=dev)
+    for nm, xx, bpe in (("quantizer_fp32_67M", x, 4 + 1 + 1 / 32), ("quantizer_bf16_67M", x.bfloat16(), 2 + 1 + 1 / 32)):
+        ms = timed(lambda: rk.mx_quantize(xx), 10)
+        gbs = xx.numel() * bpe / (ms * 1e-3) / 1e9
+        out[nm] = {"ms_per_call": ms, "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm"], "unit": "GB/s",
+                                                   "frac": gbs / peaks["hbm"], "bytes_per_element": bpe, "traffic": None,
+                                                   "note": "includes torch.empty of the outputs (allocator cache hit)"}}
+    del x
+    # V re-blocking along the keys, on the headline workload's V (2 bytes per element algorithmic)
+    ms = timed(lambda: rk.mx_rebase_v(vc, vs), 10)
+    gbs = vc.numel() * 2 * (1 + 1 / 32) / (ms * 1e-3) / 1e9
+    out["rebase_v_67M"] = {"ms_per_call": ms, "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm"], "unit": "GB/s",
+                                                           "frac": gbs / peaks["hbm"], "traffic": None}}
+    # decode with 8 query heads per KV head
+    Bd, Hd, Hkd, Ld = 64, 64, 8, 32768
+    g2 = torch.Generator(device=dev).manual_seed(78)
+    qd = torch.randn(Bd, Hd, 128, generator=g2, device=dev).bfloat16()
+    kcd = torch.randint(0, 0x7E, (Bd, Hkd, Ld, 128), generator=g2, dtype=torch.uint8, device=dev)
+    vcd = torch.randint(0, 0x7E, (Bd, Hkd, Ld, 128), generator=g2, dtype=torch.uint8, device=dev)
+    ksd = torch.randint(118, 122, (Bd, Hkd, Ld, 4), generator=g2, dtype=torch.uint8, device=dev)
+    vsd = torch.randint(118, 122, (Bd, Hkd, Ld, 4), generator=g2, dtype=torch.uint8, device=dev)
+    od = torch.empty(Bd, Hd, 128, dtype=torch.bfloat16, device=dev)
+    wsd = torch.empty(rk.attn_decode_workspace_bytes(Bd, Hd, Hkd, Ld, 128) + 16, dtype=torch.uint8, device=dev)
+    fn = lambda: rk.attn_decode(qd, kcd, vcd, ksd, vsd, out=od, workspace=wsd)
+    timed(fn, 3)
+    km = kernel_ms(fn, 5)
+    by = 2.0 * Bd * Hkd * Ld * 128 * (1 + 1 / 32) + 2 * Bd * Hd * 128 * 2
+    out["decode_B64_H64_kv8_L32768"] = {"roofline": {"bound": "hbm", "achieved": by / (km * 1e-3) / 1e9, "peak": peaks["hbm"],
+                                                     "unit": "GB/s", "frac": by / (km * 1e-3) / 1e9 / peaks["hbm"], "kernel_ms": km,
+                                                     "traffic": None}}
+    if rk.last_device_status() != 0:
+        raise SystemExit("device status non-zero after the extra configurations")
+    return out
 
 
 if __name__ == "__main__":

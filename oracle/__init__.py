@@ -41,6 +41,7 @@ class PrefillArgs(C.Structure):
         ("dump_slice", C.c_int64),
         ("dump_s", C.c_void_p), ("dump_p_codes", C.c_void_p), ("dump_p_scales", C.c_void_p),
         ("dump_m", C.c_void_p), ("dump_l", C.c_void_p),
+        ("bf16_faithful", C.c_int32),
     ]
 
 
@@ -208,10 +209,11 @@ def rebase_v(codes, scales, fmt=E4M3):
 
 def attn_prefill(q, k, v, qs, ks, vs, *, causal, softmax_scale, q_pos0=0, window=0, softcap=0.0,
                  q_fmt=E4M3, kv_fmt=E4M3, v_scale_axis=1, block_n=128, nthreads=0, slices=None,
-                 dump_slice=-1, want_lse=False):
+                 dump_slice=-1, want_lse=False, bf16_faithful=False):
     """MX prefill attention oracle. q [B,H,Sq,d] codes, k/v [B,Hkv,Skv,d] codes, scales as the C ABI takes them.
 
-    Returns dict(o_f32, o_bf16, lse?, dumps?)."""
+    bf16_faithful: re-round every intermediate to bf16 where the reference's Python model does (its numerics, not
+    the build target's fp32 softmax).  Returns dict(o_f32, o_bf16, lse?, dumps?)."""
     q, k, v, qs, ks, vs = [np.ascontiguousarray(t, np.uint8) for t in (q, k, v, qs, ks, vs)]
     B, H, Sq, d = q.shape
     Hkv, Skv = k.shape[1], k.shape[2]
@@ -227,6 +229,7 @@ def attn_prefill(q, k, v, qs, ks, vs, *, causal, softmax_scale, q_pos0=0, window
     a.nthreads = nthreads or hardware_threads()
     a.slice_begin, a.slice_end = (slices if slices else (0, 0))
     a.o_f32, a.o_bf16, a.lse = _p(o32), _p(o16), _p(lse)
+    a.bf16_faithful = int(bool(bf16_faithful))
     out = {"o_f32": o32, "o_bf16": o16}
     a.dump_slice = dump_slice
     if dump_slice >= 0:

@@ -389,6 +389,11 @@ struct rko_prefill_args {
   uint8_t* dump_p_scales;           // [Sq][Skv/32]
   float* dump_m;                    // [Sq] final running max
   float* dump_l;                    // [Sq] final l
+  // Where the numbers are rounded.  0 (the build target): fp32 softmax state, exp and accumulation, one bf16 rounding
+  // of O at the end.  1: every intermediate re-rounded to bf16 where the reference's model does it (q_bf16 of
+  // kernels/flash_attention_mx_gqa/flash_attention_model.py:222-246): the matmul results S and P.V, S * scale, corr,
+  // p, the block's sum of p, l, the O accumulator after every key block, and O / l.
+  int32_t bf16_faithful;
 };
 
 // Streaming MX attention for one (b,h) slice.  Structure:
@@ -427,6 +432,8 @@ static void prefill_slice(const rko_prefill_args& a, int64_t slice) {
   }
 
   const bool dump = (a.dump_slice == slice);
+  const bool bf = a.bf16_faithful != 0;
+  auto rb = [bf](float x) { uint16_t bits; return bf ? bf16_round_to_f32(x, &bits) : x; };   // q_bf16 in faithful mode
   const int bn = a.block_n;
   const float NEG_INF = -std::numeric_limits<float>::infinity();
   std::vector<float> s(bn), p(bn), pq(bn), o(d);
@@ -448,8 +455,9 @@ static void prefill_slice(const rko_prefill_args& a, int64_t slice) {
       }
       float bmax = NEG_INF;
       for (int c = 0; c < nk; c++) {
-        float sv = dot_f32(&Q[(size_t)i * d], &K[(size_t)(k0 + c) * d], d) * a.softmax_scale;
-        if (a.softcap > 0.0f) sv = a.softcap * std::tanh(sv / a.softcap);   // cap before mask/max
+        // faithful mode: the mesh returns S in bf16 (mx_gemm, flash_attention_model.py:76-86), then q_bf16(S * scale) (:226)
+        float sv = rb(rb(dot_f32(&Q[(size_t)i * d], &K[(size_t)(k0 + c) * d], d)) * a.softmax_scale);
+        if (a.softcap > 0.0f) sv = rb(a.softcap * std::tanh(sv / a.softcap));   // cap before mask/max
         const int kpos = k0 + c;
         bool msk = a.causal && kpos > q_pos;
         if (a.window > 0) msk = msk || (kpos + a.window <= q_pos);
@@ -459,14 +467,15 @@ static void prefill_slice(const rko_prefill_args& a, int64_t slice) {
       }
       const float m_new = std::max(m_run, bmax);
       // corr = exp(m_old - m_new); 1 while nothing has been accumulated yet.
-      const float corr = (m_run == NEG_INF) ? 1.0f : std::exp(m_run - m_new);
+      const float corr = (m_run == NEG_INF) ? 1.0f : rb(std::exp(m_run - m_new));
       float lsum = 0.0f;
       for (int c = 0; c < nk; c++) {
-        p[c] = (s[c] == NEG_INF) ? 0.0f : std::exp(s[c] - m_new);   // masked -> exactly 0
+        p[c] = (s[c] == NEG_INF) ? 0.0f : rb(std::exp(s[c] - m_new));   // masked -> exactly 0
         lsum += p[c];
       }
-      l_run = l_run * corr + lsum;
-      for (int c = 0; c < d; c++) o[c] *= corr;
+      l_run = rb(l_run * corr + rb(lsum));
+      std::vector<float> pv;
+      if (bf) { pv.assign(d, 0.0f); } else { for (int c = 0; c < d; c++) o[c] *= corr; }
       for (int g0 = 0; g0 < nk; g0 += 32) {
         const int ng = std::min(32, nk - g0);
         float pmax = 0.0f;
@@ -480,12 +489,15 @@ static void prefill_slice(const rko_prefill_args& a, int64_t slice) {
           pq[g0 + c] = decode_elem(code, kFmt[0]) * sf;
         }
       }
+      float* acc = bf ? pv.data() : o.data();
       for (int c = 0; c < nk; c++) {
         const float w = pq[c];
         if (w == 0.0f) continue;
         const float* vr = &V[(size_t)(k0 + c) * d];
-        for (int e = 0; e < d; e++) o[e] += w * vr[e];
+        for (int e = 0; e < d; e++) acc[e] += w * vr[e];
       }
+      // faithful mode: P.V comes back from the mesh in bf16 and the accumulator is re-rounded after every block (:241)
+      if (bf) for (int e = 0; e < d; e++) o[e] = rb(o[e] * corr + rb(pv[e]));
       m_run = m_new;
     }
     const float safe_l = l_run > 0.0f ? l_run : 1.0f;

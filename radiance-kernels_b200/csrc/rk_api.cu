@@ -518,7 +518,7 @@ RK_API int rk_debug_mxfp8_mma_loop(const uint8_t* a_tile, const uint8_t* b_tile,
 
 /* Test hooks (not in the public header): which prefill kernel serves d <= 128 (0 = default, 1 = the
  * two-threads-per-row kernel), and which warp role of the default kernel sleeps a little at every key tile
- * (0 = none; 1, 2 = softmax of query tile A, B; 3 = correction; 4 = TMA producer; 5 = MMA issuer). */
+ * (0 = none; 1, 2 = softmax of query tile A, B; 3 = correction; 4 = TMA producer; 5 = Q K^T issuer; 6 = P V issuer). */
 RK_API void rk_debug_set_prefill_path(int path) { g_prefill_path = path; }
 RK_API void rk_debug_set_prefill_perturb(int role) { g_prefill_perturb = role; }
 

@@ -131,6 +131,16 @@ RK_DEVINL bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   }
   return ok != 0;
 }
+// Non-blocking test of an mbarrier phase (never suspends the thread): for a look ahead whose answer is used later.
+RK_DEVINL bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
 RK_DEVINL uint64_t global_timer_ns() {
   uint64_t t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t;
 }
@@ -148,6 +158,30 @@ RK_DEVINL bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_fla
   for (uint32_t it = 1;; ++it) {
     if (mbar_try_wait<HINT_NS>(bar, parity)) return true;
     if ((it & 255u) == 0u) {
+      if (*abort_flag || *reinterpret_cast<volatile int*>(status) != 0) { *abort_flag = 1; return false; }
+      if (global_timer_ns() - t0 > limit_ns) break;
+    }
+  }
+  *abort_flag = 1;
+  atomicCAS(status, 0, code);
+  return false;
+}
+
+// Bounded wait for warps that are not on the critical path (producers, issuers, correction): between polls the
+// warp sleeps `SLEEP_NS`, so that it leaves the issue slots of its scheduler to the warps that compute.  Same
+// give-up rule as mbar_wait.
+template <uint32_t SLEEP_NS>
+RK_DEVINL bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status, int code,
+                                 uint64_t limit_ns = 2000000000ull) {
+#ifdef RK_V_TIGHTPOLL
+  return mbar_wait(bar, parity, abort_flag, status, code, limit_ns);
+#endif
+  if (mbar_try_wait<0>(bar, parity)) return true;
+  const uint64_t t0 = global_timer_ns();
+  for (uint32_t it = 1;; ++it) {
+    __nanosleep(SLEEP_NS);
+    if (mbar_try_wait<0>(bar, parity)) return true;
+    if ((it & 63u) == 0u) {
       if (*abort_flag || *reinterpret_cast<volatile int*>(status) != 0) { *abort_flag = 1; return false; }
       if (global_timer_ns() - t0 > limit_ns) break;
     }

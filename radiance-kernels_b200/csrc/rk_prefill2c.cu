@@ -10,12 +10,14 @@
 //   warps 8-11   correction: rescale_accumulate (flash_mx_impl.hpp:508-532) on the O accumulators in TMEM, off the
 //                softmax warps' critical path; warp 8+q serves TMEM lane quadrant q of both tiles
 //   warp  12     TMA producer (one elected lane)
-//   warp  13     MMA issuer (one elected lane) + TMEM allocation
-//   warps 14-15  fill the fourth warpgroup (register reallocation works on whole warpgroups)
+//   warp  13     issuer of the S = Q K^T MMAs (one elected lane) + TMEM allocation
+//   warp  14     issuer of the O += P V MMAs (one elected lane): two issuers, so that a P V waiting for its P tile
+//                never holds back the next Q K^T
+//   warp  15     fills the fourth warpgroup (register reallocation works on whole warpgroups)
 //
 // Registers are moved between the warpgroups with setmaxnreg: the softmax threads hold a whole 128-score row
 // (kRegSoftmax), correction, TMA and MMA threads need few.  The S accumulator (128 TMEM columns) is shared by the
-// two tiles: a softmax group copies its rows to registers at once and hands the columns back, the MMA warp
+// two tiles: a softmax group copies its rows to registers at once and hands the columns back, the Q K^T issuer
 // alternates QK_A, QK_B.  Every K/V tile brought in by TMA serves both query tiles.
 #include "rk_prefill.cuh"
 
@@ -24,7 +26,11 @@ namespace rk {
 namespace c2 {
 constexpr int kStages = 3;
 constexpr int kThreads = 512;
-constexpr int kWarpCorr = 8, kWarpTma = 12, kWarpMma = 13;
+#ifndef RK_SLEEP_NS
+#define RK_SLEEP_NS 100
+#endif
+constexpr uint32_t kSleepNs = RK_SLEEP_NS;     // back-off of the warps that wait off the critical path
+constexpr int kWarpCorr = 8, kWarpTma = 12, kWarpQk = 13, kWarpPv = 14;
 constexpr uint32_t kRegSoftmax = 184, kRegCorr = 88, kRegIssue = 56;   // 128 * (2*184 + 88 + 56) = 65536 registers
 // TMEM columns
 constexpr uint32_t cS = 0, cO = 128 /* + g*128 */, cSfQ = 384 /* + g*4 */, cSfK = 392 /* + st*4 */,
@@ -41,13 +47,13 @@ constexpr int sfp_off = sfv_off + kStages * kSfAtomBytes;  // [2][2]
 constexpr int bar_off = sfp_off + 4 * kSfAtomBytes;
 // barrier indices
 constexpr int bQ = 0, bKF = 1, bKE = 4, bVF = 7, bVE = 10, bSF = 13 /* +g */, bSE = 15 /* +g */,
-              bPF = 17 /* + g*2+pb */, bPV = 21 /* + g*2+pb */, bCF = 25 /* + (g*2+pb)*4+quad */, bOR = 41 /* +g */,
-              bDRAIN = 43, nBars = 44;
+              bPF = 17 /* + g*2+pb */, bPV = 21 /* + g*2+pb */, bCF = 25 /* + (g*4+slot)*4+quad */, bOR = 57 /* + g*2+pb */,
+              bDRAIN = 61, bDRAIN2 = 62, nBars = 63;
 constexpr int misc_off = bar_off + nBars * 8;
-constexpr int corr_off = misc_off + 16;                    // [2 groups][2][128] floats: the O rescale factors of a tile
-constexpr int total = corr_off + 2 * 2 * 128 * 4;
+constexpr int corr_off = misc_off + 16;                    // [2 groups][4 slots][128] floats: the O rescale factors of a tile
+constexpr int total = corr_off + 2 * 4 * 128 * 4;
 // test hook: which role sleeps a little at every key tile (schedule perturbation)
-constexpr int kPerturbSoftmaxA = 1, kPerturbSoftmaxB = 2, kPerturbCorr = 3, kPerturbTma = 4, kPerturbMma = 5;
+constexpr int kPerturbSoftmaxA = 1 /* 2 = softmax of tile B */, kPerturbCorr = 3, kPerturbTma = 4, kPerturbQk = 5, kPerturbPv = 6;
 }  // namespace c2
 
 template <uint32_t N> RK_DEVINL void reg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
@@ -66,8 +72,8 @@ __device__ __forceinline__ void softmax_row_group(const PrefillParams& p, uint8_
   uint64_t* s_empty = bars + bSE + grp;
   uint64_t* p_full = bars + bPF + grp * 2;
   uint64_t* pv_done = bars + bPV + grp * 2;
-  uint64_t* corr_full = bars + bCF + grp * 8;
-  float* corr_sm = reinterpret_cast<float*>(smem + corr_off) + grp * 256;
+  uint64_t* corr_full = bars + bCF + grp * 16;
+  float* corr_sm = reinterpret_cast<float*>(smem + corr_off) + grp * 512;
 
   const int lane = threadIdx.x & 31;
   const int quad = (threadIdx.x >> 5) & 3;
@@ -81,13 +87,19 @@ __device__ __forceinline__ void softmax_row_group(const PrefillParams& p, uint8_
 
   float m_run = NEG_INF, l_run = 0.0f;
   bool ok = true;
+  bool s_ready = false;       // result of an early, non-blocking test of the next tile's S barrier
 
   for (int j = 0; j < n_tiles && ok; ++j) {
     const int pb = j & 1;
     perturb(p, kPerturbSoftmaxA + grp, j);
-    ok = __all_sync(0xffffffffu, mbar_wait(s_full, j & 1, abort_flag, p.status, 101));
-    if (!ok) break;
+    const bool stamp = (quad == 0 && lane == 0);
+    if (stamp) RK_STAMP(grp, j, 0);
+    if (!__all_sync(0xffffffffu, s_ready)) {         // the test issued during the previous tile said "not yet"
+      ok = __all_sync(0xffffffffu, mbar_wait(s_full, j & 1, abort_flag, p.status, 101));
+      if (!ok) break;
+    }
     tc_fence_after();
+    if (stamp) RK_STAMP(grp, j, 1);
 
     float s[128];
 #pragma unroll
@@ -96,6 +108,7 @@ __device__ __forceinline__ void softmax_row_group(const PrefillParams& p, uint8_
     tc_fence_before();
     __syncwarp();
     if (lane == 0) mbar_arrive(s_empty);       // hand the S columns back: the other query tile's QK^T may use them
+    if (stamp) RK_STAMP(grp, j, 2);
 
     if (dump && j == 0) {
 #pragma unroll
@@ -121,14 +134,26 @@ __device__ __forceinline__ void softmax_row_group(const PrefillParams& p, uint8_
 #pragma unroll
       for (int c = 0; c < 128; ++c) s[c] = (c > hi || c <= lo) ? NEG_INF : s[c];
     }
+    // block maxima: eight independent chains (two per 32-key block), advanced in turn so that no instruction waits
+    // for the one before it
     float bmax[4];
+    {
+      float a0[4], a1[4];
 #pragma unroll
-    for (int g = 0; g < 4; ++g) {
-      float a0 = fmax3(s[g * 32 + 0], s[g * 32 + 1], s[g * 32 + 2]);
-      float a1 = fmax3(s[g * 32 + 3], s[g * 32 + 4], s[g * 32 + 5]);
+      for (int g = 0; g < 4; ++g) {
+        a0[g] = fmax3(s[g * 32 + 0], s[g * 32 + 1], s[g * 32 + 2]);
+        a1[g] = fmax3(s[g * 32 + 3], s[g * 32 + 4], s[g * 32 + 5]);
+      }
 #pragma unroll
-      for (int c = 6; c < 30; c += 4) { a0 = fmax3(a0, s[g * 32 + c], s[g * 32 + c + 1]); a1 = fmax3(a1, s[g * 32 + c + 2], s[g * 32 + c + 3]); }
-      bmax[g] = fmax3(a0, a1, fmaxf(s[g * 32 + 30], s[g * 32 + 31]));
+      for (int c = 6; c < 30; c += 4) {
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          a0[g] = fmax3(a0[g], s[g * 32 + c], s[g * 32 + c + 1]);
+          a1[g] = fmax3(a1[g], s[g * 32 + c + 2], s[g * 32 + c + 3]);
+        }
+      }
+#pragma unroll
+      for (int g = 0; g < 4; ++g) bmax[g] = fmax3(a0[g], a1[g], fmaxf(s[g * 32 + 30], s[g * 32 + 31]));
     }
     const float mx = fmaxf(fmax3(bmax[0], bmax[1], bmax[2]), bmax[3]);
     const float m_new = fmaxf(m_run, mx * sc_mul);
@@ -137,69 +162,88 @@ __device__ __forceinline__ void softmax_row_group(const PrefillParams& p, uint8_
     const float m_use = (m_new == NEG_INF) ? 0.0f : (SOFTCAP ? m_new : fmaf(-fabsf(m_new), 4.76837158203125e-7f, m_new));
     const float corr = (m_run == NEG_INF) ? 1.0f : ex2_approx(m_run - m_new);
     m_run = m_new;
-    // the correction warp of this lane quadrant can start on O while the exponentials run here
-    corr_sm[pb * 128 + row] = corr;
+    // The correction warp of this lane quadrant can start on O while the exponentials run here.  Slot j & 3: this
+    // group is never more than two tiles ahead of the correction warp (the wait for the P buffer below sees to
+    // that), so a slot is free again long before it comes round.
+    corr_sm[(j & 3) * 128 + row] = corr;
     __syncwarp();
-    if (lane == 0) mbar_arrive(&corr_full[pb * 4 + quad]);
-
-    // the P buffer and its scale atom are free once the P.V that read them two tiles ago has finished
-    if (j >= 2) {
-      ok = __all_sync(0xffffffffu, mbar_wait(&pv_done[pb], ((j - 2) >> 1) & 1, abort_flag, p.status, 102));
-      if (!ok) break;
-    }
+    if (lane == 0) mbar_arrive(&corr_full[(j & 3) * 4 + quad]);
+    if (stamp) RK_STAMP(grp, j, 3);
+    // The P buffer and its scale atom are free once the P.V that read them two tiles ago has finished: tested
+    // here without blocking (the answer takes a few hundred cycles to come back), waited for only if it said no.
+    const bool p_free = (j < 2) || mbar_test_wait(&pv_done[pb], ((j - 2) >> 1) & 1);
 
     // ---- p = 2^(x - m), row sum from the unquantised p, requant per 32-key block ---------------------
+    // ex2.approx.ftz never returns a subnormal, so every non-zero p has an exponent field >= 1 and one multiply by
+    // 2^(7-sc) puts the E4M3 code into bits [20,27) whatever the block scale code sc is (sc < 7 needs no other
+    // path: all its non-zero elements lie within 2^6 of the block maximum).
     uint8_t* p_tile = smem + p_off + (grp * 2 + pb) * kTileBytes + row * 128;
-    float ls0 = 0.0f, ls1 = 0.0f, ls2 = 0.0f, ls3 = 0.0f;
+    uint64_t lsA = 0ull, lsB = 0ull;                                  // two packed pairs of partial row sums
     uint32_t scale_word = 0;
+    uint64_t fmul2[4];
 #pragma unroll
     for (int g = 0; g < 4; ++g) {
-#pragma unroll
-      for (int c = 0; c < 32; c += 4) {
-        float x0, x1, x2, x3;
-        fma2(s[g * 32 + c + 0], s[g * 32 + c + 1], sc_mul, -m_use, x0, x1);
-        fma2(s[g * 32 + c + 2], s[g * 32 + c + 3], sc_mul, -m_use, x2, x3);
-        const float p0 = ex2_approx(x0), p1 = ex2_approx(x1), p2 = ex2_approx(x2), p3 = ex2_approx(x3);
-        s[g * 32 + c + 0] = p0; s[g * 32 + c + 1] = p1; s[g * 32 + c + 2] = p2; s[g * 32 + c + 3] = p3;
-        add2(ls0, ls1, p0, p1);
-        add2(ls2, ls3, p2, p3);
-      }
       const float pmax = ex2_approx(fmaf(bmax[g], sc_mul, -m_use));   // p of the block's arg-max element
       int sc = (int)(__float_as_uint(pmax) >> 23);                    // E8M0 code: se = floor(log2 pmax) <= 0
       sc = min(sc, 127);
       scale_word |= (uint32_t)sc << (8 * g);
-      uint32_t w[8];
-      if (sc >= 7) {
-        // y = p * 2^(7-sc): exponent field = E4M3 exponent field, mantissa kept, so the truncated code is
-        // y's bits [20,27); .ftz zeroes everything below 2^-6 of the block scale.
-        const float f = __uint_as_float((uint32_t)(134 - sc) << 23);
+      const float f = __uint_as_float((uint32_t)(134 - sc) << 23);   // 2^(7-sc)
+      fmul2[g] = pack2(f, f);
+    }
+    const uint64_t sc2 = pack2(sc_mul, sc_mul), nm2 = pack2(-m_use, -m_use);
+    // Four elements at a time: exponentials of block g+1 (special-function unit) next to the requantization of block
+    // g (integer and FMA pipes), in one instruction stream, so that the units work side by side.
+    auto exp4 = [&](int g, int c) {
 #pragma unroll
-        for (int q = 0; q < 8; ++q) {
-          float y0, y1, y2, y3;
-          mul2_ftz(s[g * 32 + q * 4 + 0], s[g * 32 + q * 4 + 1], f, y0, y1);
-          mul2_ftz(s[g * 32 + q * 4 + 2], s[g * 32 + q * 4 + 3], f, y2, y3);
-          w[q] = pack_u8x2(__float_as_uint(y1) >> 20, __float_as_uint(y0) >> 20,
-                           pack_u8x2(__float_as_uint(y3) >> 20, __float_as_uint(y2) >> 20, 0u));
-        }
-      } else {
-        const int sub = (sc - 7) * 8;                                 // block max below 2^-120: exact integer form
-#pragma unroll
-        for (int q = 0; q < 8; ++q) {
-          uint32_t word = 0;
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const uint32_t bits = __float_as_uint(s[g * 32 + q * 4 + e]);
-            int t = (int)(bits >> 20) - sub;
-            t = (t >= 8 && bits >= 0x00800000u) ? t : 0;
-            word |= (uint32_t)t << (8 * e);
-          }
-          w[q] = word;
-        }
+      for (int e = 0; e < 4; e += 2) {
+        float x0, x1;
+        unpack2(fma2p(pack2(s[g * 32 + c + e], s[g * 32 + c + e + 1]), sc2, nm2), x0, x1);
+        s[g * 32 + c + e] = ex2_approx(x0);
+        s[g * 32 + c + e + 1] = ex2_approx(x1);
       }
+    };
+    // y = p * 2^(7-sc): exponent field = E4M3 exponent field, mantissa kept, so the truncated code is
+    // y's bits [20,27); .ftz zeroes everything below 2^-6 of the block scale.
+    auto requant4 = [&](int g, int c) -> uint32_t {
+      const uint64_t p01 = pack2(s[g * 32 + c + 0], s[g * 32 + c + 1]);
+      const uint64_t p23 = pack2(s[g * 32 + c + 2], s[g * 32 + c + 3]);
+      lsA = add2p(lsA, p01);
+      lsB = add2p(lsB, p23);
+      uint32_t y0, y1, y2, y3;
+      unpack2u(mul2p_ftz(p01, fmul2[g]), y0, y1);
+      unpack2u(mul2p_ftz(p23, fmul2[g]), y2, y3);
+      return pack_u8x2(y1 >> 20, y0 >> 20, pack_u8x2(y3 >> 20, y2 >> 20, 0u));
+    };
+#pragma unroll
+    for (int c = 0; c < 32; c += 4) exp4(0, c);
+    if (!__all_sync(0xffffffffu, p_free)) {
+      ok = __all_sync(0xffffffffu, mbar_wait(&pv_done[pb], ((j - 2) >> 1) & 1, abort_flag, p.status, 102));
+      if (!ok) break;
+    }
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      uint32_t w[8];
+#ifdef RK_V_COARSE
+      if (g < 3) {
+#pragma unroll
+        for (int q = 0; q < 8; ++q) exp4(g + 1, q * 4);
+      }
+#pragma unroll
+      for (int q = 0; q < 8; ++q) w[q] = requant4(g, q * 4);
+#else
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        if (g < 3) exp4(g + 1, q * 4);
+        w[q] = requant4(g, q * 4);
+      }
+#endif
       const int c0 = (2 * g) ^ (row & 7), c1 = (2 * g + 1) ^ (row & 7);     // 128-byte swizzle
       *reinterpret_cast<uint4*>(p_tile + c0 * 16) = make_uint4(w[0], w[1], w[2], w[3]);
       *reinterpret_cast<uint4*>(p_tile + c1 * 16) = make_uint4(w[4], w[5], w[6], w[7]);
     }
+    float ls0, ls1, ls2, ls3;
+    unpack2(lsA, ls0, ls1);
+    unpack2(lsB, ls2, ls3);
     l_run = l_run * corr + ((ls0 + ls1) + (ls2 + ls3));
     // the row's four block scales: bytes (row%32)*16 + (row/32)*4 + 0..3 of the 512-byte scale atom
     *reinterpret_cast<uint32_t*>(smem + sfp_off + (grp * 2 + pb) * kSfAtomBytes + (row & 31) * 16 + (row >> 5) * 4) = scale_word;
@@ -214,9 +258,13 @@ __device__ __forceinline__ void softmax_row_group(const PrefillParams& p, uint8_
       }
       d32[128 * 32 + row] = scale_word;
     }
+    // a look ahead at the next tile's S barrier: asked here, used at the top of the next tile
+    s_ready = (j + 1 < n_tiles) && mbar_test_wait(s_full, (j + 1) & 1);
+    if (stamp) RK_STAMP(grp, j, 4);
     fence_proxy_async_smem();
     __syncwarp();
     if (lane == 0) mbar_arrive(&p_full[pb]);
+    if (stamp) RK_STAMP(grp, j, 5);
   }
 
   // ---- epilogue: O / l -> bf16 (finalize_O, flash_mx_impl.hpp:535-553) ----------------------------------------
@@ -273,13 +321,20 @@ __device__ __forceinline__ void correction_quadrant(const PrefillParams& p, uint
 #pragma unroll 1
     for (int g = 0; g < 2 && ok; ++g) {
       if (j >= nt[g]) continue;
-      ok = __all_sync(0xffffffffu, mbar_wait<64>(&bars[bCF + (g * 2 + pb) * 4 + quad], (j >> 1) & 1, abort_flag, p.status, 401));
+      if (quad == 0 && lane == 0) RK_STAMP(3, j, g * 4 + 0);
+      ok = __all_sync(0xffffffffu, mbar_wait_relaxed<kSleepNs>(&bars[bCF + (g * 4 + (j & 3)) * 4 + quad], (j >> 2) & 1, abort_flag, p.status, 401));
       if (!ok) break;
-      const float corr = corr_sm[(g * 2 + pb) * 128 + row];
-      if (j > 0 && __any_sync(0xffffffffu, corr != 1.0f)) {
-        ok = __all_sync(0xffffffffu, mbar_wait(&bars[bPV + g * 2 + ((j - 1) & 1)], ((j - 1) >> 1) & 1, abort_flag, p.status, 402));
+      const float corr = corr_sm[(g * 4 + (j & 3)) * 128 + row];
+      if (quad == 0 && lane == 0) RK_STAMP(3, j, g * 4 + 1);
+      if (j > 0) {
+        // Always wait for the previous P.V of this tile, rescale or not: an arrival on the O-ready barrier then
+        // implies that its previous phase has been consumed, which is what keeps the two-deep barrier from wrapping.
+        ok = __all_sync(0xffffffffu, mbar_wait_relaxed<kSleepNs>(&bars[bPV + g * 2 + ((j - 1) & 1)], ((j - 1) >> 1) & 1, abort_flag, p.status, 402));
         if (!ok) break;
+      }
+      if (j > 0 && __any_sync(0xffffffffu, corr != 1.0f)) {
         tc_fence_after();
+        if (quad == 0 && lane == 0) RK_STAMP(3, j, g * 4 + 2);
 #pragma unroll 1
         for (int ch = 0; ch < o_chunks; ++ch) {
           uint32_t r[32];
@@ -293,7 +348,8 @@ __device__ __forceinline__ void correction_quadrant(const PrefillParams& p, uint
         tc_fence_before();
       }
       __syncwarp();
-      if (lane == 0) mbar_arrive(&bars[bOR + g]);   // the tile's P.V may accumulate into O now
+      if (lane == 0) mbar_arrive(&bars[bOR + g * 2 + pb]);   // the tile's P.V may accumulate into O now
+      if (quad == 0 && lane == 0) RK_STAMP(3, j, g * 4 + 3);
     }
   }
 }
@@ -355,14 +411,14 @@ prefill2c_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     for (int g = 0; g < 2; ++g) {
       mbar_init(&bars[bSF + g], 1); mbar_init(&bars[bSE + g], 4);
       for (int i = 0; i < 2; ++i) { mbar_init(&bars[bPF + g * 2 + i], 4); mbar_init(&bars[bPV + g * 2 + i], 1); }
-      for (int i = 0; i < 8; ++i) mbar_init(&bars[bCF + g * 8 + i], 1);
-      mbar_init(&bars[bOR + g], 4);
+      for (int i = 0; i < 16; ++i) mbar_init(&bars[bCF + g * 16 + i], 1);
+      mbar_init(&bars[bOR + g * 2], 4); mbar_init(&bars[bOR + g * 2 + 1], 4);
     }
-    mbar_init(&bars[bDRAIN], 1);
+    mbar_init(&bars[bDRAIN], 1); mbar_init(&bars[bDRAIN2], 1);
     *abort_flag = 0;
     fence_barrier_init();
   }
-  if (warp == kWarpMma) { tmem_alloc(tmem_ptr, kTmemCols); tmem_relinquish(); }
+  if (warp == kWarpQk) { tmem_alloc(tmem_ptr, kTmemCols); tmem_relinquish(); }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -403,13 +459,13 @@ prefill2c_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         for (int j = 0; j < n_all && ok; ++j) {
           const int st = j % kStages, use = j / kStages;
           perturb(p, kPerturbTma, j);
-          if (use > 0) ok = mbar_wait<128>(&bars[bKE + st], (use - 1) & 1, abort_flag, p.status, 201);
+          if (use > 0) ok = mbar_wait_relaxed<kSleepNs>(&bars[bKE + st], (use - 1) & 1, abort_flag, p.status, 201);
           if (!ok) break;
           mbar_arrive_expect_tx(&bars[bKF + st], p.kv_tile_tx + kSfAtomBytes);
           tma_load_3d(smem + k_off + st * kTileBytes, &tmap_k, &bars[bKF + st], 0, (j + j0) * kBlockN, bhkv);
           bulk_load_1d(smem + sfk_off + st * kSfAtomBytes, p.k_sf + ((size_t)bhkv * p.n_kv_tiles + j + j0) * kSfAtomBytes,
                        kSfAtomBytes, &bars[bKF + st]);
-          if (use > 0) ok = mbar_wait<128>(&bars[bVE + st], (use - 1) & 1, abort_flag, p.status, 202);
+          if (use > 0) ok = mbar_wait_relaxed<kSleepNs>(&bars[bVE + st], (use - 1) & 1, abort_flag, p.status, 202);
           if (!ok) break;
           mbar_arrive_expect_tx(&bars[bVF + st], p.kv_tile_tx + kSfAtomBytes);
           if (p.v_transposed) tma_load_3d(smem + v_off + st * kTileBytes, &tmap_v, &bars[bVF + st], (j + j0) * kBlockN, 0, bhkv);
@@ -418,82 +474,101 @@ prefill2c_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                        kSfAtomBytes, &bars[bVF + st]);
         }
       }
-    } else if (warp == kWarpMma) {
-      // ================= MMA issuer =================
+    } else if (warp == kWarpQk) {
+      // ================= issuer of S = Q K^T =================
+      // One thread issues; what it runs per key tile is kept short (a lone thread executes one instruction every
+      // few cycles): descriptors are built once, a tile's descriptor is the base plus an offset in its low word.
       if (lane == 0 && n_all > 0) {
-        const uint32_t q_addr = smem_u32(smem + q_off), k_addr = smem_u32(smem + k_off);
-        const uint32_t v_addr = smem_u32(smem + v_off), pt_addr = smem_u32(smem + p_off);
+        const uint64_t dq = make_smem_desc(smem_u32(smem + q_off), 16, 1024, kLayoutSw128);
+        const uint64_t dk = make_smem_desc(smem_u32(smem + k_off), 16, 1024, kLayoutSw128);
+        const uint64_t dsfq = make_smem_desc(smem_u32(smem + sfq_off), 0, 128, kLayoutNone);
+        const uint64_t dsfk = make_smem_desc(smem_u32(smem + sfk_off), 0, 128, kLayoutNone);
+        uint32_t idesc_kk[4];
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) idesc_kk[kk] = idesc_with_sf(idesc_qk, kk, kk);
         bool ok = mbar_wait(&bars[bQ], 0, abort_flag, p.status, 301);
         if (ok) {
-          for (int g = 0; g < 2; ++g)
-            tc_cp_32x128b_warpx4(tmem_base + cSfQ + g * 4, make_smem_desc(smem_u32(smem + sfq_off + g * kSfAtomBytes), 0, 128, kLayoutNone));
+          tc_cp_32x128b_warpx4(tmem_base + cSfQ, dsfq);
+          tc_cp_32x128b_warpx4(tmem_base + cSfQ + 4, dsfq + (kSfAtomBytes >> 4));
         }
-        int s_user_g = -1, s_user_j = 0;       // who read the shared S columns last
-        auto issue_qk = [&](int g, int j, int st) -> bool {
-          if (s_user_g >= 0 && !mbar_wait(&bars[bSE + s_user_g], s_user_j & 1, abort_flag, p.status, 305)) return false;
-          tc_fence_after();
-#pragma unroll
-          for (int kk = 0; kk < 4; ++kk) {
-            const uint64_t adesc = make_smem_desc(q_addr + g * kTileBytes + kk * 32, 16, 1024, kLayoutSw128);
-            const uint64_t bdesc = make_smem_desc(k_addr + st * kTileBytes + kk * 32, 16, 1024, kLayoutSw128);
-            mma_mxf8f6f4_ss(tmem_base + cS, adesc, bdesc, idesc_with_sf(idesc_qk, kk, kk), tmem_base + cSfQ + g * 4,
-                            tmem_base + cSfK + st * 4, kk > 0 ? 1u : 0u);
-          }
-          tc_commit(&bars[bSF + g]);
-          s_user_g = g; s_user_j = j;
-          return true;
-        };
-        auto issue_pv = [&](int g, int i, bool first_of_tile, bool last_of_tile) -> bool {
-          const int pb = i & 1, st = i % kStages, use = i / kStages;
-          if (first_of_tile) {
-            if (!mbar_wait(&bars[bVF + st], use & 1, abort_flag, p.status, 303)) return false;
-            tc_cp_32x128b_warpx4(tmem_base + cSfV + st * 4, make_smem_desc(smem_u32(smem + sfv_off + st * kSfAtomBytes), 0, 128, kLayoutNone));
-          }
-          if (!mbar_wait(&bars[bPF + g * 2 + pb], (i >> 1) & 1, abort_flag, p.status, 304)) return false;
-          if (!mbar_wait(&bars[bOR + g], i & 1, abort_flag, p.status, 307)) return false;     // O rescaled for this tile
-          tc_fence_after();
-          tc_cp_32x128b_warpx4(tmem_base + cSfP + (g * 2 + pb) * 4,
-                               make_smem_desc(smem_u32(smem + sfp_off + (g * 2 + pb) * kSfAtomBytes), 0, 128, kLayoutNone));
-#pragma unroll
-          for (int kk = 0; kk < 4; ++kk) {
-            const uint64_t adesc = make_smem_desc(pt_addr + (g * 2 + pb) * kTileBytes + kk * 32, 16, 1024, kLayoutSw128);
-            // V tile [keys][d] is the MN-major B operand; a 6-bit V is stored transposed and is K-major like K
-            const uint64_t bdesc = p.v_transposed ? make_smem_desc(v_addr + st * kTileBytes + kk * 32, 16, 1024, kLayoutSw128)
-                                                  : make_smem_desc(v_addr + st * kTileBytes + kk * 4096, kTileBytes, 1024, kLayoutSw128);
-            mma_mxf8f6f4_ss(tmem_base + cO + g * 128, adesc, bdesc, idesc_with_sf(idesc_pv, kk, kk),
-                            tmem_base + cSfP + (g * 2 + pb) * 4, tmem_base + cSfV + st * 4, (i > 0 || kk > 0) ? 1u : 0u);
-          }
-          tc_commit(&bars[bPV + g * 2 + pb]);
-          if (last_of_tile) tc_commit(&bars[bVE + st]);
-          return true;
-        };
-        // PVs of tile i: group 0 first, then group 1; flags tell which one opens / closes the V stage
-        auto pv_flags = [&](int g, int i, bool& first, bool& last) {
-          const bool a = i < nt[0], bb = i < nt[1];
-          first = (g == 0) ? true : !a;
-          last = (g == 1) ? true : !bb;
-        };
+        int st = 0, use_par = 0;                 // K stage of tile j and the parity of its use
+        int last_g = -1, last_par = 0;           // which group read the shared S columns last, and at which tile parity
         for (int j = 0; j < n_all && ok; ++j) {
-          const int st = j % kStages, use = j / kStages;
-          perturb(p, kPerturbMma, j);
-          ok = mbar_wait(&bars[bKF + st], use & 1, abort_flag, p.status, 302);
+          perturb(p, kPerturbQk, j);
+          RK_STAMP(2, j, 0);
+          ok = mbar_wait_relaxed<kSleepNs>(&bars[bKF + st], use_par, abort_flag, p.status, 302);
           if (!ok) break;
-          tc_cp_32x128b_warpx4(tmem_base + cSfK + st * 4, make_smem_desc(smem_u32(smem + sfk_off + st * kSfAtomBytes), 0, 128, kLayoutNone));
-          bool f, l;
-          if (j < nt[0]) ok = issue_qk(0, j, st);
-          if (ok && j > 0 && j - 1 < nt[0]) { pv_flags(0, j - 1, f, l); ok = issue_pv(0, j - 1, f, l); }
-          if (ok && j < nt[1]) ok = issue_qk(1, j, st);
+          tc_cp_32x128b_warpx4(tmem_base + cSfK + st * 4, dsfk + (uint32_t)(st * (kSfAtomBytes >> 4)));
+          const uint64_t dkt = dk + (uint32_t)(st * (kTileBytes >> 4));
+          RK_STAMP(2, j, 1);
+#pragma unroll
+          for (int g = 0; g < 2; ++g) {
+            if (j >= nt[g]) continue;
+            if (last_g >= 0) { ok = mbar_wait(&bars[bSE + last_g], last_par, abort_flag, p.status, 305); if (!ok) break; }
+            tc_fence_after();
+            const uint64_t dqt = dq + (uint32_t)(g * (kTileBytes >> 4));
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk)
+              mma_mxf8f6f4_ss(tmem_base + cS, dqt + kk * 2, dkt + kk * 2, idesc_kk[kk], tmem_base + cSfQ + g * 4,
+                              tmem_base + cSfK + st * 4, kk > 0 ? 1u : 0u);
+            tc_commit(&bars[bSF + g]);
+            last_g = g; last_par = j & 1;
+            RK_STAMP(2, j, 2 + g);
+          }
           if (ok) tc_commit(&bars[bKE + st]);
-          if (ok && j > 0 && j - 1 < nt[1]) { pv_flags(1, j - 1, f, l); ok = issue_pv(1, j - 1, f, l); }
-        }
-        if (ok) {
-          bool f, l;
-          const int i = n_all - 1;
-          if (i < nt[0]) { pv_flags(0, i, f, l); ok = issue_pv(0, i, f, l); }
-          if (ok && i < nt[1]) { pv_flags(1, i, f, l); ok = issue_pv(1, i, f, l); }
+          if (++st == kStages) { st = 0; use_par ^= 1; }
         }
         tc_commit(&bars[bDRAIN]);
         mbar_wait(&bars[bDRAIN], 0, abort_flag, p.status, 306);
+      }
+      __syncwarp();
+    } else if (warp == kWarpPv) {
+      // ================= issuer of O += P V =================
+      if (lane == 0 && n_all > 0) {
+        const uint64_t dp = make_smem_desc(smem_u32(smem + p_off), 16, 1024, kLayoutSw128);
+        // V tile [keys][d] is the MN-major B operand (32 keys = 32 rows of 128 bytes); a 6-bit V is stored
+        // transposed and is K-major like K
+        const uint64_t dv = p.v_transposed ? make_smem_desc(smem_u32(smem + v_off), 16, 1024, kLayoutSw128)
+                                           : make_smem_desc(smem_u32(smem + v_off), kTileBytes, 1024, kLayoutSw128);
+        const uint32_t v_kk = p.v_transposed ? 2u : (uint32_t)(4096 >> 4);
+        const uint64_t dsfv = make_smem_desc(smem_u32(smem + sfv_off), 0, 128, kLayoutNone);
+        const uint64_t dsfp = make_smem_desc(smem_u32(smem + sfp_off), 0, 128, kLayoutNone);
+        uint32_t idesc_kk[4];
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) idesc_kk[kk] = idesc_with_sf(idesc_pv, kk, kk);
+        bool ok = true;
+        int st = 0, use_par = 0;
+        for (int i = 0; i < n_all && ok; ++i) {
+          const int pb = i & 1, par2 = (i >> 1) & 1;
+          perturb(p, kPerturbPv, i);
+          ok = mbar_wait_relaxed<kSleepNs>(&bars[bVF + st], use_par, abort_flag, p.status, 303);
+          if (!ok) break;
+          tc_cp_32x128b_warpx4(tmem_base + cSfV + st * 4, dsfv + (uint32_t)(st * (kSfAtomBytes >> 4)));
+          const uint64_t dvt = dv + (uint32_t)(st * (kTileBytes >> 4));
+#pragma unroll
+          for (int g = 0; g < 2; ++g) {
+            if (i >= nt[g]) continue;
+            const int gb = g * 2 + pb;
+            ok = mbar_wait_relaxed<kSleepNs>(&bars[bPF + gb], par2, abort_flag, p.status, 304) &&
+                 mbar_wait_relaxed<kSleepNs>(&bars[bOR + gb], par2, abort_flag, p.status, 307);      // P written, O rescaled for this tile
+            if (!ok) break;
+            tc_fence_after();
+            tc_cp_32x128b_warpx4(tmem_base + cSfP + gb * 4, dsfp + (uint32_t)(gb * (kSfAtomBytes >> 4)));
+            const uint64_t dpt = dp + (uint32_t)(gb * (kTileBytes >> 4));
+            mma_mxf8f6f4_ss(tmem_base + cO + g * 128, dpt, dvt, idesc_kk[0], tmem_base + cSfP + gb * 4,
+                            tmem_base + cSfV + st * 4, i > 0 ? 1u : 0u);
+#pragma unroll
+            for (int kk = 1; kk < 4; ++kk)
+              mma_mxf8f6f4_ss(tmem_base + cO + g * 128, dpt + kk * 2, dvt + kk * v_kk, idesc_kk[kk], tmem_base + cSfP + gb * 4,
+                              tmem_base + cSfV + st * 4, 1u);
+            tc_commit(&bars[bPV + gb]);
+            RK_STAMP(2, i, 4 + g);
+          }
+          if (ok) tc_commit(&bars[bVE + st]);
+          if (++st == kStages) { st = 0; use_par ^= 1; }
+        }
+        tc_commit(&bars[bDRAIN2]);
+        mbar_wait(&bars[bDRAIN2], 0, abort_flag, p.status, 308);
       }
       __syncwarp();
     }
@@ -501,7 +576,7 @@ prefill2c_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
 
   tc_fence_before();
   __syncthreads();
-  if (warp == kWarpMma) { tc_fence_after(); tmem_dealloc(tmem_base, kTmemCols); }
+  if (warp == kWarpQk) { tc_fence_after(); tmem_dealloc(tmem_base, kTmemCols); }
 }
 
 template <bool SOFTCAP>

@@ -97,7 +97,7 @@ def test_v_scale_codes_at_and_beyond_the_bf16_folding_edge(top_code):
     vs[:, :, 5::97] = top_code                      # the top code is present in every sequence
     (legacy, tc), ref = _check(q, kc, ks, vc, vs)
     big = float(np.abs(ref["o_f32"]).max())
-    assert np.abs(legacy - tc).max() <= 4e-3 * max(1.0, big)
+    assert np.abs(legacy - tc).max() <= 1e-2 * max(1.0, big)      # one bf16 step of the output at that magnitude
 
 
 def test_full_length_one_sequence():

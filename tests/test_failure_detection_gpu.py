@@ -31,12 +31,17 @@ def test_bounded_wait_runs_out_and_is_reported_and_clears():
 
     assert L.rk_debug_wait_runs_out(1000, 0, _stream()) == 0            # the kernel returns by itself
     torch.cuda.synchronize()
-    # while the word is set, launches return at once and write nothing
-    sentinel = torch.full_like(good, 7.0)
-    out = rk.attn_prefill(qc, kc, vc, qs, ks, vs, causal=True, out=sentinel.clone())
-    torch.cuda.synchronize()
-    assert torch.equal(out, sentinel)
-    assert rk.last_device_status() == WAIT_GAVE_UP                      # reported once ...
+    try:
+        # while the word is set, launches return at once and write nothing
+        sentinel = torch.full_like(good, 7.0)
+        out = rk.attn_prefill(qc, kc, vc, qs, ks, vs, causal=True, out=sentinel.clone())
+        torch.cuda.synchronize()
+        assert torch.equal(out, sentinel)
+        status = rk.last_device_status()
+    except BaseException:
+        rk.last_device_status()                                         # never leave the word set for the tests that follow
+        raise
+    assert status == WAIT_GAVE_UP                                       # reported once ...
     assert rk.last_device_status() == 0                                 # ... and cleared by the read
     again = rk.attn_prefill(qc, kc, vc, qs, ks, vs, causal=True)
     torch.cuda.synchronize()
@@ -75,7 +80,7 @@ def test_noalloc_decode_status_word_is_observable():
 @pytest.mark.parametrize("shape", [(2, 4, 2, 1024, 128, False), (1, 2, 1, 640, 64, False), (1, 4, 4, 512, 128, True)])
 def test_schedule_perturbation_leaves_every_bit_of_o(shape):
     """A few hundred nanoseconds of sleep at every key tile in one warp role at a time (softmax of query tile A,
-    of tile B, correction, TMA producer, MMA issuer): if a hand-off between roles lacked a barrier the delayed
+    of tile B, correction, TMA producer, Q K^T issuer, P V issuer): if a hand-off between roles lacked a barrier the delayed
     role would read or overwrite something too early and O would change."""
     B, H, Hkv, S, d, cap = shape
     L = rk.lib()
@@ -84,7 +89,7 @@ def test_schedule_perturbation_leaves_every_bit_of_o(shape):
     kw = dict(causal=True, softcap=30.0 if cap else 0.0)
     base = rk.attn_prefill(qc, kc, vc, qs, ks, vs, **kw)
     try:
-        for role in (1, 2, 3, 4, 5):
+        for role in (1, 2, 3, 4, 5, 6):
             L.rk_debug_set_prefill_perturb(role)
             for _ in range(2):
                 assert torch.equal(rk.attn_prefill(qc, kc, vc, qs, ks, vs, **kw), base), role
