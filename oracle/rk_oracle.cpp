@@ -503,7 +503,7 @@ static void prefill_slice(const rko_prefill_args& a, int64_t slice) {
     const float safe_l = l_run > 0.0f ? l_run : 1.0f;
     const float inv = 1.0f / safe_l;
     for (int c = 0; c < d; c++) {
-      const float val = o[c] * inv;
+      const float val = bf ? rb(o[c] / safe_l) : o[c] * inv;   // q_bf16(O / safe_l), flash_attention_model.py:246
       if (a.o_f32) a.o_f32[(qoff + i) * d + c] = val;
       if (a.o_bf16) { uint16_t bb; bf16_round_to_f32(val, &bb); a.o_bf16[(qoff + i) * d + c] = bb; }
     }
