@@ -128,9 +128,11 @@ class ClockSampler:
             self.path = None
 
     def window(self, t0, t1):
-        """Median SM clock and the throttle reasons seen between host times t0 and t1.  A region shorter than the
-        sampling period may hold no sample: the nearest one on either side is used and `samples` says 0."""
-        self._stop()
+        """Median SM clock and the throttle reasons seen between host times t0 and t1 (call after the `with` block
+        has ended: the poller's file is read when it stops).  A region shorter than the sampling period may hold
+        no sample: the nearest one on either side is used and `samples` says 0."""
+        if self.proc is not None:
+            raise RuntimeError("ClockSampler.window() before the sampler was stopped")
         inside = [s for s in self.samples if t0 <= s[0] <= t1]
         n = len(inside)
         if not inside and self.samples:
@@ -225,13 +227,22 @@ def main():
         PREFILL.update(B=4)
         DECODE.update(B=8)
         args.no_extras = True
+    windows = {}                                       # name -> (t0, t1) host times of the timed regions
     with ClockSampler(local) as sampler:               # the poller is stopped whatever happens below
-        line = run_ours(args, rank, world, local, sampler)
+        line = run_ours(args, rank, world, local, windows)
     if line is not None:
+        line["clocks"] = sampler.window(*windows["steps"])
+        if "mma_sustained" in windows and line["roofline"].get("peak_measured_mxfp8"):
+            line["roofline"]["peak_measured_mxfp8"]["sustained_clocks"] = sampler.window(*windows["mma_sustained"])
+        sus = line["roofline"].get("sustained")
+        if sus is not None and "long_loop" in windows:
+            sus["clocks"] = sampler.window(*windows["long_loop"])
+            mhz = sus["clocks"].get("sm_mhz")
+            sus["ms_x_mhz"] = sus["ms_per_step"] * mhz if mhz else None
         print(json.dumps(line), flush=True)
 
 
-def run_ours(args, rank, world, local, sampler):
+def run_ours(args, rank, world, local, windows):
     import torch
     import torch.distributed as dist
     import radiance_kernels_b200 as rk
@@ -328,7 +339,6 @@ def run_ours(args, rank, world, local, sampler):
     # ---- the tensor-pipe ceiling on this device, and the same kernel in a loop of at least 2 s ---------------
     mma_peak = None
     sustained = None
-    t_long = None
     if not args.no_extras:
         tiles = torch.randint(0, 0x7E, (2, 128 * 128), dtype=torch.uint8, device=dev)      # valid E4M3 codes
         iters = 8192
@@ -347,8 +357,9 @@ def run_ours(args, rank, world, local, sampler):
         t0 = time.time()
         sus_ms = timed(mma_loop, n_sus, warm=0)
         t1 = time.time()
+        windows["mma_sustained"] = (t0, t1)
         mma_peak = {"burst_tflops": mma_flops / (burst_ms * 1e-3) / 1e12, "sustained_tflops": mma_flops / (sus_ms * 1e-3) / 1e12,
-                    "sustained_seconds": sus_ms * n_sus * 1e-3, "sustained_clocks": sampler_window(sampler, t0, t1, rank),
+                    "sustained_seconds": sus_ms * n_sus * 1e-3,
                     "what": "tcgen05.mma kind::mxf8f6f4.block_scale M=128 N=128 K=32, operands and scales resident in shared "
                             "memory / TMEM, one CTA per SM, no TMA and no softmax in the loop"}
         # the attention kernel for at least 2 s: its sustained speed and the clock it ran at
@@ -356,7 +367,7 @@ def run_ours(args, rank, world, local, sampler):
         t0 = time.time()
         long_ms = timed(step, n_long, warm=0)
         t1 = time.time()
-        t_long = (t0, t1)
+        windows["long_loop"] = (t0, t1)
         long_kern = kernel_ms(step, 10)
         sustained = {"steps": n_long, "ms_per_step": long_ms, "kernel_ms_after_loop": long_kern,
                      "tflops": flops / (long_ms * 1e-3) / 1e12}
@@ -480,11 +491,8 @@ def run_ours(args, rank, world, local, sampler):
         launches += args.steps * 2
         del kcd, vcd, ksd, vsd
 
-    clocks = sampler_window(sampler, t_region0, t_region1, rank)
-    if sustained is not None and t_long is not None:
-        sustained["clocks"] = sampler_window(sampler, t_long[0], t_long[1], rank)
-        mhz = sustained["clocks"].get("sm_mhz")
-        sustained["ms_x_mhz"] = sustained["ms_per_step"] * mhz if mhz else None
+    windows["steps"] = (t_region0, t_region1)
+    if sustained is not None:
         if mma_peak:
             sustained["frac_of_sustained_peak"] = sustained["tflops"] / mma_peak["sustained_tflops"]
         roofline["sustained"] = sustained
@@ -504,7 +512,7 @@ def run_ours(args, rank, world, local, sampler):
             "config": {"workload": WORKLOAD if args.case == "full" else "REDUCED BATCH (profiling case, not a bench number): " + WORKLOAD, "per_gpu_batch": "B=8 H=16 (128 independent (batch, head) units per GPU)",
                        "parallelism": f"units sharded over {world} GPU(s), no collective on the data path",
                        "l2": "inputs + output (335 MB) exceed the 126 MB L2; no flush between steps"},
-            "roofline": roofline, "e2e": e2e, "gpu_launches": launches, "clocks": clocks, "decode": decode}
+            "roofline": roofline, "e2e": e2e, "gpu_launches": launches, "clocks": None, "decode": decode}
     if strong is not None:
         line["strong_scaling"] = strong
     if extras is not None:
@@ -512,10 +520,6 @@ def run_ours(args, rank, world, local, sampler):
     if cpu is not None:
         line["cpu_baseline"] = cpu
     return line
-
-
-def sampler_window(sampler, t0, t1, rank):
-    return sampler.window(t0, t1)
 
 
 def strong_scaling_leg(args, rk, dist, dev, rank, world, barrier, max_over_ranks):

@@ -221,6 +221,16 @@ RK_API int rk_rope_mx_quantize(const float* x, int64_t rows, int32_t d, const in
                                const float* cos_half, const float* sin_half, int32_t n_pos, int32_t fmt,
                                uint8_t* codes, uint8_t* scales, void* stream);
 
+/* RMSNorm fused with the block quantizer: the prologue of the QKV projection, without the fp32 round trip of the
+ * normalized activation through HBM.  Replaces phase 0 of kernels/rmsnorm_qkv_fused/kernel.cpp:96-110 (golden:
+ * rmsnorm, lib/golden/golden.py:203-216) and is bit-exact with that golden: sum of squares in index order, every
+ * product and sum rounded to fp32 on its own, rms = 1 / sqrt(ss / K + eps), y = (x * rms) * gamma.
+ *   x fp32 (x_is_bf16 = 0) or bf16 (1) [rows][K], K a multiple of 32; gamma fp32 [K]; codes [rows][K] (16-byte aligned);
+ *   scales [rows][K/32].  unit_scale = 0: y is MX-quantized along K as rk_mx_quantize does; unit_scale = 1: no block
+ *   scale, code = E4M3(y) and every scale byte 0x7F -- what the reference kernel writes (gen_data.py:33-41). */
+RK_API int rk_rmsnorm_mx_quantize(const void* x, int x_is_bf16, int64_t rows, int32_t K, const float* gamma, float eps,
+                                  int32_t fmt, int32_t unit_scale, uint8_t* codes, uint8_t* scales, void* stream);
+
 /* Append one token to an MXFP8 / MXFP6 KV cache so that decode can run in a loop: for every batch b and KV
  * head, the new K row and the new V row (fp32 [B][H_kv][d], device memory) are quantized in blocks of 32
  * along d with the rule of rk_mx_quantize and stored as row pos[b] of the cache (codes [B][H_kv][L][d],

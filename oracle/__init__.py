@@ -83,6 +83,8 @@ def lib():
         L.rko_quantize_rows_mxgolden.argtypes = [C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p]
         L.rko_rope_rows.restype = None
         L.rko_rope_rows.argtypes = [C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
+        L.rko_rmsnorm_rows.restype = None
+        L.rko_rmsnorm_rows.argtypes = [C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_float, C.c_void_p]
         L.rko_rebase_v.restype = None
         L.rko_rebase_v.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int, C.c_void_p, C.c_void_p]
         L.rko_attn_prefill.restype = C.c_int
@@ -166,6 +168,16 @@ def rope(x, pos, cos_half, sin_half):
     rows, d = x.shape
     out = np.empty_like(x)
     lib().rko_rope_rows(_p(x), rows, d, _p(pos), _p(c), _p(s), _p(out))
+    return out
+
+
+def rmsnorm(x, gamma, eps):
+    """Row RMSNorm of fp32 [rows, K] in the reference's scalar fp32 order (lib/golden/golden.py:203-216)."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    gamma = np.ascontiguousarray(gamma, dtype=np.float32)
+    rows, K = x.shape
+    out = np.empty_like(x)
+    lib().rko_rmsnorm_rows(_p(x), rows, K, _p(gamma), float(np.float32(eps)), _p(out))
     return out
 
 

@@ -334,6 +334,23 @@ void rko_rope_rows(const float* x, int64_t rows, int64_t d, const int32_t* pos, 
   }
 }
 
+// Row RMSNorm in the reference's fp32 path, lib/golden/golden.py:203-216 (rmsnorm): the sum of squares is
+// accumulated in index order, every product and sum rounded to fp32 on its own; mean = ss / K;
+// rms = 1 / sqrt(mean + eps) with the square root correctly rounded to fp32 (the golden takes it in double and
+// rounds, which gives the same fp32) and a correctly rounded fp32 division; out = (x * rms) * gamma, two roundings.
+void rko_rmsnorm_rows(const float* x, int64_t rows, int64_t K, const float* gamma, float eps, float* out) {
+  for (int64_t r = 0; r < rows; r++) {
+    const float* row = x + r * K;
+    volatile float ss = 0.0f;                      // volatile: no contraction, no reassociation
+    for (int64_t k = 0; k < K; k++) { const volatile float sq = row[k] * row[k]; ss = ss + sq; }
+    const volatile float mean = ss / (float)K;
+    const volatile float me = mean + eps;
+    const volatile float root = (float)std::sqrt((double)me);
+    const volatile float rms = 1.0f / root;
+    for (int64_t k = 0; k < K; k++) { const volatile float t = row[k] * rms; out[r * K + k] = t * gamma[k]; }
+  }
+}
+
 void rko_dequant_rows(const uint8_t* codes, const uint8_t* scales, int64_t rows, int64_t cols,
                       int fmt, float* out) {
   const Fmt& f = kFmt[fmt];

@@ -165,6 +165,22 @@ def rope_mx_quantize(x, cos_half, sin_half, *, pos=None, pos0=0, fmt=E4M3):
     return codes, scales
 
 
+def rmsnorm_mx_quantize(x, gamma, eps, fmt=E4M3, unit_scale=False):
+    """Row RMSNorm (the reference's fp32 order) then quantization along the last axis.  x fp32 or bf16 [..., K];
+    gamma fp32 [K].  Returns (codes [..., K], scales [..., K/32]); unit_scale: E4M3 under 2^0, scales all 0x7F."""
+    _need_cuda(x, gamma)
+    if x.dtype not in (torch.float32, torch.bfloat16) or gamma.dtype != torch.float32:
+        raise ValueError("rmsnorm_mx_quantize takes float32 or bfloat16 rows and a float32 gamma")
+    K = x.shape[-1]
+    _expect(gamma, "gamma", torch.float32, (K,))
+    rows = x.numel() // max(K, 1)
+    codes = torch.empty(x.shape, dtype=torch.uint8, device=x.device)
+    scales = torch.empty(x.shape[:-1] + (K // 32,), dtype=torch.uint8, device=x.device)
+    check(lib().rk_rmsnorm_mx_quantize(_ptr(x), int(x.dtype == torch.bfloat16), rows, K, _ptr(gamma), float(eps), fmt,
+                                       int(bool(unit_scale)), _ptr(codes), _ptr(scales), _stream()), "rk_rmsnorm_mx_quantize")
+    return codes, scales
+
+
 def mx_quantize_keys(x, fmt=E4M3):
     """fp32 [..., rows, cols] -> codes same shape, scales [..., ceil(rows/32), cols]; blocks run down the rows."""
     _need_cuda(x)

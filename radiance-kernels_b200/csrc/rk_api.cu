@@ -412,6 +412,15 @@ int rk_rope_mx_quantize(const float* x, int64_t rows, int32_t d, const int32_t* 
   return launch_rope_quantize_rows(x, rows, d, pos, seq_len, pos0, cos_half, sin_half, fmt, codes, scales, (cudaStream_t)stream);
 }
 
+int rk_rmsnorm_mx_quantize(const void* x, int x_is_bf16, int64_t rows, int32_t K, const float* gamma, float eps, int32_t fmt,
+                           int32_t unit_scale, uint8_t* codes, uint8_t* scales, void* stream) {
+  if (!x || !gamma || !codes || !scales) return RK_ERR_NULL_POINTER;
+  if (rows < 0 || K <= 0 || K % 32 != 0 || !(eps >= 0.0f)) return RK_ERR_BAD_SHAPE;
+  if (fmt < 0 || fmt > 3) return RK_ERR_BAD_FORMAT;
+  if (!aligned(x, 4) || !aligned(gamma, 4) || !aligned(codes, 16)) return RK_ERR_MISALIGNED;
+  return launch_rmsnorm_quantize(x, x_is_bf16 != 0, rows, K, gamma, eps, fmt, unit_scale != 0, codes, scales, (cudaStream_t)stream);
+}
+
 int rk_kv_cache_append(const float* k_new, const float* v_new, int32_t B, int32_t H_kv, int32_t L, int32_t d,
                        const int32_t* pos, int32_t fmt, uint8_t* k_codes, uint8_t* k_scales, uint8_t* v_codes,
                        uint8_t* v_scales, void* stream) {

@@ -25,6 +25,8 @@ int launch_quantize_rows_ex(const void* x, bool bf16, int64_t batch, int64_t S, 
                             uint8_t* scales, int layout, cudaStream_t st);
 int launch_quantize_keys_atoms(const float* x, int64_t batch, int64_t rows, int64_t cols, int fmt, uint8_t* codes,
                                uint8_t* scales, cudaStream_t st);
+int launch_rmsnorm_quantize(const void* x, bool bf16, int64_t rows, int K, const float* gamma, float eps, int fmt,
+                            bool unit_scale, uint8_t* codes, uint8_t* scales, cudaStream_t st);
 int launch_retile_groupscales(const uint8_t* in, int64_t batch, int64_t S, int64_t d, uint8_t* out, cudaStream_t st);
 int launch_import_kt_blocks(const uint8_t* kt, const uint8_t* kts, int64_t heads, int nblk, int Bk, int d, uint8_t* k,
                             uint8_t* ks, cudaStream_t st);

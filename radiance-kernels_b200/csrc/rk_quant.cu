@@ -20,6 +20,8 @@
 // cvt.rn.satfinite.<fmt>x2.f32 instead, which verify_encoder_kernel proves equal
 // to it on every finite fp32 input (all 2^32 bit patterns are swept in the GPU
 // tests); blocks that hold a NaN or an infinity take the integer encoder.
+#include <algorithm>
+
 #include "rk_common.cuh"
 #include "rk_internal.h"
 
@@ -213,6 +215,79 @@ __global__ void __launch_bounds__(256) rope_quantize_rows_kernel(const float* __
     if ((i0 & 31) == 0) {
       scales[r * (d / 32) + i0 / 32] = (uint8_t)sc0;
       scales[r * (d / 32) + (half + i0) / 32] = (uint8_t)sc1;
+    }
+  }
+}
+
+// RMSNorm fused with the block quantizer: the prologue of the QKV projection (kernels/rmsnorm_qkv_fused), so that the
+// normalized activation never exists in HBM as fp32.  Bit-exact with the reference's fp32 path
+// (lib/golden/golden.py:203-216): the sum of squares runs in index order with every product and sum rounded on its
+// own, mean = ss / K, rms = 1 / sqrt(mean + eps) (correctly rounded square root and division), y = (x * rms) * gamma.
+// A warp owns 32 rows.  Per 32-column chunk it loads a 32 x 32 tile with coalesced row reads into shared memory;
+// lane L then walks row L of the tile: in the first pass it extends its row's sequential sum, in the second pass
+// the chunk is exactly one MX block of its row (amax, scale, codes: 32 bytes stored at once).
+// UNIT: no block scale (code = E4M3(y) under 2^0, every scale byte 0x7F), the reference kernel's own choice
+// (kernels/rmsnorm_qkv_fused/gen_data.py:33-41: the prologue owns the row scaling).
+template <int FMT, bool BF16IN, bool UNIT>
+__global__ void __launch_bounds__(256) rmsnorm_quantize_kernel(const void* __restrict__ xin, int64_t rows, int K,
+                                                               const float* __restrict__ gamma, float eps,
+                                                               uint8_t* __restrict__ codes, uint8_t* __restrict__ scales) {
+  __shared__ float tile_all[8][32][33];
+  __shared__ float gam_all[8][32];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float (*tile)[33] = tile_all[warp];
+  float* gam = gam_all[warp];
+  const int64_t n_groups = (rows + 31) / 32;
+  for (int64_t grp = (int64_t)blockIdx.x * 8 + warp; grp < n_groups; grp += (int64_t)gridDim.x * 8) {
+    const int64_t row0 = grp * 32;
+    auto load_tile = [&](int c0) {
+#pragma unroll 8
+      for (int i = 0; i < 32; ++i) {
+        const int64_t r = row0 + i;
+        float v = 0.0f;
+        if (r < rows) {
+          if (BF16IN) v = __uint_as_float((uint32_t)reinterpret_cast<const uint16_t*>(xin)[r * K + c0 + lane] << 16);
+          else v = reinterpret_cast<const float*>(xin)[r * K + c0 + lane];
+        }
+        tile[i][lane] = v;
+      }
+    };
+    float ss = 0.0f;
+    for (int c0 = 0; c0 < K; c0 += 32) {
+      load_tile(c0);
+      __syncwarp();
+#pragma unroll
+      for (int j = 0; j < 32; ++j) { const float v = tile[lane][j]; ss = __fadd_rn(ss, __fmul_rn(v, v)); }
+      __syncwarp();
+    }
+    const float rms = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)K), eps)));
+    const int64_t r = row0 + lane;
+    for (int c0 = 0; c0 < K; c0 += 32) {
+      load_tile(c0);
+      gam[lane] = gamma[c0 + lane];
+      __syncwarp();
+      float y[32];
+      float amax = 0.0f, nonfinite = 0.0f;
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        y[j] = __fmul_rn(__fmul_rn(tile[lane][j], rms), gam[j]);
+        amax = fmaxf(amax, fabsf(y[j]));
+        nonfinite = fmaf(y[j], 0.0f, nonfinite);
+      }
+      __syncwarp();
+      uint32_t scode = UNIT ? 127u : 0u; float p2 = 1.0f;
+      if (!UNIT && amax > 0.0f) block_scale<FMT>(amax, scode, p2);
+      uint32_t w[8];
+#pragma unroll
+      for (int q = 0; q < 8; ++q)
+        w[q] = (nonfinite == 0.0f) ? hw_encode4<FMT>(y[4 * q] * p2, y[4 * q + 1] * p2, y[4 * q + 2] * p2, y[4 * q + 3] * p2)
+                                   : ref_encode4<FMT>(y[4 * q] * p2, y[4 * q + 1] * p2, y[4 * q + 2] * p2, y[4 * q + 3] * p2);
+      if (r < rows) {
+        uint4* dst = reinterpret_cast<uint4*>(codes + r * K + c0);
+        dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
+        dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+        scales[r * (K / 32) + c0 / 32] = (uint8_t)scode;
+      }
     }
   }
 }
@@ -781,6 +856,18 @@ int launch_import_kt_blocks(const uint8_t* kt, const uint8_t* kts, int64_t heads
   const int64_t ntiles = heads * nblk * (d / 32) * (Bk / 32);
   if (ntiles == 0) return RK_OK;
   import_kt_blocks_kernel<<<(int)min(ntiles, (int64_t)num_sms() * 16), 256, 0, st>>>(kt, kts, heads, nblk, Bk, d, k, ks);
+  return (int)cudaGetLastError();
+}
+
+int launch_rmsnorm_quantize(const void* x, bool bf16, int64_t rows, int K, const float* gamma, float eps, int fmt,
+                            bool unit_scale, uint8_t* codes, uint8_t* scales, cudaStream_t st) {
+  if (rows == 0 || K == 0) return RK_OK;
+  const int64_t groups = (rows + 31) / 32;
+  const int grid = (int)std::min<int64_t>((groups + 7) / 8, (int64_t)num_sms() * 8);
+#define RK_RN(BF, UN) RK_DISPATCH_FMT(fmt, (rmsnorm_quantize_kernel<F, BF, UN><<<grid, 256, 0, st>>>(x, rows, K, gamma, eps, codes, scales)))
+  if (bf16) { if (unit_scale) { RK_RN(true, true); } else { RK_RN(true, false); } }
+  else      { if (unit_scale) { RK_RN(false, true); } else { RK_RN(false, false); } }
+#undef RK_RN
   return (int)cudaGetLastError();
 }
 

@@ -27,6 +27,9 @@ reference tree is read-only) and stores only input/output vectors:
                           fp8_matmul_model from a submodule that is absent; an empty stand-in
                           module satisfies that import, and only functions that never touch it
                           are called.
+  rmsnorm_vectors.npz     lib/golden/golden.py rmsnorm (scalar fp32 accumulation order) on seeded inputs shaped
+                          like kernels/rmsnorm_qkv_fused/gen_data.py (bf16-exact X and gamma, eps 1e-5) and on
+                          plain fp32 inputs, row lengths 64 .. 1024: X, gamma, eps and the normalized output.
   rope_vectors.npz        lib/golden/golden.py rope_caches + rope_apply (HF Llama
                           rotate-half) on seeded inputs for head dims 64, 128, 256:
                           X, the half-width cos / sin caches and the rotated output.
@@ -109,6 +112,21 @@ def make_golden_py_vectors(ref):
     print("golden_py_vectors.npz:", xin.size, "encode cases,", amax_bits.size, "block_exp cases")
 
 
+def make_rmsnorm_vectors(ref):
+    G = load_golden(ref)
+    rng = np.random.default_rng(0x5A17)
+    out = {}
+    for i, (M, K, bf16_exact, eps) in enumerate(((16, 256, True, 1e-5), (8, 64, False, 1e-6), (6, 1024, False, 1e-5), (5, 96, True, 1e-3))):
+        X = (rng.standard_normal((M, K)) * np.exp2(rng.integers(-4, 5, (M, 1)))).astype(np.float32)
+        gamma = (0.75 + 0.5 * rng.random(K)).astype(np.float32)
+        if bf16_exact:
+            X, gamma = G.bf16_trunc(X), G.bf16_trunc(gamma)
+        Y = G.rmsnorm(X, gamma, eps)
+        out[f"x{i}"] = X; out[f"g{i}"] = gamma; out[f"eps{i}"] = np.float32(eps); out[f"y{i}"] = Y.astype(np.float32)
+    np.savez_compressed(HERE / "rmsnorm_vectors.npz", **out)
+    print("rmsnorm_vectors.npz:", {k: v.shape for k, v in out.items() if k.startswith("y")})
+
+
 def make_rope_vectors(ref):
     G = load_golden(ref)
     rng = np.random.default_rng(777)
@@ -176,4 +194,5 @@ if __name__ == "__main__":
     make_simt_quant_kat(ref)
     make_golden_py_vectors(ref)
     make_rope_vectors(ref)
+    make_rmsnorm_vectors(ref)
     make_attn_fp32_ref_vectors(ref)

@@ -230,3 +230,12 @@ def test_bf16_faithful_mode_is_a_different_target_at_the_reported_distance():
     # every output of the faithful mode is a bf16 value
     bits = obf["o_f32"].view(np.uint32)
     assert np.all((bits & 0xFFFF) == 0)
+
+
+def test_rmsnorm_matches_the_reference_golden_bit_for_bit():
+    """rko_rmsnorm_rows against lib/golden/golden.py rmsnorm (scalar fp32 accumulation order): fixture made by
+    importing the reference's module (tests/golden/make_golden.py)."""
+    z = np.load(os.path.join(G, "rmsnorm_vectors.npz"))
+    for i in range(4):
+        y = oracle.rmsnorm(z[f"x{i}"], z[f"g{i}"], float(z[f"eps{i}"]))
+        assert np.array_equal(y.view(np.uint32), z[f"y{i}"].view(np.uint32)), i
