@@ -231,6 +231,17 @@ RK_API int rk_rope_mx_quantize(const float* x, int64_t rows, int32_t d, const in
 RK_API int rk_rmsnorm_mx_quantize(const void* x, int x_is_bf16, int64_t rows, int32_t K, const float* gamma, float eps,
                                   int32_t fmt, int32_t unit_scale, uint8_t* codes, uint8_t* scales, void* stream);
 
+/* MX matmul in the accumulate semantics of the MX-Gemmini mesh: C = A . B with E8M0 scales per 32-element K group,
+ * rounded where the hardware rounds.  Replaces the mesh call of the reference's GEMM and batched-decode projection
+ * kernels (the kernels/gemm_mxgemmini family, kernels/gemv_batched_fp8_m128/kernel.cpp:1-33) and is bit-exact with their
+ * golden program lib/golden/mx_golden.cpp:114-144 (16 accumulator stages per 16-deep K step, products truncated to 3
+ * fraction bits and saturated at 448, bf16 accumulation across K steps), overflow to inf / NaN included.
+ *   a E4M3 codes [M][K] (A_in), b E4M3 codes [K][N] (B_in), a_scales E8M0 [K/32][M] (A_scales_row),
+ *   b_scales E8M0 [K/32][N] (B_scales_col), c_bf16 [M][N] (C_out_bf16).  M, N multiples of 16, K of 32; a 16-byte aligned.
+ * Only the fp8 form of the golden is provided (its LUT-indexed fp6 and nibble-packed fp4 forms are mesh-specific). */
+RK_API int rk_mx_gemm_hw(const uint8_t* a, const uint8_t* b, const uint8_t* a_scales, const uint8_t* b_scales, int32_t M,
+                         int32_t N, int32_t K, void* c_bf16, void* stream);
+
 /* Append one token to an MXFP8 / MXFP6 KV cache so that decode can run in a loop: for every batch b and KV
  * head, the new K row and the new V row (fp32 [B][H_kv][d], device memory) are quantized in blocks of 32
  * along d with the rule of rk_mx_quantize and stored as row pos[b] of the cache (codes [B][H_kv][L][d],

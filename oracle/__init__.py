@@ -83,6 +83,8 @@ def lib():
         L.rko_quantize_rows_mxgolden.argtypes = [C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p]
         L.rko_rope_rows.restype = None
         L.rko_rope_rows.argtypes = [C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
+        L.rko_mx_gemm_hw.restype = None
+        L.rko_mx_gemm_hw.argtypes = [C.c_void_p] * 4 + [C.c_int] * 3 + [C.c_void_p, C.c_int]
         L.rko_rmsnorm_rows.restype = None
         L.rko_rmsnorm_rows.argtypes = [C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_float, C.c_void_p]
         L.rko_rebase_v.restype = None
@@ -169,6 +171,17 @@ def rope(x, pos, cos_half, sin_half):
     out = np.empty_like(x)
     lib().rko_rope_rows(_p(x), rows, d, _p(pos), _p(c), _p(s), _p(out))
     return out
+
+
+def mx_gemm_hw(A, B, SA, SB, nthreads=0):
+    """MX matmul in the mesh's accumulate semantics (lib/golden/mx_golden.cpp:114-144).  A [M,K], B [K,N] E4M3 codes,
+    SA [K/32,M], SB [K/32,N] E8M0 codes -> C bf16 bits uint16 [M,N]."""
+    A, B, SA, SB = [np.ascontiguousarray(t, np.uint8) for t in (A, B, SA, SB)]
+    M, K = A.shape
+    N = B.shape[1]
+    Cc = np.empty((M, N), np.uint16)
+    lib().rko_mx_gemm_hw(_p(A), _p(B), _p(SA), _p(SB), M, N, K, _p(Cc), nthreads or hardware_threads())
+    return Cc
 
 
 def rmsnorm(x, gamma, eps):

@@ -379,6 +379,104 @@ void rko_rebase_v(const uint8_t* codes, const uint8_t* scales, int64_t S, int64_
   rko_quantize_cols(tmp.data(), S, d, fmt, out_codes, out_scales, 1);
 }
 
+// ------------------------------ MX matmul, hardware accumulate semantics --------------------------
+// The reference's golden for the MX-Gemmini matmul models the mesh itself (lib/golden/mx_golden.cpp:114-144): per
+// 16-deep K step the partial sum flows down a systolic column whose accumulator widens as it goes (ACC_E / ACC_M,
+// :44-48), every product is truncated to 3 fraction bits and saturated at 448 (mx_product_quantize_trunc,
+// lib/golden/mx_fp_math.h:44-71), both addends are re-rounded to the stage's format before an exact add that is
+// rounded again (fp_quantize_rne / fp_add_exact, :120-189); after 16 stages the sum is scaled by the two E8M0 codes
+// of the 32-element K group and added into a bf16 accumulator.  Restated here in integer form; pinned against the
+// reference's own program built under oracle/_ref (tests/test_oracle_golden.py).
+
+// x rounded to the nearest value of a float format with `ebits` exponent and `mbits` fraction bits (ties to even),
+// gradual underflow, overflow to infinity; zero results are +0 (mx_fp_math.h:120-172).
+static float quantize_rne_fmt(float x, int ebits, int mbits) {
+  if (x != x) return std::numeric_limits<float>::quiet_NaN();
+  if (std::isinf(x) || x == 0.0f) return x == 0.0f ? 0.0f : x;
+  uint32_t b; std::memcpy(&b, &x, 4);
+  const bool neg = (b >> 31) != 0;
+  const int e_raw = (int)((b >> 23) & 0xFF);
+  const uint64_t sig = e_raw ? ((b & 0x7FFFFFu) | 0x800000u) : (b & 0x7FFFFFu);   // |x| = sig * 2^ex
+  const int ex = (e_raw ? e_raw : 1) - 150;
+  const int top = 63 - __builtin_clzll(sig);
+  const int bias = (1 << (ebits - 1)) - 1, emin = 1 - bias, emax = bias;
+  const int E = ex + top;                                    // floor(log2 |x|)
+  const int qexp = std::max(E, emin) - mbits;                // exponent of the format's quantum at this magnitude
+  const int sh = qexp - ex;
+  uint64_t q;
+  if (sh <= 0) q = sig << (-sh);
+  else if (sh >= 40) q = 0;
+  else {
+    const uint64_t rem = sig & ((1ull << sh) - 1), half = 1ull << (sh - 1);
+    q = sig >> sh;
+    if (rem > half || (rem == half && (q & 1))) ++q;
+  }
+  if (q == 0) return 0.0f;
+  const int qtop = 63 - __builtin_clzll(q);
+  if (qtop + qexp > emax) return neg ? -std::numeric_limits<float>::infinity() : std::numeric_limits<float>::infinity();
+  const float r = std::ldexp((float)q, qexp);
+  return neg ? -r : r;
+}
+
+static float add_then_round(float x, float y, int ebits, int mbits) {     // fp_add_exact, mx_fp_math.h:179-189
+  if (x != x || y != y) return std::numeric_limits<float>::quiet_NaN();
+  if (std::isinf(x) || std::isinf(y)) {
+    if (std::isinf(x) && std::isinf(y) && std::signbit(x) != std::signbit(y)) return std::numeric_limits<float>::quiet_NaN();
+    return std::isinf(x) ? x : y;
+  }
+  if (x == 0.0f) return y;
+  if (y == 0.0f) return x;
+  return quantize_rne_fmt(x + y, ebits, mbits);
+}
+
+// bf16 rounding as the reference does it: zero magnitudes come out as +0 (mx_fp_math.h:11-35)
+static float bf16_round_ref(float x) {
+  uint16_t bits;
+  const float r = bf16_round_to_f32(x, &bits);
+  return (r == 0.0f) ? 0.0f : r;
+}
+
+// A codes [M][K], B codes [K][N] (E4M3), SA [K/32][M], SB [K/32][N] (E8M0) -> C bf16 bits [M][N].
+// M, N, K multiples of 16, K of 32.  A NaN comes out as 0x7FC0.
+void rko_mx_gemm_hw(const uint8_t* A, const uint8_t* B, const uint8_t* SA, const uint8_t* SB, int M, int N, int K,
+                    uint16_t* C, int nthreads) {
+  static const int kAccE[16] = {4, 4, 4, 4, 4, 4, 4, 4, 4, 4, 4, 4, 4, 4, 4, 8};
+  static const int kAccM[16] = {4, 4, 4, 4, 4, 4, 4, 4, 5, 5, 6, 6, 6, 6, 6, 7};
+  const Fmt& f8 = kFmt[0];
+  parallel_for((int64_t)M * N, nthreads, [&](int64_t idx) {
+    const int m = (int)(idx / N), n = (int)(idx % N);
+    float acc = 0.0f;
+    for (int k0 = 0; k0 < K; k0 += 16) {
+      float ct = 0.0f;
+      for (int kk = 0; kk < 16; kk++) {
+        const float prod = decode_elem(A[(size_t)m * K + k0 + kk], f8) * decode_elem(B[(size_t)(k0 + kk) * N + n], f8);
+        float pq;
+        if (prod == 0.0f) pq = 0.0f;
+        else {
+          uint32_t pb; std::memcpy(&pb, &prod, 4);
+          pb &= 0xFFF00000u;                                   // truncate to 3 fraction bits
+          std::memcpy(&pq, &pb, 4);
+          if (std::fabs(pq) > 448.0f) pq = std::signbit(pq) ? -448.0f : 448.0f;
+        }
+        const int ae = kAccE[kk], am = kAccM[kk];
+        const float cq = (ae == 8) ? bf16_round_ref(ct) : quantize_rne_fmt(ct, ae, am);
+        const float pr = (ae == 8) ? bf16_round_ref(pq) : quantize_rne_fmt(pq, ae, am);
+        ct = add_then_round(cq, pr, ae, am);
+      }
+      const int g = k0 / 32;
+      int e = (int)SA[(size_t)g * M + m] + (int)SB[(size_t)g * N + n] - 127;
+      e = e < 0 ? 0 : (e > 254 ? 254 : e);
+      const float scaled = bf16_round_ref(ct * e8m0_decode((uint8_t)e));
+      acc = bf16_round_ref(add_then_round(bf16_round_ref(acc), bf16_round_ref(scaled), 8, 7));
+    }
+    uint16_t bits;
+    const float r = bf16_round_to_f32(acc, &bits);
+    if (r != r) bits = 0x7FC0;
+    else if (r == 0.0f) bits = 0;
+    C[idx] = bits;
+  });
+}
+
 // ------------------------------ prefill attention --------------------------
 struct rko_prefill_args {
   const uint8_t* q;        // [B][H][Sq][d] codes

@@ -62,6 +62,7 @@ SYMBOLS = {
                                       C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p]),
     "rk_rmsnorm_mx_quantize": (C.c_int, [C.c_void_p, C.c_int, C.c_int64, C.c_int32, C.c_void_p, C.c_float, C.c_int32, C.c_int32,
                                          C.c_void_p, C.c_void_p, C.c_void_p]),
+    "rk_mx_gemm_hw": (C.c_int, [C.c_void_p] * 4 + [C.c_int32] * 3 + [C.c_void_p, C.c_void_p]),
     "rk_kv_cache_append": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_int32,
                                      C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "rk_profile_set_events": (None, [C.c_void_p, C.c_void_p]),

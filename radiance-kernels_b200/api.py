@@ -181,6 +181,21 @@ def rmsnorm_mx_quantize(x, gamma, eps, fmt=E4M3, unit_scale=False):
     return codes, scales
 
 
+def mx_gemm_hw(a, b, a_scales, b_scales):
+    """MX matmul in the mesh's accumulate semantics (bit-exact with the reference's mx_golden program).  a [M,K], b [K,N]
+    E4M3 codes; a_scales [K/32,M], b_scales [K/32,N] E8M0 codes.  Returns C as bf16 [M,N]."""
+    _need_cuda(a, b, a_scales, b_scales)
+    if a.dim() != 2 or b.dim() != 2:
+        raise ValueError("a must be [M,K] and b [K,N]")
+    M, K = a.shape
+    N = b.shape[1]
+    _expect(a, "a", torch.uint8, (M, K)); _expect(b, "b", torch.uint8, (K, N))
+    _expect(a_scales, "a_scales", torch.uint8, (K // 32, M)); _expect(b_scales, "b_scales", torch.uint8, (K // 32, N))
+    c = torch.empty((M, N), dtype=torch.bfloat16, device=a.device)
+    check(lib().rk_mx_gemm_hw(_ptr(a), _ptr(b), _ptr(a_scales), _ptr(b_scales), M, N, K, _ptr(c), _stream()), "rk_mx_gemm_hw")
+    return c
+
+
 def mx_quantize_keys(x, fmt=E4M3):
     """fp32 [..., rows, cols] -> codes same shape, scales [..., ceil(rows/32), cols]; blocks run down the rows."""
     _need_cuda(x)

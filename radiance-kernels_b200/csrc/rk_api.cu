@@ -421,6 +421,14 @@ int rk_rmsnorm_mx_quantize(const void* x, int x_is_bf16, int64_t rows, int32_t K
   return launch_rmsnorm_quantize(x, x_is_bf16 != 0, rows, K, gamma, eps, fmt, unit_scale != 0, codes, scales, (cudaStream_t)stream);
 }
 
+int rk_mx_gemm_hw(const uint8_t* a, const uint8_t* b, const uint8_t* a_scales, const uint8_t* b_scales, int32_t M, int32_t N,
+                  int32_t K, void* c_bf16, void* stream) {
+  if (!a || !b || !a_scales || !b_scales || !c_bf16) return RK_ERR_NULL_POINTER;
+  if (M < 0 || N < 0 || K < 0 || M % 16 != 0 || N % 16 != 0 || K % 32 != 0) return RK_ERR_BAD_SHAPE;
+  if (!aligned(a, 16) || !aligned(c_bf16, 2)) return RK_ERR_MISALIGNED;
+  return launch_mx_gemm_hw(a, b, a_scales, b_scales, M, N, K, reinterpret_cast<uint16_t*>(c_bf16), (cudaStream_t)stream);
+}
+
 int rk_kv_cache_append(const float* k_new, const float* v_new, int32_t B, int32_t H_kv, int32_t L, int32_t d,
                        const int32_t* pos, int32_t fmt, uint8_t* k_codes, uint8_t* k_scales, uint8_t* v_codes,
                        uint8_t* v_scales, void* stream) {

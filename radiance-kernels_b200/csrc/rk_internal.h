@@ -27,6 +27,8 @@ int launch_quantize_keys_atoms(const float* x, int64_t batch, int64_t rows, int6
                                uint8_t* scales, cudaStream_t st);
 int launch_rmsnorm_quantize(const void* x, bool bf16, int64_t rows, int K, const float* gamma, float eps, int fmt,
                             bool unit_scale, uint8_t* codes, uint8_t* scales, cudaStream_t st);
+int launch_mx_gemm_hw(const uint8_t* A, const uint8_t* B, const uint8_t* SA, const uint8_t* SB, int M, int N, int K,
+                      uint16_t* C, cudaStream_t st);
 int launch_retile_groupscales(const uint8_t* in, int64_t batch, int64_t S, int64_t d, uint8_t* out, cudaStream_t st);
 int launch_import_kt_blocks(const uint8_t* kt, const uint8_t* kts, int64_t heads, int nblk, int Bk, int d, uint8_t* k,
                             uint8_t* ks, cudaStream_t st);

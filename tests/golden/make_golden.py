@@ -30,6 +30,10 @@ reference tree is read-only) and stores only input/output vectors:
   rmsnorm_vectors.npz     lib/golden/golden.py rmsnorm (scalar fp32 accumulation order) on seeded inputs shaped
                           like kernels/rmsnorm_qkv_fused/gen_data.py (bf16-exact X and gamma, eps 1e-5) and on
                           plain fp32 inputs, row lengths 64 .. 1024: X, gamma, eps and the normalized output.
+  mx_gemm_hw_vectors.npz  the reference's mx_golden program (lib/golden/mx_golden.cpp, built by `make -C oracle ref`)
+                          run on operands drawn as kernels/gemm_mxgemmini/gen_mxgemm_data.py draws them (E4M3 codes
+                          with |value| < 2, scale codes 0x7B..0x82, seed = sha256 of the shape): A, B, SA, SB and
+                          the bf16 output for 64x64x64, 64x64x128, 128x128x256, and one overflowing case.
   rope_vectors.npz        lib/golden/golden.py rope_caches + rope_apply (HF Llama
                           rotate-half) on seeded inputs for head dims 64, 128, 256:
                           X, the half-width cos / sin caches and the rotated output.
@@ -110,6 +114,43 @@ def make_golden_py_vectors(ref):
                         amax_bits=amax_bits, block_exp=bexp, pow2_ok=ok, pow2_neg_e=p2,
                         cap_x=cap_x, cap_y=cap_y)
     print("golden_py_vectors.npz:", xin.size, "encode cases,", amax_bits.size, "block_exp cases")
+
+
+def run_mx_golden(exe, A, B, SA, SB, tmp):
+    M, K = A.shape
+    N = B.shape[1]
+    names = {}
+    for n, arr in (("A", A), ("B", B), ("SA", SA), ("SB", SB)):
+        names[n] = os.path.join(tmp, n + ".bin")
+        np.ascontiguousarray(arr).tofile(names[n])
+    out = os.path.join(tmp, "C.bin")
+    env = {k: v for k, v in os.environ.items() if not k.startswith("MX_")}
+    subprocess.run([exe, str(M), str(N), str(K), names["A"], names["B"], names["SA"], names["SB"], out], check=True, env=env)
+    return np.fromfile(out, np.uint16).reshape(M, N)
+
+
+def make_mx_gemm_hw_vectors(ref):
+    import hashlib
+    G = load_golden(ref)
+    exe = HERE.parent.parent / "oracle" / "_ref" / "mx_golden"
+    if not exe.exists():
+        subprocess.run(["make", "-C", str(HERE.parent.parent / "oracle"), "ref", "REF=" + str(ref)], check=True)
+    out = {}
+    with tempfile.TemporaryDirectory() as tmp:
+        for i, (M, N, K, full_range) in enumerate(((64, 64, 64, False), (64, 64, 128, False), (128, 128, 256, False), (32, 32, 64, True))):
+            seed = int.from_bytes(hashlib.sha256(f"fp8_{M}_{N}_{K}".encode()).digest()[:4], "little")     # gen_mxgemm_data.py:35-39
+            rng = np.random.default_rng(seed)
+            A = G.rand_fp8(rng, M * K).reshape(M, K)
+            B = G.rand_fp8(rng, K * N).reshape(K, N)
+            if full_range:      # exponent fields up to 14: products overflow the 4-bit-exponent stages to inf / NaN
+                A = (A | (rng.integers(0, 2, A.shape).astype(np.uint8) << 6)).astype(np.uint8)
+                A[(A & 0x7F) == 0x7F] = 0x7E
+            SA = rng.integers(0x7B, 0x83, size=(K // 32, M), dtype=np.uint8)
+            SB = rng.integers(0x7B, 0x83, size=(K // 32, N), dtype=np.uint8)
+            out[f"a{i}"] = A; out[f"b{i}"] = B; out[f"sa{i}"] = SA; out[f"sb{i}"] = SB
+            out[f"c{i}"] = run_mx_golden(str(exe), A, B, SA, SB, tmp)
+    np.savez_compressed(HERE / "mx_gemm_hw_vectors.npz", **out)
+    print("mx_gemm_hw_vectors.npz:", {k: v.shape for k, v in out.items() if k.startswith("c")})
 
 
 def make_rmsnorm_vectors(ref):
@@ -195,4 +236,5 @@ if __name__ == "__main__":
     make_golden_py_vectors(ref)
     make_rope_vectors(ref)
     make_rmsnorm_vectors(ref)
+    make_mx_gemm_hw_vectors(ref)
     make_attn_fp32_ref_vectors(ref)

@@ -239,3 +239,35 @@ def test_rmsnorm_matches_the_reference_golden_bit_for_bit():
     for i in range(4):
         y = oracle.rmsnorm(z[f"x{i}"], z[f"g{i}"], float(z[f"eps{i}"]))
         assert np.array_equal(y.view(np.uint32), z[f"y{i}"].view(np.uint32)), i
+
+
+def test_mx_gemm_hardware_accumulate_matches_the_reference_program():
+    """rko_mx_gemm_hw against outputs of the reference's own mx_golden program (lib/golden/mx_golden.cpp:114-144) on
+    operands drawn as kernels/gemm_mxgemmini/gen_mxgemm_data.py draws them, plus one case whose products overflow the
+    mesh's 4-bit-exponent accumulator stages (inf / NaN in the golden): committed fixture; when oracle/_ref holds the
+    program it is also run afresh on a new seed."""
+    z = np.load(os.path.join(G, "mx_gemm_hw_vectors.npz"))
+    for i in range(4):
+        got = oracle.mx_gemm_hw(z[f"a{i}"], z[f"b{i}"], z[f"sa{i}"], z[f"sb{i}"])
+        assert np.array_equal(got, z[f"c{i}"]), i
+    exe = oracle.ref_mx_golden_path()
+    if exe is None:
+        return
+    import subprocess
+    import tempfile
+    rng = np.random.default_rng(123)
+    M, N, K = 32, 48, 96
+    code = lambda shape: ((rng.integers(0, 2, shape) << 7) | (rng.integers(0, 9, shape) << 3) | rng.integers(0, 8, shape)).astype(np.uint8)
+    A, B = code((M, K)), code((K, N))
+    SA = rng.integers(0x78, 0x88, (K // 32, M)).astype(np.uint8)
+    SB = rng.integers(0x78, 0x88, (K // 32, N)).astype(np.uint8)
+    with tempfile.TemporaryDirectory() as tmp:
+        names = []
+        for n, arr in (("A", A), ("B", B), ("SA", SA), ("SB", SB)):
+            names.append(os.path.join(tmp, n + ".bin"))
+            arr.tofile(names[-1])
+        out = os.path.join(tmp, "C.bin")
+        env = {k: v for k, v in os.environ.items() if not k.startswith("MX_")}
+        subprocess.run([exe, str(M), str(N), str(K)] + names + [out], check=True, env=env)
+        want = np.fromfile(out, np.uint16).reshape(M, N)
+    assert np.array_equal(oracle.mx_gemm_hw(A, B, SA, SB), want)
