@@ -100,9 +100,8 @@ def lib():
         L.rk_debug_mxfp8_mma_loop.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]
         L.rk_debug_wait_runs_out.restype = C.c_int
         L.rk_debug_wait_runs_out.argtypes = [C.c_int, C.c_int, C.c_void_p]
-        for name in ("rk_debug_set_prefill_path", "rk_debug_set_prefill_perturb"):
-            getattr(L, name).restype = None
-            getattr(L, name).argtypes = [C.c_int]
+        L.rk_debug_set_prefill_perturb.restype = None
+        L.rk_debug_set_prefill_perturb.argtypes = [C.c_int]
         _LIB = L
     return _LIB
 

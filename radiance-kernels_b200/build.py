@@ -12,7 +12,7 @@ import sys
 
 HERE = pathlib.Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
-SOURCES = ["rk_api.cu", "rk_quant.cu", "rk_prefill.cu", "rk_prefill2q.cu", "rk_prefill2c.cu", "rk_peak.cu", "rk_mxgemm.cu", "rk_decode.cu"]
+SOURCES = ["rk_api.cu", "rk_quant.cu", "rk_prefill.cu", "rk_prefill2c.cu", "rk_peak.cu", "rk_mxgemm.cu", "rk_decode.cu"]
 HEADERS = ["rk_common.cuh", "rk_internal.h", "rk_prefill.cuh"]
 LIB = HERE / "librk_mx_attn.so"
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-std=c++17", "-O3", "-lineinfo",

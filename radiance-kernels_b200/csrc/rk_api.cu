@@ -9,7 +9,7 @@
 #include "rk_internal.h"
 
 namespace rk {
-extern int g_prefill_path, g_prefill_perturb;
+extern int g_prefill_perturb;
 
 // The status word kernels record a given-up wait in: part of the library image (zero at load) on every device,
 // so it can never fail to allocate; its device address is looked up once per device.
@@ -533,10 +533,8 @@ RK_API int rk_debug_mxfp8_mma_loop(const uint8_t* a_tile, const uint8_t* b_tile,
   return launch_mxfp8_mma_loop(a_tile, b_tile, iters, (cudaStream_t)stream);
 }
 
-/* Test hooks (not in the public header): which prefill kernel serves d <= 128 (0 = default, 1 = the
- * two-threads-per-row kernel), and which warp role of the default kernel sleeps a little at every key tile
- * (0 = none; 1, 2 = softmax of query tile A, B; 3 = correction; 4 = TMA producer; 5 = Q K^T issuer; 6 = P V issuer). */
-RK_API void rk_debug_set_prefill_path(int path) { g_prefill_path = path; }
+/* Test hook (not in the public header): which warp role of the d <= 128 prefill kernel sleeps a little at every key
+ * tile (0 = none; 1, 2 = softmax of query tile A, B; 3 = correction; 4 = TMA producer; 5 = Q K^T issuer; 6 = P V issuer). */
 RK_API void rk_debug_set_prefill_perturb(int role) { g_prefill_perturb = role; }
 
 }  // extern "C"

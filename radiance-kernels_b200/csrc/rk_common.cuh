@@ -173,9 +173,6 @@ RK_DEVINL bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_fla
 template <uint32_t SLEEP_NS>
 RK_DEVINL bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status, int code,
                                  uint64_t limit_ns = 2000000000ull) {
-#ifdef RK_V_TIGHTPOLL
-  return mbar_wait(bar, parity, abort_flag, status, code, limit_ns);
-#endif
   if (mbar_try_wait<0>(bar, parity)) return true;
   const uint64_t t0 = global_timer_ns();
   for (uint32_t it = 1;; ++it) {

@@ -581,7 +581,6 @@ static int launch_cfg(const CUtensorMap& tq, const CUtensorMap& tk, const CUtens
 }
 
 float* g_prefill_dbg = nullptr;   // set by rk_debug_set_prefill_dump (tests only)
-int g_prefill_path = 0;
 int g_prefill_perturb = 0;
 
 int launch_prefill(const rk_prefill_args& a, const uint8_t* q_codes, const uint8_t* k_codes, const uint8_t* v_codes,
@@ -629,10 +628,7 @@ int launch_prefill(const rk_prefill_args& a, const uint8_t* q_codes, const uint8
   const uint32_t idesc_pv = make_idesc(RK_FMT_E4M3, a.kv_fmt, false, /*B MN-major*/ !kv6, 128, 128);
   dim3 grid(p.n_q_tiles * a.H * a.B, 1, 1);
   const bool cap = a.softcap > 0.0f;
-  if (a.d <= 128) {                                     // two query tiles per CTA
-    return g_prefill_path == 1 ? launch_prefill2q(tq, tk, tv, p, idesc_qk, idesc_pv, cap, a.B, st)
-                               : launch_prefill2c(tq, tk, tv, p, idesc_qk, idesc_pv, cap, a.B, st);
-  }
+  if (a.d <= 128) return launch_prefill2c(tq, tk, tv, p, idesc_qk, idesc_pv, cap, a.B, st);   // two query tiles per CTA
   return cap ? launch_cfg<2, 2, true>(tq, tk, tv, p, idesc_qk, idesc_pv, grid, st)
              : launch_cfg<2, 2, false>(tq, tk, tv, p, idesc_qk, idesc_pv, grid, st);
 }

@@ -89,13 +89,9 @@ int make_tmap_u8_3d(CUtensorMap* m, const void* base, int64_t BH, int64_t S, int
 int make_tmap_u6_3d(CUtensorMap* m, const void* base, int64_t BH, int64_t rows, int64_t cols_padded);
 extern float* g_prefill_dbg;
 
-// Two 128-row query tiles per CTA (d <= 128); defined in rk_prefill2q.cu.
-int launch_prefill2q(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const PrefillParams& p,
-                     uint32_t idesc_qk, uint32_t idesc_pv, bool softcap, int B, cudaStream_t st);
 // Two query tiles per CTA, one thread per row, correction warps (d <= 128); defined in rk_prefill2c.cu.
 int launch_prefill2c(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const PrefillParams& p,
                      uint32_t idesc_qk, uint32_t idesc_pv, bool softcap, int B, cudaStream_t st);
-extern int g_prefill_path;      // test hook: 0 = default kernel by shape, 1 = the two-threads-per-row kernel for d <= 128
 extern int g_prefill_perturb;   // test hook: PrefillParams::perturb of the next launches
 
 }  // namespace rk

@@ -223,20 +223,11 @@ __device__ __forceinline__ void softmax_row_group(const PrefillParams& p, uint8_
 #pragma unroll
     for (int g = 0; g < 4; ++g) {
       uint32_t w[8];
-#ifdef RK_V_COARSE
-      if (g < 3) {
-#pragma unroll
-        for (int q = 0; q < 8; ++q) exp4(g + 1, q * 4);
-      }
-#pragma unroll
-      for (int q = 0; q < 8; ++q) w[q] = requant4(g, q * 4);
-#else
 #pragma unroll
       for (int q = 0; q < 8; ++q) {
         if (g < 3) exp4(g + 1, q * 4);
         w[q] = requant4(g, q * 4);
       }
-#endif
       const int c0 = (2 * g) ^ (row & 7), c1 = (2 * g + 1) ^ (row & 7);     // 128-byte swizzle
       *reinterpret_cast<uint4*>(p_tile + c0 * 16) = make_uint4(w[0], w[1], w[2], w[3]);
       *reinterpret_cast<uint4*>(p_tile + c1 * 16) = make_uint4(w[4], w[5], w[6], w[7]);
