@@ -13,10 +13,12 @@
 //   pack_scales_to_sfmem (flash_mx_impl.hpp:625-639)   -> one st.shared per row + tcgen05.cp
 //   rescale_accumulate / finalize_O (:508-553)         -> O kept in TMEM, rescaled in place
 //
-// One CTA = one 128-row query tile of one (batch, head).  576 threads:
+// One CTA = one 128-row query tile of one (batch, head).  608 threads:
 //   warps 0-15  softmax: four threads per query row (TMEM lane = row), one 32-key block of the tile each
 //   warp  16    TMA producer (one elected lane)
-//   warp  17    MMA issuer  (one elected lane), TMEM allocation
+//   warp  17    issuer of the S = Q K^T MMAs (one elected lane), TMEM allocation
+//   warp  18    issuer of the O += P V MMAs (one elected lane): a P V that waits for its P tile never holds back
+//               the next Q K^T, and each issuing thread runs a short instruction stream per key tile
 // Keys are walked in tiles of 128 (the online-softmax step, "block_n").
 //
 // Roofline: tensor-core bound by FLOP count (4*S_q*S_kv*d per head, half of it
@@ -42,8 +44,8 @@ struct SmemLayout {
   static constexpr int sfv_off = sfk_off + KV_STAGES * DCH * kSfAtomBytes;
   static constexpr int sfp_off = sfv_off + KV_STAGES * DCH * kSfAtomBytes;
   static constexpr int bar_off = sfp_off + 2 * kSfAtomBytes;
-  // barriers: q_full, k_full[S], k_empty[S], v_full[S], v_empty[S], s_full, s_empty, p_full[2], pv_done[2], drain, pair[4]
-  static constexpr int n_bars = 1 + 4 * KV_STAGES + 2 + 4 + 1 + 4;
+  // barriers: q_full, k_full[S], k_empty[S], v_full[S], v_empty[S], s_full, s_empty, p_full[2], pv_done[2], drain, pair[4], drain2
+  static constexpr int n_bars = 1 + 4 * KV_STAGES + 2 + 4 + 1 + 4 + 1;
   static constexpr int misc_off = bar_off + n_bars * 8;
   static constexpr int xchg_off = misc_off + 16;          // row-max / row-sum exchange: 3 x kParts x 128 floats
   static constexpr int total = xchg_off + 3 * kParts * 128 * 4;
@@ -343,6 +345,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
   uint64_t* p_full = s_empty + 1;
   uint64_t* pv_done = p_full + 2;
   uint64_t* drain = pv_done + 2;
+  uint64_t* drain2 = drain + 5;       // after the four pair barriers
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -381,7 +384,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
     mbar_init(s_full, 1); mbar_init(s_empty, kNumSoftmaxWarps);
     mbar_init(&p_full[0], kNumSoftmaxWarps); mbar_init(&p_full[1], kNumSoftmaxWarps);
     mbar_init(&pv_done[0], 1); mbar_init(&pv_done[1], 1);
-    mbar_init(drain, 1);
+    mbar_init(drain, 1); mbar_init(drain2, 1);
     for (int i = 0; i < 4; ++i) mbar_init(&drain[1 + i], kParts);
     *abort_flag = 0;
     fence_barrier_init();
@@ -438,78 +441,95 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         }
       }
     }
-  } else {
-    // ================= MMA issuer =================
+  } else if (warp == kNumSoftmaxWarps + 1) {
+    // ================= issuer of S = Q K^T =================
+    // One thread issues; what it runs per key tile is kept short (a lone thread executes one instruction every few
+    // cycles): descriptors are built once, a tile's descriptor is the base plus an offset in its low word.
     if (lane == 0) {
-      const uint32_t q_addr = smem_u32(smem + L::q_off), k_addr = smem_u32(smem + L::k_off);
-      const uint32_t v_addr = smem_u32(smem + L::v_off), pt_addr = smem_u32(smem + L::p_off);
+      const uint64_t dq = make_smem_desc(smem_u32(smem + L::q_off), 16, 1024, kLayoutSw128);
+      const uint64_t dk = make_smem_desc(smem_u32(smem + L::k_off), 16, 1024, kLayoutSw128);
+      const uint64_t dsfq = make_smem_desc(smem_u32(smem + L::sfq_off), 0, 128, kLayoutNone);
+      const uint64_t dsfk = make_smem_desc(smem_u32(smem + L::sfk_off), 0, 128, kLayoutNone);
+      uint32_t idesc_kk[4];
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk) idesc_kk[kk] = idesc_with_sf(idesc_qk, kk, kk);
       bool ok = mbar_wait(q_full, 0, abort_flag, p.status, 301);
       if (ok) {
-        for (int ch = 0; ch < DCH; ++ch)
-          tc_cp_32x128b_warpx4(tmem_base + kColSfQ + ch * 4,
-                               make_smem_desc(smem_u32(smem + L::sfq_off + ch * kSfAtomBytes), 0, 128, kLayoutNone));
-      }
-      auto issue_pv = [&](int i) -> bool {
-        const int pb = i & 1, st = i % KV_STAGES, use = i / KV_STAGES;
-        if (!mbar_wait(&v_full[st], use & 1, abort_flag, p.status, 303)) return false;
-        RK_STAMP(2, i + 1, 4);
-        if (!mbar_wait(&p_full[pb], (i >> 1) & 1, abort_flag, p.status, 304)) return false;
-        tc_fence_after();
-        RK_STAMP(2, i + 1, 5);
-        tc_cp_32x128b_warpx4(tmem_base + kColSfP + pb * 4,
-                             make_smem_desc(smem_u32(smem + L::sfp_off + pb * kSfAtomBytes), 0, 128, kLayoutNone));
-        for (int ch = 0; ch < DCH; ++ch)
-          tc_cp_32x128b_warpx4(tmem_base + kColSfV + st * 8 + ch * 4,
-                               make_smem_desc(smem_u32(smem + L::sfv_off + (st * DCH + ch) * kSfAtomBytes), 0, 128, kLayoutNone));
-        for (int ch = 0; ch < DCH; ++ch) {
 #pragma unroll
-          for (int kk = 0; kk < 4; ++kk) {
-            // A = P tile, K-major: 32 keys = 32 bytes along the swizzled 128-byte row
-            const uint64_t adesc = make_smem_desc(pt_addr + pb * kTileBytes + kk * 32, 16, 1024, kLayoutSw128);
-            // B = V tile, MN-major (d contiguous): 32 keys = 32 rows of 128 bytes
-            // (6-bit V is stored transposed, [d][keys]: K-major like the K tile of QK^T)
-            const uint64_t bdesc = p.v_transposed
-                ? make_smem_desc(v_addr + (st * DCH + ch) * kTileBytes + kk * 32, 16, 1024, kLayoutSw128)
-                : make_smem_desc(v_addr + (st * DCH + ch) * kTileBytes + kk * 4096, kTileBytes, 1024, kLayoutSw128);
-            mma_mxf8f6f4_ss(tmem_base + kColO + ch * 128, adesc, bdesc, idesc_with_sf(idesc_pv, kk, kk),
-                            tmem_base + kColSfP + pb * 4, tmem_base + kColSfV + st * 8 + ch * 4, (i > 0 || kk > 0) ? 1u : 0u);
-          }
-        }
-        tc_commit(&v_empty[st]);
-        tc_commit(&pv_done[pb]);
-        return true;
-      };
+        for (int ch = 0; ch < DCH; ++ch) tc_cp_32x128b_warpx4(tmem_base + kColSfQ + ch * 4, dsfq + (uint32_t)(ch * (kSfAtomBytes >> 4)));
+      }
+      int st = 0, use_par = 0;
       for (int j = 0; j < n_tiles && ok; ++j) {
-        const int st = j % KV_STAGES, use = j / KV_STAGES;
         RK_STAMP(2, j, 0);
-        ok = mbar_wait(&k_full[st], use & 1, abort_flag, p.status, 302);
+        ok = mbar_wait(&k_full[st], use_par, abort_flag, p.status, 302);
         RK_STAMP(2, j, 1);
         if (ok && j > 0) ok = mbar_wait(s_empty, (j - 1) & 1, abort_flag, p.status, 305);
         if (!ok) break;
         tc_fence_after();
         RK_STAMP(2, j, 2);
-        for (int ch = 0; ch < DCH; ++ch)
-          tc_cp_32x128b_warpx4(tmem_base + kColSfK + st * 8 + ch * 4,
-                               make_smem_desc(smem_u32(smem + L::sfk_off + (st * DCH + ch) * kSfAtomBytes), 0, 128, kLayoutNone));
-        for (int ch = 0; ch < DCH; ++ch) {
 #pragma unroll
-          for (int kk = 0; kk < 4; ++kk) {
-            const uint64_t adesc = make_smem_desc(q_addr + ch * kTileBytes + kk * 32, 16, 1024, kLayoutSw128);
-            const uint64_t bdesc = make_smem_desc(k_addr + (st * DCH + ch) * kTileBytes + kk * 32, 16, 1024, kLayoutSw128);
-            mma_mxf8f6f4_ss(tmem_base + kColS, adesc, bdesc, idesc_with_sf(idesc_qk, kk, kk),
-                            tmem_base + kColSfQ + ch * 4, tmem_base + kColSfK + st * 8 + ch * 4, (ch > 0 || kk > 0) ? 1u : 0u);
-          }
+        for (int ch = 0; ch < DCH; ++ch)
+          tc_cp_32x128b_warpx4(tmem_base + kColSfK + st * 8 + ch * 4, dsfk + (uint32_t)((st * DCH + ch) * (kSfAtomBytes >> 4)));
+#pragma unroll
+        for (int ch = 0; ch < DCH; ++ch) {
+          const uint64_t dqt = dq + (uint32_t)(ch * (kTileBytes >> 4));
+          const uint64_t dkt = dk + (uint32_t)((st * DCH + ch) * (kTileBytes >> 4));
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk)
+            mma_mxf8f6f4_ss(tmem_base + kColS, dqt + kk * 2, dkt + kk * 2, idesc_kk[kk], tmem_base + kColSfQ + ch * 4,
+                            tmem_base + kColSfK + st * 8 + ch * 4, (ch > 0 || kk > 0) ? 1u : 0u);
         }
         tc_commit(&k_empty[st]);
         tc_commit(s_full);
         RK_STAMP(2, j, 3);
-        if (j > 0) ok = issue_pv(j - 1);
-        RK_STAMP(2, j, 6);
+        if (++st == KV_STAGES) { st = 0; use_par ^= 1; }
       }
-      if (ok) ok = issue_pv(n_tiles - 1);
       // make sure nothing issued from this thread is still running before TMEM is released
       tc_commit(drain);
       mbar_wait(drain, 0, abort_flag, p.status, 306);
+    }
+    __syncwarp();
+  } else {
+    // ================= issuer of O += P V =================
+    if (lane == 0) {
+      const uint64_t dp = make_smem_desc(smem_u32(smem + L::p_off), 16, 1024, kLayoutSw128);
+      // B = V tile, MN-major (d contiguous): 32 keys = 32 rows of 128 bytes; a 6-bit V is stored transposed,
+      // [d][keys], and is K-major like the K tile of QK^T
+      const uint64_t dv = p.v_transposed ? make_smem_desc(smem_u32(smem + L::v_off), 16, 1024, kLayoutSw128)
+                                         : make_smem_desc(smem_u32(smem + L::v_off), kTileBytes, 1024, kLayoutSw128);
+      const uint32_t v_kk = p.v_transposed ? 2u : (uint32_t)(4096 >> 4);
+      const uint64_t dsfp = make_smem_desc(smem_u32(smem + L::sfp_off), 0, 128, kLayoutNone);
+      const uint64_t dsfv = make_smem_desc(smem_u32(smem + L::sfv_off), 0, 128, kLayoutNone);
+      uint32_t idesc_kk[4];
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk) idesc_kk[kk] = idesc_with_sf(idesc_pv, kk, kk);
+      bool ok = true;
+      int st = 0, use_par = 0;
+      for (int i = 0; i < n_tiles && ok; ++i) {
+        const int pb = i & 1;
+        ok = mbar_wait(&v_full[st], use_par, abort_flag, p.status, 303) &&
+             mbar_wait(&p_full[pb], (i >> 1) & 1, abort_flag, p.status, 304);
+        if (!ok) break;
+        tc_fence_after();
+        tc_cp_32x128b_warpx4(tmem_base + kColSfP + pb * 4, dsfp + (uint32_t)(pb * (kSfAtomBytes >> 4)));
+#pragma unroll
+        for (int ch = 0; ch < DCH; ++ch)
+          tc_cp_32x128b_warpx4(tmem_base + kColSfV + st * 8 + ch * 4, dsfv + (uint32_t)((st * DCH + ch) * (kSfAtomBytes >> 4)));
+        const uint64_t dpt = dp + (uint32_t)(pb * (kTileBytes >> 4));
+#pragma unroll
+        for (int ch = 0; ch < DCH; ++ch) {
+          const uint64_t dvt = dv + (uint32_t)((st * DCH + ch) * (kTileBytes >> 4));
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk)
+            mma_mxf8f6f4_ss(tmem_base + kColO + ch * 128, dpt + kk * 2, dvt + kk * v_kk, idesc_kk[kk],
+                            tmem_base + kColSfP + pb * 4, tmem_base + kColSfV + st * 8 + ch * 4, (i > 0 || kk > 0) ? 1u : 0u);
+        }
+        tc_commit(&v_empty[st]);
+        tc_commit(&pv_done[pb]);
+        if (++st == KV_STAGES) { st = 0; use_par ^= 1; }
+      }
+      tc_commit(drain2);
+      mbar_wait(drain2, 0, abort_flag, p.status, 308);
     }
     __syncwarp();
   }

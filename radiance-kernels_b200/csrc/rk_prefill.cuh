@@ -14,7 +14,7 @@ constexpr int kTileBytes = 128 * 128;      // one [128 rows][128 B] swizzled til
 constexpr int kSfAtomBytes = 512;
 constexpr int kParts = 4;                       // threads per query row (each owns 128 / kParts keys of a tile)
 constexpr int kNumSoftmaxWarps = 4 * kParts;
-constexpr int kNumThreads = (kNumSoftmaxWarps + 2) * 32;
+constexpr int kNumThreads = (kNumSoftmaxWarps + 3) * 32;   // + TMA producer, Q K^T issuer, P V issuer
 constexpr uint32_t kTmemCols = 512;
 
 // TMEM column map
