@@ -16,13 +16,19 @@ _LIB = None
 E4M3, E5M2, E2M3, E3M2 = 0, 1, 2, 3
 
 
+def reference_dir():
+    """Where the reference's source tree lies: $RK_REFERENCE_DIR, else a directory named `reference` beside this
+    repository's checkout.  It need not exist (the prebuilt oracle/_ref files are used then)."""
+    return os.environ.get("RK_REFERENCE_DIR") or str(_HERE.parent.parent / "reference")
+
+
 def build(force=False):
     """Compile liboracle.so (and oracle/_ref when the reference tree is present)."""
     so = _HERE / "liboracle.so"
     src = _HERE / "rk_oracle.cpp"
     if force or not so.exists() or so.stat().st_mtime < src.stat().st_mtime:
         subprocess.run(["make", "-C", str(_HERE), "liboracle.so"], check=True, stdout=subprocess.DEVNULL)
-    ref = os.environ.get("RK_REFERENCE_DIR", "/root/reference")
+    ref = reference_dir()
     if os.path.isdir(ref) and (force or not (_HERE / "_ref" / "libref_codec.so").exists()):
         subprocess.run(["make", "-C", str(_HERE), "ref", "REF=" + ref], check=True, stdout=subprocess.DEVNULL)
 

@@ -230,7 +230,8 @@ def make_attn_fp32_ref_vectors(ref):
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default=os.environ.get("RK_REFERENCE_DIR", "/root/reference"))
+    ap.add_argument("--ref", default=os.environ.get("RK_REFERENCE_DIR") or str(HERE.parents[2] / "reference"),
+                    help="the reference's source tree (default: $RK_REFERENCE_DIR, else ../reference beside this checkout)")
     ref = pathlib.Path(ap.parse_args().ref)
     make_simt_quant_kat(ref)
     make_golden_py_vectors(ref)
