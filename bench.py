@@ -26,6 +26,7 @@ import os
 import subprocess
 import sys
 import tempfile
+import threading
 import time
 
 import numpy as np
@@ -72,19 +73,54 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """nvidia-smi clocks / throttle reasons, time-stamped, sampled while the benchmark runs; `window(t0, t1)`
-    summarises the samples whose time stamps fall inside one timed region (host clock, seconds)."""
+    """SM clock, power and throttle reasons, time-stamped, sampled while the benchmark runs: read-only NVML queries
+    from a thread every few milliseconds (so that a timed region of some ten milliseconds still holds samples),
+    and an `nvidia-smi -lms` poller beside it as the fallback.  `window(t0, t1)` summarises the samples whose
+    time stamps fall inside one timed region (host clock, seconds)."""
     Q = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
          "clocks_event_reasons.sw_power_cap")
     NAMES = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
 
-    def __init__(self, gpu_index, period_ms=50):
-        self.gpu, self.period_ms = gpu_index, period_ms
+    def __init__(self, gpu_index, period_ms=50, nvml_period_ms=2.0, uuid=None):
+        self.gpu, self.period_ms, self.nvml_period = gpu_index, period_ms, nvml_period_ms * 1e-3
+        self.uuid = uuid
         self.proc = self.path = self.fh = None
         self.samples = []
+        self.nvml_samples = []
+        self._thread = None
+        self._stop_flag = threading.Event()
+
+    def _nvml_loop(self):
+        try:
+            import pynvml as nv
+            nv.nvmlInit()
+            try:
+                h = nv.nvmlDeviceGetHandleByUUID(("GPU-" + self.uuid).encode()) if self.uuid else None
+            except Exception:
+                h = None
+            if h is None:
+                h = nv.nvmlDeviceGetHandleByIndex(self.gpu)
+            mx = float(nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM))
+            bits = (("hw_slowdown", nv.nvmlClocksEventReasonHwSlowdown if hasattr(nv, "nvmlClocksEventReasonHwSlowdown")
+                     else nv.nvmlClocksThrottleReasonHwSlowdown),
+                    ("hw_thermal_slowdown", nv.nvmlClocksThrottleReasonHwThermalSlowdown),
+                    ("sw_thermal_slowdown", nv.nvmlClocksThrottleReasonSwThermalSlowdown),
+                    ("sw_power_cap", nv.nvmlClocksThrottleReasonSwPowerCap))
+            reasons_fn = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or nv.nvmlDeviceGetCurrentClocksThrottleReasons
+            while not self._stop_flag.is_set():
+                t = time.time()
+                mhz = float(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM))
+                mask = int(reasons_fn(h))
+                watts = nv.nvmlDeviceGetPowerUsage(h) / 1000.0
+                self.nvml_samples.append((t, mhz, mx, watts, [n for n, b in bits if mask & b]))
+                self._stop_flag.wait(self.nvml_period)
+        except Exception:
+            return                                   # the nvidia-smi poller still runs
 
     def __enter__(self):
+        self._thread = threading.Thread(target=self._nvml_loop, daemon=True)
+        self._thread.start()
         try:
             fd, self.path = tempfile.mkstemp(suffix=".csv")
             self.fh = os.fdopen(fd, "w")
@@ -100,6 +136,10 @@ class ClockSampler:
         return False
 
     def _stop(self):
+        self._stop_flag.set()
+        if self._thread is not None:
+            self._thread.join(timeout=5)
+            self._thread = None
         if self.proc is not None:
             self.proc.terminate()
             try:
@@ -133,15 +173,20 @@ class ClockSampler:
         no sample: the nearest one on either side is used and `samples` says 0."""
         if self.proc is not None:
             raise RuntimeError("ClockSampler.window() before the sampler was stopped")
-        inside = [s for s in self.samples if t0 <= s[0] <= t1]
+        source = "nvml"
+        inside = [s for s in self.nvml_samples if t0 <= s[0] <= t1]
+        if not inside:
+            source = "nvidia-smi"
+            inside = [s for s in self.samples if t0 <= s[0] <= t1]
         n = len(inside)
-        if not inside and self.samples:
-            inside = sorted(self.samples, key=lambda s: min(abs(s[0] - t0), abs(s[0] - t1)))[:2]
+        if not inside and (self.samples or self.nvml_samples):
+            source = "nearest"
+            inside = sorted(self.samples + self.nvml_samples, key=lambda s: min(abs(s[0] - t0), abs(s[0] - t1)))[:2]
         if not inside:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
         return {"sm_mhz": float(np.median([s[1] for s in inside])), "sm_max_mhz": float(max(s[2] for s in inside)),
                 "power_w_max": float(max(s[3] for s in inside)),
-                "reasons": sorted({r for s in inside for r in s[4]}), "samples": n}
+                "reasons": sorted({r for s in inside for r in s[4]}), "samples": n, "source": source}
 
 
 def cpu_sample(kind, nthreads, seconds_target=10.0):
@@ -228,7 +273,11 @@ def main():
         DECODE.update(B=8)
         args.no_extras = True
     windows = {}                                       # name -> (t0, t1) host times of the timed regions
-    with ClockSampler(local) as sampler:               # the poller is stopped whatever happens below
+    try:
+        uuid = str(torch.cuda.get_device_properties(local).uuid)
+    except Exception:
+        uuid = None
+    with ClockSampler(local, uuid=uuid) as sampler:    # the pollers are stopped whatever happens below
         line = run_ours(args, rank, world, local, windows)
     if line is not None:
         line["clocks"] = sampler.window(*windows["steps"])

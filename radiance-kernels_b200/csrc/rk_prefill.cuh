@@ -78,10 +78,16 @@ RK_DEVINL uint32_t pack_u8x2(uint32_t hi, uint32_t lo, uint32_t c) {
 }
 
 #ifdef RK_X_STAMPS
-#define RK_STAMP(slot, j, k) do { if (p.dbg && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (j) < 32) \
+#ifndef RK_X_STAMP_BLOCK
+#define RK_X_STAMP_BLOCK 0
+#endif
+#define RK_STAMP(slot, j, k) do { if (p.dbg && blockIdx.x == RK_X_STAMP_BLOCK && blockIdx.y == 0 && blockIdx.z == 0 && (j) < 32) \
     reinterpret_cast<unsigned*>(p.dbg)[24576 + (slot) * 512 + (j) * 8 + (k)] = (unsigned)clock64(); } while (0)
+#define RK_STAMP_RAW(idx) do { if (p.dbg && blockIdx.x == RK_X_STAMP_BLOCK) \
+    reinterpret_cast<unsigned*>(p.dbg)[24576 + 2048 + (idx)] = (unsigned)clock64(); } while (0)
 #else
 #define RK_STAMP(slot, j, k) do {} while (0)
+#define RK_STAMP_RAW(idx) do {} while (0)
 #endif
 
 

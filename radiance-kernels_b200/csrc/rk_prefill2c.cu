@@ -156,6 +156,9 @@ __device__ __forceinline__ void softmax_row_group(const PrefillParams& p, uint8_
       for (int g = 0; g < 4; ++g) bmax[g] = fmax3(a0[g], a1[g], fmaxf(s[g * 32 + 30], s[g * 32 + 31]));
     }
     const float mx = fmaxf(fmax3(bmax[0], bmax[1], bmax[2]), bmax[3]);
+    // The running maximum follows every tile (rescale_accumulate, flash_mx_impl.hpp:508-532).  Letting it lag
+    // while the maximum grows little would save most O rescales, but p would then differ from the reference's by a
+    // factor that is no power of two, its truncated E4M3 codes with it, and O by the size of the truncation noise.
     const float m_new = fmaxf(m_run, mx * sc_mul);
     // exponent = fma(s, scale, -m): lowering m by 2^-21 |m| keeps the row-max p in [1, 1 + 1e-5) in spite of
     // the rounding residue of s*scale; the common factor cancels in O = sum(p v) / sum(p).
@@ -265,6 +268,7 @@ __device__ __forceinline__ void softmax_row_group(const PrefillParams& p, uint8_
   }
   if (ok) {
     tc_fence_after();
+    if (quad == 0 && lane == 0) RK_STAMP(grp, 0, 6);
     const float inv_l = (l_run > 0.0f) ? 1.0f / l_run : 1.0f;
     const bool live = q_row < p.S_q;
     __nv_bfloat16* orow = p.o + ((size_t)bh * p.S_q + q_row) * p.d;
@@ -272,25 +276,34 @@ __device__ __forceinline__ void softmax_row_group(const PrefillParams& p, uint8_
       p.dbg[128 * 128 + 128 * 32 + 128 + row * 2 + 0] = m_run;
       p.dbg[128 * 128 + 128 * 32 + 128 + row * 2 + 1] = l_run;
     }
+    // the row's registers are free now: all of O is fetched with one wait (two halves when d > 64)
+    const int n_c32 = p.d / 32;
 #pragma unroll 1
-    for (int c32 = 0; c32 < p.d / 32; ++c32) {
-      uint32_t r[32];
-      tmem_ld32(tmem_base + lane_addr + cO + grp * 128 + c32 * 32, r);
+    for (int h = 0; h < n_c32; h += 2) {
+      uint32_t r[64];
+      tmem_ld32(tmem_base + lane_addr + cO + grp * 128 + h * 32, r);
+      if (h + 1 < n_c32) tmem_ld32(tmem_base + lane_addr + cO + grp * 128 + (h + 1) * 32, r + 32);
       tc_wait_ld();
       if (live) {
-        uint32_t packed[16];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(r[2 * i]) * inv_l, __uint_as_float(r[2 * i + 1]) * inv_l);
-          packed[i] = *reinterpret_cast<const uint32_t*>(&b2);
+        for (int c = 0; c < 2; ++c) {
+          if (h + c < n_c32) {
+            uint32_t packed[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(r[c * 32 + 2 * i]) * inv_l, __uint_as_float(r[c * 32 + 2 * i + 1]) * inv_l);
+              packed[i] = *reinterpret_cast<const uint32_t*>(&b2);
+            }
+            uint4* dst = reinterpret_cast<uint4*>(orow + (h + c) * 32);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) dst[i] = make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
+          }
         }
-        uint4* dst = reinterpret_cast<uint4*>(orow + c32 * 32);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) dst[i] = make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
       }
     }
     if (p.lse && live)
       p.lse[(size_t)bh * p.S_q + q_row] = (l_run > 0.0f) ? m_run * 0.6931471805599453f + logf(l_run) : NEG_INF;
+    if (quad == 0 && lane == 0) RK_STAMP(grp, 0, 7);
   }
   tc_fence_before();
 }
@@ -359,6 +372,7 @@ prefill2c_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (*reinterpret_cast<volatile int*>(p.status) != 0) return;   // an earlier launch gave up on a wait
+  if (threadIdx.x == 0) RK_STAMP(2, 0, 6);
   const int n_pairs = (p.n_q_tiles + 1) / 2;
   // Work order over the 1-D grid: (batch, head) pairs are taken in groups of p.head_group; inside a group the
   // heaviest (latest) query-tile pairs of all its heads come first and the lightest last, so the grid ends on
@@ -396,27 +410,63 @@ prefill2c_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   }
   const int n_all = max(nt[0], nt[1]);
 
-  if (threadIdx.x == 0) {
-    mbar_init(&bars[bQ], 1);
-    for (int i = 0; i < kStages; ++i) { mbar_init(&bars[bKF + i], 1); mbar_init(&bars[bKE + i], 1); mbar_init(&bars[bVF + i], 1); mbar_init(&bars[bVE + i], 1); }
-    for (int g = 0; g < 2; ++g) {
-      mbar_init(&bars[bSF + g], 1); mbar_init(&bars[bSE + g], 4);
-      for (int i = 0; i < 2; ++i) { mbar_init(&bars[bPF + g * 2 + i], 4); mbar_init(&bars[bPV + g * 2 + i], 1); }
-      for (int i = 0; i < 16; ++i) mbar_init(&bars[bCF + g * 16 + i], 1);
-      mbar_init(&bars[bOR + g * 2], 4); mbar_init(&bars[bOR + g * 2 + 1], 4);
+  // The TMA producer's lane sets up the barriers its first loads complete on and starts them at once (Q, and
+  // K/V of the first key tile), so that their latency runs under the rest of the set-up; the other barriers
+  // are set up one per thread.  Arrival counts: S-empty, P-full and O-ready take one arrival per warp of four.
+  auto issue_kv = [&](int j) {
+    const int st = j % kStages;
+    mbar_arrive_expect_tx(&bars[bKF + st], p.kv_tile_tx + kSfAtomBytes);
+    tma_load_3d(smem + k_off + st * kTileBytes, &tmap_k, &bars[bKF + st], 0, (j + j0) * kBlockN, bhkv);
+    bulk_load_1d(smem + sfk_off + st * kSfAtomBytes, p.k_sf + ((size_t)bhkv * p.n_kv_tiles + j + j0) * kSfAtomBytes,
+                 kSfAtomBytes, &bars[bKF + st]);
+  };
+  auto issue_v = [&](int j) {
+    const int st = j % kStages;
+    mbar_arrive_expect_tx(&bars[bVF + st], p.kv_tile_tx + kSfAtomBytes);
+    if (p.v_transposed) tma_load_3d(smem + v_off + st * kTileBytes, &tmap_v, &bars[bVF + st], (j + j0) * kBlockN, 0, bhkv);
+    else tma_load_3d(smem + v_off + st * kTileBytes, &tmap_v, &bars[bVF + st], 0, (j + j0) * kBlockN, bhkv);
+    bulk_load_1d(smem + sfv_off + st * kSfAtomBytes, p.v_sf + ((size_t)bhkv * p.n_kv_tiles + j + j0) * kSfAtomBytes,
+                 kSfAtomBytes, &bars[bVF + st]);
+  };
+  if (warp == kWarpTma) {
+    if (lane == 0) {
+      *abort_flag = 0;
+      mbar_init(&bars[bQ], 1);
+      for (int i = 0; i < kStages; ++i) { mbar_init(&bars[bKF + i], 1); mbar_init(&bars[bVF + i], 1); }
+      fence_barrier_init();
+      if (n_all > 0) {
+        prefetch_tmap(&tmap_q); prefetch_tmap(&tmap_k); prefetch_tmap(&tmap_v);
+        const int nq = (2 * qp + 1 < p.n_q_tiles) ? 2 : 1;
+        mbar_arrive_expect_tx(&bars[bQ], nq * (p.q_tile_tx + kSfAtomBytes));
+        for (int g = 0; g < nq; ++g) {
+          tma_load_3d(smem + q_off + g * kTileBytes, &tmap_q, &bars[bQ], 0, (2 * qp + g) * kBlockM, bh);
+          bulk_load_1d(smem + sfq_off + g * kSfAtomBytes, p.q_sf + ((size_t)bh * p.n_q_tiles + 2 * qp + g) * kSfAtomBytes,
+                       kSfAtomBytes, &bars[bQ]);
+        }
+        issue_kv(0);
+        issue_v(0);
+      }
     }
-    mbar_init(&bars[bDRAIN], 1); mbar_init(&bars[bDRAIN2], 1);
-    *abort_flag = 0;
-    fence_barrier_init();
+  } else {
+    const int i = (int)threadIdx.x;                  // barrier index this thread sets up (warps 0 and 1 suffice)
+    if (i > bQ && i < nBars && !(i >= bKF && i < bKF + kStages) && !(i >= bVF && i < bVF + kStages)) {
+      const bool per_warp = (i >= bSE && i < bSE + 2) || (i >= bPF && i < bPF + 4) || (i >= bOR && i < bOR + 4);
+      mbar_init(&bars[i], per_warp ? 4 : 1);
+      fence_barrier_init();
+    }
   }
-  if (warp == kWarpQk) { tmem_alloc(tmem_ptr, kTmemCols); tmem_relinquish(); }
+  if (threadIdx.x == 0) RK_STAMP_RAW(0);
+  if (warp == kWarpQk) { if (lane == 0) RK_STAMP_RAW(1); tmem_alloc(tmem_ptr, kTmemCols); tmem_relinquish(); if (lane == 0) RK_STAMP_RAW(2); }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_ptr;
+  if (threadIdx.x == 0) RK_STAMP_RAW(3);
+  if (threadIdx.x == kWarpTma * 32) RK_STAMP_RAW(4);
 
   if (warp < kWarpCorr) {
     reg_inc<kRegSoftmax>();
+    if (threadIdx.x == 0) RK_STAMP_RAW(5);
     const int grp = warp >> 2;
     const int qt = 2 * qp + grp;
     if (nt[grp] > 0) {
@@ -435,34 +485,21 @@ prefill2c_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     correction_quadrant(p, smem, bars, tmem_base, abort_flag, nt, n_all);
   } else {
     reg_dec<kRegIssue>();
+    if (threadIdx.x == kWarpQk * 32) RK_STAMP_RAW(6);
     if (warp == kWarpTma) {
       // ================= TMA producer =================
+      // Q and the first key tile are already on their way (issued before the block-wide barrier above)
       if (lane == 0 && n_all > 0) {
-        prefetch_tmap(&tmap_q); prefetch_tmap(&tmap_k); prefetch_tmap(&tmap_v);
-        const int nq = (2 * qp + 1 < p.n_q_tiles) ? 2 : 1;
-        mbar_arrive_expect_tx(&bars[bQ], nq * (p.q_tile_tx + kSfAtomBytes));
-        for (int g = 0; g < nq; ++g) {
-          tma_load_3d(smem + q_off + g * kTileBytes, &tmap_q, &bars[bQ], 0, (2 * qp + g) * kBlockM, bh);
-          bulk_load_1d(smem + sfq_off + g * kSfAtomBytes, p.q_sf + ((size_t)bh * p.n_q_tiles + 2 * qp + g) * kSfAtomBytes,
-                       kSfAtomBytes, &bars[bQ]);
-        }
         bool ok = true;
-        for (int j = 0; j < n_all && ok; ++j) {
+        for (int j = 1; j < n_all && ok; ++j) {
           const int st = j % kStages, use = j / kStages;
           perturb(p, kPerturbTma, j);
           if (use > 0) ok = mbar_wait_relaxed<kSleepNs>(&bars[bKE + st], (use - 1) & 1, abort_flag, p.status, 201);
           if (!ok) break;
-          mbar_arrive_expect_tx(&bars[bKF + st], p.kv_tile_tx + kSfAtomBytes);
-          tma_load_3d(smem + k_off + st * kTileBytes, &tmap_k, &bars[bKF + st], 0, (j + j0) * kBlockN, bhkv);
-          bulk_load_1d(smem + sfk_off + st * kSfAtomBytes, p.k_sf + ((size_t)bhkv * p.n_kv_tiles + j + j0) * kSfAtomBytes,
-                       kSfAtomBytes, &bars[bKF + st]);
+          issue_kv(j);
           if (use > 0) ok = mbar_wait_relaxed<kSleepNs>(&bars[bVE + st], (use - 1) & 1, abort_flag, p.status, 202);
           if (!ok) break;
-          mbar_arrive_expect_tx(&bars[bVF + st], p.kv_tile_tx + kSfAtomBytes);
-          if (p.v_transposed) tma_load_3d(smem + v_off + st * kTileBytes, &tmap_v, &bars[bVF + st], (j + j0) * kBlockN, 0, bhkv);
-          else tma_load_3d(smem + v_off + st * kTileBytes, &tmap_v, &bars[bVF + st], 0, (j + j0) * kBlockN, bhkv);
-          bulk_load_1d(smem + sfv_off + st * kSfAtomBytes, p.v_sf + ((size_t)bhkv * p.n_kv_tiles + j + j0) * kSfAtomBytes,
-                       kSfAtomBytes, &bars[bVF + st]);
+          issue_v(j);
         }
       }
     } else if (warp == kWarpQk) {
@@ -477,7 +514,9 @@ prefill2c_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         uint32_t idesc_kk[4];
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk) idesc_kk[kk] = idesc_with_sf(idesc_qk, kk, kk);
+        RK_STAMP_RAW(7);
         bool ok = mbar_wait(&bars[bQ], 0, abort_flag, p.status, 301);
+        RK_STAMP_RAW(8);
         if (ok) {
           tc_cp_32x128b_warpx4(tmem_base + cSfQ, dsfq);
           tc_cp_32x128b_warpx4(tmem_base + cSfQ + 4, dsfq + (kSfAtomBytes >> 4));
@@ -567,6 +606,7 @@ prefill2c_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
 
   tc_fence_before();
   __syncthreads();
+  if (threadIdx.x == 0) RK_STAMP(2, 0, 7);
   if (warp == kWarpQk) { tc_fence_after(); tmem_dealloc(tmem_base, kTmemCols); }
 }
 
