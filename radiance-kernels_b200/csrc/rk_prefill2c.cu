@@ -19,6 +19,8 @@
 // (kRegSoftmax), correction, TMA and MMA threads need few.  The S accumulator (128 TMEM columns) is shared by the
 // two tiles: a softmax group copies its rows to registers at once and hands the columns back, the Q K^T issuer
 // alternates QK_A, QK_B.  Every K/V tile brought in by TMA serves both query tiles.
+#include <type_traits>
+
 #include "rk_prefill.cuh"
 
 namespace rk {
@@ -64,7 +66,12 @@ RK_DEVINL void perturb(const PrefillParams& p, int role, int j) {
 }
 
 // ---- softmax warps: thread = query row -----------------------------------------------------------------------
-template <bool SOFTCAP>
+// The body of a key tile exists twice: PLAIN for tiles no row of which needs a mask (every tile below the causal
+// diagonal), and the general one with the mask code; the stage dump (tests) only in the DUMP instantiation of the
+// kernel.  The loop over plain tiles is what runs nearly all the time, and it is kept small and contiguous: this
+// kernel's softmax warps stall on instruction fetch, and code that sits inside the loop costs time even when it
+// is jumped over.
+template <bool SOFTCAP, bool DUMP>
 __device__ __forceinline__ void softmax_row_group(const PrefillParams& p, uint8_t* smem, uint64_t* bars, uint32_t tmem_base,
                                                   volatile int* abort_flag, int grp, int qt, int bh, int n_tiles, int j0) {
   using namespace c2;
@@ -82,21 +89,21 @@ __device__ __forceinline__ void softmax_row_group(const PrefillParams& p, uint8_
   const int q_row = qt * kBlockM + row;
   const int q_pos = p.q_pos0 + q_row;
   const float NEG_INF = __int_as_float(0xff800000);
-  const bool dump = p.dbg && qt == p.n_q_tiles - 1 && bh == 0;
+  const bool dump = DUMP && p.dbg && qt == p.n_q_tiles - 1 && bh == 0;
   const float sc_mul = SOFTCAP ? 1.0f : p.scale_log2;
 
   float m_run = NEG_INF, l_run = 0.0f;
   bool ok = true;
   bool s_ready = false;       // result of an early, non-blocking test of the next tile's S barrier
 
-  for (int j = 0; j < n_tiles && ok; ++j) {
+  auto tile = [&](const int j, auto plain_tag) -> bool {
+    constexpr bool PLAIN = decltype(plain_tag)::value;
     const int pb = j & 1;
     perturb(p, kPerturbSoftmaxA + grp, j);
     const bool stamp = (quad == 0 && lane == 0);
     if (stamp) RK_STAMP(grp, j, 0);
     if (!__all_sync(0xffffffffu, s_ready)) {         // the test issued during the previous tile said "not yet"
-      ok = __all_sync(0xffffffffu, mbar_wait(s_full, j & 1, abort_flag, p.status, 101));
-      if (!ok) break;
+      if (!__all_sync(0xffffffffu, mbar_wait(s_full, j & 1, abort_flag, p.status, 101))) return false;
     }
     tc_fence_after();
     if (stamp) RK_STAMP(grp, j, 1);
@@ -110,7 +117,7 @@ __device__ __forceinline__ void softmax_row_group(const PrefillParams& p, uint8_
     if (lane == 0) mbar_arrive(s_empty);       // hand the S columns back: the other query tile's QK^T may use them
     if (stamp) RK_STAMP(grp, j, 2);
 
-    if (dump && j == 0) {
+    if (DUMP && dump && j == 0) {
 #pragma unroll
       for (int c = 0; c < 128; ++c) p.dbg[row * 128 + c] = s[c];
     }
@@ -119,7 +126,7 @@ __device__ __forceinline__ void softmax_row_group(const PrefillParams& p, uint8_
     const int key0 = (j + j0) * kBlockN;                      // first key of this tile (j counts from the first tile inside the window)
     const bool tail = (key0 + kBlockN > p.S_kv);
     const bool diag = p.causal && (key0 + kBlockN - 1 > p.q_pos0 + qt * kBlockM);
-    const bool need_mask = tail || diag || (p.window > 0);
+    const bool need_mask = !PLAIN && (tail || diag || (p.window > 0));
     if (SOFTCAP) {
 #pragma unroll
       for (int c = 0; c < 128; ++c) {
@@ -127,7 +134,7 @@ __device__ __forceinline__ void softmax_row_group(const PrefillParams& p, uint8_
         s[c] = p.cap_log2 * fmaf(-2.0f, rcp_approx(1.0f + e), 1.0f);
       }
     }
-    if (need_mask) {
+    if (__builtin_expect(need_mask, 0)) {
       int hi = p.S_kv - 1 - key0;                             // masked iff c > hi || c <= lo
       if (p.causal) hi = min(hi, q_pos - key0);
       const int lo = (p.window > 0) ? (q_pos - p.window - key0) : -1;
@@ -220,8 +227,7 @@ __device__ __forceinline__ void softmax_row_group(const PrefillParams& p, uint8_
 #pragma unroll
     for (int c = 0; c < 32; c += 4) exp4(0, c);
     if (!__all_sync(0xffffffffu, p_free)) {
-      ok = __all_sync(0xffffffffu, mbar_wait(&pv_done[pb], ((j - 2) >> 1) & 1, abort_flag, p.status, 102));
-      if (!ok) break;
+      if (!__all_sync(0xffffffffu, mbar_wait(&pv_done[pb], ((j - 2) >> 1) & 1, abort_flag, p.status, 102))) return false;
     }
 #pragma unroll
     for (int g = 0; g < 4; ++g) {
@@ -242,7 +248,7 @@ __device__ __forceinline__ void softmax_row_group(const PrefillParams& p, uint8_
     // the row's four block scales: bytes (row%32)*16 + (row/32)*4 + 0..3 of the 512-byte scale atom
     *reinterpret_cast<uint32_t*>(smem + sfp_off + (grp * 2 + pb) * kSfAtomBytes + (row & 31) * 16 + (row >> 5) * 4) = scale_word;
 
-    if (dump && j == 0) {
+    if (DUMP && dump && j == 0) {
       uint32_t* d32 = reinterpret_cast<uint32_t*>(p.dbg + 128 * 128);
 #pragma unroll
       for (int lc = 0; lc < 8; ++lc) {
@@ -259,7 +265,24 @@ __device__ __forceinline__ void softmax_row_group(const PrefillParams& p, uint8_
     __syncwarp();
     if (lane == 0) mbar_arrive(&p_full[pb]);
     if (stamp) RK_STAMP(grp, j, 5);
+    return true;
+  };
+
+  // Tiles 0 .. n_plain-1 need no mask for any row of this query tile: no sliding window, all 128 keys inside S_kv,
+  // and the tile's last key not beyond the first row's position.  Both bounds grow with j, so the plain tiles come
+  // first; the general body decides again for every tile it gets.
+  int n_plain = 0;
+  if (p.window == 0) {
+    n_plain = min(n_tiles, p.S_kv / kBlockN - j0);
+    if (p.causal) {
+      const int t = p.q_pos0 + qt * kBlockM - (kBlockN - 1);            // plain iff (j + j0) * kBlockN <= t
+      n_plain = min(n_plain, t < 0 ? 0 : t / kBlockN + 1 - j0);
+    }
+    n_plain = max(n_plain, 0);
   }
+  int j = 0;
+  for (; j < n_plain && ok; ++j) ok = tile(j, std::true_type{});
+  for (; j < n_tiles && ok; ++j) ok = tile(j, std::false_type{});
 
   // ---- epilogue: O / l -> bf16 (finalize_O, flash_mx_impl.hpp:535-553) ----------------------------------------
   if (ok) {
@@ -272,7 +295,7 @@ __device__ __forceinline__ void softmax_row_group(const PrefillParams& p, uint8_
     const float inv_l = (l_run > 0.0f) ? 1.0f / l_run : 1.0f;
     const bool live = q_row < p.S_q;
     __nv_bfloat16* orow = p.o + ((size_t)bh * p.S_q + q_row) * p.d;
-    if (dump) {
+    if (DUMP && dump) {
       p.dbg[128 * 128 + 128 * 32 + 128 + row * 2 + 0] = m_run;
       p.dbg[128 * 128 + 128 * 32 + 128 + row * 2 + 1] = l_run;
     }
@@ -358,7 +381,7 @@ __device__ __forceinline__ void correction_quadrant(const PrefillParams& p, uint
   }
 }
 
-template <bool SOFTCAP>
+template <bool SOFTCAP, bool DUMP>
 __global__ void __launch_bounds__(c2::kThreads, 1)
 prefill2c_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                  const __grid_constant__ CUtensorMap tmap_v, const PrefillParams p, const uint32_t idesc_qk,
@@ -470,7 +493,7 @@ prefill2c_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     const int grp = warp >> 2;
     const int qt = 2 * qp + grp;
     if (nt[grp] > 0) {
-      softmax_row_group<SOFTCAP>(p, smem, bars, tmem_base, abort_flag, grp, qt, bh, nt[grp], j0);
+      softmax_row_group<SOFTCAP, DUMP>(p, smem, bars, tmem_base, abort_flag, grp, qt, bh, nt[grp], j0);
     } else if (qt < p.n_q_tiles) {
       // no visible key: O = 0 (the l <= 0 guard of finalize_O, kernels/flash_attention_mx_gemma/flash_mx_impl.hpp:554-560)
       const int q_row = qt * kBlockM + (int)(threadIdx.x & 127);
@@ -610,11 +633,11 @@ prefill2c_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   if (warp == kWarpQk) { tc_fence_after(); tmem_dealloc(tmem_base, kTmemCols); }
 }
 
-template <bool SOFTCAP>
+template <bool SOFTCAP, bool DUMP>
 static int launch2c_cfg(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const PrefillParams& p,
                         uint32_t idesc_qk, uint32_t idesc_pv, dim3 grid, cudaStream_t st) {
   const int smem_bytes = c2::total + 1024;
-  auto kern = prefill2c_kernel<SOFTCAP>;
+  auto kern = prefill2c_kernel<SOFTCAP, DUMP>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
   if (e != cudaSuccess) return (int)e;
   if (g_ev_before && g_ev_after) cudaEventRecord(g_ev_before, st);
@@ -626,8 +649,11 @@ static int launch2c_cfg(const CUtensorMap& tq, const CUtensorMap& tk, const CUte
 int launch_prefill2c(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const PrefillParams& p,
                      uint32_t idesc_qk, uint32_t idesc_pv, bool softcap, int B, cudaStream_t st) {
   dim3 grid(((p.n_q_tiles + 1) / 2) * p.H * B, 1, 1);
-  return softcap ? launch2c_cfg<true>(tq, tk, tv, p, idesc_qk, idesc_pv, grid, st)
-                 : launch2c_cfg<false>(tq, tk, tv, p, idesc_qk, idesc_pv, grid, st);
+  if (p.dbg)      // the stage dump lives in an instantiation of its own, so that the kernel that ships carries none of its code
+    return softcap ? launch2c_cfg<true, true>(tq, tk, tv, p, idesc_qk, idesc_pv, grid, st)
+                   : launch2c_cfg<false, true>(tq, tk, tv, p, idesc_qk, idesc_pv, grid, st);
+  return softcap ? launch2c_cfg<true, false>(tq, tk, tv, p, idesc_qk, idesc_pv, grid, st)
+                 : launch2c_cfg<false, false>(tq, tk, tv, p, idesc_qk, idesc_pv, grid, st);
 }
 
 }  // namespace rk
