@@ -167,6 +167,22 @@ RK_DEVINL bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_fla
   return false;
 }
 
+// The same bound in a form that costs a dozen instructions where it is inlined: SM cycles instead of the global
+// timer, and nothing recorded here.  The caller reports the failure (report_wait_failure) outside its hot loop.
+constexpr long long kWaitLimitCycles = 4000000000ll;      // about two seconds at 1.9 GHz
+RK_DEVINL bool mbar_wait_lean(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try_wait<0>(bar, parity)) return true;
+  const long long t0 = clock64();
+  do {
+    if (mbar_try_wait<0>(bar, parity)) return true;
+  } while (!*abort_flag && clock64() - t0 < kWaitLimitCycles);
+  return false;
+}
+RK_DEVINL void report_wait_failure(volatile int* abort_flag, int* status, int code) {
+  *abort_flag = 1;
+  atomicCAS(status, 0, code);
+}
+
 // Bounded wait for warps that are not on the critical path (producers, issuers, correction): between polls the
 // warp sleeps `SLEEP_NS`, so that it leaves the issue slots of its scheduler to the warps that compute.  Same
 // give-up rule as mbar_wait.

@@ -62,7 +62,7 @@ template <uint32_t N> RK_DEVINL void reg_inc() { asm volatile("setmaxnreg.inc.sy
 template <uint32_t N> RK_DEVINL void reg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
 
 RK_DEVINL void perturb(const PrefillParams& p, int role, int j) {
-  if (p.perturb == role) __nanosleep(400 + 97 * (j & 7));
+  if (__builtin_expect(p.perturb == role, 0)) __nanosleep(400 + 97 * (j & 7));
 }
 
 // ---- softmax warps: thread = query row -----------------------------------------------------------------------
@@ -95,6 +95,7 @@ __device__ __forceinline__ void softmax_row_group(const PrefillParams& p, uint8_
   float m_run = NEG_INF, l_run = 0.0f;
   bool ok = true;
   bool s_ready = false;       // result of an early, non-blocking test of the next tile's S barrier
+  int fail = 0;               // which wait gave up (reported after the loops: the tile body carries no reporting code)
 
   auto tile = [&](const int j, auto plain_tag) -> bool {
     constexpr bool PLAIN = decltype(plain_tag)::value;
@@ -102,8 +103,8 @@ __device__ __forceinline__ void softmax_row_group(const PrefillParams& p, uint8_
     perturb(p, kPerturbSoftmaxA + grp, j);
     const bool stamp = (quad == 0 && lane == 0);
     if (stamp) RK_STAMP(grp, j, 0);
-    if (!__all_sync(0xffffffffu, s_ready)) {         // the test issued during the previous tile said "not yet"
-      if (!__all_sync(0xffffffffu, mbar_wait(s_full, j & 1, abort_flag, p.status, 101))) return false;
+    if (__builtin_expect(!__all_sync(0xffffffffu, s_ready), 0)) {   // the test issued during the previous tile said "not yet"
+      if (!__all_sync(0xffffffffu, mbar_wait_lean(s_full, j & 1, abort_flag))) { fail = 101; return false; }
     }
     tc_fence_after();
     if (stamp) RK_STAMP(grp, j, 1);
@@ -226,8 +227,8 @@ __device__ __forceinline__ void softmax_row_group(const PrefillParams& p, uint8_
     };
 #pragma unroll
     for (int c = 0; c < 32; c += 4) exp4(0, c);
-    if (!__all_sync(0xffffffffu, p_free)) {
-      if (!__all_sync(0xffffffffu, mbar_wait(&pv_done[pb], ((j - 2) >> 1) & 1, abort_flag, p.status, 102))) return false;
+    if (__builtin_expect(!__all_sync(0xffffffffu, p_free), 0)) {
+      if (!__all_sync(0xffffffffu, mbar_wait_lean(&pv_done[pb], ((j - 2) >> 1) & 1, abort_flag))) { fail = 102; return false; }
     }
 #pragma unroll
     for (int g = 0; g < 4; ++g) {
@@ -283,6 +284,7 @@ __device__ __forceinline__ void softmax_row_group(const PrefillParams& p, uint8_
   int j = 0;
   for (; j < n_plain && ok; ++j) ok = tile(j, std::true_type{});
   for (; j < n_tiles && ok; ++j) ok = tile(j, std::false_type{});
+  if (!ok) report_wait_failure(abort_flag, p.status, fail);
 
   // ---- epilogue: O / l -> bf16 (finalize_O, flash_mx_impl.hpp:535-553) ----------------------------------------
   if (ok) {
@@ -534,9 +536,6 @@ prefill2c_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         const uint64_t dk = make_smem_desc(smem_u32(smem + k_off), 16, 1024, kLayoutSw128);
         const uint64_t dsfq = make_smem_desc(smem_u32(smem + sfq_off), 0, 128, kLayoutNone);
         const uint64_t dsfk = make_smem_desc(smem_u32(smem + sfk_off), 0, 128, kLayoutNone);
-        uint32_t idesc_kk[4];
-#pragma unroll
-        for (int kk = 0; kk < 4; ++kk) idesc_kk[kk] = idesc_with_sf(idesc_qk, kk, kk);
         RK_STAMP_RAW(7);
         bool ok = mbar_wait(&bars[bQ], 0, abort_flag, p.status, 301);
         RK_STAMP_RAW(8);
@@ -554,15 +553,17 @@ prefill2c_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
           tc_cp_32x128b_warpx4(tmem_base + cSfK + st * 4, dsfk + (uint32_t)(st * (kSfAtomBytes >> 4)));
           const uint64_t dkt = dk + (uint32_t)(st * (kTileBytes >> 4));
           RK_STAMP(2, j, 1);
-#pragma unroll
+          // rolled on purpose (as in the P V issuer below): this warp shares its scheduler's instruction cache with
+          // two softmax warps, and a lone thread loses nothing by a few loop instructions
+#pragma unroll 1
           for (int g = 0; g < 2; ++g) {
-            if (j >= nt[g]) continue;
+            if (j >= (g == 0 ? nt[0] : nt[1])) continue;
             if (last_g >= 0) { ok = mbar_wait(&bars[bSE + last_g], last_par, abort_flag, p.status, 305); if (!ok) break; }
             tc_fence_after();
             const uint64_t dqt = dq + (uint32_t)(g * (kTileBytes >> 4));
-#pragma unroll
+#pragma unroll 1
             for (int kk = 0; kk < 4; ++kk)
-              mma_mxf8f6f4_ss(tmem_base + cS, dqt + kk * 2, dkt + kk * 2, idesc_kk[kk], tmem_base + cSfQ + g * 4,
+              mma_mxf8f6f4_ss(tmem_base + cS, dqt + kk * 2, dkt + kk * 2, idesc_with_sf(idesc_qk, kk, kk), tmem_base + cSfQ + g * 4,
                               tmem_base + cSfK + st * 4, kk > 0 ? 1u : 0u);
             tc_commit(&bars[bSF + g]);
             last_g = g; last_par = j & 1;
@@ -586,9 +587,6 @@ prefill2c_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         const uint32_t v_kk = p.v_transposed ? 2u : (uint32_t)(4096 >> 4);
         const uint64_t dsfv = make_smem_desc(smem_u32(smem + sfv_off), 0, 128, kLayoutNone);
         const uint64_t dsfp = make_smem_desc(smem_u32(smem + sfp_off), 0, 128, kLayoutNone);
-        uint32_t idesc_kk[4];
-#pragma unroll
-        for (int kk = 0; kk < 4; ++kk) idesc_kk[kk] = idesc_with_sf(idesc_pv, kk, kk);
         bool ok = true;
         int st = 0, use_par = 0;
         for (int i = 0; i < n_all && ok; ++i) {
@@ -598,9 +596,9 @@ prefill2c_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
           if (!ok) break;
           tc_cp_32x128b_warpx4(tmem_base + cSfV + st * 4, dsfv + (uint32_t)(st * (kSfAtomBytes >> 4)));
           const uint64_t dvt = dv + (uint32_t)(st * (kTileBytes >> 4));
-#pragma unroll
+#pragma unroll 1
           for (int g = 0; g < 2; ++g) {
-            if (i >= nt[g]) continue;
+            if (i >= (g == 0 ? nt[0] : nt[1])) continue;
             const int gb = g * 2 + pb;
             ok = mbar_wait_relaxed<kSleepNs>(&bars[bPF + gb], par2, abort_flag, p.status, 304) &&
                  mbar_wait_relaxed<kSleepNs>(&bars[bOR + gb], par2, abort_flag, p.status, 307);      // P written, O rescaled for this tile
@@ -608,12 +606,10 @@ prefill2c_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             tc_fence_after();
             tc_cp_32x128b_warpx4(tmem_base + cSfP + gb * 4, dsfp + (uint32_t)(gb * (kSfAtomBytes >> 4)));
             const uint64_t dpt = dp + (uint32_t)(gb * (kTileBytes >> 4));
-            mma_mxf8f6f4_ss(tmem_base + cO + g * 128, dpt, dvt, idesc_kk[0], tmem_base + cSfP + gb * 4,
-                            tmem_base + cSfV + st * 4, i > 0 ? 1u : 0u);
-#pragma unroll
-            for (int kk = 1; kk < 4; ++kk)
-              mma_mxf8f6f4_ss(tmem_base + cO + g * 128, dpt + kk * 2, dvt + kk * v_kk, idesc_kk[kk], tmem_base + cSfP + gb * 4,
-                              tmem_base + cSfV + st * 4, 1u);
+#pragma unroll 1
+            for (int kk = 0; kk < 4; ++kk)
+              mma_mxf8f6f4_ss(tmem_base + cO + g * 128, dpt + kk * 2, dvt + kk * v_kk, idesc_with_sf(idesc_pv, kk, kk),
+                              tmem_base + cSfP + gb * 4, tmem_base + cSfV + st * 4, (i > 0 || kk > 0) ? 1u : 0u);
             tc_commit(&bars[bPV + gb]);
             RK_STAMP(2, i, 4 + g);
           }
