@@ -56,7 +56,7 @@ struct SmemLayout {
 // w >> 2 of the tile, so a thread's keys are exactly one MX block of P.  The kParts threads of a row
 // exchange their block maxima through shared memory (one bounded mbarrier per quadrant, one arrival per
 // warp); everything else is private.
-template <int DCH, int KV_STAGES, bool SOFTCAP>
+template <int DCH, int KV_STAGES, bool SOFTCAP, bool DUMP>
 __device__ __forceinline__ void softmax_rows(const PrefillParams& p, uint8_t* smem, uint64_t* bars, uint32_t tmem_base,
                                              volatile int* abort_flag, int qt, int bh, int n_tiles, int j0) {
   using L = SmemLayout<DCH, KV_STAGES>;
@@ -127,7 +127,7 @@ __device__ __forceinline__ void softmax_rows(const PrefillParams& p, uint8_t* sm
     if (lane == 0) mbar_arrive(s_empty);        // one arrival per warp: S may be overwritten once all 16 have read
     if (lane == 0 && sslot < 2) RK_STAMP(sslot, j, 2);
 
-    if (p.dbg && qt == p.n_q_tiles - 1 && bh == 0 && j == 0) {
+    if (DUMP && p.dbg && qt == p.n_q_tiles - 1 && bh == 0 && j == 0) {
 #pragma unroll
       for (int c = 0; c < 32; ++c) p.dbg[row * 128 + part * 32 + c] = s[c];
     }
@@ -230,7 +230,7 @@ __device__ __forceinline__ void softmax_rows(const PrefillParams& p, uint8_t* sm
     l_run = l_run * corr + ((ls0 + ls1) + (ls2 + ls3));
     smem[L::sfp_off + pb * kSfAtomBytes + (row & 31) * 16 + (row >> 5) * 4 + part] = (uint8_t)sc;
 
-    if (p.dbg && qt == p.n_q_tiles - 1 && bh == 0 && j == 0) {
+    if (DUMP && p.dbg && qt == p.n_q_tiles - 1 && bh == 0 && j == 0) {
       // P codes as written (un-swizzled view) and the scale bytes, after the 128x128 S dump
       uint32_t* d32 = reinterpret_cast<uint32_t*>(p.dbg + 128 * 128);
 #pragma unroll
@@ -294,7 +294,7 @@ __device__ __forceinline__ void softmax_rows(const PrefillParams& p, uint8_t* sm
     const bool live = q_row < p.S_q;
     __nv_bfloat16* orow = p.o + ((size_t)bh * p.S_q + q_row) * p.d;
     const int ncols = p.d / kParts;                 // 16, 32 or 64 output columns per thread
-    if (p.dbg && qt == p.n_q_tiles - 1 && bh == 0 && part == 0) {
+    if (DUMP && p.dbg && qt == p.n_q_tiles - 1 && bh == 0 && part == 0) {
       p.dbg[128 * 128 + 128 * 32 + 128 + row * 2 + 0] = m_run;
       p.dbg[128 * 128 + 128 * 32 + 128 + row * 2 + 1] = l_tot;
     }
@@ -323,7 +323,7 @@ __device__ __forceinline__ void softmax_rows(const PrefillParams& p, uint8_t* sm
 }
 
 // ---- the kernel ---------------------------------------------------------------------------------
-template <int DCH, int KV_STAGES, bool SOFTCAP>
+template <int DCH, int KV_STAGES, bool SOFTCAP, bool DUMP>
 __global__ void __launch_bounds__(kNumThreads, 1)
 prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                const __grid_constant__ CUtensorMap tmap_v, const PrefillParams p, const uint32_t idesc_qk,
@@ -406,7 +406,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
       }
     }
   } else if (warp < kNumSoftmaxWarps) {
-    softmax_rows<DCH, KV_STAGES, SOFTCAP>(p, smem, bars, tmem_base, abort_flag, qt, bh, n_tiles, j0);
+    softmax_rows<DCH, KV_STAGES, SOFTCAP, DUMP>(p, smem, bars, tmem_base, abort_flag, qt, bh, n_tiles, j0);
   } else if (warp == kNumSoftmaxWarps) {
     // ================= TMA producer =================
     if (lane == 0) {
@@ -586,12 +586,12 @@ int make_tmap_u6_3d(CUtensorMap* m, const void* base, int64_t BH, int64_t rows, 
   return r == CUDA_SUCCESS ? RK_OK : RK_ERR_BAD_SHAPE;
 }
 
-template <int DCH, int KV_STAGES, bool SOFTCAP>
+template <int DCH, int KV_STAGES, bool SOFTCAP, bool DUMP>
 static int launch_cfg(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const PrefillParams& p,
                       uint32_t idesc_qk, uint32_t idesc_pv, dim3 grid, cudaStream_t st) {
   using L = SmemLayout<DCH, KV_STAGES>;
   const int smem_bytes = L::total + 1024;
-  auto kern = prefill_kernel<DCH, KV_STAGES, SOFTCAP>;
+  auto kern = prefill_kernel<DCH, KV_STAGES, SOFTCAP, DUMP>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
   if (e != cudaSuccess) return (int)e;
   if (g_ev_before && g_ev_after) cudaEventRecord(g_ev_before, st);
@@ -649,8 +649,11 @@ int launch_prefill(const rk_prefill_args& a, const uint8_t* q_codes, const uint8
   dim3 grid(p.n_q_tiles * a.H * a.B, 1, 1);
   const bool cap = a.softcap > 0.0f;
   if (a.d <= 128) return launch_prefill2c(tq, tk, tv, p, idesc_qk, idesc_pv, cap, a.B, st);   // two query tiles per CTA
-  return cap ? launch_cfg<2, 2, true>(tq, tk, tv, p, idesc_qk, idesc_pv, grid, st)
-             : launch_cfg<2, 2, false>(tq, tk, tv, p, idesc_qk, idesc_pv, grid, st);
+  if (p.dbg)      // the stage dump lives in instantiations of its own: the kernels that ship carry none of its code
+    return cap ? launch_cfg<2, 2, true, true>(tq, tk, tv, p, idesc_qk, idesc_pv, grid, st)
+               : launch_cfg<2, 2, false, true>(tq, tk, tv, p, idesc_qk, idesc_pv, grid, st);
+  return cap ? launch_cfg<2, 2, true, false>(tq, tk, tv, p, idesc_qk, idesc_pv, grid, st)
+             : launch_cfg<2, 2, false, false>(tq, tk, tv, p, idesc_qk, idesc_pv, grid, st);
 }
 
 }  // namespace rk
