@@ -25,6 +25,7 @@
 // when causal); in practice the softmax/requant ALU work per S element bounds it.
 #include <cuda.h>
 #include <algorithm>
+#include <type_traits>
 #include <cuda_bf16.h>
 
 #include "rk_common.cuh"
@@ -81,12 +82,15 @@ __device__ __forceinline__ void softmax_rows(const PrefillParams& p, uint8_t* sm
   float l_run = 0.0f;      // this thread's share of the row sum
   bool ok = true;
 
-  for (int j = 0; j < n_tiles && ok; ++j) {
+  // The body of a key tile exists twice: PLAIN for tiles no row of which needs a mask, and the general one with the
+  // mask code.  The loop over plain tiles runs nearly all the time and is kept small and contiguous (the softmax
+  // warps stall on instruction fetch; code inside the loop costs time even when it is jumped over).
+  auto tile = [&](const int j, auto plain_tag) -> bool {
+    constexpr bool PLAIN = decltype(plain_tag)::value;
     const int pb = j & 1;
     const int sslot = (warp == 0) ? 0 : (warp == 15 ? 1 : 7);
     if (lane == 0 && sslot < 2) RK_STAMP(sslot, j, 0);
-    ok = __all_sync(0xffffffffu, mbar_wait(s_full, j & 1, abort_flag, p.status, 101));
-    if (!ok) break;
+    if (!__all_sync(0xffffffffu, mbar_wait(s_full, j & 1, abort_flag, p.status, 101))) return false;
     tc_fence_after();
     if (lane == 0 && sslot < 2) RK_STAMP(sslot, j, 1);
 
@@ -94,7 +98,7 @@ __device__ __forceinline__ void softmax_rows(const PrefillParams& p, uint8_t* sm
     const int key0 = (j + j0) * kBlockN;                      // first key of this tile (j counts from the first tile inside the window)
     const bool tail = (key0 + kBlockN > p.S_kv);
     const bool diag = p.causal && (key0 + kBlockN - 1 > p.q_pos0 + qt * kBlockM);
-    const bool need_mask = tail || diag || (p.window > 0);
+    const bool need_mask = !PLAIN && (tail || diag || (p.window > 0));
     int hi = p.S_kv - 1 - key0;
     if (p.causal) hi = min(hi, q_pos - key0);
     const int lo = (p.window > 0) ? (q_pos - p.window - key0) : -1;
@@ -157,8 +161,7 @@ __device__ __forceinline__ void softmax_rows(const PrefillParams& p, uint8_t* sm
       xchg[(pb * kParts + part) * 128 + row] = bmax;
       __syncwarp();
       if (lane == 0) mbar_arrive(&quadbar[quad]);
-      ok = __all_sync(0xffffffffu, mbar_wait(&quadbar[quad], j & 1, abort_flag, p.status, 104));
-      if (!ok) break;
+      if (!__all_sync(0xffffffffu, mbar_wait(&quadbar[quad], j & 1, abort_flag, p.status, 104))) return false;
 #pragma unroll
       for (int o = 1; o < kParts; ++o) mx = fmaxf(mx, xchg[(pb * kParts + ((part + o) & (kParts - 1))) * 128 + row]);
     }
@@ -193,9 +196,11 @@ __device__ __forceinline__ void softmax_rows(const PrefillParams& p, uint8_t* sm
     int sc = (int)(__float_as_uint(pmax) >> 23);
     sc = min(sc, 127);
     uint32_t w[8];
-    if (sc >= 7) {
+    {
       // y = p * 2^(7-sc) has exponent field E - se + 7 = the E4M3 exponent field and keeps the mantissa,
       // so the truncated code is y's bits [20,27); .ftz zeroes everything below 2^-6 of the block scale.
+      // ex2.approx.ftz never returns a subnormal, so this holds whatever sc is (a block whose maximum lies
+      // below 2^-120 needs no other path: its non-zero elements all lie within 2^6 of that maximum).
       const float f = __uint_as_float((uint32_t)(134 - sc) << 23);
 #pragma unroll
       for (int q = 0; q < 8; ++q) {
@@ -204,21 +209,6 @@ __device__ __forceinline__ void softmax_rows(const PrefillParams& p, uint8_t* sm
         mul2_ftz(s[q * 4 + 2], s[q * 4 + 3], f, y2, y3);
         w[q] = pack_u8x2(__float_as_uint(y1) >> 20, __float_as_uint(y0) >> 20,
                          pack_u8x2(__float_as_uint(y3) >> 20, __float_as_uint(y2) >> 20, 0u));
-      }
-    } else {
-      // block max below 2^-120 (or zero): exact integer form of the same rule
-      const int sub = (sc - 7) * 8;
-#pragma unroll
-      for (int q = 0; q < 8; ++q) {
-        uint32_t word = 0;
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const uint32_t bits = __float_as_uint(s[q * 4 + e]);
-          int t = (int)(bits >> 20) - sub;
-          t = (t >= 8 && bits >= 0x00800000u) ? t : 0;
-          word |= (uint32_t)t << (8 * e);
-        }
-        w[q] = word;
       }
     }
     {
@@ -247,8 +237,7 @@ __device__ __forceinline__ void softmax_rows(const PrefillParams& p, uint8_t* sm
     // ---- rescale this thread's share of O in TMEM once the previous PV has landed (it had the whole
     //      exp/requant phase above to finish, so this wait is normally free) ----------------------------
     if (j > 0) {
-      ok = __all_sync(0xffffffffu, mbar_wait(&pv_done[(j - 1) & 1], ((j - 1) >> 1) & 1, abort_flag, p.status, 102));
-      if (!ok) break;
+      if (!__all_sync(0xffffffffu, mbar_wait(&pv_done[(j - 1) & 1], ((j - 1) >> 1) & 1, abort_flag, p.status, 102))) return false;
       tc_fence_after();
       if (__any_sync(0xffffffffu, corr != 1.0f)) {
 #pragma unroll 1
@@ -270,7 +259,24 @@ __device__ __forceinline__ void softmax_rows(const PrefillParams& p, uint8_t* sm
     __syncwarp();
     if (lane == 0) mbar_arrive(&p_full[pb]);
     if (lane == 0 && sslot < 2) RK_STAMP(sslot, j, 6);
+    return true;
+  };
+
+  // Tiles 0 .. n_plain-1 need no mask for any row of this query tile: no sliding window, all 128 keys inside S_kv,
+  // and the tile's last key not beyond the first row's position.  Both bounds grow with j, so the plain tiles come
+  // first; the general body decides again for every tile it gets.
+  int n_plain = 0;
+  if (p.window == 0) {
+    n_plain = min(n_tiles, p.S_kv / kBlockN - j0);
+    if (p.causal) {
+      const int t = p.q_pos0 + qt * kBlockM - (kBlockN - 1);            // plain iff (j + j0) * kBlockN <= t
+      n_plain = min(n_plain, t < 0 ? 0 : t / kBlockN + 1 - j0);
+    }
+    n_plain = max(n_plain, 0);
   }
+  int j = 0;
+  for (; j < n_plain && ok; ++j) ok = tile(j, std::true_type{});
+  for (; j < n_tiles && ok; ++j) ok = tile(j, std::false_type{});
 
   // ---- epilogue: O / l -> bf16, each thread d / kParts of the columns -------------------------------
   float l_tot = l_run;
