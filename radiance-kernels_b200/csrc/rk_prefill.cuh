@@ -72,6 +72,23 @@ RK_DEVINL void unpack2u(uint64_t v, uint32_t& lo, uint32_t& hi) { asm("mov.b64 {
 RK_DEVINL uint64_t fma2p(uint64_t a, uint64_t b, uint64_t c) { uint64_t d; asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c)); return d; }
 RK_DEVINL uint64_t add2p(uint64_t a, uint64_t b) { uint64_t d; asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b)); return d; }
 RK_DEVINL uint64_t mul2p_ftz(uint64_t a, uint64_t b) { uint64_t d; asm("mul.rn.ftz.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b)); return d; }
+// Soft cap of two scores in the log2 domain: cap_log2 * tanh(s * scale / cap), tanh(y) = 1 - 2 / (1 + e^(2y)).
+// The exponential is the one special-function instruction; the reciprocal is three Newton steps on the FMA pipe from
+// an integer first guess (error 0.12 -> 1.4e-2 -> 2e-4 -> 4e-8), because the special-function unit is what bounds
+// the capped kernels (it also has the softmax exponential to do).  k2 = 2 log2(e) scale / cap; the exponent is
+// clamped so that 1 + e stays finite.
+RK_DEVINL void softcap_pair(float& s0, float& s1, float k2, uint64_t one2, uint64_t m2cap2, uint64_t cap2) {
+  const float e0 = ex2_approx(fminf(s0 * k2, 126.0f)), e1 = ex2_approx(fminf(s1 * k2, 126.0f));
+  const uint64_t z = add2p(pack2(e0, e1), one2);                       // 1 + e in [1, 2^126]
+  uint32_t z0, z1;
+  unpack2u(z, z0, z1);
+  uint64_t r = pack2(__uint_as_float(0x7EF311C7u - z0), __uint_as_float(0x7EF311C7u - z1));
+  const uint64_t nz = z ^ 0x8000000080000000ull;                       // -z
+#pragma unroll
+  for (int it = 0; it < 3; ++it) r = fma2p(r, fma2p(nz, r, one2), r);   // r += r * (1 - z r)
+  unpack2(fma2p(r, m2cap2, cap2), s0, s1);                              // cap_log2 * (1 - 2 r)
+}
+
 // two ints (0..255 each) into bytes 1:0 of the result, bytes 3:2 taken from the low half of c
 RK_DEVINL uint32_t pack_u8x2(uint32_t hi, uint32_t lo, uint32_t c) {
   uint32_t d; asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(hi), "r"(lo), "r"(c)); return d;
