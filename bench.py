@@ -667,6 +667,7 @@ def run_extras(rk, L, dev, peaks, peak_burst, timed, kernel_ms, qc, qs, vc, vs):
     prefill_case("prefill_gqa_B4_H32_kv8_S8192_d128", 4, 32, 8, 8192, 128)
     prefill_case("prefill_gemma_B2_H16_kv8_S8192_d256_cap50", 2, 16, 8, 8192, 256, mul=0.5, softcap=50.0)
     prefill_case("prefill_gemma_mxfp6_e2m3q_e3m2kv", 2, 16, 8, 8192, 256, mul=0.5, softcap=50.0, q_fmt=rk.E2M3, kv_fmt=rk.E3M2)
+    prefill_case("prefill_gqa_mxfp4_e2m1_B4_H32_kv8_S8192_d128", 4, 32, 8, 8192, 128, mul=0.5, q_fmt=rk.E2M1, kv_fmt=rk.E2M1)
 
     # quantizer: fp32 and bf16 input, 67 M elements (one tensor of the headline workload)
     x = torch.randn(8 * 16 * 4096, 128, device=dev)

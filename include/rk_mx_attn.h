@@ -51,7 +51,8 @@ extern "C" {
 
 /* Element formats (codes as in OCP MX; E4M3 and E3M2 decode exactly as
  * lib/golden/mx_fp_math.h:227-236,256-264). */
-enum { RK_FMT_E4M3 = 0, RK_FMT_E5M2 = 1, RK_FMT_E2M3 = 2, RK_FMT_E3M2 = 3 };
+enum { RK_FMT_E4M3 = 0, RK_FMT_E5M2 = 1, RK_FMT_E2M3 = 2, RK_FMT_E3M2 = 3,
+       RK_FMT_E2M1 = 4 /* FP4: lib/golden/mx_fp_math.h:238-246 (fp4_e2m1_decode), kernels/flash_attention_mx_gqa/fp6_attn_relerr.py:31-36 */ };
 
 /* Where V's block-32 scales run.
  * KEYS: scales [B][H_kv][ceil(S_kv/32)][d], the reference's own V layout
@@ -151,7 +152,7 @@ typedef struct rk_prefill_args {
   int32_t window;          /* >0: also mask key_pos <= q_pos - window (FA_WINDOW); 0 = off */
   float softcap;           /* >0: s <- cap*tanh(s/cap) after the softmax scale, before mask/max; 0 = off */
   float softmax_scale;     /* FA_SOFTMAX_SCALE; 0 selects 1/sqrt(d) */
-  int32_t q_fmt, kv_fmt;   /* RK_FMT_*; 6-bit codes (E2M3 / E3M2) come one per byte and are packed into the
+  int32_t q_fmt, kv_fmt;   /* RK_FMT_*; 6-bit (E2M3 / E3M2) and 4-bit (E2M1) codes come one per byte and are packed into the
                               workspace for the tensor core; P is always E4M3 as in the reference */
   int32_t v_scale_axis;    /* RK_V_SCALES_ALONG_KEYS | RK_V_SCALES_ALONG_D */
   int32_t block_n;         /* keys per online-softmax step; 0 = default.  On return from

@@ -13,7 +13,7 @@ import numpy as np
 _HERE = pathlib.Path(__file__).resolve().parent
 _LIB = None
 
-E4M3, E5M2, E2M3, E3M2 = 0, 1, 2, 3
+E4M3, E5M2, E2M3, E3M2, E2M1 = 0, 1, 2, 3, 4
 
 
 def reference_dir():
@@ -122,6 +122,11 @@ def ref_codec():
     R.ref_fp6_e3m2_decode.argtypes = [C.c_uint8]
     R.ref_f32_to_bf16_rne.restype = C.c_uint16
     R.ref_f32_to_bf16_rne.argtypes = [C.c_float]
+    if hasattr(R, "ref_fp4_e2m1_decode"):            # shims built before the FP4 format was added lack these two
+        R.ref_fp4_e2m1_decode.restype = C.c_float
+        R.ref_fp4_e2m1_decode.argtypes = [C.c_uint8]
+        R.ref_bf16_bits_to_fp4_e2m1_code.restype = C.c_uint8
+        R.ref_bf16_bits_to_fp4_e2m1_code.argtypes = [C.c_uint16]
     return R
 
 

@@ -47,17 +47,19 @@ inline float bits_f32(uint32_t u) { float f; std::memcpy(&f, &u, 4); return f; }
 // ---------------------------------------------------------------------------
 // Element formats.  ebits/mbits/bias and the largest finite magnitude
 // (1 + max_mant/2^mbits) * 2^emax.  E4M3 follows lib/golden/mx_fp_math.h:205-236
-// (no inf, top code 0x7E = 448).  E5M2 / E2M3 / E3M2 generalise the same
-// encoder; E3M2 decode follows lib/golden/mx_fp_math.h:256-264.
+// (no inf, top code 0x7E = 448).  E5M2 / E2M3 / E3M2 / E2M1 generalise the same
+// encoder; E3M2 decode follows lib/golden/mx_fp_math.h:256-264, E2M1 (FP4)
+// decode lib/golden/mx_fp_math.h:238-246.
 // ---------------------------------------------------------------------------
 struct Fmt { int ebits, mbits, bias, emax_unb, max_mant; uint32_t scale_thresh; };
 // scale_thresh: mantissa threshold of block_exp (lib/golden/golden.py:161-165),
 // i.e. the fp32 mantissa of the format's largest finite value.
-const Fmt kFmt[4] = {
+const Fmt kFmt[5] = {
     /*E4M3*/ {4, 3, 7, 8, 6, 0x600000u},    // 448   = 1.75  * 2^8
     /*E5M2*/ {5, 2, 15, 15, 3, 0x600000u},  // 57344 = 1.75  * 2^15
     /*E2M3*/ {2, 3, 1, 2, 7, 0x700000u},    // 7.5   = 1.875 * 2^2
     /*E3M2*/ {3, 2, 3, 4, 3, 0x600000u},    // 28    = 1.75  * 2^4
+    /*E2M1*/ {2, 1, 1, 2, 1, 0x400000u},    // 6     = 1.5   * 2^2
 };
 
 inline float fmt_max(const Fmt& f) {

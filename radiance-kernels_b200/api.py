@@ -12,7 +12,7 @@ import torch
 
 from ._lib import DecodeArgs, PrefillArgs, check, lib
 
-E4M3, E5M2, E2M3, E3M2 = 0, 1, 2, 3
+E4M3, E5M2, E2M3, E3M2, E2M1 = 0, 1, 2, 3, 4
 V_SCALES_ALONG_KEYS, V_SCALES_ALONG_D = 0, 1
 SCALES_ROWMAJOR, SCALES_GROUPMAJOR, SCALES_SF_ATOMS = 0, 1, 2
 

@@ -45,6 +45,9 @@ int* device_status_word() { return dev_state().status; }
 extern float* g_prefill_dbg;
 cudaEvent_t g_ev_before = nullptr, g_ev_after = nullptr;
 
+// bits of an element code in the packed form the tensor core reads: 8, 6 (E2M3, E3M2) or 4 (E2M1)
+static int fmt_bits(int fmt) { return fmt == RK_FMT_E2M1 ? 4 : fmt >= RK_FMT_E2M3 ? 6 : 8; }
+
 struct PrefillWs { size_t q_sf, k_sf, v_sf, v_codes, q6, k6, v6t, total; };
 
 static PrefillWs prefill_ws(const rk_prefill_args& a) {
@@ -56,7 +59,8 @@ static PrefillWs prefill_ws(const rk_prefill_args& a) {
   w.v_sf = off; off = align_up(off + (size_t)a.B * a.H_kv * nkt * dch * 512, 1024);
   w.v_codes = off;
   if (a.v_scale_axis == RK_V_SCALES_ALONG_D) off = align_up(off + (size_t)a.B * a.H_kv * a.S_kv * a.d, 1024);
-  // 6-bit operands: densely packed copies (Q, K along d; V transposed, along the keys), rows padded to 128 codes
+  // 6-bit and 4-bit operands: densely packed copies (Q, K along d; V transposed, along the keys), rows padded to
+  // 128 codes; sized for 6 bits, which also holds 4
   const size_t dp = dch * 128, skp = nkt * 128;
   w.q6 = off;
   if (a.q_fmt >= RK_FMT_E2M3) off = align_up(off + (size_t)a.B * a.H * a.S_q * dp * 3 / 4, 1024);
@@ -75,7 +79,7 @@ static int check_prefill_shape(const rk_prefill_args* a) {
   if (a->H % a->H_kv != 0) return RK_ERR_BAD_SHAPE;
   if (a->window < 0 || a->softcap < 0.0f || a->softmax_scale < 0.0f) return RK_ERR_BAD_SHAPE;
   if (a->v_scale_axis != RK_V_SCALES_ALONG_KEYS && a->v_scale_axis != RK_V_SCALES_ALONG_D) return RK_ERR_BAD_FORMAT;
-  if (a->q_fmt < 0 || a->q_fmt > 3 || a->kv_fmt < 0 || a->kv_fmt > 3) return RK_ERR_BAD_FORMAT;
+  if (a->q_fmt < 0 || a->q_fmt > RK_FMT_E2M1 || a->kv_fmt < 0 || a->kv_fmt > RK_FMT_E2M1) return RK_ERR_BAD_FORMAT;
   if (a->block_n != 0 && a->block_n != 128) return RK_ERR_UNSUPPORTED;
   if (a->q_scale_layout < 0 || a->q_scale_layout > RK_SCALES_SF_ATOMS || a->k_scale_layout < 0 ||
       a->k_scale_layout > RK_SCALES_SF_ATOMS)
@@ -113,7 +117,7 @@ int rk_version(void) { return 200; }
 int rk_mx_quantize(const float* x, int64_t rows, int64_t cols, int fmt, uint8_t* codes, uint8_t* scales, void* stream) {
   if (!x || !codes || !scales) return RK_ERR_NULL_POINTER;
   if (rows < 0 || cols < 0 || cols % 32 != 0) return RK_ERR_BAD_SHAPE;
-  if (fmt < 0 || fmt > 3) return RK_ERR_BAD_FORMAT;
+  if (fmt < 0 || fmt > RK_FMT_E2M1) return RK_ERR_BAD_FORMAT;
   if (!aligned(x, 16) || !aligned(codes, 8)) return RK_ERR_MISALIGNED;
   return launch_quantize_rows(x, rows, cols, fmt, codes, scales, (cudaStream_t)stream);
 }
@@ -121,7 +125,7 @@ int rk_mx_quantize(const float* x, int64_t rows, int64_t cols, int fmt, uint8_t*
 int rk_mx_quantize_bf16(const void* x, int64_t rows, int64_t cols, int fmt, uint8_t* codes, uint8_t* scales, void* stream) {
   if (!x || !codes || !scales) return RK_ERR_NULL_POINTER;
   if (rows < 0 || cols < 0 || cols % 32 != 0) return RK_ERR_BAD_SHAPE;
-  if (fmt < 0 || fmt > 3) return RK_ERR_BAD_FORMAT;
+  if (fmt < 0 || fmt > RK_FMT_E2M1) return RK_ERR_BAD_FORMAT;
   if (!aligned(x, 16) || !aligned(codes, 8)) return RK_ERR_MISALIGNED;
   return launch_quantize_rows_bf16(x, rows, cols, fmt, codes, scales, (cudaStream_t)stream);
 }
@@ -130,7 +134,7 @@ int rk_mx_quantize_keys(const float* x, int64_t batch, int64_t rows, int64_t col
                         uint8_t* scales, void* stream) {
   if (!x || !codes || !scales) return RK_ERR_NULL_POINTER;
   if (batch < 0 || rows < 0 || cols < 0 || cols % 4 != 0) return RK_ERR_BAD_SHAPE;
-  if (fmt < 0 || fmt > 3) return RK_ERR_BAD_FORMAT;
+  if (fmt < 0 || fmt > RK_FMT_E2M1) return RK_ERR_BAD_FORMAT;
   if (!aligned(x, 16) || !aligned(codes, 4) || !aligned(scales, 4)) return RK_ERR_MISALIGNED;
   return launch_quantize_keys(x, batch, rows, cols, fmt, codes, scales, (cudaStream_t)stream);
 }
@@ -139,7 +143,7 @@ int rk_mx_quantize_ex(const void* x, int x_is_bf16, int64_t batch, int64_t S, in
                       uint8_t* scales, int scale_layout, void* stream) {
   if (!x || !codes || !scales) return RK_ERR_NULL_POINTER;
   if (batch < 0 || S < 0 || d < 0 || d % 32 != 0) return RK_ERR_BAD_SHAPE;
-  if (fmt < 0 || fmt > 3) return RK_ERR_BAD_FORMAT;
+  if (fmt < 0 || fmt > RK_FMT_E2M1) return RK_ERR_BAD_FORMAT;
   if (scale_layout < 0 || scale_layout > RK_SCALES_SF_ATOMS) return RK_ERR_BAD_FORMAT;
   if (!aligned(x, 16) || !aligned(codes, 8)) return RK_ERR_MISALIGNED;
   cudaStream_t st = (cudaStream_t)stream;
@@ -160,7 +164,7 @@ int rk_mx_quantize_keys_ex(const float* x, int64_t batch, int64_t rows, int64_t 
   if (scale_layout != RK_SCALES_SF_ATOMS) return RK_ERR_BAD_FORMAT;
   if (!x || !codes || !scales) return RK_ERR_NULL_POINTER;
   if (batch < 0 || rows < 0 || cols < 0 || cols % 4 != 0) return RK_ERR_BAD_SHAPE;
-  if (fmt < 0 || fmt > 3) return RK_ERR_BAD_FORMAT;
+  if (fmt < 0 || fmt > RK_FMT_E2M1) return RK_ERR_BAD_FORMAT;
   if (!aligned(x, 16) || !aligned(codes, 4) || !aligned(scales, 16)) return RK_ERR_MISALIGNED;
   cudaStream_t st = (cudaStream_t)stream;
   if (rows % 128 != 0 || cols % 128 != 0) {
@@ -182,7 +186,7 @@ int rk_mx_rebase_v(const uint8_t* codes, const uint8_t* scales, int64_t batch, i
                    uint8_t* out_codes, uint8_t* out_scales, void* stream) {
   if (!codes || !scales || !out_codes || !out_scales) return RK_ERR_NULL_POINTER;
   if (batch < 0 || S < 0 || d <= 0 || d % 32 != 0) return RK_ERR_BAD_SHAPE;
-  if (fmt < 0 || fmt > 3) return RK_ERR_BAD_FORMAT;
+  if (fmt < 0 || fmt > RK_FMT_E2M1) return RK_ERR_BAD_FORMAT;
   if (!aligned(codes, 4) || !aligned(out_codes, 4) || !aligned(out_scales, 4)) return RK_ERR_MISALIGNED;
   return launch_rebase_v(codes, scales, batch, S, d, fmt, out_codes, out_scales, false, (cudaStream_t)stream);
 }
@@ -242,13 +246,13 @@ int rk_attn_prefill(const rk_prefill_args* a, void* stream) {
   const uint8_t* q_codes = a->q;
   const uint8_t* k_codes = a->k;
   if (a->q_fmt >= RK_FMT_E2M3) {
-    if ((rc = launch_pack6_rows(a->q, bhq * a->S_q, a->d, ws + w.q6, st)) != RK_OK) return rc;
+    if ((rc = launch_pack_rows(a->q, bhq * a->S_q, a->d, fmt_bits(a->q_fmt), ws + w.q6, st)) != RK_OK) return rc;
     q_codes = ws + w.q6;
   }
   if (a->kv_fmt >= RK_FMT_E2M3) {
-    if ((rc = launch_pack6_rows(a->k, bhkv * a->S_kv, a->d, ws + w.k6, st)) != RK_OK) return rc;
+    if ((rc = launch_pack_rows(a->k, bhkv * a->S_kv, a->d, fmt_bits(a->kv_fmt), ws + w.k6, st)) != RK_OK) return rc;
     k_codes = ws + w.k6;
-    if ((rc = launch_pack6_transpose(v_codes, bhkv, a->S_kv, a->d, ws + w.v6t, st)) != RK_OK) return rc;
+    if ((rc = launch_pack_transpose(v_codes, bhkv, a->S_kv, a->d, fmt_bits(a->kv_fmt), ws + w.v6t, st)) != RK_OK) return rc;
     v_codes = ws + w.v6t;
   }
   return launch_prefill(*a, q_codes, k_codes, v_codes, q_sf, k_sf, v_sf, st);
@@ -407,7 +411,7 @@ int rk_rope_mx_quantize(const float* x, int64_t rows, int32_t d, const int32_t* 
   if (!x || !cos_half || !sin_half || !codes || !scales) return RK_ERR_NULL_POINTER;
   if (rows < 0 || d <= 0 || d % 64 != 0 || n_pos <= 0) return RK_ERR_BAD_SHAPE;      // both halves are whole blocks
   if (!pos && (seq_len <= 0 || pos0 < 0 || (int64_t)pos0 + seq_len > n_pos)) return RK_ERR_BAD_SHAPE;
-  if (fmt < 0 || fmt > 3) return RK_ERR_BAD_FORMAT;
+  if (fmt < 0 || fmt > RK_FMT_E2M1) return RK_ERR_BAD_FORMAT;
   if (!aligned(x, 16) || !aligned(cos_half, 16) || !aligned(sin_half, 16) || !aligned(codes, 8)) return RK_ERR_MISALIGNED;
   return launch_rope_quantize_rows(x, rows, d, pos, seq_len, pos0, cos_half, sin_half, fmt, codes, scales, (cudaStream_t)stream);
 }
@@ -416,7 +420,7 @@ int rk_rmsnorm_mx_quantize(const void* x, int x_is_bf16, int64_t rows, int32_t K
                            int32_t unit_scale, uint8_t* codes, uint8_t* scales, void* stream) {
   if (!x || !gamma || !codes || !scales) return RK_ERR_NULL_POINTER;
   if (rows < 0 || K <= 0 || K % 32 != 0 || !(eps >= 0.0f)) return RK_ERR_BAD_SHAPE;
-  if (fmt < 0 || fmt > 3) return RK_ERR_BAD_FORMAT;
+  if (fmt < 0 || fmt > RK_FMT_E2M1) return RK_ERR_BAD_FORMAT;
   if (!aligned(x, 4) || !aligned(gamma, 4) || !aligned(codes, 16)) return RK_ERR_MISALIGNED;
   return launch_rmsnorm_quantize(x, x_is_bf16 != 0, rows, K, gamma, eps, fmt, unit_scale != 0, codes, scales, (cudaStream_t)stream);
 }
@@ -434,7 +438,7 @@ int rk_kv_cache_append(const float* k_new, const float* v_new, int32_t B, int32_
                        uint8_t* v_scales, void* stream) {
   if (!k_new || !v_new || !pos || !k_codes || !k_scales || !v_codes || !v_scales) return RK_ERR_NULL_POINTER;
   if (B < 0 || H_kv < 0 || L <= 0 || d <= 0 || d % 32 != 0) return RK_ERR_BAD_SHAPE;
-  if (fmt < 0 || fmt > 3) return RK_ERR_BAD_FORMAT;
+  if (fmt < 0 || fmt > RK_FMT_E2M1) return RK_ERR_BAD_FORMAT;
   if (!aligned(k_new, 16) || !aligned(v_new, 16) || !aligned(k_codes, 8) || !aligned(v_codes, 8)) return RK_ERR_MISALIGNED;
   return launch_kv_append(k_new, v_new, B, H_kv, L, d, pos, fmt, k_codes, k_scales, v_codes, v_scales, (cudaStream_t)stream);
 }

@@ -19,6 +19,8 @@ template <> struct FmtT<0> { static constexpr int ebits = 4, mbits = 3, bias = 7
 template <> struct FmtT<1> { static constexpr int ebits = 5, mbits = 2, bias = 15, emax = 15, max_mant = 3; static constexpr uint32_t thresh = 0x600000u; };
 template <> struct FmtT<2> { static constexpr int ebits = 2, mbits = 3, bias = 1,  emax = 2,  max_mant = 7; static constexpr uint32_t thresh = 0x700000u; };
 template <> struct FmtT<3> { static constexpr int ebits = 3, mbits = 2, bias = 3,  emax = 4,  max_mant = 3; static constexpr uint32_t thresh = 0x600000u; };
+// E2M1 (FP4; lib/golden/mx_fp_math.h:238-246 fp4_e2m1_decode): 0, 0.5, 1, 1.5, 2, 3, 4, 6
+template <> struct FmtT<4> { static constexpr int ebits = 2, mbits = 1, bias = 1,  emax = 2,  max_mant = 1; static constexpr uint32_t thresh = 0x400000u; };
 
 template <int FMT> RK_DEVINL float fmt_max() {
   using F = FmtT<FMT>;
@@ -310,8 +312,8 @@ constexpr uint32_t kLayoutNone = 0, kLayoutSw128 = 2;
 // Instruction descriptor of kind::mxf8f6f4.block_scale (dense):
 //  [4,6) B scale id  [7,10) A format  [10,13) B format  [15] A MN-major  [16] B MN-major
 //  [17,23) N>>3  [23] scale format (1 = E8M0)  [24,29) M>>4  [29,31) A scale id
-// Hardware element-format ids: E4M3 0, E5M2 1, E2M3 3, E3M2 4.
-__host__ __device__ inline constexpr uint32_t hw_fmt_id(int fmt) { return fmt == 0 ? 0u : fmt == 1 ? 1u : fmt == 2 ? 3u : 4u; }
+// Hardware element-format ids: E4M3 0, E5M2 1, E2M3 3, E3M2 4, E2M1 5.
+__host__ __device__ inline constexpr uint32_t hw_fmt_id(int fmt) { return fmt == 0 ? 0u : fmt == 1 ? 1u : fmt == 2 ? 3u : fmt == 3 ? 4u : 5u; }
 __host__ __device__ inline constexpr uint32_t make_idesc(int a_fmt, int b_fmt, bool a_mn, bool b_mn, int M, int N) {
   return (hw_fmt_id(a_fmt) << 7) | (hw_fmt_id(b_fmt) << 10) | ((a_mn ? 1u : 0u) << 15) | ((b_mn ? 1u : 0u) << 16) |
          ((uint32_t)(N >> 3) << 17) | (1u << 23) | ((uint32_t)(M >> 4) << 24);

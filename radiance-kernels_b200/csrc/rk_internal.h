@@ -18,8 +18,8 @@ int launch_quantize_keys(const float* x, int64_t batch, int64_t rows, int64_t co
 int launch_rebase_v(const uint8_t* codes, const uint8_t* scales, int64_t batch, int64_t S, int64_t d, int fmt,
                     uint8_t* out_codes, uint8_t* out_scales, bool tiled, cudaStream_t st);
 int launch_retile_rowscales(const uint8_t* in, int64_t batch, int64_t S, int64_t d, uint8_t* out, cudaStream_t st);
-int launch_pack6_rows(const uint8_t* in, int64_t rows, int64_t d, uint8_t* out, cudaStream_t st);
-int launch_pack6_transpose(const uint8_t* in, int64_t batch, int64_t S, int64_t d, uint8_t* out, cudaStream_t st);
+int launch_pack_rows(const uint8_t* in, int64_t rows, int64_t d, int bits, uint8_t* out, cudaStream_t st);
+int launch_pack_transpose(const uint8_t* in, int64_t batch, int64_t S, int64_t d, int bits, uint8_t* out, cudaStream_t st);
 int launch_verify_encoder(int fmt, unsigned long long* mismatches, uint32_t* first_bad, cudaStream_t st);
 int launch_quantize_rows_ex(const void* x, bool bf16, int64_t batch, int64_t S, int64_t d, int fmt, uint8_t* codes,
                             uint8_t* scales, int layout, cudaStream_t st);
@@ -35,7 +35,7 @@ int launch_import_kt_blocks(const uint8_t* kt, const uint8_t* kts, int64_t heads
 int launch_retile_keyscales(const uint8_t* in, int64_t batch, int64_t S, int64_t d, uint8_t* out, cudaStream_t st);
 
 // q/k/v_codes: byte codes as the caller gave them, or -- for 6-bit formats -- the packed copies made by
-// launch_pack6_rows (Q, K) and launch_pack6_transpose (V, stored [d][keys]).
+// launch_pack_rows (Q, K) and launch_pack_transpose (V, stored [d][keys]).
 int launch_prefill(const rk_prefill_args& a, const uint8_t* q_codes, const uint8_t* k_codes, const uint8_t* v_codes,
                    const uint8_t* q_sf, const uint8_t* k_sf, const uint8_t* v_sf, cudaStream_t st);
 

@@ -577,15 +577,16 @@ int make_tmap_u8_3d(CUtensorMap* m, const void* base, int64_t BH, int64_t S, int
 
 // Packed 6-bit tensor [BH][rows][cols_padded codes], cols_padded a multiple of 128; a box is 128 codes x 128 rows
 // and lands in shared memory as 128 bytes per row (16 codes in 12 bytes + 4 bytes of padding, 128-byte swizzle).
-int make_tmap_u6_3d(CUtensorMap* m, const void* base, int64_t BH, int64_t rows, int64_t cols_padded) {
+// bits = 4: the same with 16 codes in 8 bytes + 8 bytes of padding (16U4_ALIGN16B).
+int make_tmap_sub8_3d(CUtensorMap* m, const void* base, int64_t BH, int64_t rows, int64_t cols_padded, int bits) {
   EncodeTiledFn enc = encode_fn();
   if (!enc) return RK_ERR_NO_DEVICE;
-  const cuuint64_t row_bytes = (cuuint64_t)cols_padded * 3 / 4;
+  const cuuint64_t row_bytes = (cuuint64_t)cols_padded * bits / 8;
   cuuint64_t dims[3] = {(cuuint64_t)cols_padded, (cuuint64_t)rows, (cuuint64_t)BH};
   cuuint64_t strides[2] = {row_bytes, row_bytes * (cuuint64_t)rows};
   cuuint32_t box[3] = {128, 128, 1};
   cuuint32_t estr[3] = {1, 1, 1};
-  CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_16U6_ALIGN16B, 3, const_cast<void*>(base), dims, strides, box, estr,
+  CUresult r = enc(m, bits == 4 ? CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B : CU_TENSOR_MAP_DATA_TYPE_16U6_ALIGN16B, 3, const_cast<void*>(base), dims, strides, box, estr,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? RK_OK : RK_ERR_BAD_SHAPE;
@@ -612,13 +613,14 @@ int launch_prefill(const rk_prefill_args& a, const uint8_t* q_codes, const uint8
                    const uint8_t* q_sf, const uint8_t* k_sf, const uint8_t* v_sf, cudaStream_t st) {
   CUtensorMap tq, tk, tv;
   int rc;
-  const bool q6 = a.q_fmt >= RK_FMT_E2M3, kv6 = a.kv_fmt >= RK_FMT_E2M3;
+  const bool q6 = a.q_fmt >= RK_FMT_E2M3, kv6 = a.kv_fmt >= RK_FMT_E2M3;                  // packed sub-byte operands
+  const int qbits = a.q_fmt == RK_FMT_E2M1 ? 4 : 6, kvbits = a.kv_fmt == RK_FMT_E2M1 ? 4 : 6;
   const int64_t dp = (a.d + 127) / 128 * 128, skp = ((int64_t)a.S_kv + 127) / 128 * 128;
-  rc = q6 ? make_tmap_u6_3d(&tq, q_codes, (int64_t)a.B * a.H, a.S_q, dp) : make_tmap_u8_3d(&tq, q_codes, (int64_t)a.B * a.H, a.S_q, a.d);
+  rc = q6 ? make_tmap_sub8_3d(&tq, q_codes, (int64_t)a.B * a.H, a.S_q, dp, qbits) : make_tmap_u8_3d(&tq, q_codes, (int64_t)a.B * a.H, a.S_q, a.d);
   if (rc != RK_OK) return rc;
-  rc = kv6 ? make_tmap_u6_3d(&tk, k_codes, (int64_t)a.B * a.H_kv, a.S_kv, dp) : make_tmap_u8_3d(&tk, k_codes, (int64_t)a.B * a.H_kv, a.S_kv, a.d);
+  rc = kv6 ? make_tmap_sub8_3d(&tk, k_codes, (int64_t)a.B * a.H_kv, a.S_kv, dp, kvbits) : make_tmap_u8_3d(&tk, k_codes, (int64_t)a.B * a.H_kv, a.S_kv, a.d);
   if (rc != RK_OK) return rc;
-  rc = kv6 ? make_tmap_u6_3d(&tv, v_codes, (int64_t)a.B * a.H_kv, a.d, skp) : make_tmap_u8_3d(&tv, v_codes, (int64_t)a.B * a.H_kv, a.S_kv, a.d);
+  rc = kv6 ? make_tmap_sub8_3d(&tv, v_codes, (int64_t)a.B * a.H_kv, a.d, skp, kvbits) : make_tmap_u8_3d(&tv, v_codes, (int64_t)a.B * a.H_kv, a.S_kv, a.d);
   if (rc != RK_OK) return rc;
 
   PrefillParams p;
@@ -642,8 +644,8 @@ int launch_prefill(const rk_prefill_args& a, const uint8_t* q_codes, const uint8
   p.q_pos0 = a.q_pos0; p.causal = a.causal; p.window = a.window;
   p.v_transposed = kv6 ? 1 : 0;
   p.perturb = g_prefill_perturb;
-  p.q_tile_tx = q6 ? kTileBytes * 3 / 4 : kTileBytes;
-  p.kv_tile_tx = kv6 ? kTileBytes * 3 / 4 : kTileBytes;
+  p.q_tile_tx = q6 ? kTileBytes * qbits / 8 : kTileBytes;
+  p.kv_tile_tx = kv6 ? kTileBytes * kvbits / 8 : kTileBytes;
   const float scale = a.softmax_scale > 0.0f ? a.softmax_scale : 1.0f / sqrtf((float)a.d);
   p.scale_log2 = scale * 1.4426950408889634f;
   p.cap_log2 = a.softcap * 1.4426950408889634f;

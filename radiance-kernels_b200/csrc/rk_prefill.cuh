@@ -37,7 +37,7 @@ struct PrefillParams {
   int n_q_tiles, n_kv_tiles;
   int head_group;      // (batch, head) pairs per work-order group: the heaviest query tiles of a whole group run first
   int q_pos0, causal, window;
-  int q_tile_tx, kv_tile_tx;   // bytes one Q / K / V tile load adds to its mbarrier: 16384, or 12288 for 6-bit tensors
+  int q_tile_tx, kv_tile_tx;   // bytes one Q / K / V tile load adds to its mbarrier: 16384, 12288 for 6-bit, 8192 for 4-bit tensors
                                // (the transaction counts the packed source bytes, not the padded shared-memory image)
   int v_transposed;    // V tiles are [d][keys] (K-major B operand; 6-bit V) instead of [keys][d]
   int perturb;         // test hook: warp role that sleeps a little at every key tile (0 = none)
@@ -112,7 +112,7 @@ RK_DEVINL uint32_t pack_u8x2(uint32_t hi, uint32_t lo, uint32_t c) {
 
 
 int make_tmap_u8_3d(CUtensorMap* m, const void* base, int64_t BH, int64_t S, int64_t d);
-int make_tmap_u6_3d(CUtensorMap* m, const void* base, int64_t BH, int64_t rows, int64_t cols_padded);
+int make_tmap_sub8_3d(CUtensorMap* m, const void* base, int64_t BH, int64_t rows, int64_t cols_padded, int bits);
 extern float* g_prefill_dbg;
 
 // Two query tiles per CTA, one thread per row, correction warps (d <= 128); defined in rk_prefill2c.cu.

@@ -36,6 +36,8 @@ template <int FMT> RK_DEVINL uint32_t hw_encode4(float a, float b, float c, floa
   else if (FMT == 1)
     asm("{\n\t.reg .b16 lo, hi;\n\tcvt.rn.satfinite.e5m2x2.f32 lo, %2, %1;\n\tcvt.rn.satfinite.e5m2x2.f32 hi, %4, %3;\n\tmov.b32 %0, {lo, hi};\n\t}"
         : "=r"(r) : "f"(a), "f"(b), "f"(c), "f"(d));
+  else if (FMT == 4)      // 4-bit codes cross the interfaces one per byte: the integer encoder serves them
+    r = encode_rne<4>(a) | (encode_rne<4>(b) << 8) | (encode_rne<4>(c) << 16) | (encode_rne<4>(d) << 24);
   else if (FMT == 2)
     asm("{\n\t.reg .b16 lo, hi;\n\tcvt.rn.satfinite.e2m3x2.f32 lo, %2, %1;\n\tcvt.rn.satfinite.e2m3x2.f32 hi, %4, %3;\n\tmov.b32 %0, {lo, hi};\n\t}"
         : "=r"(r) : "f"(a), "f"(b), "f"(c), "f"(d));
@@ -722,11 +724,16 @@ __global__ void __launch_bounds__(256) import_kt_blocks_kernel(const uint8_t* __
   }
 }
 
-// ---- 6-bit operands ---------------------------------------------------------------------------------
-// The tensor core reads 6-bit elements from shared memory as 16 codes in 12 bytes + 4 bytes of padding;
-// TMA (data type 16U6_ALIGN16B) produces that from a densely packed global tensor whose rows hold a multiple
-// of 128 codes: code i of a row sits at bits [6i, 6i+6) of the row's little-endian bit stream.
-RK_DEVINL void pack16x6(const uint32_t (&c)[16], uint32_t (&w)[3]) {
+// 16 codes of BITS bits each -> BITS/2 32-bit words, code i in bits [BITS*i, BITS*i + BITS) (the order TMA's
+// 16U6_ALIGN16B / 16U4_ALIGN16B types expand from)
+template <int BITS> RK_DEVINL void pack16(const uint32_t* c, uint32_t* w) {
+  if (BITS == 4) {
+    uint32_t a = 0, b = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { a |= (c[i] & 0xFu) << (4 * i); b |= (c[8 + i] & 0xFu) << (4 * i); }
+    w[0] = a; w[1] = b;
+    return;
+  }
   uint64_t lo = 0, hi = 0;     // 96 bits
 #pragma unroll
   for (int i = 0; i < 16; ++i) {
@@ -738,8 +745,9 @@ RK_DEVINL void pack16x6(const uint32_t (&c)[16], uint32_t (&w)[3]) {
   w[0] = (uint32_t)lo; w[1] = (uint32_t)(lo >> 32); w[2] = (uint32_t)hi;
 }
 
-// byte codes [rows][d] -> packed [rows][dp * 3/4 bytes], dp = d rounded up to 128, padding codes 0
-__global__ void pack6_rows_kernel(const uint8_t* __restrict__ in, int64_t rows, int64_t d, int64_t dp, uint8_t* __restrict__ out) {
+// byte codes [rows][d] -> packed [rows][dp * BITS/8 bytes], dp = d rounded up to 128, padding codes 0
+template <int BITS>
+__global__ void pack_rows_kernel(const uint8_t* __restrict__ in, int64_t rows, int64_t d, int64_t dp, uint8_t* __restrict__ out) {
   const int64_t groups = dp / 16, total = rows * groups;
   for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (int64_t)gridDim.x * blockDim.x) {
     const int64_t r = t / groups, gidx = t % groups;
@@ -753,16 +761,18 @@ __global__ void pack6_rows_kernel(const uint8_t* __restrict__ in, int64_t rows, 
 #pragma unroll
       for (int i = 0; i < 16; ++i) c[i] = 0;
     }
-    pack16x6(c, w);
-    uint32_t* o = reinterpret_cast<uint32_t*>(out + r * (dp * 3 / 4) + gidx * 12);
-    o[0] = w[0]; o[1] = w[1]; o[2] = w[2];
+    pack16<BITS>(c, w);
+    uint32_t* o = reinterpret_cast<uint32_t*>(out + r * (dp * BITS / 8) + gidx * (2 * BITS));
+    o[0] = w[0]; o[1] = w[1];
+    if (BITS == 6) o[2] = w[2];
   }
 }
 
-// byte codes [batch][S][d] -> packed transposed [batch][d][Sp * 3/4 bytes], Sp = S rounded up to 128.
+// byte codes [batch][S][d] -> packed transposed [batch][d][Sp * BITS/8 bytes], Sp = S rounded up to 128.
 // One CTA = one tile of 128 keys x 128 columns through shared memory: coalesced 16-byte reads along d, then each
-// thread packs 16 keys of one column and the 8 threads of a column write 96 contiguous bytes.
-__global__ void __launch_bounds__(256) pack6_transpose_kernel(const uint8_t* __restrict__ in, int64_t batch, int64_t S, int64_t d,
+// thread packs 16 keys of one column and the 8 threads of a column write 96 (64) contiguous bytes.
+template <int BITS>
+__global__ void __launch_bounds__(256) pack_transpose_kernel(const uint8_t* __restrict__ in, int64_t batch, int64_t S, int64_t d,
                                                               int64_t Sp, uint8_t* __restrict__ out) {
   __shared__ uint8_t tile[128][128 + 4];                       // [key][col], rows padded by one word against bank conflicts
   const int64_t ktiles = Sp / 128, ctiles = (d + 127) / 128;
@@ -785,9 +795,10 @@ __global__ void __launch_bounds__(256) pack6_transpose_kernel(const uint8_t* __r
       uint32_t c[16], w[3];
 #pragma unroll
       for (int k = 0; k < 16; ++k) c[k] = tile[gi * 16 + k][col];
-      pack16x6(c, w);
-      uint32_t* o = reinterpret_cast<uint32_t*>(out + (bt * d + col0 + col) * (Sp * 3 / 4) + (kt * 8 + gi) * 12);
-      o[0] = w[0]; o[1] = w[1]; o[2] = w[2];
+      pack16<BITS>(c, w);
+      uint32_t* o = reinterpret_cast<uint32_t*>(out + (bt * d + col0 + col) * (Sp * BITS / 8) + (kt * 8 + gi) * (2 * BITS));
+      o[0] = w[0]; o[1] = w[1];
+      if (BITS == 6) o[2] = w[2];
     }
   }
 }
@@ -804,6 +815,7 @@ static int grid_for(int64_t work_items, int threads, int per_sm) {
     case 1: { constexpr int F = 1; __VA_ARGS__; } break; \
     case 2: { constexpr int F = 2; __VA_ARGS__; } break; \
     case 3: { constexpr int F = 3; __VA_ARGS__; } break; \
+    case 4: { constexpr int F = 4; __VA_ARGS__; } break; \
     default: return RK_ERR_BAD_FORMAT;             \
   }
 
@@ -932,17 +944,21 @@ int launch_retile_keyscales(const uint8_t* in, int64_t batch, int64_t S, int64_t
   return (int)cudaGetLastError();
 }
 
-int launch_pack6_rows(const uint8_t* in, int64_t rows, int64_t d, uint8_t* out, cudaStream_t st) {
+// bits = 6 (E2M3, E3M2) or 4 (E2M1)
+int launch_pack_rows(const uint8_t* in, int64_t rows, int64_t d, int bits, uint8_t* out, cudaStream_t st) {
   const int64_t dp = (d + 127) / 128 * 128, total = rows * (dp / 16);
   if (total == 0) return RK_OK;
-  pack6_rows_kernel<<<grid_for(total, 256, 8), 256, 0, st>>>(in, rows, d, dp, out);
+  if (bits == 4) pack_rows_kernel<4><<<grid_for(total, 256, 8), 256, 0, st>>>(in, rows, d, dp, out);
+  else pack_rows_kernel<6><<<grid_for(total, 256, 8), 256, 0, st>>>(in, rows, d, dp, out);
   return (int)cudaGetLastError();
 }
 
-int launch_pack6_transpose(const uint8_t* in, int64_t batch, int64_t S, int64_t d, uint8_t* out, cudaStream_t st) {
+int launch_pack_transpose(const uint8_t* in, int64_t batch, int64_t S, int64_t d, int bits, uint8_t* out, cudaStream_t st) {
   const int64_t Sp = (S + 127) / 128 * 128, tiles = batch * (Sp / 128) * ((d + 127) / 128);
   if (tiles == 0) return RK_OK;
-  pack6_transpose_kernel<<<(int)min(tiles, (int64_t)num_sms() * 8), 256, 0, st>>>(in, batch, S, d, Sp, out);
+  const int grid = (int)min(tiles, (int64_t)num_sms() * 8);
+  if (bits == 4) pack_transpose_kernel<4><<<grid, 256, 0, st>>>(in, batch, S, d, Sp, out);
+  else pack_transpose_kernel<6><<<grid, 256, 0, st>>>(in, batch, S, d, Sp, out);
   return (int)cudaGetLastError();
 }
 

@@ -59,6 +59,11 @@ def test_gemma_prefill_mxfp6_e2m3_q_e3m2_kv():
                  slices=[(0, 1), (1, 14)])
 
 
+def test_gqa_prefill_mxfp4_e2m1_b4_h32_kv8_s8192_d128():
+    """The FP4 variant at the GQA shape: E2M1 queries, keys and values (P stays E4M3)."""
+    _run_prefill(4, 32, 8, 8192, 128, seed=25, mul=0.5, q_fmt=rk.E2M1, kv_fmt=rk.E2M1, slices=[(0, 3), (3, 28)])
+
+
 def test_decode_batch64_h32_kv8_l32768():
     """Llama decode: batch 64, 32 query heads on 8 KV heads, d=128, KV length 32768 for every sequence.  Three
     (batch, KV head) units against the oracle; all outputs finite and inside the hull of the decoded V."""

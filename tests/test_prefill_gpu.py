@@ -103,6 +103,31 @@ def test_mxfp6_operands_e2m3_q_e3m2_kv():
         assert ma <= MAX_ABS and rl <= REL_L2, (d, ma, rl)
 
 
+def test_mxfp4_operands_e2m1():
+    """FP4 variant (lib/golden/mx_fp_math.h:238-246; the reference studies it in
+    kernels/flash_attention_mx_gqa/fp6_attn_relerr.py:31-36): E2M1 queries, keys and values under E8M0 block scales,
+    P stays E4M3; the 4-bit codes cross the interface one per byte and are packed two per byte for the tensor core.
+    Also E2M1 keys/values under E4M3 queries, the mix a 4-bit KV cache gives."""
+    import oracle
+    for (B, H, Hkv, Sq, Skv, d, axis, qf) in ((1, 2, 1, 256, 256, 128, rk.V_SCALES_ALONG_D, rk.E2M1),
+                                              (1, 4, 2, 200, 333, 64, rk.V_SCALES_ALONG_KEYS, rk.E2M1),
+                                              (1, 2, 1, 384, 384, 256, rk.V_SCALES_ALONG_D, rk.E2M1),
+                                              (2, 4, 2, 512, 512, 128, rk.V_SCALES_ALONG_KEYS, rk.E4M3)):
+        Q, K, V = randn_qkv(B, H, Hkv, Sq, Skv, d, seed=37, mul=0.5)
+        qc, qs = rk.mx_quantize(Q, qf)
+        kc, ks = rk.mx_quantize(K, rk.E2M1)
+        vc, vs = rk.mx_quantize(V, rk.E2M1) if axis == rk.V_SCALES_ALONG_D else rk.mx_quantize_keys(V, rk.E2M1)
+        assert int(qc.max()) < (16 if qf == rk.E2M1 else 256) and int(kc.max()) < 16 and int(vc.max()) < 16
+        o = rk.attn_prefill(qc, kc, vc, qs, ks, vs, causal=True, softcap=50.0 if d == 256 else 0.0, q_fmt=qf, kv_fmt=rk.E2M1,
+                            v_scale_axis=axis)
+        torch.cuda.synchronize()
+        assert rk.last_device_status() == 0
+        ref = oracle.attn_prefill(np_(qc), np_(kc), np_(vc), np_(qs), np_(ks), np_(vs), causal=True, softmax_scale=d ** -0.5,
+                                  softcap=50.0 if d == 256 else 0.0, q_fmt=qf, kv_fmt=rk.E2M1, v_scale_axis=axis, block_n=128)
+        ma, rl = errors(np_(o.float()), ref["o_f32"])
+        assert ma <= MAX_ABS and rl <= REL_L2, (d, ma, rl)
+
+
 def test_lse_output():
     r = prefill_vs_oracle(1, 2, 1, 256, 256, 128, causal=True, want_lse=True, seed=12)
     _check(r)

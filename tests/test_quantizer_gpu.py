@@ -53,7 +53,7 @@ def test_hardware_converter_equals_reference_encoder_on_every_fp32(fmt):
     assert int(count.item()) == 0, f"{int(count.item())} mismatches, first at bits {int(first.item()) & 0xFFFFFFFF:#010x}"
 
 
-@pytest.mark.parametrize("fmt", [rk.E4M3, rk.E5M2, rk.E2M3, rk.E3M2])
+@pytest.mark.parametrize("fmt", [rk.E4M3, rk.E5M2, rk.E2M3, rk.E3M2, rk.E2M1])
 def test_quantize_rows_bit_exact(fmt):
     g = torch.Generator(device="cuda").manual_seed(11 + fmt)
     x = torch.randn(512, 1024, generator=g, device="cuda")
@@ -100,10 +100,10 @@ def test_quantize_keys_and_rebase_bit_exact():
         assert np.array_equal(np_(rc[b]), oc) and np.array_equal(np_(rs[b]), os_)
 
 
-@pytest.mark.parametrize("fmt", [0, 1, 2, 3])
+@pytest.mark.parametrize("fmt", [0, 1, 2, 3, 4])
 @pytest.mark.parametrize("S,d", [(32 * 7 + 5, 256), (96, 64), (40, 128), (32, 32)])
 def test_rebase_bit_exact_on_adversarial_codes(S, d, fmt):
-    """Every branch of the integer re-blocking, for all four element formats: random raw codes (zeros, subnormals,
+    """Every branch of the integer re-blocking, for all five element formats: random raw codes (zeros, subnormals,
     both signs; the E4M3 NaN encodings replaced) under scale codes that vary row to row by up to 2^24, extreme
     scale codes that must take the generic path, all-zero columns, ragged tails, and widths where a warp spans
     several key blocks."""
