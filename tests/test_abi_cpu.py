@@ -122,7 +122,7 @@ def test_producer_and_cache_entry_points_reject_bad_arguments():
     assert L.rk_kv_cache_append(None, ok, 1, 1, 128, 128, ok, 0, ok, ok, ok, ok, None) == -1
     assert L.rk_kv_cache_append(ok, ok, 1, 1, 128, 100, ok, 0, ok, ok, ok, ok, None) == -2
     assert L.rk_kv_cache_append(ok, ok, 1, 1, 0, 128, ok, 0, ok, ok, ok, ok, None) == -2
-    assert L.rk_kv_cache_append(ok, ok, 1, 1, 128, 128, ok, 4, ok, ok, ok, ok, None) == -3
+    assert L.rk_kv_cache_append(ok, ok, 1, 1, 128, 128, ok, 5, ok, ok, ok, ok, None) == -3
     assert L.rk_kv_cache_append(ok + 4, ok, 1, 1, 128, 128, ok, 0, ok, ok, ok, ok, None) == -5
 
 
