@@ -446,6 +446,7 @@ int launch_decode(const rk_decode_args& a, int nsplit, cudaStream_t st) {
   p.scale_log2 = scale * 1.4426950408889634f;
   cudaError_t e;
   dim3 grid(nsplit, a.H_kv, a.B);
+  if (!decode_uses_tc(a) && a.kv_fmt != RK_FMT_E4M3) return RK_ERR_UNSUPPORTED;   // the mma.sync kernel converts E4M3 bytes itself
   if (decode_uses_tc(a)) {
     DecodeTcParams t;
     t.q = p.q; t.k_scale = p.k_scale; t.v_scale = p.v_scale; t.kv_len = p.kv_len;
@@ -455,8 +456,10 @@ int launch_decode(const rk_decode_args& a, int nsplit, cudaStream_t st) {
     const int smem_bytes = (eight ? dtc::Lay<8>::total : dtc::Lay<4>::total) + 1024;
     auto kern = eight ? decode_tc_kernel<8> : decode_tc_kernel<4>;
     if ((e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes)) != cudaSuccess) return (int)e;
-    const uint32_t idesc_qk = make_idesc(0, 0, false, false, 128, dtc::kNq);
-    const uint32_t idesc_pv = make_idesc(0, 0, true, false, 128, eight ? dtc::Lay<8>::kNp : dtc::Lay<4>::kNp);
+    // A = the cache tile in its own 8-bit format (E4M3 or E5M2: no thread decodes a cache byte, so the format is
+    // one field of the instruction descriptor), B = the MXFP8 terms of Q / P, always E4M3
+    const uint32_t idesc_qk = make_idesc(a.kv_fmt, RK_FMT_E4M3, false, false, 128, dtc::kNq);
+    const uint32_t idesc_pv = make_idesc(a.kv_fmt, RK_FMT_E4M3, true, false, 128, eight ? dtc::Lay<8>::kNp : dtc::Lay<4>::kNp);
     if (g_ev_before && g_ev_after) cudaEventRecord(g_ev_before, st);
     kern<<<grid, dtc::kThreads, smem_bytes, st>>>(tk, tv, t, idesc_qk, idesc_pv);
     if (g_ev_before && g_ev_after) cudaEventRecord(g_ev_after, st);

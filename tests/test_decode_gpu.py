@@ -10,21 +10,21 @@ from helpers import MAX_ABS, REL_L2, errors, np_
 pytestmark = pytest.mark.gpu
 
 
-def run(B, H, Hkv, L, lens=None, seed=0, num_splits=0, want_lse=False, vmul=1.0):
+def run(B, H, Hkv, L, lens=None, seed=0, num_splits=0, want_lse=False, vmul=1.0, kv_fmt=rk.E4M3):
     d = 128
     g = torch.Generator(device="cuda").manual_seed(seed)
     q = torch.randn(B, H, d, generator=g, device="cuda").bfloat16()
     K = torch.randn(B, Hkv, L, d, generator=g, device="cuda")
     V = torch.randn(B, Hkv, L, d, generator=g, device="cuda") * vmul
-    kc, ks = rk.mx_quantize(K)
-    vc, vs = rk.mx_quantize(V)
+    kc, ks = rk.mx_quantize(K, kv_fmt)
+    vc, vs = rk.mx_quantize(V, kv_fmt)
     kl = None if lens is None else torch.tensor(lens, dtype=torch.int32, device="cuda")
     lse = torch.empty(B, H, dtype=torch.float32, device="cuda") if want_lse else None
-    o = rk.attn_decode(q, kc, vc, ks, vs, kv_len=kl, num_splits=num_splits, lse=lse)
+    o = rk.attn_decode(q, kc, vc, ks, vs, kv_len=kl, num_splits=num_splits, lse=lse, kv_fmt=kv_fmt)
     torch.cuda.synchronize()
     assert rk.last_device_status() == 0
     ref = oracle.attn_decode(np_(q.view(torch.uint16)), np_(kc), np_(vc), np_(ks), np_(vs), softmax_scale=d ** -0.5,
-                             kv_len=None if lens is None else np.array(lens, np.int32), want_lse=want_lse)
+                             kv_len=None if lens is None else np.array(lens, np.int32), want_lse=want_lse, kv_fmt=kv_fmt)
     got = np_(o.float())
     assert np.isfinite(got).all()
     ma, rl = errors(got, ref["o_f32"])
@@ -37,6 +37,14 @@ def run(B, H, Hkv, L, lens=None, seed=0, num_splits=0, want_lse=False, vmul=1.0)
 @pytest.mark.parametrize("grp", [1, 2, 4, 8])
 def test_group_sizes(grp):
     run(2, 2 * grp, 2, 1024, seed=grp)
+
+
+@pytest.mark.parametrize("grp", [1, 4, 8])
+def test_e5m2_cache(grp):
+    """An E5M2 cache (what rk_kv_cache_append writes with fmt = RK_FMT_E5M2): the tcgen05 kernel feeds the raw tiles
+    to block-scaled MMAs, so the cache format is one field of the instruction descriptor."""
+    run(2, 2 * grp, 2, 2048, seed=60 + grp, kv_fmt=rk.E5M2, want_lse=True)
+    run(2, 2 * grp, 2, 1000, lens=[1000, 37], seed=70 + grp, kv_fmt=rk.E5M2)
 
 
 def test_llama_shape_small_batch():
