@@ -174,7 +174,7 @@ RK_API int rk_attn_prefill(const rk_prefill_args* a, void* stream);
  * (256-byte aligned, at least rk_attn_prefill_host_arena_bytes()), runs rk_attn_prefill and
  * copies O (and lse) back.  The reference's counterpart is the host stub that
  * releases the kernel and waits for it (kernels/flash_attention_mx_gqa/host.cpp:5-18).
- * The (batch, KV head) units are independent, so the call is cut into up to 16 chunks of whole
+ * The (batch, KV head) units are independent, so the call is cut into a few (five) chunks of whole
  * units and pipelined: while one chunk is computed on `stream`, the next one crosses the bus on
  * a copy stream of the library and the previous one's output goes back on a second one (host
  * buffers should be pinned for the copies to overlap).  Results are those of rk_attn_prefill.

@@ -297,8 +297,8 @@ int host_pipe_init(HostPipe& hp) {
 }
 }  // namespace
 
-// Host buffers in, host buffer out.  The (batch, KV head) units are independent, so the call is cut into up to
-// 16 chunks of whole units and pipelined: chunk c+1 crosses PCIe on a copy stream while chunk c is computed on
+// Host buffers in, host buffer out.  The (batch, KV head) units are independent, so the call is cut into a few
+// chunks of whole units and pipelined: chunk c+1 crosses PCIe on a copy stream while chunk c is computed on
 // the caller's stream and the output of chunk c-1 goes back on a second copy stream.
 int rk_attn_prefill_host(const rk_prefill_args* h, void* arena, size_t arena_bytes, void* stream) {
   int rc = check_prefill_shape(h);
@@ -331,16 +331,31 @@ int rk_attn_prefill_host(const rk_prefill_args* h, void* arena, size_t arena_byt
   HostPipe& hp = g_host_pipe[dev & 63];
   if ((rc = host_pipe_init(hp)) != RK_OK) return rc;
 
-  // chunks: whole batches when there are many, ranges of KV heads inside a batch when there are few
+  // Chunks are contiguous ranges of (batch, KV head) units; a range of n units is a problem of its own with
+  // B = n, H = heads per KV head, H_kv = 1.  Every copy costs some tens of microseconds on top of its bytes, so there
+  // are few of them: all scales go over first (three copies), then five chunks of 1/2, 1/4, 1/8, 1/16 and 1/16 of
+  // the units -- what cannot overlap with the inbound copies is the last chunk's compute and its copy back, so the
+  // last chunks are the small ones (measured on C2: 2 chunks 5.67 ms, 3 5.55, 4 5.01-5.21, 5 4.99-5.13, 6 5.02, 8 5.14;
+  // eight equal chunks with per-chunk scale copies 6.7).
   const int grp = h->H / h->H_kv;
+  const int64_t units = (int64_t)h->B * h->H_kv;
 #ifndef RK_HOST_CHUNKS
-#define RK_HOST_CHUNKS 8
+#define RK_HOST_CHUNKS 5
 #endif
-  constexpr int kTarget = RK_HOST_CHUNKS;              // chunks aimed at (<= kHostMaxChunks): more chunks, shorter pipeline head and tail
-  static_assert(kTarget <= kHostMaxChunks, "event pool");
-  const int batches_per_chunk = h->B >= kTarget ? (h->B + kTarget - 1) / kTarget : 1;
-  const int chunks_per_batch = h->B >= kTarget ? 1 : std::max(1, std::min(h->H_kv, kTarget / h->B));
-  const int kv_per_chunk = (h->H_kv + chunks_per_batch - 1) / chunks_per_batch;
+  constexpr int kTarget = RK_HOST_CHUNKS;
+  static_assert(kTarget >= 1 && kTarget <= kHostMaxChunks, "event pool");
+  int64_t chunk_units[kHostMaxChunks];
+  int n_chunks = 0;
+  {
+    int64_t left = units;
+    for (int i = 0; i < kTarget && left > 0; ++i) {
+      int64_t n = (i == kTarget - 1) ? left : std::max<int64_t>(1, (units + (2ll << i) - 1) / (2ll << i));
+      n = std::min(n, left);
+      chunk_units[n_chunks++] = n;
+      left -= n;
+    }
+    if (left > 0) chunk_units[n_chunks - 1] += left;
+  }
 
   // an error in the middle leaves copies and kernels queued on three streams: wait for them before handing the
   // buffers back to the caller
@@ -351,41 +366,38 @@ int rk_attn_prefill_host(const rk_prefill_args* h, void* arena, size_t arena_byt
   if ((e = cudaEventRecord(hp.start, st)) != cudaSuccess) return drain((int)e);
   if ((e = cudaStreamWaitEvent(hp.h2d, hp.start, 0)) != cudaSuccess) return drain((int)e);
   if ((e = cudaStreamWaitEvent(hp.d2h, hp.start, 0)) != cudaSuccess) return drain((int)e);
-  int c = 0;
-  for (int b0 = 0; b0 < h->B; b0 += batches_per_chunk) {
-    const int nb = std::min(batches_per_chunk, h->B - b0);
-    for (int kv0 = 0; kv0 < h->H_kv; kv0 += kv_per_chunk, ++c) {
-      const int nkv = std::min(kv_per_chunk, h->H_kv - kv0);
-      // first (batch, head) of the chunk; a chunk of several batches always spans all heads (kv0 = 0)
-      const size_t qh = (size_t)b0 * h->H + (size_t)kv0 * grp, kh = (size_t)b0 * h->H_kv + kv0;
-      const size_t nqh = (size_t)nb * nkv * grp, nkh = (size_t)nb * nkv;
-      const size_t q_row = (size_t)h->S_q * h->d, k_row = (size_t)h->S_kv * h->d;
+  const size_t q_row = (size_t)h->S_q * h->d, k_row = (size_t)h->S_kv * h->d;
 #define RK_CP(dst, src, o, n) if ((e = cudaMemcpyAsync((dst) + (o), reinterpret_cast<const uint8_t*>(src) + (o), n, cudaMemcpyHostToDevice, hp.h2d)) != cudaSuccess) return drain((int)e)
-      RK_CP(dq, h->q, qh * q_row, nqh * q_row);
-      RK_CP(dk, h->k, kh * k_row, nkh * k_row);
-      RK_CP(dv, h->v, kh * k_row, nkh * k_row);
-      RK_CP(dqs, h->q_scale, qh * q_row / 32, nqh * q_row / 32);
-      RK_CP(dks, h->k_scale, kh * k_row / 32, nkh * k_row / 32);
-      RK_CP(dvs, h->v_scale, kh * vs_head, nkh * vs_head);
-#undef RK_CP
-      if ((e = cudaEventRecord(hp.in[c], hp.h2d)) != cudaSuccess) return drain((int)e);
-      if ((e = cudaStreamWaitEvent(st, hp.in[c], 0)) != cudaSuccess) return drain((int)e);
-      rk_prefill_args d = *h;
-      d.B = nb; d.H = nkv * grp; d.H_kv = nkv;
-      d.q = dq + qh * q_row; d.k = dk + kh * k_row; d.v = dv + kh * k_row;
-      d.q_scale = dqs + qh * q_row / 32; d.k_scale = dks + kh * k_row / 32; d.v_scale = dvs + kh * vs_head;
-      d.o = dout + qh * q_row * 2;
-      d.lse = h->lse ? reinterpret_cast<float*>(dlse) + qh * h->S_q : nullptr;
-      d.workspace = ws; d.workspace_bytes = ws_bytes;       // chunks run one after the other on `st`: one workspace serves all
-      if ((rc = rk_attn_prefill(&d, stream)) != RK_OK) return drain(rc);
-      if ((e = cudaEventRecord(hp.out[c], st)) != cudaSuccess) return drain((int)e);
-      if ((e = cudaStreamWaitEvent(hp.d2h, hp.out[c], 0)) != cudaSuccess) return drain((int)e);
-      if ((e = cudaMemcpyAsync(reinterpret_cast<uint8_t*>(h->o) + qh * q_row * 2, dout + qh * q_row * 2, nqh * q_row * 2,
-                               cudaMemcpyDeviceToHost, hp.d2h)) != cudaSuccess) return drain((int)e);
-      if (h->lse && (e = cudaMemcpyAsync(h->lse + qh * h->S_q, reinterpret_cast<float*>(dlse) + qh * h->S_q,
-                                         nqh * h->S_q * 4, cudaMemcpyDeviceToHost, hp.d2h)) != cudaSuccess) return drain((int)e);
-    }
+  RK_CP(dqs, h->q_scale, 0, qs);
+  RK_CP(dks, h->k_scale, 0, ks);
+  RK_CP(dvs, h->v_scale, 0, vs);
+  int64_t u0 = 0;
+  for (int c = 0; c < n_chunks; ++c) {
+    const int64_t nu = chunk_units[c];
+    const size_t qh = (size_t)u0 * grp, kh = (size_t)u0;             // first query head / KV head of the chunk
+    const size_t nqh = (size_t)nu * grp, nkh = (size_t)nu;
+    RK_CP(dq, h->q, qh * q_row, nqh * q_row);
+    RK_CP(dk, h->k, kh * k_row, nkh * k_row);
+    RK_CP(dv, h->v, kh * k_row, nkh * k_row);
+    if ((e = cudaEventRecord(hp.in[c], hp.h2d)) != cudaSuccess) return drain((int)e);
+    if ((e = cudaStreamWaitEvent(st, hp.in[c], 0)) != cudaSuccess) return drain((int)e);
+    rk_prefill_args d = *h;
+    d.B = (int32_t)nu; d.H = grp; d.H_kv = 1;
+    d.q = dq + qh * q_row; d.k = dk + kh * k_row; d.v = dv + kh * k_row;
+    d.q_scale = dqs + qh * q_row / 32; d.k_scale = dks + kh * k_row / 32; d.v_scale = dvs + kh * vs_head;
+    d.o = dout + qh * q_row * 2;
+    d.lse = h->lse ? reinterpret_cast<float*>(dlse) + qh * h->S_q : nullptr;
+    d.workspace = ws; d.workspace_bytes = ws_bytes;       // chunks run one after the other on `st`: one workspace serves all
+    if ((rc = rk_attn_prefill(&d, stream)) != RK_OK) return drain(rc);
+    if ((e = cudaEventRecord(hp.out[c], st)) != cudaSuccess) return drain((int)e);
+    if ((e = cudaStreamWaitEvent(hp.d2h, hp.out[c], 0)) != cudaSuccess) return drain((int)e);
+    if ((e = cudaMemcpyAsync(reinterpret_cast<uint8_t*>(h->o) + qh * q_row * 2, dout + qh * q_row * 2, nqh * q_row * 2,
+                             cudaMemcpyDeviceToHost, hp.d2h)) != cudaSuccess) return drain((int)e);
+    if (h->lse && (e = cudaMemcpyAsync(h->lse + qh * h->S_q, reinterpret_cast<float*>(dlse) + qh * h->S_q,
+                                       nqh * h->S_q * 4, cudaMemcpyDeviceToHost, hp.d2h)) != cudaSuccess) return drain((int)e);
+    u0 += nu;
   }
+#undef RK_CP
   if ((e = cudaEventRecord(hp.end, hp.d2h)) != cudaSuccess) return drain((int)e);
   if ((e = cudaStreamWaitEvent(st, hp.end, 0)) != cudaSuccess) return drain((int)e);
   return (int)cudaStreamSynchronize(st);
