@@ -516,6 +516,10 @@ int rk_attn_decode_noalloc_status(void) { return noalloc_status_read_clear(); }
 
 void rk_profile_set_events(void* before, void* after) { g_ev_before = (cudaEvent_t)before; g_ev_after = (cudaEvent_t)after; }
 
+/* The rk_debug_* hooks below and rk_profile_set_events above set plain process-wide variables that the launch
+ * functions read: they are for tests and measurements run from one host thread, with no library call in flight on
+ * another thread while a hook is changed.  The entry points of the public header keep no such state. */
+
 /* Test hook (not in the public header): sweeps all 2^32 fp32 bit patterns and counts the inputs on which the
  * hardware element converter and the reference's integer encoder disagree (device outputs: a 64-bit count and
  * the smallest offending bit pattern, which the caller initialises to 0 and 0xFFFFFFFF). */
