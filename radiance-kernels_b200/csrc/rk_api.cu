@@ -4,6 +4,7 @@
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#include <cmath>
 #include <mutex>
 
 #include "rk_internal.h"
@@ -459,14 +460,23 @@ int rk_attn_decode_num_splits(const rk_decode_args* a) {
   if (check_decode_shape(a) != RK_OK) return 0;
   const int tiles = (a->L + 127) / 128;
   if (a->num_splits > 0) return a->num_splits < tiles ? a->num_splits : tiles;
-  // two CTAs fit on an SM; pick the split count (each split >= 4 key tiles) whose CTA count fills
-  // whole waves best, preferring fewer splits on ties
+  // Pick the split count with the lowest modelled time (microseconds; fitted to B = 1 .. 64 at L = 4096 .. 32768 with
+  // 32 and 64 heads on 8): streaming time = bytes / bandwidth, where the bandwidth grows with the number of CTAs in
+  // flight as (CTAs / slots)^0.8 up to the 6.5 TB/s of a full machine (two CTAs fit on an SM; 128 CTAs reach 3.3
+  // TB/s, 256 reach 5) and a last, partly filled wave costs half of what strict waves would; plus 10 us for the
+  // first wave and 3 for each further one.  Fewer splits win unless more are 3 % faster.  (The wave-efficiency rule
+  // used before took 23 splits at B = 8, L = 32768: 142 us against 118 with 4; and 4 at B = 64, L = 4096: 146 us
+  // against 126 with 1.)
   const long slots = (long)decode_ctas_per_sm(*a) * num_sms(), units = (long)a->B * a->H_kv;
-  int best = 1; double best_eff = -1.0;
+  const double stream_us = (double)units * tiles * (2.0 * 128 * 132 / 6.5e6);      // K + V tile with scales at 6.5 TB/s
+  int best = 1; double best_t = 1e30;
   for (int s = 1; s <= 64 && (s == 1 || tiles / s >= 4); ++s) {
     const long ctas = units * s, waves = (ctas + slots - 1) / slots;
-    const double eff = (double)ctas / (double)(waves * slots);
-    if (eff > best_eff + 0.02) { best_eff = eff; best = s; }
+    double bw = 1.0;
+    if (ctas < slots) bw = std::pow((double)ctas / (double)slots, 0.8);
+    else bw = 0.5 * (1.0 + (double)ctas / (double)(waves * slots));
+    const double t = 10.0 + 3.0 * (double)(waves - 1) + stream_us / bw;
+    if (t < best_t * 0.97) { best_t = t; best = s; }
   }
   return best;
 }
