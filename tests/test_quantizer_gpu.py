@@ -86,6 +86,18 @@ def test_quantize_exhaustive_bf16_inputs():
     assert np.array_equal(np_(codes), oc) and np.array_equal(np_(scales), os_)
 
 
+@pytest.mark.parametrize("fmt", [rk.E5M2, rk.E3M2, rk.E2M1])
+def test_quantize_keys_other_formats_bit_exact(fmt):
+    """Blocks of 32 along the keys (the V layout the attention kernels take as it lies) in the non-default formats,
+    the 4-bit one included, ragged row count."""
+    g = torch.Generator(device="cuda").manual_seed(50 + fmt)
+    x = torch.randn(2, 150, 128, generator=g, device="cuda") * 2.0
+    ck, sk = rk.mx_quantize_keys(x, fmt)
+    for b in range(2):
+        oc, os_ = oracle.quantize(np_(x[b]), fmt, axis=0)
+        assert np.array_equal(np_(ck[b]), oc) and np.array_equal(np_(sk[b]), os_)
+
+
 def test_quantize_keys_and_rebase_bit_exact():
     g = torch.Generator(device="cuda").manual_seed(5)
     x = torch.randn(3, 200, 128, generator=g, device="cuda") * 3.0       # ragged: 200 rows = 6 blocks + 8

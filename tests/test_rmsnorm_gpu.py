@@ -37,7 +37,8 @@ def test_reference_golden_inputs_bit_exact():
 
 
 @pytest.mark.parametrize("rows,K,fmt,unit,bf16", [(64, 256, 0, True, True), (100, 4096, 0, False, False), (33, 128, 3, False, False),
-                                                  (257, 1024, 1, False, True), (1, 32, 0, False, False), (70, 2048, 2, False, False)])
+                                                  (257, 1024, 1, False, True), (1, 32, 0, False, False), (70, 2048, 2, False, False),
+                                                  (48, 512, 4, False, False), (96, 256, 4, False, True)])
 def test_rmsnorm_quantize_matches_oracle(rows, K, fmt, unit, bf16):
     rng = np.random.default_rng(rows * 7 + K)
     x = (rng.standard_normal((rows, K)) * np.exp2(rng.integers(-6, 7, (rows, 1)))).astype(np.float32)
