@@ -477,7 +477,7 @@ def run_ours(args, rank, world, local, windows):
                    copy_ceiling_note="pinned cudaMemcpyAsync of the step's input bytes in and output bytes out on two streams, "
                                      "all ranks at once, no compute")
         del runner, host, dsts
-    launches = args.steps * 4          # 2 scale re-tilings, V re-blocking, attention kernel per step
+    launches = args.steps * 2          # per step: the V re-blocking launch (which also re-tiles the Q and K scales) and the attention kernel
 
     # ---- one global batch sharded over the ranks by (batch, KV head) units (N > 1) ------------------------------
     strong = None

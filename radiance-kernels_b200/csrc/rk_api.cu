@@ -214,19 +214,25 @@ int rk_attn_prefill(const rk_prefill_args* a, void* stream) {
   const uint8_t* q_sf = ws + w.q_sf;
   const uint8_t* k_sf = ws + w.k_sf;
   const uint8_t* v_sf = ws + w.v_sf;
-  if (a->q_scale_layout == RK_SCALES_SF_ATOMS) {
-    if (!aligned(a->q_scale, 16)) return RK_ERR_MISALIGNED;
-    q_sf = a->q_scale;
-  } else if ((rc = (a->q_scale_layout == RK_SCALES_GROUPMAJOR ? launch_retile_groupscales : launch_retile_rowscales)(
-                  a->q_scale, bhq, a->S_q, a->d, ws + w.q_sf, st)) != RK_OK) {
-    return rc;
-  }
-  if (a->k_scale_layout == RK_SCALES_SF_ATOMS) {
-    if (!aligned(a->k_scale, 16)) return RK_ERR_MISALIGNED;
-    k_sf = a->k_scale;
-  } else if ((rc = (a->k_scale_layout == RK_SCALES_GROUPMAJOR ? launch_retile_groupscales : launch_retile_rowscales)(
-                  a->k_scale, bhkv, a->S_kv, a->d, ws + w.k_sf, st)) != RK_OK) {
-    return rc;
+  // the usual call (row-major Q and K scales, V scaled along d): the V re-blocking launch re-tiles the Q and K scales
+  // on the side, two launches in all instead of four
+  const bool fused_retile = a->q_scale_layout == RK_SCALES_ROWMAJOR && a->k_scale_layout == RK_SCALES_ROWMAJOR &&
+                            a->v_scale_axis == RK_V_SCALES_ALONG_D;
+  if (!fused_retile) {
+    if (a->q_scale_layout == RK_SCALES_SF_ATOMS) {
+      if (!aligned(a->q_scale, 16)) return RK_ERR_MISALIGNED;
+      q_sf = a->q_scale;
+    } else if ((rc = (a->q_scale_layout == RK_SCALES_GROUPMAJOR ? launch_retile_groupscales : launch_retile_rowscales)(
+                    a->q_scale, bhq, a->S_q, a->d, ws + w.q_sf, st)) != RK_OK) {
+      return rc;
+    }
+    if (a->k_scale_layout == RK_SCALES_SF_ATOMS) {
+      if (!aligned(a->k_scale, 16)) return RK_ERR_MISALIGNED;
+      k_sf = a->k_scale;
+    } else if ((rc = (a->k_scale_layout == RK_SCALES_GROUPMAJOR ? launch_retile_groupscales : launch_retile_rowscales)(
+                    a->k_scale, bhkv, a->S_kv, a->d, ws + w.k_sf, st)) != RK_OK) {
+      return rc;
+    }
   }
   const uint8_t* v_codes = a->v;
   if (a->v_scale_axis == RK_V_SCALES_ALONG_D) {
@@ -235,7 +241,9 @@ int rk_attn_prefill(const rk_prefill_args* a, void* stream) {
       cudaError_t e = cudaMemsetAsync(ws + w.v_sf, 0x7F, w.v_codes - w.v_sf, st);
       if (e != cudaSuccess) return (int)e;
     }
-    if ((rc = launch_rebase_v(a->v, a->v_scale, bhkv, a->S_kv, a->d, a->kv_fmt, ws + w.v_codes, ws + w.v_sf, true, st)) != RK_OK)
+    if ((rc = launch_rebase_v(a->v, a->v_scale, bhkv, a->S_kv, a->d, a->kv_fmt, ws + w.v_codes, ws + w.v_sf, true, st,
+                              fused_retile ? a->q_scale : nullptr, bhq, a->S_q, ws + w.q_sf, fused_retile ? a->k_scale : nullptr,
+                              ws + w.k_sf)) != RK_OK)
       return rc;
     v_codes = ws + w.v_codes;
   } else if (a->v_scale_layout == RK_SCALES_SF_ATOMS) {

@@ -16,7 +16,9 @@ int launch_quantize_rows_bf16(const void* x, int64_t rows, int64_t cols, int fmt
 int launch_quantize_rows(const float* x, int64_t rows, int64_t cols, int fmt, uint8_t* codes, uint8_t* scales, cudaStream_t st);
 int launch_quantize_keys(const float* x, int64_t batch, int64_t rows, int64_t cols, int fmt, uint8_t* codes, uint8_t* scales, cudaStream_t st);
 int launch_rebase_v(const uint8_t* codes, const uint8_t* scales, int64_t batch, int64_t S, int64_t d, int fmt,
-                    uint8_t* out_codes, uint8_t* out_scales, bool tiled, cudaStream_t st);
+                    uint8_t* out_codes, uint8_t* out_scales, bool tiled, cudaStream_t st, const uint8_t* q_scales = nullptr,
+                    int64_t bhq = 0, int64_t S_q = 0, uint8_t* q_atoms = nullptr, const uint8_t* k_scales = nullptr,
+                    uint8_t* k_atoms = nullptr);
 int launch_retile_rowscales(const uint8_t* in, int64_t batch, int64_t S, int64_t d, uint8_t* out, cudaStream_t st);
 int launch_pack_rows(const uint8_t* in, int64_t rows, int64_t d, int bits, uint8_t* out, cudaStream_t st);
 int launch_pack_transpose(const uint8_t* in, int64_t batch, int64_t S, int64_t d, int bits, uint8_t* out, cudaStream_t st);

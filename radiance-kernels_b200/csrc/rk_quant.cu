@@ -495,6 +495,30 @@ template <int FMT> __device__ __noinline__ uint32_t rb_rare_recode(uint32_t cw, 
   return out;
 }
 
+// scales along d, row-major [batch][S][d/32]  ->  atoms [batch][ntile][dch][512]
+// (rows beyond S and blocks beyond d/32 get code 0x7F = 2^0); one thread per (atom, row) writes 4 bytes.
+RK_DEVINL void retile_rowscales_body(const uint8_t* __restrict__ in, int64_t batch, int64_t S, int64_t d,
+                                     uint8_t* __restrict__ out, int64_t tid, int64_t nthreads) {
+  const int64_t nbd = d / 32, ntile = (S + 127) / 128, dch = (d + 127) / 128;
+  const int64_t total = batch * ntile * dch * 128;
+  for (int64_t t = tid; t < total; t += nthreads) {
+    const int r = (int)(t % 128);
+    const int64_t atom = t / 128, ch = atom % dch, tile = (atom / dch) % ntile, bt = atom / (dch * ntile);
+    const int64_t row = tile * 128 + r;
+    uint32_t w = 0;
+#pragma unroll
+    for (int kb = 0; kb < 4; kb++) {
+      const int64_t blk = ch * 4 + kb;
+      const uint32_t sc = (row < S && blk < nbd) ? in[(bt * S + row) * nbd + blk] : 0x7Fu;
+      w |= sc << (8 * kb);
+    }
+    *reinterpret_cast<uint32_t*>(out + atom * 512 + sf_atom_offset(r, 0)) = w;
+  }
+}
+// Two row-major scale tensors (Q's and K's) that the re-blocking launch re-tiles on the side, so that the usual
+// prefill call is two launches (this one and the attention kernel) instead of four; in == nullptr: nothing to do.
+struct RetileJobs { const uint8_t* in[2]; uint8_t* out[2]; int64_t batch[2], S[2], d[2]; };
+
 // Four lanes share one unit = 16 adjacent columns x one 32-key block: lane "rg" holds rows 8 rg .. 8 rg + 7 as
 // eight 16-byte words in registers between the two passes (all loads of a thread in flight together), the
 // column maxima meet by two shuffles.  A warp covers 8 adjacent units, so each 16-byte access of a warp touches
@@ -503,7 +527,13 @@ template <int FMT> __device__ __noinline__ uint32_t rb_rare_recode(uint32_t cw, 
 template <int FMT, bool TILED>
 __global__ void __launch_bounds__(128, 4) rebase_v_kernel(const uint8_t* __restrict__ codes, const uint8_t* __restrict__ scales,
                                                           int64_t batch, int64_t S, int64_t d,
-                                                          uint8_t* __restrict__ out_codes, uint8_t* __restrict__ out_scales) {
+                                                          uint8_t* __restrict__ out_codes, uint8_t* __restrict__ out_scales,
+                                                          const RetileJobs jobs) {
+#pragma unroll
+  for (int jb = 0; jb < 2; ++jb)
+    if (jobs.in[jb])
+      retile_rowscales_body(jobs.in[jb], jobs.batch[jb], jobs.S[jb], jobs.d[jb], jobs.out[jb],
+                            (int64_t)blockIdx.x * blockDim.x + threadIdx.x, (int64_t)gridDim.x * blockDim.x);
   const int64_t c16n = d / 16, nkb = (S + 31) / 32, nbd = d / 32;
   const int64_t units = batch * nkb * c16n;
   const int64_t ntile = (S + 127) / 128, dch = (d + 127) / 128;   // atom grid of the TILED layout
@@ -651,25 +681,9 @@ __global__ void retile_keyscales_kernel(const uint8_t* __restrict__ in, int64_t 
   }
 }
 
-// scales along d, row-major [batch][S][d/32]  ->  atoms [batch][ntile][dch][512]
-// (rows beyond S and blocks beyond d/32 get code 0x7F = 2^0).
 __global__ void retile_rowscales_kernel(const uint8_t* __restrict__ in, int64_t batch, int64_t S, int64_t d,
                                         uint8_t* __restrict__ out) {
-  const int64_t nbd = d / 32, ntile = (S + 127) / 128, dch = (d + 127) / 128;
-  const int64_t total = batch * ntile * dch * 128;   // one thread per (atom, row): writes 4 bytes
-  for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (int64_t)gridDim.x * blockDim.x) {
-    const int r = (int)(t % 128);
-    const int64_t atom = t / 128, ch = atom % dch, tile = (atom / dch) % ntile, bt = atom / (dch * ntile);
-    const int64_t row = tile * 128 + r;
-    uint32_t w = 0;
-#pragma unroll
-    for (int kb = 0; kb < 4; kb++) {
-      const int64_t blk = ch * 4 + kb;
-      const uint32_t s = (row < S && blk < nbd) ? in[(bt * S + row) * nbd + blk] : 0x7Fu;
-      w |= s << (8 * kb);
-    }
-    *reinterpret_cast<uint32_t*>(out + atom * 512 + sf_atom_offset(r, 0)) = w;
-  }
+  retile_rowscales_body(in, batch, S, d, out, (int64_t)blockIdx.x * blockDim.x + threadIdx.x, (int64_t)gridDim.x * blockDim.x);
 }
 
 // scales along d, group-major [batch][d/32][S] (the reference's QK_A_scales_row[FA_GK][FA_SQ] per head,
@@ -920,13 +934,21 @@ int launch_kv_append(const float* k_new, const float* v_new, int B, int H_kv, in
   return (int)cudaGetLastError();
 }
 
+// q_scales / k_scales (optional, both or neither): row-major E8M0 scales of Q [bhq][S_q][d/32] and K [batch][S][d/32]
+// re-tiled into atoms by the same launch.
 int launch_rebase_v(const uint8_t* codes, const uint8_t* scales, int64_t batch, int64_t S, int64_t d, int fmt,
-                    uint8_t* out_codes, uint8_t* out_scales, bool tiled, cudaStream_t st) {
+                    uint8_t* out_codes, uint8_t* out_scales, bool tiled, cudaStream_t st, const uint8_t* q_scales,
+                    int64_t bhq, int64_t S_q, uint8_t* q_atoms, const uint8_t* k_scales, uint8_t* k_atoms) {
   const int64_t total = ((batch * ((S + 31) / 32) * (d / 16) + 7) / 8) * 32;     // 4 lanes per 16-column unit, whole warps
   if (total == 0) return RK_OK;
   const int grid = grid_for(total, 128, 8);
-  if (tiled) { RK_DISPATCH_FMT(fmt, (rebase_v_kernel<F, true><<<grid, 128, 0, st>>>(codes, scales, batch, S, d, out_codes, out_scales))); }
-  else       { RK_DISPATCH_FMT(fmt, (rebase_v_kernel<F, false><<<grid, 128, 0, st>>>(codes, scales, batch, S, d, out_codes, out_scales))); }
+  RetileJobs jobs = {};
+  if (q_scales && k_scales) {
+    jobs.in[0] = q_scales; jobs.out[0] = q_atoms; jobs.batch[0] = bhq; jobs.S[0] = S_q; jobs.d[0] = d;
+    jobs.in[1] = k_scales; jobs.out[1] = k_atoms; jobs.batch[1] = batch; jobs.S[1] = S; jobs.d[1] = d;
+  }
+  if (tiled) { RK_DISPATCH_FMT(fmt, (rebase_v_kernel<F, true><<<grid, 128, 0, st>>>(codes, scales, batch, S, d, out_codes, out_scales, jobs))); }
+  else       { RK_DISPATCH_FMT(fmt, (rebase_v_kernel<F, false><<<grid, 128, 0, st>>>(codes, scales, batch, S, d, out_codes, out_scales, jobs))); }
   return (int)cudaGetLastError();
 }
 
