@@ -96,11 +96,12 @@ RK_DEVINL uint32_t pack_u8x2(uint32_t hi, uint32_t lo, uint32_t c) {
 
 #ifdef RK_X_STAMPS
 // Timeline stamps (measurement builds only): clock64 of chosen events of one CTA, written into the dump buffer.
-// The CTA is RK_X_STAMP_BLOCK, or p.perturb - 1000 when the perturbation hook is set to 1000 + block index.
+// The CTA is RK_X_STAMP_BLOCK, or the block index b when the perturbation hook is set to 1000 + b (+ 100000 * (s + 1)
+// to pick the s-th work item of a persistent CTA).
 #ifndef RK_X_STAMP_BLOCK
 #define RK_X_STAMP_BLOCK 0
 #endif
-#define RK_STAMP_CTA ((int)blockIdx.x == (p.perturb >= 1000 ? p.perturb - 1000 : RK_X_STAMP_BLOCK))
+#define RK_STAMP_CTA ((int)blockIdx.x == (p.perturb % 100000 >= 1000 ? p.perturb % 100000 - 1000 : RK_X_STAMP_BLOCK))
 #define RK_STAMP(slot, j, k) do { if (p.dbg && RK_STAMP_CTA && (j) < 32) \
     reinterpret_cast<unsigned*>(p.dbg)[24576 + (slot) * 512 + (j) * 8 + (k)] = (unsigned)clock64(); } while (0)
 #define RK_STAMP_RAW(idx) do { if (p.dbg && RK_STAMP_CTA) \
