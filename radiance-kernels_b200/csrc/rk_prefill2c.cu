@@ -489,26 +489,8 @@ prefill2c_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   if (threadIdx.x == 0) RK_STAMP_RAW(3);
   if (threadIdx.x == kWarpTma * 32) RK_STAMP_RAW(4);
 
-  if (warp < kWarpCorr) {
-    reg_inc<kRegSoftmax>();
-    if (threadIdx.x == 0) RK_STAMP_RAW(5);
-    const int grp = warp >> 2;
-    const int qt = 2 * qp + grp;
-    if (nt[grp] > 0) {
-      softmax_row_group<SOFTCAP, DUMP>(p, smem, bars, tmem_base, abort_flag, grp, qt, bh, nt[grp], j0);
-    } else if (qt < p.n_q_tiles) {
-      // no visible key: O = 0 (the l <= 0 guard of finalize_O, kernels/flash_attention_mx_gemma/flash_mx_impl.hpp:554-560)
-      const int q_row = qt * kBlockM + (int)(threadIdx.x & 127);
-      if (q_row < p.S_q) {
-        __nv_bfloat16* orow = p.o + ((size_t)bh * p.S_q + q_row) * p.d;
-        for (int c = 0; c < p.d; c += 8) *reinterpret_cast<uint4*>(orow + c) = make_uint4(0, 0, 0, 0);
-        if (p.lse) p.lse[(size_t)bh * p.S_q + q_row] = __int_as_float(0xff800000);
-      }
-    }
-  } else if (warp < kWarpTma) {
-    reg_dec<kRegCorr>();
-    correction_quadrant(p, smem, bars, tmem_base, abort_flag, nt, n_all);
-  } else {
+  // (The softmax branch comes last in the code: measured 1-1.5 % faster than first.)
+  if (warp >= kWarpTma) {
     reg_dec<kRegIssue>();
     if (threadIdx.x == kWarpQk * 32) RK_STAMP_RAW(6);
     if (warp == kWarpTma) {
@@ -620,6 +602,25 @@ prefill2c_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         mbar_wait(&bars[bDRAIN2], 0, abort_flag, p.status, 308);
       }
       __syncwarp();
+    }
+  } else if (warp >= kWarpCorr) {
+    reg_dec<kRegCorr>();
+    correction_quadrant(p, smem, bars, tmem_base, abort_flag, nt, n_all);
+  } else {
+    reg_inc<kRegSoftmax>();
+    if (threadIdx.x == 0) RK_STAMP_RAW(5);
+    const int grp = warp >> 2;
+    const int qt = 2 * qp + grp;
+    if (nt[grp] > 0) {
+      softmax_row_group<SOFTCAP, DUMP>(p, smem, bars, tmem_base, abort_flag, grp, qt, bh, nt[grp], j0);
+    } else if (qt < p.n_q_tiles) {
+      // no visible key: O = 0 (the l <= 0 guard of finalize_O, kernels/flash_attention_mx_gemma/flash_mx_impl.hpp:554-560)
+      const int q_row = qt * kBlockM + (int)(threadIdx.x & 127);
+      if (q_row < p.S_q) {
+        __nv_bfloat16* orow = p.o + ((size_t)bh * p.S_q + q_row) * p.d;
+        for (int c = 0; c < p.d; c += 8) *reinterpret_cast<uint4*>(orow + c) = make_uint4(0, 0, 0, 0);
+        if (p.lse) p.lse[(size_t)bh * p.S_q + q_row] = __int_as_float(0xff800000);
+      }
     }
   }
 
