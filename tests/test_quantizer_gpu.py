@@ -177,7 +177,7 @@ def test_quantize_full_size_idempotent():
     assert (s2 <= s1).all()
 
 
-@pytest.mark.parametrize("fmt", [0, 1, 2, 3])
+@pytest.mark.parametrize("fmt", [0, 1, 2, 3, 4])
 def test_rope_quantize_bit_exact_against_reference_rope_golden(fmt):
     """The fused RoPE + quantizer: codes and scales equal oracle.quantize of the reference's own rope_apply output
     (tests/golden/rope_vectors.npz, made by lib/golden/golden.py), for head dims 64 / 128 / 256 and every format."""
