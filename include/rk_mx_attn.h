@@ -279,6 +279,17 @@ RK_API int rk_attn_decode_noalloc(const rk_decode_args* a, void* stream);
  * clears the word, allocates nothing.  No counterpart in the reference. */
 RK_API int rk_attn_decode_noalloc_status(void);
 
+/* ---------------------------------------------------------------------------
+ * Sharding over GPUs (one process per GPU).  The path has no exchange step: (batch, KV head) units are
+ * independent (the head map of kernels/flash_attention_mx_gqa/kernel.cpp:109-115 keeps a KV head and its query
+ * heads together).  rk_shard_units gives rank `rank` of `world` its contiguous block [*begin, *end) of
+ * n_units = B * H_kv units (the first n_units % world ranks get one unit more).  A block of n units is a problem
+ * of its own for rk_attn_prefill / rk_attn_decode: B = n, H = H / H_kv, H_kv = 1, pointers advanced to the block's
+ * first unit (query heads [begin * H/H_kv, end * H/H_kv) of the flattened [B*H] axis).  Gathering O on one
+ * device, where a caller wants that, is the caller's collective (the blocks are contiguous in [B][H][S][d]).
+ * ------------------------------------------------------------------------- */
+RK_API int rk_shard_units(int64_t n_units, int32_t rank, int32_t world, int64_t* begin, int64_t* end);
+
 /* Profiling aid (no reference counterpart): when both are non-NULL, the next rk_attn_prefill /
  * rk_attn_decode calls record cudaEvent_t `before` right before their main kernel (the tiled
  * attention kernel / the split-KV kernel) and `after` right after it, on the call's stream, so a

@@ -65,6 +65,7 @@ SYMBOLS = {
     "rk_mx_gemm_hw": (C.c_int, [C.c_void_p] * 4 + [C.c_int32] * 3 + [C.c_void_p, C.c_void_p]),
     "rk_kv_cache_append": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_int32,
                                      C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "rk_shard_units": (C.c_int, [C.c_int64, C.c_int32, C.c_int32, C.POINTER(C.c_int64), C.POINTER(C.c_int64)]),
     "rk_profile_set_events": (None, [C.c_void_p, C.c_void_p]),
     "rk_last_device_status": (C.c_int, []),
 }

@@ -379,7 +379,7 @@ def last_device_status():
 
 
 def shard_range(n_units, rank, world):
-    """Contiguous block partition of n_units independent (batch, KV-head) units over `world` ranks."""
-    base, rem = divmod(n_units, world)
-    lo = rank * base + min(rank, rem)
-    return lo, lo + base + (1 if rank < rem else 0)
+    """Contiguous block partition of n_units independent (batch, KV-head) units over `world` ranks (rk_shard_units)."""
+    lo, hi = C.c_int64(), C.c_int64()
+    check(lib().rk_shard_units(n_units, rank, world, C.byref(lo), C.byref(hi)), "rk_shard_units")
+    return lo.value, hi.value

@@ -519,6 +519,15 @@ int rk_attn_decode_noalloc(const rk_decode_args* a, void* stream) {
   return launch_decode_noalloc(*a, (cudaStream_t)stream);
 }
 
+int rk_shard_units(int64_t n_units, int32_t rank, int32_t world, int64_t* begin, int64_t* end) {
+  if (!begin || !end) return RK_ERR_NULL_POINTER;
+  if (n_units < 0 || world <= 0 || rank < 0 || rank >= world) return RK_ERR_BAD_SHAPE;
+  const int64_t base = n_units / world, rem = n_units % world;
+  *begin = rank * base + (rank < rem ? rank : rem);
+  *end = *begin + base + (rank < rem ? 1 : 0);
+  return RK_OK;
+}
+
 int rk_last_device_status(void) {
   int* w = device_status_word();
   if (!w) return RK_ERR_NO_DEVICE;

@@ -144,6 +144,15 @@ def test_shard_range_covers_units_once():
             assert got == list(range(n))
 
 
+def test_shard_units_argument_errors():
+    L = rk.lib()
+    lo, hi = C.c_int64(), C.c_int64()
+    assert L.rk_shard_units(16, 0, 4, None, C.byref(hi)) == -1
+    assert L.rk_shard_units(16, 4, 4, C.byref(lo), C.byref(hi)) == -2
+    assert L.rk_shard_units(16, 0, 0, C.byref(lo), C.byref(hi)) == -2
+    assert L.rk_shard_units(3, 3, 8, C.byref(lo), C.byref(hi)) == 0 and (lo.value, hi.value) == (3, 3)   # more ranks than units
+
+
 def test_front_end_rejects_wrong_dtypes_and_shapes():
     """The Python front end checks dtype and exact shape of every tensor against B/H/H_kv/S/d before a pointer
     reaches the library (the checks run on CPU tensors here; nothing is launched)."""
