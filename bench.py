@@ -647,6 +647,15 @@ def run_extras(rk, L, dev, peaks, peak_burst, timed, kernel_ms, qc, qs, vc, vs):
         K = torch.randn(B, Hkv, S, d, generator=g, device=dev) * mul
         V = torch.randn(B, Hkv, S, d, generator=g, device=dev) * mul
         q_c, q_s = rk.mx_quantize(Q, q_fmt); k_c, k_s = rk.mx_quantize(K, kv_fmt); v_c, v_s = rk.mx_quantize(V, kv_fmt)
+        prepared = None
+        if q_fmt >= rk.E2M3 and kv_fmt >= rk.E2M3:
+            # the same operands prepared once, as a cache kept in a 6- or 4-bit format holds them: dense codes, V blocked
+            # along the keys, scale-factor atoms -- the call is then the attention kernel alone
+            _, q_a = rk.mx_quantize_ex(Q, q_fmt, rk.SCALES_SF_ATOMS)
+            _, k_a = rk.mx_quantize_ex(K, kv_fmt, rk.SCALES_SF_ATOMS)
+            v_k, v_a = rk.mx_quantize_keys_ex(V, kv_fmt, rk.SCALES_SF_ATOMS)
+            prepared = (rk.mx_pack_rows(q_c, q_fmt), rk.mx_pack_rows(k_c, kv_fmt), rk.mx_pack_vt(v_k, kv_fmt), q_a, k_a, v_a)
+            del v_k
         del Q, K, V
         o = torch.empty(B, H, S, d, dtype=torch.bfloat16, device=dev)
         ws = torch.empty(rk.attn_prefill_workspace_bytes(B, H, Hkv, S, S, d, rk.V_SCALES_ALONG_D, q_fmt, kv_fmt) + 256,
@@ -663,6 +672,14 @@ def run_extras(rk, L, dev, peaks, peak_burst, timed, kernel_ms, qc, qs, vc, vs):
                      "roofline": {"bound": "tensor", "achieved": fl / (km * 1e-3) / 1e12, "peak": peak_burst, "unit": "TFLOP/s",
                                   "frac": fl / (km * 1e-3) / 1e12 / peak_burst, "kernel_ms": km,
                                   "frac_of_nominal": fl / (km * 1e-3) / 1e12 / NOMINAL_FP8_TFLOPS, "traffic": None}}
+        if prepared is not None:
+            def fn_prepared():
+                rk.attn_prefill_packed(*prepared, S_q=S, S_kv=S, d=d, q_fmt=q_fmt, kv_fmt=kv_fmt, causal=True, softcap=softcap,
+                                       q_scale_layout=rk.SCALES_SF_ATOMS, k_scale_layout=rk.SCALES_SF_ATOMS,
+                                       v_scale_layout=rk.SCALES_SF_ATOMS, out=o, workspace=ws)
+            pms = timed(fn_prepared, steps)
+            out[name].update(prepared_ms_per_call=pms, prepared_tflops=fl / (pms * 1e-3) / 1e12,
+                             prepared_note="dense codes (rk_mx_pack_rows / rk_mx_pack_vt) and scale-factor atoms handed over: one launch")
 
     prefill_case("prefill_gqa_B4_H32_kv8_S8192_d128", 4, 32, 8, 8192, 128)
     prefill_case("prefill_gemma_B2_H16_kv8_S8192_d256_cap50", 2, 16, 8, 8192, 256, mul=0.5, softcap=50.0)

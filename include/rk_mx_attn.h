@@ -126,6 +126,20 @@ RK_API int rk_import_kt_blocks(const uint8_t* kt_blocks, const uint8_t* kt_scale
 RK_API int rk_mx_rebase_v(const uint8_t* codes, const uint8_t* scales, int64_t batch, int64_t S, int64_t d,
                    int fmt, uint8_t* out_codes, uint8_t* out_scales, void* stream);
 
+/* Dense 6-bit / 4-bit operands, the form the tensor maps of the attention kernel read (a KV cache
+ * kept in E2M3, E3M2 or E2M1 is prepared once and used by many calls).  No reference counterpart: the
+ * reference's FP6 kernels keep one code per byte (kernels/flash_attention_mx_fp6/README.md:14-18).
+ *   rows form (Q, K): codes [rows][d] one per byte -> [rows][dp * bits / 8] bytes, dp = d rounded up to
+ *     128, codes little-endian bit-packed in order (code i of a row at bits [i*bits, (i+1)*bits)),
+ *     padding codes 0;
+ *   transposed form (V, blocked along the keys): codes [batch][S][d] -> [batch][d][Sp * bits / 8] bytes,
+ *     Sp = S rounded up to 128, the keys of one column packed the same way.
+ * d must be a multiple of 16; fmt one of RK_FMT_E2M3, RK_FMT_E3M2 (bits = 6), RK_FMT_E2M1 (bits = 4). */
+RK_API size_t rk_mx_packed_rows_bytes(int64_t rows, int64_t d, int fmt);
+RK_API int rk_mx_pack_rows(const uint8_t* codes, int64_t rows, int64_t d, int fmt, uint8_t* out, void* stream);
+RK_API size_t rk_mx_packed_vt_bytes(int64_t batch, int64_t S, int64_t d, int fmt);
+RK_API int rk_mx_pack_vt(const uint8_t* v_codes, int64_t batch, int64_t S, int64_t d, int fmt, uint8_t* out, void* stream);
+
 /* ---------------------------------------------------------------------------
  * Prefill attention.  Replaces fa_entry(void*, tid, threads, block_id) of
  * kernels/flash_attention_mx_gqa/kernel.cpp:91-184 (GQA + causal),
@@ -153,7 +167,8 @@ typedef struct rk_prefill_args {
   float softcap;           /* >0: s <- cap*tanh(s/cap) after the softmax scale, before mask/max; 0 = off */
   float softmax_scale;     /* FA_SOFTMAX_SCALE; 0 selects 1/sqrt(d) */
   int32_t q_fmt, kv_fmt;   /* RK_FMT_*; 6-bit (E2M3 / E3M2) and 4-bit (E2M1) codes come one per byte and are packed into the
-                              workspace for the tensor core; P is always E4M3 as in the reference */
+                              workspace for the tensor core, unless q_packed / kv_packed say that they are dense
+                              already; P is always E4M3 as in the reference */
   int32_t v_scale_axis;    /* RK_V_SCALES_ALONG_KEYS | RK_V_SCALES_ALONG_D */
   int32_t block_n;         /* keys per online-softmax step; 0 = default.  On return from
                               rk_attn_prefill_block_n() the value the kernel uses (128). */
@@ -162,6 +177,12 @@ typedef struct rk_prefill_args {
   int32_t v_scale_layout;  /* RK_SCALES_ROWMAJOR (0), or RK_SCALES_SF_ATOMS with v_scale_axis = RK_V_SCALES_ALONG_KEYS */
   void* workspace;         /* >= rk_attn_prefill_workspace_bytes(), 256-byte aligned */
   size_t workspace_bytes;
+  int32_t q_packed;        /* 1: q is the dense form written by rk_mx_pack_rows (6- and 4-bit formats only) */
+  int32_t kv_packed;       /* 1: k is the dense form of rk_mx_pack_rows and v the dense transposed form of
+                              rk_mx_pack_vt (6- and 4-bit formats only; V blocked along the keys,
+                              v_scale_axis = RK_V_SCALES_ALONG_KEYS).  With scale-factor atoms for all three
+                              scale tensors such a call launches the attention kernel alone.  Not taken by
+                              rk_attn_prefill_host. */
 } rk_prefill_args;
 
 /* Keys per online-softmax step the kernel uses (results depend on it; an oracle

@@ -24,6 +24,7 @@ class PrefillArgs(C.Structure):
         ("q_fmt", C.c_int32), ("kv_fmt", C.c_int32), ("v_scale_axis", C.c_int32), ("block_n", C.c_int32),
         ("q_scale_layout", C.c_int32), ("k_scale_layout", C.c_int32), ("v_scale_layout", C.c_int32),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+        ("q_packed", C.c_int32), ("kv_packed", C.c_int32),
     ]
 
 
@@ -48,6 +49,10 @@ SYMBOLS = {
     "rk_mx_quantize_keys_ex": (C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
     "rk_import_kt_blocks": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p]),
     "rk_mx_rebase_v": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "rk_mx_packed_rows_bytes": (C.c_size_t, [C.c_int64, C.c_int64, C.c_int]),
+    "rk_mx_pack_rows": (C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_int, C.c_void_p, C.c_void_p]),
+    "rk_mx_packed_vt_bytes": (C.c_size_t, [C.c_int64, C.c_int64, C.c_int64, C.c_int]),
+    "rk_mx_pack_vt": (C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int, C.c_void_p, C.c_void_p]),
     "rk_attn_prefill_block_n": (C.c_int, [C.POINTER(PrefillArgs)]),
     "rk_attn_prefill_workspace_bytes": (C.c_size_t, [C.POINTER(PrefillArgs)]),
     "rk_attn_prefill": (C.c_int, [C.POINTER(PrefillArgs), C.c_void_p]),

@@ -267,6 +267,81 @@ def attn_prefill(q, k, v, q_scale, k_scale, v_scale, *, causal, softmax_scale=0.
     return o
 
 
+def mx_pack_rows(codes, fmt):
+    """6- or 4-bit codes one per byte [..., d] -> the dense rows form [..., dp * bits / 8] (dp = d rounded up to 128)."""
+    _need_cuda(codes)
+    if codes.dtype != torch.uint8 or codes.dim() < 2:
+        raise ValueError("mx_pack_rows takes uint8 codes [..., d]")
+    d = codes.shape[-1]
+    rows = codes.numel() // max(d, 1)
+    nbytes = lib().rk_mx_packed_rows_bytes(rows, d, fmt)
+    if nbytes == 0 and rows > 0:
+        raise ValueError("mx_pack_rows: format has no dense form (E2M3, E3M2, E2M1 only)")
+    out = torch.empty(codes.shape[:-1] + (nbytes // max(rows, 1),), dtype=torch.uint8, device=codes.device)
+    check(lib().rk_mx_pack_rows(_ptr(codes), rows, d, fmt, _ptr(out), _stream()), "rk_mx_pack_rows")
+    return out
+
+
+def mx_pack_vt(v_codes, fmt):
+    """V codes blocked along the keys, one per byte [..., S, d] -> the dense transposed form [..., d, Sp * bits / 8]."""
+    _need_cuda(v_codes)
+    if v_codes.dtype != torch.uint8 or v_codes.dim() < 2:
+        raise ValueError("mx_pack_vt takes uint8 codes [..., S, d]")
+    S, d = v_codes.shape[-2], v_codes.shape[-1]
+    batch = v_codes.numel() // max(S * d, 1)
+    nbytes = lib().rk_mx_packed_vt_bytes(batch, S, d, fmt)
+    if nbytes == 0 and batch > 0:
+        raise ValueError("mx_pack_vt: format has no dense form (E2M3, E3M2, E2M1 only)")
+    out = torch.empty(v_codes.shape[:-2] + (d, nbytes // max(batch * d, 1)), dtype=torch.uint8, device=v_codes.device)
+    check(lib().rk_mx_pack_vt(_ptr(v_codes), batch, S, d, fmt, _ptr(out), _stream()), "rk_mx_pack_vt")
+    return out
+
+
+def attn_prefill_packed(q, k, vt, q_scale, k_scale, v_scale, *, S_q, S_kv, d, q_fmt, kv_fmt, causal, softmax_scale=0.0,
+                        q_pos0=0, window=0, softcap=0.0, q_scale_layout=SCALES_ROWMAJOR, k_scale_layout=SCALES_ROWMAJOR,
+                        v_scale_layout=SCALES_ROWMAJOR, out=None, lse=None, workspace=None):
+    """Prefill over dense 6- / 4-bit operands: q [B,H,S_q,*] and k [B,H_kv,S_kv,*] from mx_pack_rows, vt
+    [B,H_kv,d,*] from mx_pack_vt (V blocked along the keys, v_scale along the keys).  Returns O bf16 [B,H,S_q,d]."""
+    _need_cuda(q, k, vt, q_scale, k_scale, v_scale, out, lse, workspace)
+    if q.dim() != 4 or k.dim() != 4 or vt.dim() != 4:
+        raise ValueError("q, k and vt are 4-d packed tensors")
+    B, H = q.shape[0], q.shape[1]
+    H_kv = k.shape[1]
+    L = lib()
+    _expect(q, "q", torch.uint8, (B, H, S_q, L.rk_mx_packed_rows_bytes(1, d, q_fmt)))
+    _expect(k, "k", torch.uint8, (B, H_kv, S_kv, L.rk_mx_packed_rows_bytes(1, d, kv_fmt)))
+    _expect(vt, "vt", torch.uint8, (B, H_kv, d, L.rk_mx_packed_vt_bytes(1, S_kv, 1, kv_fmt)))
+    _expect(q_scale, "q_scale", torch.uint8, _scale_shape((B, H), S_q, d, q_scale_layout))
+    _expect(k_scale, "k_scale", torch.uint8, _scale_shape((B, H_kv), S_kv, d, k_scale_layout))
+    if v_scale_layout == SCALES_ROWMAJOR:
+        _expect(v_scale, "v_scale", torch.uint8, (B, H_kv, (S_kv + 31) // 32, d))
+    elif v_scale_layout == SCALES_SF_ATOMS:
+        _expect(v_scale, "v_scale", torch.uint8, _atoms_shape((B, H_kv), S_kv, d))
+    else:
+        raise ValueError("V scales along the keys are row-major or scale-factor atoms")
+    _expect(out, "out", torch.bfloat16, (B, H, S_q, d))
+    _expect(lse, "lse", torch.float32, (B, H, S_q))
+    o = out if out is not None else torch.empty((B, H, S_q, d), dtype=torch.bfloat16, device=q.device)
+    a = PrefillArgs()
+    a.q, a.k, a.v = _ptr(q), _ptr(k), _ptr(vt)
+    a.q_scale, a.k_scale, a.v_scale = _ptr(q_scale), _ptr(k_scale), _ptr(v_scale)
+    a.o, a.lse = _ptr(o), _ptr(lse)
+    a.B, a.H, a.H_kv, a.S_q, a.S_kv, a.d = B, H, H_kv, S_q, S_kv, d
+    a.q_pos0, a.causal, a.window = q_pos0, int(bool(causal)), window
+    a.softcap, a.softmax_scale = float(softcap), float(softmax_scale)
+    a.q_fmt, a.kv_fmt, a.v_scale_axis, a.block_n = q_fmt, kv_fmt, V_SCALES_ALONG_KEYS, 0
+    a.q_scale_layout, a.k_scale_layout, a.v_scale_layout = q_scale_layout, k_scale_layout, v_scale_layout
+    a.q_packed, a.kv_packed = 1, 1
+    need = L.rk_attn_prefill_workspace_bytes(C.byref(a))
+    if workspace is None:
+        workspace = torch.empty(max(need, 1024), dtype=torch.uint8, device=q.device)
+    elif workspace.dtype != torch.uint8:
+        raise ValueError("workspace must be a uint8 tensor")
+    a.workspace, a.workspace_bytes = _ptr(workspace), workspace.numel()
+    check(L.rk_attn_prefill(C.byref(a), _stream()), "rk_attn_prefill")
+    return o
+
+
 class PrefillHostRunner:
     """Prefill through the host-buffer entry point (rk_attn_prefill_host): inputs and output live in
     pinned host memory, the device arena is allocated once and reused."""

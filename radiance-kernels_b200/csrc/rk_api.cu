@@ -64,11 +64,11 @@ static PrefillWs prefill_ws(const rk_prefill_args& a) {
   // 128 codes; sized for 6 bits, which also holds 4
   const size_t dp = dch * 128, skp = nkt * 128;
   w.q6 = off;
-  if (a.q_fmt >= RK_FMT_E2M3) off = align_up(off + (size_t)a.B * a.H * a.S_q * dp * 3 / 4, 1024);
+  if (a.q_fmt >= RK_FMT_E2M3 && !a.q_packed) off = align_up(off + (size_t)a.B * a.H * a.S_q * dp * 3 / 4, 1024);
   w.k6 = off;
-  if (a.kv_fmt >= RK_FMT_E2M3) off = align_up(off + (size_t)a.B * a.H_kv * a.S_kv * dp * 3 / 4, 1024);
+  if (a.kv_fmt >= RK_FMT_E2M3 && !a.kv_packed) off = align_up(off + (size_t)a.B * a.H_kv * a.S_kv * dp * 3 / 4, 1024);
   w.v6t = off;
-  if (a.kv_fmt >= RK_FMT_E2M3) off = align_up(off + (size_t)a.B * a.H_kv * a.d * skp * 3 / 4, 1024);
+  if (a.kv_fmt >= RK_FMT_E2M3 && !a.kv_packed) off = align_up(off + (size_t)a.B * a.H_kv * a.d * skp * 3 / 4, 1024);
   w.total = off;
   return w;
 }
@@ -88,6 +88,9 @@ static int check_prefill_shape(const rk_prefill_args* a) {
   if (a->v_scale_layout != RK_SCALES_ROWMAJOR &&
       !(a->v_scale_layout == RK_SCALES_SF_ATOMS && a->v_scale_axis == RK_V_SCALES_ALONG_KEYS))
     return RK_ERR_BAD_FORMAT;
+  // dense sub-byte operands: only formats that have a dense form; V then has to be blocked along the keys already
+  if (a->q_packed && a->q_fmt < RK_FMT_E2M3) return RK_ERR_BAD_FORMAT;
+  if (a->kv_packed && (a->kv_fmt < RK_FMT_E2M3 || a->v_scale_axis != RK_V_SCALES_ALONG_KEYS)) return RK_ERR_BAD_FORMAT;
   return RK_OK;
 }
 
@@ -192,6 +195,34 @@ int rk_mx_rebase_v(const uint8_t* codes, const uint8_t* scales, int64_t batch, i
   return launch_rebase_v(codes, scales, batch, S, d, fmt, out_codes, out_scales, false, (cudaStream_t)stream);
 }
 
+static size_t packed_len(int64_t n, int fmt) { return (size_t)((n + 127) / 128 * 128) * fmt_bits(fmt) / 8; }
+
+size_t rk_mx_packed_rows_bytes(int64_t rows, int64_t d, int fmt) {
+  if (rows < 0 || d <= 0 || fmt < RK_FMT_E2M3 || fmt > RK_FMT_E2M1) return 0;
+  return (size_t)rows * packed_len(d, fmt);
+}
+
+int rk_mx_pack_rows(const uint8_t* codes, int64_t rows, int64_t d, int fmt, uint8_t* out, void* stream) {
+  if (!codes || !out) return RK_ERR_NULL_POINTER;
+  if (rows < 0 || d <= 0 || d % 16 != 0) return RK_ERR_BAD_SHAPE;
+  if (fmt < RK_FMT_E2M3 || fmt > RK_FMT_E2M1) return RK_ERR_BAD_FORMAT;
+  if (!aligned(codes, 16) || !aligned(out, 16)) return RK_ERR_MISALIGNED;
+  return launch_pack_rows(codes, rows, d, fmt_bits(fmt), out, (cudaStream_t)stream);
+}
+
+size_t rk_mx_packed_vt_bytes(int64_t batch, int64_t S, int64_t d, int fmt) {
+  if (batch < 0 || S <= 0 || d <= 0 || fmt < RK_FMT_E2M3 || fmt > RK_FMT_E2M1) return 0;
+  return (size_t)batch * d * packed_len(S, fmt);
+}
+
+int rk_mx_pack_vt(const uint8_t* v_codes, int64_t batch, int64_t S, int64_t d, int fmt, uint8_t* out, void* stream) {
+  if (!v_codes || !out) return RK_ERR_NULL_POINTER;
+  if (batch < 0 || S <= 0 || d <= 0 || d % 16 != 0) return RK_ERR_BAD_SHAPE;
+  if (fmt < RK_FMT_E2M3 || fmt > RK_FMT_E2M1) return RK_ERR_BAD_FORMAT;
+  if (!aligned(v_codes, 16) || !aligned(out, 16)) return RK_ERR_MISALIGNED;
+  return launch_pack_transpose(v_codes, batch, S, d, fmt_bits(fmt), out, (cudaStream_t)stream);
+}
+
 int rk_attn_prefill_block_n(const rk_prefill_args* a) { (void)a; return 128; }
 
 size_t rk_attn_prefill_workspace_bytes(const rk_prefill_args* a) {
@@ -254,11 +285,11 @@ int rk_attn_prefill(const rk_prefill_args* a, void* stream) {
   }
   const uint8_t* q_codes = a->q;
   const uint8_t* k_codes = a->k;
-  if (a->q_fmt >= RK_FMT_E2M3) {
+  if (a->q_fmt >= RK_FMT_E2M3 && !a->q_packed) {
     if ((rc = launch_pack_rows(a->q, bhq * a->S_q, a->d, fmt_bits(a->q_fmt), ws + w.q6, st)) != RK_OK) return rc;
     q_codes = ws + w.q6;
   }
-  if (a->kv_fmt >= RK_FMT_E2M3) {
+  if (a->kv_fmt >= RK_FMT_E2M3 && !a->kv_packed) {
     if ((rc = launch_pack_rows(a->k, bhkv * a->S_kv, a->d, fmt_bits(a->kv_fmt), ws + w.k6, st)) != RK_OK) return rc;
     k_codes = ws + w.k6;
     if ((rc = launch_pack_transpose(v_codes, bhkv, a->S_kv, a->d, fmt_bits(a->kv_fmt), ws + w.v6t, st)) != RK_OK) return rc;
@@ -313,8 +344,9 @@ int rk_attn_prefill_host(const rk_prefill_args* h, void* arena, size_t arena_byt
   int rc = check_prefill_shape(h);
   if (rc != RK_OK) return rc;
   if (!h->q || !h->k || !h->v || !h->q_scale || !h->k_scale || !h->v_scale || !h->o || !arena) return RK_ERR_NULL_POINTER;
-  // the chunk offsets below are those of row-major scales
-  if (h->q_scale_layout != RK_SCALES_ROWMAJOR || h->k_scale_layout != RK_SCALES_ROWMAJOR || h->v_scale_layout != RK_SCALES_ROWMAJOR)
+  // the chunk offsets below are those of row-major scales and of codes one per byte
+  if (h->q_scale_layout != RK_SCALES_ROWMAJOR || h->k_scale_layout != RK_SCALES_ROWMAJOR || h->v_scale_layout != RK_SCALES_ROWMAJOR ||
+      h->q_packed || h->kv_packed)
     return RK_ERR_UNSUPPORTED;
   if (arena_bytes < rk_attn_prefill_host_arena_bytes(h) || !aligned(arena, 256)) return RK_ERR_WORKSPACE;
   cudaStream_t st = (cudaStream_t)stream;

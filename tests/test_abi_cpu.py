@@ -126,6 +126,28 @@ def test_producer_and_cache_entry_points_reject_bad_arguments():
     assert L.rk_kv_cache_append(ok + 4, ok, 1, 1, 128, 128, ok, 0, ok, ok, ok, ok, None) == -5
 
 
+def test_dense_operand_entry_points_reject_bad_arguments():
+    L = rk.lib()
+    ok = 4096
+    assert L.rk_mx_packed_rows_bytes(10, 128, 2) == 10 * 96 and L.rk_mx_packed_rows_bytes(10, 64, 4) == 10 * 64
+    assert L.rk_mx_packed_rows_bytes(10, 128, 0) == 0                      # E4M3 has no dense form
+    assert L.rk_mx_packed_vt_bytes(3, 333, 64, 3) == 3 * 64 * 384 * 6 // 8
+    assert L.rk_mx_pack_rows(None, 4, 128, 2, ok, None) == -1
+    assert L.rk_mx_pack_rows(ok, 4, 100, 2, ok, None) == -2
+    assert L.rk_mx_pack_rows(ok, 4, 128, 1, ok, None) == -3
+    assert L.rk_mx_pack_rows(ok + 4, 4, 128, 2, ok, None) == -5
+    assert L.rk_mx_pack_vt(ok, 1, 0, 128, 4, ok, None) == -2
+    assert L.rk_mx_pack_vt(ok, 1, 128, 128, 0, ok, None) == -3
+    assert L.rk_attn_prefill(C.byref(_pargs(q_packed=1)), None) == -3               # E4M3 queries cannot be dense
+    assert L.rk_attn_prefill(C.byref(_pargs(kv_fmt=3, kv_packed=1, v_scale_axis=1)), None) == -3   # dense V must be blocked along the keys
+    # dense operands need no packing space in the workspace
+    a, b = _pargs(q_fmt=2, kv_fmt=3, v_scale_axis=0), _pargs(q_fmt=2, kv_fmt=3, v_scale_axis=0, q_packed=1, kv_packed=1)
+    assert L.rk_attn_prefill_workspace_bytes(C.byref(b)) < L.rk_attn_prefill_workspace_bytes(C.byref(a))
+    for f in ("q", "k", "v", "q_scale", "k_scale", "v_scale", "o"):
+        setattr(b, f, ok)
+    assert L.rk_attn_prefill_host(C.byref(b), ok, 1 << 30, None) == -6              # the host entry point takes bytes only
+
+
 def test_no_cpu_fallback():
     """The product path has no CPU route: calling it with CPU tensors raises instead of computing."""
     import torch

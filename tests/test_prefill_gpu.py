@@ -128,6 +128,46 @@ def test_mxfp4_operands_e2m1():
         assert ma <= MAX_ABS and rl <= REL_L2, (d, ma, rl)
 
 
+def test_dense_sub_byte_operands_give_the_same_output():
+    """Operands handed over in the dense 6- / 4-bit form (rk_mx_pack_rows, rk_mx_pack_vt) -- what a KV cache kept in
+    those formats holds -- give bit for bit the output of the call that packs them itself, and with scale-factor
+    atoms on top the same again."""
+    for (B, H, Hkv, Sq, Skv, d, qf, kvf, cap) in ((1, 4, 2, 200, 333, 64, rk.E2M3, rk.E3M2, 0.0),
+                                                    (2, 4, 2, 512, 512, 128, rk.E2M1, rk.E2M1, 0.0),
+                                                    (1, 2, 1, 384, 384, 256, rk.E2M3, rk.E3M2, 50.0)):
+        Q, K, V = randn_qkv(B, H, Hkv, Sq, Skv, d, seed=41, mul=0.5)
+        qc, qs = rk.mx_quantize(Q, qf)
+        kc, ks = rk.mx_quantize(K, kvf)
+        vc, vs = rk.mx_quantize_keys(V, kvf)
+        want = rk.attn_prefill(qc, kc, vc, qs, ks, vs, causal=True, softcap=cap, q_fmt=qf, kv_fmt=kvf,
+                               v_scale_axis=rk.V_SCALES_ALONG_KEYS)
+        qp, kp, vtp = rk.mx_pack_rows(qc, qf), rk.mx_pack_rows(kc, kvf), rk.mx_pack_vt(vc, kvf)
+        bits_q, bits_kv = (4 if qf == rk.E2M1 else 6), (4 if kvf == rk.E2M1 else 6)
+        dp, sp = (d + 127) // 128 * 128, (Skv + 127) // 128 * 128
+        assert qp.shape == (B, H, Sq, dp * bits_q // 8) and kp.shape == (B, Hkv, Skv, dp * bits_kv // 8)
+        assert vtp.shape == (B, Hkv, d, sp * bits_kv // 8)
+        kw = dict(S_q=Sq, S_kv=Skv, d=d, q_fmt=qf, kv_fmt=kvf, causal=True, softcap=cap)
+        got = rk.attn_prefill_packed(qp, kp, vtp, qs, ks, vs, **kw)
+        assert torch.equal(got, want)
+        # the first codes of a row, unpacked by hand
+        row = qp[0, 0, 0].cpu().numpy().astype(np.uint64)
+        word = int(row[0]) | int(row[1]) << 8 | int(row[2]) << 16
+        first = [(word >> (bits_q * i)) & ((1 << bits_q) - 1) for i in range(3)]
+        assert first == [int(x) for x in qc[0, 0, 0, :3].cpu()]
+        # prepared all the way: scale-factor atoms as well, so that the call is the attention kernel alone
+        _, qa = rk.mx_quantize_ex(Q, qf, rk.SCALES_SF_ATOMS)
+        _, ka = rk.mx_quantize_ex(K, kvf, rk.SCALES_SF_ATOMS)
+        _, va = rk.mx_quantize_keys_ex(V, kvf, rk.SCALES_SF_ATOMS)
+        got2 = rk.attn_prefill_packed(qp, kp, vtp, qa, ka, va, q_scale_layout=rk.SCALES_SF_ATOMS,
+                                      k_scale_layout=rk.SCALES_SF_ATOMS, v_scale_layout=rk.SCALES_SF_ATOMS, **kw)
+        assert torch.equal(got2, want)
+        torch.cuda.synchronize()
+        assert rk.last_device_status() == 0
+    # 8-bit formats have no dense form (the front end stops it; the library would answer RK_ERR_BAD_FORMAT)
+    with pytest.raises((rk.RkError, ValueError)):
+        rk.attn_prefill_packed(qp, kp, vtp, qs, ks, vs, S_q=Sq, S_kv=Skv, d=d, q_fmt=rk.E4M3, kv_fmt=rk.E3M2, causal=True)
+
+
 def test_lse_output():
     r = prefill_vs_oracle(1, 2, 1, 256, 256, 128, causal=True, want_lse=True, seed=12)
     _check(r)
