@@ -222,7 +222,9 @@ typedef struct rk_decode_args {
   float* lse;              /* optional fp32 [B][H] */
   int32_t B, H, H_kv, L, d;   /* d == 128; H / H_kv in {1,2,4,8} */
   float softmax_scale;     /* 0 selects 1/sqrt(d) */
-  int32_t kv_fmt;          /* RK_FMT_E4M3 or RK_FMT_E5M2 (8-bit caches; rk_attn_decode_noalloc: E4M3 only) */
+  int32_t kv_fmt;          /* RK_FMT_*: what rk_kv_cache_append writes, one code per byte.  E4M3 and E5M2 go through the
+                              tensor-core kernel; E2M3, E3M2 and E2M1 caches are converted by the threads of the
+                              mma.sync kernel (about two thirds of its speed).  rk_attn_decode_noalloc: E4M3 only */
   int32_t num_splits;      /* 0 = choose; otherwise 1..64 */
   void* workspace;         /* >= rk_attn_decode_workspace_bytes(), 16-byte aligned */
   size_t workspace_bytes;

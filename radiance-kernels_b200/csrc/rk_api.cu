@@ -453,7 +453,7 @@ static int check_decode_shape(const rk_decode_args* a) {
   const int grp = a->H / a->H_kv;
   if (grp != 1 && grp != 2 && grp != 4 && grp != 8) return RK_ERR_BAD_SHAPE;
   if (a->L % 4 != 0) return RK_ERR_BAD_SHAPE;   // keeps every scale-row copy a 16-byte multiple
-  if (a->kv_fmt != RK_FMT_E4M3 && a->kv_fmt != RK_FMT_E5M2) return RK_ERR_UNSUPPORTED;   // 8-bit caches only
+  if (a->kv_fmt < 0 || a->kv_fmt > RK_FMT_E2M1) return RK_ERR_BAD_FORMAT;
   if (a->num_splits < 0 || a->num_splits > 64 || a->softmax_scale < 0.0f) return RK_ERR_BAD_SHAPE;
   return RK_OK;
 }

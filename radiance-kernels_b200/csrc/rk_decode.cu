@@ -67,23 +67,43 @@ RK_DEVINL float e8m0_byte_to_f32(uint32_t word, int blk) {
   const uint32_t sh = blk < 3 ? (word << (23 - 8 * blk)) : (word >> 1);
   return __uint_as_float(sh & 0x7F800000u);
 }
-// two packed E4M3 (low 16 bits of x) -> f16x2, exact
-RK_DEVINL uint32_t e4m3x2_to_f16x2(uint32_t x) {
+// Element formats of the cache, one code per byte (FMT = RK_FMT_*).  EB / MB: exponent and mantissa bits; F = 127 - bias.
+template <int FMT> struct DecFmt;
+template <> struct DecFmt<0> { static constexpr int EB = 4, MB = 3, F = 120; };   // E4M3
+template <> struct DecFmt<1> { static constexpr int EB = 5, MB = 2, F = 112; };   // E5M2
+template <> struct DecFmt<2> { static constexpr int EB = 2, MB = 3, F = 126; };   // E2M3
+template <> struct DecFmt<3> { static constexpr int EB = 3, MB = 2, F = 124; };   // E3M2
+template <> struct DecFmt<4> { static constexpr int EB = 2, MB = 1, F = 126; };   // E2M1
+// four codes of a word -> f16x2 of codes 0,1 (HI = false) or 2,3 (HI = true), exact: one hardware conversion per
+// pair.  An E2M1 code (s ee m) is the E2M3 code (s ee m00) of the same value.
+template <int FMT, bool HI> RK_DEVINL uint32_t codes_to_f16x2(uint32_t x) {
   uint32_t r;
-  asm("{\n\t.reg .b16 lo, hi;\n\tmov.b32 {lo, hi}, %1;\n\tcvt.rn.f16x2.e4m3x2 %0, lo;\n\t}" : "=r"(r) : "r"(x));
+  if (FMT == 4) x = ((x & 0x08080808u) << 2) | ((x & 0x07070707u) << 2);
+  if (FMT == 0) {
+    if (HI) asm("{\n\t.reg .b16 lo, hi;\n\tmov.b32 {lo, hi}, %1;\n\tcvt.rn.f16x2.e4m3x2 %0, hi;\n\t}" : "=r"(r) : "r"(x));
+    else    asm("{\n\t.reg .b16 lo, hi;\n\tmov.b32 {lo, hi}, %1;\n\tcvt.rn.f16x2.e4m3x2 %0, lo;\n\t}" : "=r"(r) : "r"(x));
+  } else if (FMT == 1) {
+    if (HI) asm("{\n\t.reg .b16 lo, hi;\n\tmov.b32 {lo, hi}, %1;\n\tcvt.rn.f16x2.e5m2x2 %0, hi;\n\t}" : "=r"(r) : "r"(x));
+    else    asm("{\n\t.reg .b16 lo, hi;\n\tmov.b32 {lo, hi}, %1;\n\tcvt.rn.f16x2.e5m2x2 %0, lo;\n\t}" : "=r"(r) : "r"(x));
+  } else if (FMT == 3) {
+    if (HI) asm("{\n\t.reg .b16 lo, hi;\n\tmov.b32 {lo, hi}, %1;\n\tcvt.rn.f16x2.e3m2x2 %0, hi;\n\t}" : "=r"(r) : "r"(x));
+    else    asm("{\n\t.reg .b16 lo, hi;\n\tmov.b32 {lo, hi}, %1;\n\tcvt.rn.f16x2.e3m2x2 %0, lo;\n\t}" : "=r"(r) : "r"(x));
+  } else {
+    if (HI) asm("{\n\t.reg .b16 lo, hi;\n\tmov.b32 {lo, hi}, %1;\n\tcvt.rn.f16x2.e2m3x2 %0, hi;\n\t}" : "=r"(r) : "r"(x));
+    else    asm("{\n\t.reg .b16 lo, hi;\n\tmov.b32 {lo, hi}, %1;\n\tcvt.rn.f16x2.e2m3x2 %0, lo;\n\t}" : "=r"(r) : "r"(x));
+  }
   return r;
 }
-RK_DEVINL uint32_t e4m3x2_hi_to_f16x2(uint32_t x) {
+// z holds two codes in bytes 1 and 3 (bytes 0 and 2 arbitrary): each code c becomes the bf16 whose exponent
+// field starts with c's exponent field and whose mantissa starts with c's mantissa, i.e. value(c) * 2^-F
+// (normals and subnormals alike; for E4M3: sign | (c & 0x7F) << 4).
+template <int FMT> RK_DEVINL uint32_t hi_bytes_to_bf16x2_scaled(uint32_t z) {
+  using D = DecFmt<FMT>;
+  constexpr uint32_t kMag = (((1u << (D::EB + D::MB)) - 1u) << 8) * 0x00010001u;
+  const uint32_t mag = (z & kMag) >> (D::MB + 1);
+  const uint32_t sgn = z << (7 - D::EB - D::MB);          // the sign bit to bit 15 of its half
   uint32_t r;
-  asm("{\n\t.reg .b16 lo, hi;\n\tmov.b32 {lo, hi}, %1;\n\tcvt.rn.f16x2.e4m3x2 %0, hi;\n\t}" : "=r"(r) : "r"(x));
-  return r;
-}
-// z holds two E4M3 codes in bytes 1 and 3 (bytes 0 and 2 arbitrary): each code c becomes the bf16
-// with bits sign | (c & 0x7F) << 4, i.e. value(c) * 2^-120 (normals and subnormals alike).
-RK_DEVINL uint32_t e4m3_hi_bytes_to_bf16x2_scaled(uint32_t z) {
-  const uint32_t mag = (z & 0x7F007F00u) >> 4;
-  uint32_t r;
-  asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(r) : "r"(z), "r"(0x80008000u), "r"(mag));   // (z & C) | mag
+  asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(r) : "r"(sgn), "r"(0x80008000u), "r"(mag));   // (sgn & C) | mag
   return r;
 }
 RK_DEVINL uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
@@ -102,6 +122,7 @@ RK_DEVINL uint32_t ue8m0x2_to_bf16x2(uint32_t x) {
   return r;
 }
 
+template <int FMT>
 __global__ void __launch_bounds__(kDecThreads, 2)
 decode_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v, const DecodeParams p) {
   extern __shared__ __align__(1024) uint8_t dsmem_raw[];
@@ -230,7 +251,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant_
             for (int hh = 0; hh < 2; ++hh) {
               const int i = blk * 2 + hh;
               const uint32_t w = *reinterpret_cast<const uint32_t*>(rowp + ((i ^ (krow & 7)) << 4) + 4 * t);
-              mma_f16_16816(c, qa[i][0], 0u, qa[i][1], 0u, e4m3x2_to_f16x2(w), e4m3x2_hi_to_f16x2(w));
+              mma_f16_16816(c, qa[i][0], 0u, qa[i][1], 0u, codes_to_f16x2<FMT, false>(w), codes_to_f16x2<FMT, true>(w));
             }
             s0 = fmaf(c[0], e8m0_byte_to_f32(ksc, blk), s0);
             s1 = fmaf(c[1], e8m0_byte_to_f32(ksc1, blk), s1);
@@ -300,8 +321,9 @@ decode_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant_
             vref = vloc;
           }
         }
-        // bf16x2 of 2^(120 + 127 - vref): undoes the bit placement of V and moves P * 2^(sv-127) to the reference scale
-        const uint32_t two120 = ((uint32_t)(374 - vref) << 7) * 0x00010001u;
+        // bf16x2 of 2^(F + 127 - vref), F = 120 for E4M3: undoes the bit placement of V and moves P * 2^(sv-127) to the
+        // reference scale
+        const uint32_t two120 = ((uint32_t)(254 + DecFmt<FMT>::F - vref) << 7) * 0x00010001u;
         // ---------------- O += P V, two k-steps of 16 keys ----------------
   #pragma unroll
         for (int ks = 0; ks < 2; ++ks) {
@@ -332,8 +354,8 @@ decode_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant_
             for (int e = 0; e < 4; ++e) {
               // bytes e of the two rows -> byte 1 and byte 3 of the fragment register
               const uint32_t sel = 0x4000u * 0 + ((4u + e) << 12) + ((uint32_t)e << 4);   // {b3,b2,b1,b0} = {w1[e], x, w0[e], x}
-              const uint32_t b0 = e4m3_hi_bytes_to_bf16x2_scaled(prmt(w0, w1, sel));
-              const uint32_t b1 = e4m3_hi_bytes_to_bf16x2_scaled(prmt(w8, w9, sel));
+              const uint32_t b0 = hi_bytes_to_bf16x2_scaled<FMT>(prmt(w0, w1, sel));
+              const uint32_t b1 = hi_bytes_to_bf16x2_scaled<FMT>(prmt(w8, w9, sel));
               mma_bf16_16816(oacc[grp][e], a0, 0u, a2, 0u, b0, b1);
             }
           }
@@ -422,7 +444,8 @@ namespace rk {
 // else (and a forced choice through the test hook: 1 = mma.sync kernel, 2 = tcgen05 kernel) takes the mma.sync kernel.
 int g_decode_path = 0;
 bool decode_uses_tc(const rk_decode_args& a) {
-  const bool can = a.d == 128 && a.H_kv > 0 && a.H / a.H_kv <= dtc::kMaxGrp;
+  // 6-bit and 4-bit caches hold one code per byte, which the tensor core does not read: the mma.sync kernel converts them
+  const bool can = a.d == 128 && a.H_kv > 0 && a.H / a.H_kv <= dtc::kMaxGrp && a.kv_fmt <= RK_FMT_E5M2;
   if (g_decode_path == 1) return false;
   return can;
 }
@@ -446,7 +469,6 @@ int launch_decode(const rk_decode_args& a, int nsplit, cudaStream_t st) {
   p.scale_log2 = scale * 1.4426950408889634f;
   cudaError_t e;
   dim3 grid(nsplit, a.H_kv, a.B);
-  if (!decode_uses_tc(a) && a.kv_fmt != RK_FMT_E4M3) return RK_ERR_UNSUPPORTED;   // the mma.sync kernel converts E4M3 bytes itself
   if (decode_uses_tc(a)) {
     DecodeTcParams t;
     t.q = p.q; t.k_scale = p.k_scale; t.v_scale = p.v_scale; t.kv_len = p.kv_len;
@@ -464,9 +486,11 @@ int launch_decode(const rk_decode_args& a, int nsplit, cudaStream_t st) {
     kern<<<grid, dtc::kThreads, smem_bytes, st>>>(tk, tv, t, idesc_qk, idesc_pv);
     if (g_ev_before && g_ev_after) cudaEventRecord(g_ev_after, st);
   } else {
-    if ((e = cudaFuncSetAttribute(decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDecSmemBytes)) != cudaSuccess) return (int)e;
+    auto kern = a.kv_fmt == RK_FMT_E5M2 ? decode_kernel<1> : a.kv_fmt == RK_FMT_E2M3 ? decode_kernel<2> :
+                a.kv_fmt == RK_FMT_E3M2 ? decode_kernel<3> : a.kv_fmt == RK_FMT_E2M1 ? decode_kernel<4> : decode_kernel<0>;
+    if ((e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kDecSmemBytes)) != cudaSuccess) return (int)e;
     if (g_ev_before && g_ev_after) cudaEventRecord(g_ev_before, st);
-    decode_kernel<<<grid, kDecThreads, kDecSmemBytes, st>>>(tk, tv, p);
+    kern<<<grid, kDecThreads, kDecSmemBytes, st>>>(tk, tv, p);
     if (g_ev_before && g_ev_after) cudaEventRecord(g_ev_after, st);
   }
   if ((e = cudaGetLastError()) != cudaSuccess) return (int)e;
@@ -593,8 +617,8 @@ int launch_decode_noalloc(const rk_decode_args& a, cudaStream_t st) {
   p.B = a.B; p.H = a.H; p.H_kv = a.H_kv; p.L = a.L; p.grp = a.H / a.H_kv; p.nsplit = nsplit;
   const float scale = a.softmax_scale > 0.0f ? a.softmax_scale : 1.0f / sqrtf((float)a.d);
   p.scale_log2 = scale * 1.4426950408889634f;
-  if ((e = cudaFuncSetAttribute(decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDecSmemBytes)) != cudaSuccess) return (int)e;
-  decode_kernel<<<dim3(nsplit, a.H_kv, a.B), kDecThreads, kDecSmemBytes, st>>>(tk, tv, p);
+  if ((e = cudaFuncSetAttribute(decode_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, kDecSmemBytes)) != cudaSuccess) return (int)e;
+  decode_kernel<0><<<dim3(nsplit, a.H_kv, a.B), kDecThreads, kDecSmemBytes, st>>>(tk, tv, p);
   if ((e = cudaGetLastError()) != cudaSuccess) return (int)e;
   decode_combine_kernel<<<(int)((BH + 3) / 4), 128, 0, st>>>(p.part_o, p.part_ml, nsplit, (int)BH,
                                                             reinterpret_cast<__nv_bfloat16*>(a.o), a.lse);

@@ -86,8 +86,8 @@ def test_decode_argument_errors():
     assert L.rk_attn_decode(C.byref(a), None) == -2
     a.H, a.L = 8, 1022
     assert L.rk_attn_decode(C.byref(a), None) == -2
-    a.L, a.kv_fmt = 1024, 2                               # 8-bit caches only (E4M3, E5M2)
-    assert L.rk_attn_decode(C.byref(a), None) == -6
+    a.L, a.kv_fmt = 1024, 5                               # no such format
+    assert L.rk_attn_decode(C.byref(a), None) == -3
     a.kv_fmt, a.num_splits = 0, 3
     assert L.rk_attn_decode_num_splits(C.byref(a)) == 3
     assert L.rk_attn_decode_workspace_bytes(C.byref(a)) == 2 * 8 * 3 * 130 * 4

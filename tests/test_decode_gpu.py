@@ -28,7 +28,8 @@ def run(B, H, Hkv, L, lens=None, seed=0, num_splits=0, want_lse=False, vmul=1.0,
     got = np_(o.float())
     assert np.isfinite(got).all()
     ma, rl = errors(got, ref["o_f32"])
-    assert ma <= MAX_ABS and rl <= REL_L2, (ma, rl)
+    big = max(1.0, float(np.abs(ref["o_f32"]).max()))        # output magnitudes follow V's: the absolute bound with them
+    assert ma <= MAX_ABS * big and rl <= REL_L2, (ma, rl)
     if want_lse:
         assert np.abs(np_(lse) - ref["lse"]).max() < 2e-3
     return got, ref
@@ -45,6 +46,25 @@ def test_e5m2_cache(grp):
     to block-scaled MMAs, so the cache format is one field of the instruction descriptor."""
     run(2, 2 * grp, 2, 2048, seed=60 + grp, kv_fmt=rk.E5M2, want_lse=True)
     run(2, 2 * grp, 2, 1000, lens=[1000, 37], seed=70 + grp, kv_fmt=rk.E5M2)
+
+
+@pytest.mark.parametrize("fmt", [rk.E2M3, rk.E3M2, rk.E2M1])
+def test_six_and_four_bit_caches(fmt):
+    """Caches in the 6-bit and 4-bit formats rk_kv_cache_append can write (one code per byte): the tensor core does
+    not read that form, so these go through the kernel whose threads convert the codes (hardware conversions to f16 for
+    K, bit placement into bf16 for V)."""
+    run(2, 8, 2, 2048, seed=80 + fmt, kv_fmt=fmt, want_lse=True)
+    run(2, 16, 2, 1000, lens=[1000, 37], seed=90 + fmt, kv_fmt=fmt)
+    run(1, 2, 2, 512, seed=95 + fmt, kv_fmt=fmt, vmul=300.0)            # large V block scales
+
+
+def test_e5m2_cache_through_the_converting_kernel():
+    """The same E5M2 cache through the mma.sync kernel (test hook), which is templated on the cache format."""
+    try:
+        rk.lib().rk_debug_set_decode_path(1)
+        run(2, 8, 2, 2048, seed=61, kv_fmt=rk.E5M2, want_lse=True)
+    finally:
+        rk.lib().rk_debug_set_decode_path(0)
 
 
 def test_llama_shape_small_batch():
