@@ -139,13 +139,7 @@ __device__ __forceinline__ void softmax_rows(const PrefillParams& p, uint8_t* sm
     // ---- (soft-cap,) mask, block max ---------------------------------------------------------------
     // Without a cap the max is taken on the raw scores (the scale is positive) and the scale is folded
     // into the exponent's FMA; with a cap s[] is replaced by the capped score in the log2 domain.
-    if (SOFTCAP) {
-      // cap * tanh(s * scale / cap), pre-multiplied by log2 e (softcap_pair)
-      const float k2 = 2.0f * 1.4426950408889634f * p.inv_cap_scale;
-      const uint64_t one2 = pack2(1.0f, 1.0f), m2cap2 = pack2(-2.0f * p.cap_log2, -2.0f * p.cap_log2), cap2 = pack2(p.cap_log2, p.cap_log2);
-#pragma unroll
-      for (int c = 0; c < 32; c += 2) softcap_pair(s[c], s[c + 1], k2, one2, m2cap2, cap2);
-    }
+    if (SOFTCAP) softcap_scores(s, p.scale_log2, p.cap_log2, p.inv_cap_scale);   // cap * tanh(s * scale / cap), pre-multiplied by log2 e
     if (need_mask) {
 #pragma unroll
       for (int c = 0; c < 32; ++c) s[c] = (part * 32 + c > hi || part * 32 + c <= lo) ? NEG_INF : s[c];

@@ -89,6 +89,45 @@ RK_DEVINL void softcap_pair(float& s0, float& s1, float k2, uint64_t one2, uint6
   unpack2(fma2p(r, m2cap2, cap2), s0, s1);                              // cap_log2 * (1 - 2 r)
 }
 
+RK_DEVINL float fmin3(float a, float b, float c) { float d; asm("min.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c)); return d; }
+RK_DEVINL uint64_t mul2p(uint64_t a, uint64_t b) { uint64_t d; asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b)); return d; }
+
+// The soft cap of a whole set of scores, in place: s <- cap_log2 * tanh(s * scale / cap).
+// While every |s * scale / cap| of the warp's scores is at most 1/8 (logits of a model that caps at 50 are two orders
+// of magnitude below that) tanh is its series y - y^3/3 + 2 y^5/15 - 17 y^7/315 (next term below 1.4e-9 of y),
+// evaluated in s^2 with the constants folded into the coefficients: five packed FMA-pipe operations per pair of
+// scores and no special-function operation, against an exponential and a Newton reciprocal per score in
+// softcap_pair, which is kept for the scores that are not small (the decision is per warp and per key tile).
+template <int N>
+RK_DEVINL void softcap_scores(float (&s)[N], float scale_log2, float cap_log2, float inv_cap_scale) {
+  static_assert(N % 2 == 0 && N >= 4, "pairs");
+  float hi = fmax3(s[0], s[1], s[2]), lo = fmin3(s[0], s[1], s[2]);
+#pragma unroll
+  for (int c = 3; c + 1 < N; c += 2) { hi = fmax3(hi, s[c], s[c + 1]); lo = fmin3(lo, s[c], s[c + 1]); }
+  hi = fmaxf(hi, s[N - 1]); lo = fminf(lo, s[N - 1]);
+  const bool small = fmaxf(hi, -lo) * inv_cap_scale <= 0.125f;          // false for NaN
+  if (__all_sync(0xffffffffu, small)) {
+    const float q = inv_cap_scale * inv_cap_scale;
+    const float c1 = -0.3333333333f * q * scale_log2, c2 = 0.1333333333f * q * q * scale_log2,
+                c3 = -0.05396825397f * q * q * q * scale_log2;
+    const uint64_t k1 = pack2(c1, c1), k2 = pack2(c2, c2), k3 = pack2(c3, c3), a2 = pack2(scale_log2, scale_log2);
+#pragma unroll
+    for (int c = 0; c < N; c += 2) {
+      const uint64_t v = pack2(s[c], s[c + 1]);
+      const uint64_t z = mul2p(v, v);
+      uint64_t t = fma2p(z, k3, k2);
+      t = fma2p(z, t, k1);
+      t = fma2p(z, t, a2);
+      unpack2(mul2p(v, t), s[c], s[c + 1]);
+    }
+  } else {
+    const float k2 = 2.0f * 1.4426950408889634f * inv_cap_scale;
+    const uint64_t one2 = pack2(1.0f, 1.0f), m2cap2 = pack2(-2.0f * cap_log2, -2.0f * cap_log2), cap2 = pack2(cap_log2, cap_log2);
+#pragma unroll
+    for (int c = 0; c < N; c += 2) softcap_pair(s[c], s[c + 1], k2, one2, m2cap2, cap2);
+  }
+}
+
 // two ints (0..255 each) into bytes 1:0 of the result, bytes 3:2 taken from the low half of c
 RK_DEVINL uint32_t pack_u8x2(uint32_t hi, uint32_t lo, uint32_t c) {
   uint32_t d; asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(hi), "r"(lo), "r"(c)); return d;

@@ -128,13 +128,7 @@ __device__ __forceinline__ void softmax_row_group(const PrefillParams& p, uint8_
     const bool tail = (key0 + kBlockN > p.S_kv);
     const bool diag = p.causal && (key0 + kBlockN - 1 > p.q_pos0 + qt * kBlockM);
     const bool need_mask = !PLAIN && (tail || diag || (p.window > 0));
-    if (SOFTCAP) {
-      // cap * tanh(s * scale / cap), pre-multiplied by log2 e (softcap_pair)
-      const float k2 = 2.0f * 1.4426950408889634f * p.inv_cap_scale;
-      const uint64_t one2 = pack2(1.0f, 1.0f), m2cap2 = pack2(-2.0f * p.cap_log2, -2.0f * p.cap_log2), cap2 = pack2(p.cap_log2, p.cap_log2);
-#pragma unroll
-      for (int c = 0; c < 128; c += 2) softcap_pair(s[c], s[c + 1], k2, one2, m2cap2, cap2);
-    }
+    if (SOFTCAP) softcap_scores(s, p.scale_log2, p.cap_log2, p.inv_cap_scale);   // cap * tanh(s * scale / cap), pre-multiplied by log2 e
     if (__builtin_expect(need_mask, 0)) {
       int hi = p.S_kv - 1 - key0;                             // masked iff c > hi || c <= lo
       if (p.causal) hi = min(hi, q_pos - key0);

@@ -49,6 +49,15 @@ def test_gemma_reference_style_cap_bites_window():
     _check(prefill_vs_oracle(1, 8, 4, 256, 512, 256, causal=True, softcap=50.0, qmul=50.0, q_pos0=256, window=128))
 
 
+@pytest.mark.parametrize("d", [128, 256])
+def test_softcap_scores_on_both_sides_of_the_series_limit(d):
+    """The capped kernels evaluate tanh by its series while a warp's scores of a key tile stay below cap / 8 and by
+    the exponential form otherwise: with Q scaled by 1.6 the largest |score| of a tile lies around that limit
+    (6.25 at cap 50), so both forms run inside one launch and must meet the oracle's tanh."""
+    _check(prefill_vs_oracle(1, 4, 2, 640, 640, d, causal=True, softcap=50.0, qmul=1.6, seed=23))
+    _check(prefill_vs_oracle(1, 2, 2, 384, 384, d, causal=False, softcap=30.0, qmul=1.0, seed=24))
+
+
 def test_sliding_window_d128():
     _check(prefill_vs_oracle(1, 2, 1, 640, 640, 128, causal=True, window=200, seed=4))
 
