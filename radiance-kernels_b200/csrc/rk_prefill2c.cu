@@ -71,6 +71,15 @@ RK_DEVINL void perturb(const PrefillParams& p, int role, int j) {
 // kernel.  The loop over plain tiles is what runs nearly all the time, and it is kept small and contiguous: this
 // kernel's softmax warps stall on instruction fetch, and code that sits inside the loop costs time even when it
 // is jumped over.
+// The blocking form of the two waits a key tile starts with (its S, and the P buffer it will write): out of line, so
+// that the tile body carries only the test of two flags.  Returns 0, or the code of the wait that gave up.
+__device__ __forceinline__ int wait_tile_inputs(uint64_t* s_full, uint32_t s_parity, uint64_t* pv_done, uint32_t pv_parity,
+                                             int need_pv, volatile int* abort_flag) {
+  if (!mbar_wait_lean(s_full, s_parity, abort_flag)) return 101;
+  if (need_pv && !mbar_wait_lean(pv_done, pv_parity, abort_flag)) return 102;
+  return 0;
+}
+
 template <bool SOFTCAP, bool DUMP>
 __device__ __forceinline__ void softmax_row_group(const PrefillParams& p, uint8_t* smem, uint64_t* bars, uint32_t tmem_base,
                                                   volatile int* abort_flag, int grp, int qt, int bh, int n_tiles, int j0) {
@@ -94,7 +103,7 @@ __device__ __forceinline__ void softmax_row_group(const PrefillParams& p, uint8_
 
   float m_run = NEG_INF, l_run = 0.0f;
   bool ok = true;
-  bool s_ready = false;       // result of an early, non-blocking test of the next tile's S barrier
+  bool s_ready = false;       // results of early, non-blocking tests of the next tile's S barrier and P buffer
   int fail = 0;               // which wait gave up (reported after the loops: the tile body carries no reporting code)
 
   auto tile = [&](const int j, auto plain_tag) -> bool {
@@ -103,8 +112,9 @@ __device__ __forceinline__ void softmax_row_group(const PrefillParams& p, uint8_
     perturb(p, kPerturbSoftmaxA + grp, j);
     const bool stamp = (quad == 0 && lane == 0);
     if (stamp) RK_STAMP(grp, j, 0);
-    if (__builtin_expect(!__all_sync(0xffffffffu, s_ready), 0)) {   // the test issued during the previous tile said "not yet"
-      if (!__all_sync(0xffffffffu, mbar_wait_lean(s_full, j & 1, abort_flag))) { fail = 101; return false; }
+    if (__builtin_expect(!__all_sync(0xffffffffu, s_ready), 0)) {   // a test issued during the previous tile said "not yet"
+      const int w = wait_tile_inputs(s_full, j & 1, &pv_done[pb], ((j - 2) >> 1) & 1, j >= 2, abort_flag);
+      if (__any_sync(0xffffffffu, w != 0)) { fail = w ? w : 101; return false; }
     }
     tc_fence_after();
     if (stamp) RK_STAMP(grp, j, 1);
@@ -168,15 +178,12 @@ __device__ __forceinline__ void softmax_row_group(const PrefillParams& p, uint8_
     const float corr = (m_run == NEG_INF) ? 1.0f : ex2_approx(m_run - m_new);
     m_run = m_new;
     // The correction warp of this lane quadrant can start on O while the exponentials run here.  Slot j & 3: this
-    // group is never more than two tiles ahead of the correction warp (the wait for the P buffer below sees to
-    // that), so a slot is free again long before it comes round.
+    // group is never more than two tiles ahead of the correction warp (the wait for the P buffer at the top of the
+    // tile sees to that), so a slot is free again long before it comes round.
     corr_sm[(j & 3) * 128 + row] = corr;
     __syncwarp();
     if (lane == 0) mbar_arrive(&corr_full[(j & 3) * 4 + quad]);
     if (stamp) RK_STAMP(grp, j, 3);
-    // The P buffer and its scale atom are free once the P.V that read them two tiles ago has finished: tested
-    // here without blocking (the answer takes a few hundred cycles to come back), waited for only if it said no.
-    const bool p_free = (j < 2) || mbar_test_wait(&pv_done[pb], ((j - 2) >> 1) & 1);
 
     // ---- p = 2^(x - m), row sum from the unquantised p, requant per 32-key block ---------------------
     // ex2.approx.ftz never returns a subnormal, so every non-zero p has an exponent field >= 1 and one multiply by
@@ -221,9 +228,6 @@ __device__ __forceinline__ void softmax_row_group(const PrefillParams& p, uint8_
     };
 #pragma unroll
     for (int c = 0; c < 32; c += 4) exp4(0, c);
-    if (__builtin_expect(!__all_sync(0xffffffffu, p_free), 0)) {
-      if (!__all_sync(0xffffffffu, mbar_wait_lean(&pv_done[pb], ((j - 2) >> 1) & 1, abort_flag))) { fail = 102; return false; }
-    }
 #pragma unroll
     for (int g = 0; g < 4; ++g) {
       uint32_t w[8];
@@ -253,8 +257,10 @@ __device__ __forceinline__ void softmax_row_group(const PrefillParams& p, uint8_
       }
       d32[128 * 32 + row] = scale_word;
     }
-    // a look ahead at the next tile's S barrier: asked here, used at the top of the next tile
-    s_ready = (j + 1 < n_tiles) && mbar_test_wait(s_full, (j + 1) & 1);
+    // a look ahead at the next tile's S barrier and at its P buffer (free once the P.V that read it two tiles
+    // before has finished): asked here, used at the top of the next tile
+    s_ready = (j + 1 < n_tiles) && mbar_test_wait(s_full, (j + 1) & 1) &&
+              (j < 1 || mbar_test_wait(&pv_done[(j + 1) & 1], ((j - 1) >> 1) & 1));
     if (stamp) RK_STAMP(grp, j, 4);
     fence_proxy_async_smem();
     __syncwarp();
