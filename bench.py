@@ -54,7 +54,7 @@ def prefill_algorithmic_bytes(c):
 
 # DRAM traffic of one launch from the ncu captures summarised under profiles/ (dram__bytes_read.sum +
 # dram__bytes_write.sum), per unit of work; both kernels' traffic is proportional to the unit count.
-NCU_PREFILL_DRAM_BYTES_PER_HEAD = (170.424064e6 + 33.314560e6) / 64         # S=4096, d=128, causal
+NCU_PREFILL_DRAM_BYTES_PER_HEAD = (158.141440e6 + 38.027776e6) / 64         # S=4096, d=128, causal
 NCU_DECODE_DRAM_BYTES_PER_SEQUENCE = (553.775104e6 + 6.571264e6) / 8        # H_kv=8, L=32768, d=128
 
 
@@ -426,7 +426,7 @@ def run_ours(args, rank, world, local, windows):
     roofline = {"bound": "tensor", "achieved": achieved, "peak": peak_burst, "unit": "TFLOP/s",
                 "frac": achieved / peak_burst,
                 "traffic": NCU_PREFILL_DRAM_BYTES_PER_HEAD * c["B"] * c["H"] if (c["S"], c["d"]) == (4096, 128) else None,
-                "traffic_note": "ncu dram read+write of one launch at B=4 (203.74 MB for 64 (batch, head) units), scaled by "
+                "traffic_note": "ncu dram read+write of one launch at B=4 (196.17 MB for 64 (batch, head) units), scaled by "
                                 "the unit count; algorithmic bytes per launch: %d" % prefill_algorithmic_bytes(c),
                 "kernel": "prefill2c_kernel<false>", "kernel_ms": kern_ms,
                 "peak_measured_mxfp8": mma_peak,
