@@ -503,7 +503,17 @@ RK_DEVINL void retile_rowscales_body(const uint8_t* __restrict__ in, int64_t bat
   const int64_t total = batch * ntile * dch * 128;
   for (int64_t t = tid; t < total; t += nthreads) {
     const int r = (int)(t % 128);
-    const int64_t atom = t / 128, ch = atom % dch, tile = (atom / dch) % ntile, bt = atom / (dch * ntile);
+    const int64_t atom = t / 128;
+    int64_t ch, tile, bt;
+    if (total < (int64_t)1 << 31) {           // 32-bit divisions whenever the index fits
+      const uint32_t a32 = (uint32_t)atom, q = a32 / (uint32_t)dch;
+      ch = a32 - q * (uint32_t)dch;
+      const uint32_t b32 = q / (uint32_t)ntile;
+      tile = q - b32 * (uint32_t)ntile;
+      bt = b32;
+    } else {
+      ch = atom % dch; tile = (atom / dch) % ntile; bt = atom / (dch * ntile);
+    }
     const int64_t row = tile * 128 + r;
     uint32_t w = 0;
 #pragma unroll
@@ -544,7 +554,18 @@ __global__ void __launch_bounds__(128, 4) rebase_v_kernel(const uint8_t* __restr
     const int64_t u = w * 8 + (lane & 7);
     const bool valid = u < units;
     const int64_t uu = valid ? u : 0;
-    const int64_t c16 = uu % c16n, kb = (uu / c16n) % nkb, bt = uu / (c16n * nkb);
+    // unit index -> (batch, key block, column group): in 32 bits whenever it fits (a 64-bit division by a run-time
+    // value is about a hundred instructions, and there are three of them per unit)
+    int64_t c16, kb, bt;
+    if (units < (int64_t)1 << 31) {
+      const uint32_t u32 = (uint32_t)uu, q = u32 / (uint32_t)c16n;
+      c16 = u32 - q * (uint32_t)c16n;
+      const uint32_t b32 = q / (uint32_t)nkb;
+      kb = q - b32 * (uint32_t)nkb;
+      bt = b32;
+    } else {
+      c16 = uu % c16n; kb = (uu / c16n) % nkb; bt = uu / (c16n * nkb);
+    }
     const int64_t r0 = kb * 32;
     const int n = valid ? (int)min((int64_t)32, S - r0) : 0;      // keys of this block that exist
     const uint8_t* cb = codes + (bt * S + r0) * d + c16 * 16;
