@@ -217,16 +217,18 @@ def test_decode_ignores_poisoned_cache_past_kv_len():
     assert ma <= MAX_ABS and rl <= REL_L2, (ma, rl)
 
 
-def test_kv_cache_append_then_decode_in_a_loop():
+@pytest.mark.parametrize("fmt", [rk.E4M3, rk.E3M2, rk.E2M1])
+def test_kv_cache_append_then_decode_in_a_loop(fmt):
     """Tokens appended one at a time give the cache that quantizing the whole tensor gives (bit for bit, and equal
-    to the CPU oracle's rows); decode over the growing cache matches the oracle at every length tried."""
+    to the CPU oracle's rows); decode over the growing cache matches the oracle at every length tried.  Every format
+    the append kernel writes is one the decode entry point reads."""
     B, Hkv, H, L, d, T = 2, 2, 8, 160, 128, 150
     g = torch.Generator(device="cuda").manual_seed(31)
     K = torch.randn(B, Hkv, L, d, generator=g, device="cuda")
     V = torch.randn(B, Hkv, L, d, generator=g, device="cuda") * 3.0
     q = torch.randn(B, H, d, generator=g, device="cuda").bfloat16()
-    kc_all, ks_all = rk.mx_quantize(K)
-    vc_all, vs_all = rk.mx_quantize(V)
+    kc_all, ks_all = rk.mx_quantize(K, fmt)
+    vc_all, vs_all = rk.mx_quantize(V, fmt)
     kc = torch.full((B, Hkv, L, d), 0x7F, dtype=torch.uint8, device="cuda")      # unwritten rows are poison
     vc = torch.full_like(kc, 0x7F)
     ks = torch.full((B, Hkv, L, d // 32), 0xFF, dtype=torch.uint8, device="cuda")
@@ -234,15 +236,15 @@ def test_kv_cache_append_then_decode_in_a_loop():
     lens = [0, 0]
     for t in range(T):
         pos = torch.tensor([t, t if t < 100 else -1], dtype=torch.int32, device="cuda")   # sequence 1 stops at 100 tokens
-        rk.kv_cache_append(K[:, :, t].contiguous(), V[:, :, t].contiguous(), pos, kc, ks, vc, vs)
+        rk.kv_cache_append(K[:, :, t].contiguous(), V[:, :, t].contiguous(), pos, kc, ks, vc, vs, fmt=fmt)
         lens = [t + 1, min(t + 1, 100)]
         if t in (0, 31, 99, 127, 128, T - 1):
             kl = torch.tensor(lens, dtype=torch.int32, device="cuda")
-            o = rk.attn_decode(q, kc, vc, ks, vs, kv_len=kl)
+            o = rk.attn_decode(q, kc, vc, ks, vs, kv_len=kl, kv_fmt=fmt)
             torch.cuda.synchronize()
             assert rk.last_device_status() == 0
             ref = oracle.attn_decode(np_(q.view(torch.uint16)), np_(kc_all), np_(vc_all), np_(ks_all), np_(vs_all),
-                                     softmax_scale=d ** -0.5, kv_len=np.array(lens, np.int32))
+                                     softmax_scale=d ** -0.5, kv_len=np.array(lens, np.int32), kv_fmt=fmt)
             got = np_(o.float())
             assert np.isfinite(got).all()
             ma, rl = errors(got, ref["o_f32"])
@@ -250,5 +252,5 @@ def test_kv_cache_append_then_decode_in_a_loop():
     assert torch.equal(kc[0, :, :T], kc_all[0, :, :T]) and torch.equal(ks[0, :, :T], ks_all[0, :, :T])
     assert torch.equal(vc[0, :, :T], vc_all[0, :, :T]) and torch.equal(vs[0, :, :T], vs_all[0, :, :T])
     assert torch.equal(kc[1, :, :100], kc_all[1, :, :100]) and bool((kc[1, :, 100:] == 0x7F).all())
-    oc, os_ = oracle.quantize(np_(V[0, 0, :T]), axis=1)
+    oc, os_ = oracle.quantize(np_(V[0, 0, :T]), axis=1, fmt=fmt)
     assert np.array_equal(np_(vc[0, 0, :T]), oc) and np.array_equal(np_(vs[0, 0, :T]), os_)
