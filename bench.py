@@ -411,6 +411,12 @@ def run_ours(args, rank, world, local, windows):
                     "sustained_seconds": sus_ms * n_sus * 1e-3,
                     "what": "tcgen05.mma kind::mxf8f6f4.block_scale M=128 N=128 K=32, operands and scales resident in shared "
                             "memory / TMEM, one CTA per SM, no TMA and no softmax in the loop"}
+        code = rk.last_device_status()                                # reads and clears the device status word
+        if code != 0:
+            # the measurement aid gave up on a bounded wait: its figures are void, the product kernels are not
+            # affected (later launches run normally once the word is cleared); fall back to the 2 x bf16 proxy
+            sys.stderr.write(f"tensor-pipe ceiling loop: device status {code}, measured ceiling dropped\n")
+            mma_peak = None
         # the attention kernel for at least 2 s: its sustained speed and the clock it ran at
         n_long = max(args.steps, int(2200.0 / ms_step))
         t0 = time.time()
@@ -535,8 +541,9 @@ def run_ours(args, rank, world, local, windows):
                                "traffic_note": "ncu dram read+write of one launch at B=8 (560.35 MB), scaled by B",
                                "kernel": "decode_tc_kernel", "kernel_ms": dk, "frac_of_nominal": by / (dk * 1e-3) / 1e9 / NOMINAL_HBM_GBS,
                                "peak_note": f"{peaks['source']} HBM copy bandwidth; nominal {NOMINAL_HBM_GBS:.0f} GB/s"}}
-        if rk.last_device_status() != 0:
-            raise SystemExit("device status non-zero after the decode leg")
+        code = rk.last_device_status()
+        if code != 0:
+            raise SystemExit(f"device status {code} after the decode leg (a bounded device-side wait gave up)")
         launches += args.steps * 2
         del kcd, vcd, ksd, vsd
 
@@ -717,8 +724,9 @@ def run_extras(rk, L, dev, peaks, peak_burst, timed, kernel_ms, qc, qs, vc, vs):
     out["decode_B64_H64_kv8_L32768"] = {"roofline": {"bound": "hbm", "achieved": by / (km * 1e-3) / 1e9, "peak": peaks["hbm"],
                                                      "unit": "GB/s", "frac": by / (km * 1e-3) / 1e9 / peaks["hbm"], "kernel_ms": km,
                                                      "traffic": None}}
-    if rk.last_device_status() != 0:
-        raise SystemExit("device status non-zero after the extra configurations")
+    code = rk.last_device_status()
+    if code != 0:
+        raise SystemExit(f"device status {code} after the extra configurations (a bounded device-side wait gave up)")
     return out
 
 

@@ -26,14 +26,14 @@ mxfp8_mma_loop_kernel(const uint8_t* __restrict__ a_tile, const uint8_t* __restr
   using namespace peak;
   extern __shared__ __align__(1024) uint8_t peak_smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(peak_smem_raw) + 1023) & ~(uintptr_t)1023);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + bar_off);       // [0] loads, [1] drain, [2] pacing
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + bar_off);       // [0] loads, [1] drain, [2], [3] pacing
   uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(smem + misc_off);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + misc_off + 4);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (*reinterpret_cast<volatile int*>(status) != 0) return;
 
   if (threadIdx.x == 0) {
-    mbar_init(&bars[0], 1); mbar_init(&bars[1], 1); mbar_init(&bars[2], 1);
+    mbar_init(&bars[0], 1); mbar_init(&bars[1], 1); mbar_init(&bars[2], 1); mbar_init(&bars[3], 1);
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -56,7 +56,7 @@ mxfp8_mma_loop_kernel(const uint8_t* __restrict__ a_tile, const uint8_t* __restr
       const uint32_t sfa = tmem_base + 256, sfb = tmem_base + 260;
       tc_cp_32x128b_warpx4(sfa, make_smem_desc(smem_u32(smem + sf_off), 0, 128, kLayoutNone));
       tc_cp_32x128b_warpx4(sfb, make_smem_desc(smem_u32(smem + sf_off + 512), 0, 128, kLayoutNone));
-      uint32_t pace_phase = 0;
+      uint32_t batch = 0;            // batches of 64 products committed so far
       for (int i = 0; i < iters && ok; ++i) {
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk) {
@@ -64,10 +64,15 @@ mxfp8_mma_loop_kernel(const uint8_t* __restrict__ a_tile, const uint8_t* __restr
           const uint64_t bdesc = make_smem_desc(b_addr + kk * 32, 16, 1024, kLayoutSw128);
           mma_mxf8f6f4_ss(tmem_base + (i & 1) * 128, adesc, bdesc, idesc_with_sf(idesc, kk, kk), sfa, sfb, kk > 0 ? 1u : 0u);
         }
-        // every 64 products: wait for the ones issued 64 products ago, so the queue of outstanding work stays bounded
+        // Every 64 products: wait for the batch issued before this one, so the queue of outstanding work stays
+        // bounded.  Batch k commits to pacing barrier k & 1 and is waited for before batch k + 2 commits to the
+        // same barrier: a barrier never completes two phases unobserved.  (With both batches on one barrier a
+        // parity wait saw the phase it asked for AND the next one completed once in ~10 000 launches, read that as
+        // "not yet" and ran into its limit.)
         if ((i & 63) == 63) {
-          tc_commit(&bars[2]);
-          if (i >= 127) { ok = mbar_wait(&bars[2], pace_phase & 1, abort_flag, status, 802); ++pace_phase; }
+          tc_commit(&bars[2 + (batch & 1)]);
+          if (batch >= 1) ok = mbar_wait(&bars[2 + ((batch - 1) & 1)], ((batch - 1) >> 1) & 1, abort_flag, status, 802);
+          ++batch;
         }
       }
       tc_commit(&bars[1]);
