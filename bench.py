@@ -483,6 +483,13 @@ def run_ours(args, rank, world, local, windows):
                    copy_ceiling_note="pinned cudaMemcpyAsync of the step's input bytes in and output bytes out on two streams, "
                                      "all ranks at once, no compute")
         del runner, host, dsts
+    code = rk.last_device_status()
+    if code != 0:       # the long loop or the end-to-end leg: reported with the line, the device-resident numbers above stand
+        sys.stderr.write(f"device status {code} after the sustained loop / end-to-end leg (a bounded device-side wait gave up)\n")
+        if e2e is not None:
+            e2e["device_status"] = code
+        if sustained is not None:
+            sustained["device_status"] = code
     launches = args.steps * 2          # per step: the V re-blocking launch (which also re-tiles the Q and K scales) and the attention kernel
 
     # ---- one global batch sharded over the ranks by (batch, KV head) units (N > 1) ------------------------------
@@ -726,7 +733,9 @@ def run_extras(rk, L, dev, peaks, peak_burst, timed, kernel_ms, qc, qs, vc, vs):
                                                      "traffic": None}}
     code = rk.last_device_status()
     if code != 0:
-        raise SystemExit(f"device status {code} after the extra configurations (a bounded device-side wait gave up)")
+        # reported, not fatal for the headline line: the word is cleared by reading it and later launches run normally
+        sys.stderr.write(f"device status {code} after the extra configurations (a bounded device-side wait gave up)\n")
+        out["device_status"] = code
     return out
 
 
