@@ -96,3 +96,23 @@ def test_schedule_perturbation_leaves_every_bit_of_o(shape):
     finally:
         L.rk_debug_set_prefill_perturb(0)
     assert rk.last_device_status() == 0
+
+
+def test_tensor_pipe_ceiling_loop_never_runs_into_its_waits():
+    """The GEMM-only loop bench.py measures the tensor-pipe ceiling with paces itself through two alternating
+    mbarriers (one barrier per batch in flight: a barrier that completes two phases before its waiter looks reads as
+    "not yet", and a single pacing barrier did that about once in 10 000 launches).  A few thousand launches, short
+    and long, must leave the device status word at zero."""
+    import ctypes as C
+    L = rk.lib()
+    if not hasattr(L, "rk_debug_mxfp8_mma_loop"):
+        pytest.skip("measurement aid not exported")
+    L.rk_debug_mxfp8_mma_loop.restype = C.c_int
+    L.rk_debug_mxfp8_mma_loop.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]
+    tiles = torch.randint(0, 0x7E, (2, 128 * 128), dtype=torch.uint8, device="cuda")
+    st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    for iters, n in ((64, 500), (200, 1500), (1024, 500), (8192, 100)):
+        for _ in range(n):
+            assert L.rk_debug_mxfp8_mma_loop(C.c_void_p(tiles[0].data_ptr()), C.c_void_p(tiles[1].data_ptr()), iters, st) == 0
+        torch.cuda.synchronize()
+        assert rk.last_device_status() == 0, iters
